@@ -1,0 +1,159 @@
+/*
+ * moe_b200.h - C ABI of the sm_100a mixture-of-experts feed-forward layer.
+ *
+ * This is the boundary a host language binds (Rust `extern "C"`, Python ctypes,
+ * C++).  It stands in for the Rust-internal interface of the reference crate
+ * `rusting_brain` 2.0.2, which has no FFI of its own for this path: each entry
+ * names the reference item it replaces (file:line inside the crate).
+ *
+ * Conventions
+ *   - every function returns a moe_status (0 = ok) unless stated otherwise;
+ *     moe_last_error() gives the text of the last failure on a handle
+ *   - a handle belongs to one device and one layer and is not thread safe
+ *   - "dev" pointers are device memory of that device, "host" pointers are host
+ *     memory; activations are row-major [tokens, d_model], f32 for
+ *     MOE_PRECISION_F32 handles and bf16 for MOE_PRECISION_BF16 / _Q8 handles
+ *   - weights cross the boundary in the reference's layout: f32, row-major
+ *     [out_features, in_features] (param.rs:620-625); the library repacks them
+ *   - gradients are plain dL/dW (the reference's device buffers hold -dL/dW,
+ *     gpu_transformer.rs:18-22; that sign convention does not cross this ABI)
+ *   - there is no CPU fallback: without a usable device every call fails
+ */
+#ifndef MOE_B200_H
+#define MOE_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct moe_layer moe_layer_t;
+
+/* NetworkError variants this path can raise (network.rs:19-83). */
+typedef enum {
+  MOE_OK = 0,
+  MOE_INVALID_CONFIG = 1,
+  MOE_INVALID_INPUT = 2,
+  MOE_CUDA_ERROR = 3,
+  MOE_OUT_OF_MEMORY = 4,
+  MOE_UNSUPPORTED = 5,
+  MOE_TIMEOUT = 6,
+  MOE_COMM_ERROR = 7,
+  MOE_POISONED = 8
+} moe_status;
+
+typedef enum {
+  MOE_PRECISION_F32 = 0,  /* f32 storage and f32 FMA products (TransformerBuilder::mixed_precision(false)) */
+  MOE_PRECISION_BF16 = 1, /* bf16 activations and weights on the tensor cores, f32 accumulate and f32 master weights */
+  MOE_PRECISION_Q8 = 2    /* inference only: int8 expert weights with one f32 scale per output row, bf16 activations */
+} moe_precision;
+
+/* Which projection of the layer; order follows MoeLayer::params_mut (moe.rs:516-525). */
+typedef enum {
+  MOE_W_ROUTER = 0,      /* [num_experts, d_model] */
+  MOE_W_GATE = 1,        /* [d_ff, d_model], per expert */
+  MOE_W_UP = 2,          /* [d_ff, d_model], per expert */
+  MOE_W_DOWN = 3,        /* [d_model, d_ff], per expert */
+  MOE_W_SHARED_GATE = 4,
+  MOE_W_SHARED_UP = 5,
+  MOE_W_SHARED_DOWN = 6
+} moe_weight;
+
+/* MoeConfig (moe.rs:26-39) plus what the builder passes around it
+ * (TransformerBuilder::experts / moe_d_ff / shared_expert / aux_loss_weight /
+ * router_z_loss_weight / mixed_precision, transformer.rs:320-437). */
+typedef struct {
+  int32_t d_model;
+  int32_t num_experts;
+  int32_t experts_per_token;
+  int32_t d_ff;
+  int32_t shared_expert;          /* 0 / 1 */
+  float aux_loss_weight;          /* DEFAULT_AUX_LOSS_WEIGHT = 0.01 */
+  float router_z_loss_weight;     /* DEFAULT_ROUTER_Z_LOSS_WEIGHT = 1e-3, 0 disables */
+  int32_t precision;              /* moe_precision */
+  int32_t max_tokens;             /* largest `tokens` any call will pass; sizes the workspace */
+  int32_t device;                 /* CUDA device ordinal */
+  int32_t training;               /* 0: forward only (no gradient or optimizer state is allocated) */
+  /* Expert parallelism: this handle owns experts [ep_rank*E/ep_size, (ep_rank+1)*E/ep_size).
+   * ep_size = 1 is the single-device layer. */
+  int32_t ep_rank;
+  int32_t ep_size;
+} moe_config_t;
+
+/* MoeConfig::validate (moe.rs:68-86) and the shape rules of the chosen precision. */
+int32_t moe_config_validate(const moe_config_t* cfg, char* message, int32_t message_len);
+
+/* Device bytes moe_create will allocate; lets a caller apply the reference's
+ * budget check before upload (TransformerLm::to_cuda, transformer.rs:1265-1277). */
+int64_t moe_workspace_bytes(const moe_config_t* cfg);
+
+/* MoeLayer::new (moe.rs:215-231) + Param::move_to_cuda: allocates weights (zeroed),
+ * gradients, Adam moments and the workspace.  Weight initialisation stays with
+ * the caller (moe_set_weight_f32). */
+int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out);
+void moe_destroy(moe_layer_t* layer);
+const char* moe_last_error(const moe_layer_t* layer);
+/* Clears a sticky failure (the reference's poisoned GpuContext has to be rebuilt;
+ * here the handle can be reused once the cause is gone). */
+int32_t moe_clear_error(moe_layer_t* layer);
+
+/* Param upload / download (Param::move_to_cuda, DeviceParam::download,
+ * gpu_transformer.rs:393-556).  `expert` is ignored for router and shared weights;
+ * in an expert-parallel handle it is the GLOBAL expert index and must be owned. */
+int32_t moe_set_weight_f32(moe_layer_t* layer, int32_t which, int32_t expert, const float* host, int32_t rows, int32_t cols);
+int32_t moe_get_weight_f32(moe_layer_t* layer, int32_t which, int32_t expert, float* host, int32_t rows, int32_t cols);
+int32_t moe_get_grad_f32(moe_layer_t* layer, int32_t which, int32_t expert, float* host, int32_t rows, int32_t cols);
+int32_t moe_get_moments_f32(moe_layer_t* layer, int32_t which, int32_t expert, float* m_host, float* v_host, int32_t rows, int32_t cols);
+int32_t moe_set_moments_f32(moe_layer_t* layer, int32_t which, int32_t expert, const float* m_host, const float* v_host, int32_t rows, int32_t cols);
+/* Quantized (quantized.rs:17-24): int8 [rows, cols] + f32 scale[rows], w ~ q * scale. MOE_PRECISION_Q8 handles only. */
+int32_t moe_set_weight_q8(moe_layer_t* layer, int32_t which, int32_t expert, const int8_t* q_host, const float* scale_host, int32_t rows, int32_t cols);
+
+/* MoeLayer::forward_train / forward (moe.rs:237-341), device pointers.
+ *   x_dev       [tokens, d_model]
+ *   valid_dev   optional [tokens] bytes, 0 = padding row (Layout::valid, batch.rs:225-269)
+ *   y_dev       [tokens, d_model]; accumulate != 0 adds into it (the reference's device
+ *               path accumulates into the residual stream, gpu_model.rs:2314-2346)
+ *   save_for_backward  keep what moe_backward needs (forward_train) or not (forward)
+ *   stream      a cudaStream_t (0 = default stream) */
+int32_t moe_forward(moe_layer_t* layer, const void* x_dev, int32_t tokens, int32_t cols, const uint8_t* valid_dev,
+                    void* y_dev, int32_t accumulate, int32_t save_for_backward, void* stream);
+/* Test hook: as moe_forward, but the router projection is replaced by the given
+ * f32 logits [tokens, num_experts]; used for the bit-exact routing checks. */
+int32_t moe_forward_from_logits(moe_layer_t* layer, const void* x_dev, const float* logits_dev, int32_t tokens,
+                                int32_t cols, const uint8_t* valid_dev, void* y_dev, int32_t accumulate,
+                                int32_t save_for_backward, void* stream);
+/* MoeLayer::backward (moe.rs:348-489): weight gradients accumulate into the handle
+ * (moe_zero_grad clears them), the auxiliary-loss gradients are included, and
+ * grad_x_dev receives dL/dx (added to it when accumulate != 0). */
+int32_t moe_backward(moe_layer_t* layer, const void* grad_y_dev, void* grad_x_dev, int32_t accumulate, void* stream);
+int32_t moe_zero_grad(moe_layer_t* layer, void* stream);
+/* Param::step with Optimizer::Adam over every weight of the layer (param.rs:562-589);
+ * `step` is the already incremented global step, `scale` multiplies the gradient. Clears gradients. */
+int32_t moe_step_adam(moe_layer_t* layer, float lr, float beta1, float beta2, float eps, float weight_decay,
+                      int32_t step, float scale, void* stream);
+
+/* The same calls with HOST buffers: f32 [tokens, d_model] in and out, copies included
+ * (what TransformerLm::forward_batch does around the device path). valid_host may be null. */
+int32_t moe_forward_host(moe_layer_t* layer, const float* x_host, int32_t tokens, int32_t cols, const uint8_t* valid_host,
+                         float* y_host, int32_t save_for_backward);
+int32_t moe_backward_host(moe_layer_t* layer, const float* grad_y_host, float* grad_x_host);
+
+/* MoeCache accessors (moe.rs:131-188), copied to host after synchronising the
+ * stream of the last forward.  Any pointer may be null. */
+int32_t moe_get_losses(moe_layer_t* layer, float* aux_loss, float* z_loss);
+/* expert_of / gates: [tokens*k] (expert -1 and gate 0 on padding rows);
+ * counts: [num_experts]; token_of / slot_of: the stable expert-major permutation,
+ * length sum(counts).  Returns the number of routed rows through *routed. */
+int32_t moe_get_routing(moe_layer_t* layer, int32_t* expert_of, float* gates, int32_t* counts, int32_t* token_of,
+                        int32_t* slot_of, int32_t* routed);
+/* logits / probabilities [tokens, E] and log-sum-exp [tokens] of the last forward. */
+int32_t moe_get_router_cache(moe_layer_t* layer, float* logits, float* probabilities, float* log_sum_exp);
+
+/* Device synchronisation for timing (TransformerLm::synchronize, transformer.rs:1323-1334). */
+int32_t moe_synchronize(moe_layer_t* layer);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_H */

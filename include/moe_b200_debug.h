@@ -1,0 +1,33 @@
+/*
+ * moe_b200_debug.h - test hooks of libmoe_b200.so.  Not part of the drop-in
+ * boundary: these entries have no counterpart in the reference crate; they let the
+ * parity tests drive one kernel at a time.
+ */
+#ifndef MOE_B200_DEBUG_H
+#define MOE_B200_DEBUG_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* One grouped tensor-core GEMM on caller-provided device buffers (bf16 operands).
+ * variant 0: out0[r, N]  = A[r, K] * B_g[N, K]^T                         (bf16 out)
+ *         1: as 0 with the SwiGLU epilogue: out0 = h [r, N/2], out1 = (g|u) [r, N] or null
+ *         2: out0[r, N]  = A[r, K] * B_g[K, N]                           (bf16 out)
+ *         3: as 2 with the SwiGLU-backward epilogue: aux = (g|u) [r, 2N], out0 = (dg|du) [r, 2N]
+ *         4: out0_g[M, N] (+)= A[rows_g, M]^T * B[rows_g, N]             (f32 out)
+ * group_row0 / tile_start are device arrays of n_groups+1 ints (row groups padded to 128).
+ * error_flag is a device int that receives a non-zero code if a bounded wait gives up. */
+int32_t moe_debug_tc_gemm(int32_t variant, const void* a, const void* b, void* out0, void* out1, const void* aux,
+                          const int32_t* group_row0, const int32_t* tile_start, int32_t n_groups, int32_t rows,
+                          int32_t m, int32_t n, int32_t k, int32_t accumulate, int32_t* error_flag, void* stream);
+
+/* Number of kernel launches issued by this library in the calling process. */
+int64_t moe_debug_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_B200_DEBUG_H */

@@ -1,0 +1,12 @@
+"""B200-native (sm_100a) mixture-of-experts feed-forward layer.
+
+A from-scratch CUDA implementation of the hot path of the reference crate's
+``src/moe.rs`` behind a C ABI (``include/moe_b200.h``).  This package is the
+host-side mirror of the reference's ``MoeConfig`` / ``MoeLayer`` / ``MoeCache``
+interface over that ABI.
+"""
+from .moe import (CudaError, InvalidConfig, InvalidInput, MoeCache, MoeConfig, MoeLayer, NetworkError,
+                  DEFAULT_AUX_LOSS_WEIGHT, DEFAULT_ROUTER_Z_LOSS_WEIGHT)
+
+__all__ = ["MoeConfig", "MoeLayer", "MoeCache", "NetworkError", "InvalidConfig", "InvalidInput", "CudaError",
+           "DEFAULT_AUX_LOSS_WEIGHT", "DEFAULT_ROUTER_Z_LOSS_WEIGHT"]

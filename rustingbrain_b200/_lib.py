@@ -1,0 +1,86 @@
+"""ctypes binding of libmoe_b200.so (the C ABI declared in include/moe_b200.h).
+
+The library is the product: if it is missing or cannot be loaded this module
+raises, it never substitutes a host implementation.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libmoe_b200.so")
+
+OK, INVALID_CONFIG, INVALID_INPUT, CUDA_ERROR, OUT_OF_MEMORY, UNSUPPORTED, TIMEOUT, COMM_ERROR, POISONED = range(9)
+PRECISION_F32, PRECISION_BF16, PRECISION_Q8 = 0, 1, 2
+W_ROUTER, W_GATE, W_UP, W_DOWN, W_SHARED_GATE, W_SHARED_UP, W_SHARED_DOWN = range(7)
+
+
+class MoeConfigC(C.Structure):
+    _fields_ = [
+        ("d_model", C.c_int32), ("num_experts", C.c_int32), ("experts_per_token", C.c_int32), ("d_ff", C.c_int32),
+        ("shared_expert", C.c_int32), ("aux_loss_weight", C.c_float), ("router_z_loss_weight", C.c_float),
+        ("precision", C.c_int32), ("max_tokens", C.c_int32), ("device", C.c_int32), ("training", C.c_int32),
+        ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
+    ]
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            "libmoe_b200.so is not built (run `python -m rustingbrain_b200.build`); there is no host fallback")
+    L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    vp, i32, f32 = C.c_void_p, C.c_int32, C.c_float
+    fp, ip, bp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.POINTER(C.c_uint8)
+    cfgp = C.POINTER(MoeConfigC)
+    sig = {
+        "moe_config_validate": (i32, [cfgp, C.c_char_p, i32]),
+        "moe_workspace_bytes": (C.c_int64, [cfgp]),
+        "moe_create": (i32, [cfgp, C.POINTER(vp)]),
+        "moe_destroy": (None, [vp]),
+        "moe_last_error": (C.c_char_p, [vp]),
+        "moe_clear_error": (i32, [vp]),
+        "moe_set_weight_f32": (i32, [vp, i32, i32, vp, i32, i32]),
+        "moe_get_weight_f32": (i32, [vp, i32, i32, vp, i32, i32]),
+        "moe_get_grad_f32": (i32, [vp, i32, i32, vp, i32, i32]),
+        "moe_get_moments_f32": (i32, [vp, i32, i32, vp, vp, i32, i32]),
+        "moe_set_moments_f32": (i32, [vp, i32, i32, vp, vp, i32, i32]),
+        "moe_set_weight_q8": (i32, [vp, i32, i32, vp, vp, i32, i32]),
+        "moe_forward": (i32, [vp, vp, i32, i32, vp, vp, i32, i32, vp]),
+        "moe_forward_from_logits": (i32, [vp, vp, vp, i32, i32, vp, vp, i32, i32, vp]),
+        "moe_backward": (i32, [vp, vp, vp, i32, vp]),
+        "moe_zero_grad": (i32, [vp, vp]),
+        "moe_step_adam": (i32, [vp, f32, f32, f32, f32, f32, i32, f32, vp]),
+        "moe_forward_host": (i32, [vp, fp, i32, i32, bp, fp, i32]),
+        "moe_backward_host": (i32, [vp, fp, fp]),
+        "moe_get_losses": (i32, [vp, fp, fp]),
+        "moe_get_routing": (i32, [vp, ip, fp, ip, ip, ip, ip]),
+        "moe_get_router_cache": (i32, [vp, fp, fp, fp]),
+        "moe_synchronize": (i32, [vp]),
+        "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
+        "moe_debug_launch_count": (C.c_int64, []),
+    }
+    for name, (res, args) in sig.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = L
+    return L
+
+
+def exported_symbols():
+    """Names the headers under include/ declare; used by the load test."""
+    import re
+    inc = os.path.join(_HERE, "..", "include")
+    names = []
+    for h in sorted(os.listdir(inc)):
+        if h.endswith(".h"):
+            text = open(os.path.join(inc, h)).read()
+            names += re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight")))

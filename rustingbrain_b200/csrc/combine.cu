@@ -1,0 +1,386 @@
+// Combine (forward) and the HBM-bound halves of the backward pass.
+//
+//   combine_kernel      y[t] = sum_{slots, ascending expert} gate * y_perm[row] + shared[t]
+//                       (reference moe.rs:290-319; replaces the f32-atomic
+//                       scatter_add_scaled, cuda_training.rs:294, by a per-token
+//                       gather-reduce in a fixed order: deterministic, no atomics).
+//   gather_grad_kernel  grad_y_perm[row] = gate * grad_y[token] and
+//                       grad_gate[slot] = <grad_y[token], y_perm[row]>
+//                       (moe.rs:375-383, 404-415; gather_scale_rows + row_dot_scatter,
+//                       cuda_training.rs:293, 300-312, in one pass over grad_y).
+//   router_bwd_kernel   top-k renormalisation backward, load-balancing term, softmax
+//                       backward and z-loss in one kernel (moe.rs:420-481;
+//                       moe_grad_probs + moe_aux_grad + router_grad_logits,
+//                       cuda_training.rs:314-316).
+//   unpermute_kernel    grad_x[t] = shared + sum_{slots} grad_x_perm[row] + grad_logits[t] W_r
+//                       (moe.rs:356-361, 389-399, 483-486; scatter_add_rows + router dgrad).
+//   router_wgrad        dW_r = grad_logits^T x, two-stage fixed-order reduction.
+//
+// One warp handles one token; rows move as 16-byte vectors.
+
+#include "kernels.cuh"
+
+namespace moe {
+
+constexpr int CB_WARPS = 8;
+
+template <typename T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  __device__ static void load(const T* p, float* v);
+  __device__ static void store(T* p, const float* v);
+};
+template <> __device__ inline void Vec16<float>::load(const float* p, float* v) {
+  const float4 q = *reinterpret_cast<const float4*>(p);
+  v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+}
+template <> __device__ inline void Vec16<float>::store(float* p, const float* v) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <> __device__ inline void Vec16<bf16>::load(const bf16* p, float* v) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+    v[2 * i] = __low2float(h);
+    v[2 * i + 1] = __high2float(h);
+  }
+}
+template <> __device__ inline void Vec16<bf16>::store(bf16* p, const float* v) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// The token's routed slots in ascending expert order (the order in which the
+// reference accumulates a token's contributions).  Returns the count.
+__device__ inline int ordered_slots(const int* expert_of, const int* slot_pos, const float* gates, int t, int k,
+                                    int* pos, float* gate) {
+  int ex[MAX_TOPK];
+  int n = 0;
+  for (int j = 0; j < k; ++j) {
+    const int e = expert_of[(size_t)t * k + j];
+    if (e < 0) continue;
+    const int p = slot_pos[(size_t)t * k + j];
+    const float g = gates ? gates[(size_t)t * k + j] : 1.f;
+    int i = n++;
+    while (i > 0 && ex[i - 1] > e) {
+      ex[i] = ex[i - 1]; pos[i] = pos[i - 1]; gate[i] = gate[i - 1];
+      --i;
+    }
+    ex[i] = e; pos[i] = p; gate[i] = g;
+  }
+  return n;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
+  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= a.tokens) return;
+  int pos[MAX_TOPK];
+  float gate[MAX_TOPK];
+  const int n = ordered_slots(a.expert_of, a.slot_pos, a.gates, t, a.k, pos, gate);
+  const T* yp = (const T*)a.y_perm;
+  const T* sh = (const T*)a.shared;
+  T* y = (T*)a.y + (size_t)t * a.d;
+  constexpr int V = Vec16<T>::N;
+  const int d = a.d;
+  if (d % V == 0) {
+    for (int c = lane * V; c < d; c += 32 * V) {
+      float acc[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = 0.f;
+      for (int j = 0; j < n; ++j) {
+        float v[V];
+        Vec16<T>::load(yp + (size_t)pos[j] * d + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j], v[i]));
+      }
+      if (sh) {
+        float v[V];
+        Vec16<T>::load(sh + (size_t)t * d + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      if (a.accumulate) {
+        float v[V];
+        Vec16<T>::load(y + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(v[i], acc[i]);
+      }
+      Vec16<T>::store(y + c, acc);
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) {
+      float acc = 0.f;
+      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, __fmul_rn(gate[j], to_f32<T>(yp[(size_t)pos[j] * d + c])));
+      if (sh) acc = __fadd_rn(acc, to_f32<T>(sh[(size_t)t * d + c]));
+      if (a.accumulate) acc = __fadd_rn(to_f32<T>(y[c]), acc);
+      y[c] = from_f32<T>(acc);
+    }
+  }
+}
+
+cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  const int grid = ceil_div(a.tokens, CB_WARPS);
+  if (precision == PREC_BF16) { combine_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  else { combine_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradArgs a) {
+  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= a.tokens) return;
+  const int k = a.k, d = a.d;
+  int pos[MAX_TOPK];
+  float gate[MAX_TOPK], dot[MAX_TOPK];
+  for (int j = 0; j < k; ++j) {
+    pos[j] = a.slot_pos[(size_t)t * k + j];
+    gate[j] = a.gates[(size_t)t * k + j];
+    dot[j] = 0.f;
+  }
+  const T* gy = (const T*)a.grad_y + (size_t)t * d;
+  const T* yp = (const T*)a.y_perm;
+  T* gyp = (T*)a.grad_y_perm;
+  constexpr int V = Vec16<T>::N;
+  if (d % V == 0) {
+    for (int c = lane * V; c < d; c += 32 * V) {
+      float g[V];
+      Vec16<T>::load(gy + c, g);
+      for (int j = 0; j < k; ++j) {
+        if (pos[j] < 0) continue;
+        float o[V], s[V];
+        Vec16<T>::load(yp + (size_t)pos[j] * d + c, o);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          dot[j] = fmaf(g[i], o[i], dot[j]);
+          s[i] = gate[j] * g[i];
+        }
+        Vec16<T>::store(gyp + (size_t)pos[j] * d + c, s);
+      }
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) {
+      const float g = to_f32<T>(gy[c]);
+      for (int j = 0; j < k; ++j) {
+        if (pos[j] < 0) continue;
+        dot[j] = fmaf(g, to_f32<T>(yp[(size_t)pos[j] * d + c]), dot[j]);
+        gyp[(size_t)pos[j] * d + c] = from_f32<T>(gate[j] * g);
+      }
+    }
+  }
+  for (int j = 0; j < k; ++j) {
+    const float s = warp_sum(dot[j]);
+    if (lane == 0) a.grad_gates[(size_t)t * k + j] = pos[j] < 0 ? 0.f : s;
+  }
+}
+
+cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  const int grid = ceil_div(a.tokens, CB_WARPS);
+  if (precision == PREC_BF16) { gather_grad_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  else { gather_grad_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  return cudaGetLastError();
+}
+
+constexpr int RB_ROWS = 64;
+
+__global__ void __launch_bounds__(RB_ROWS) router_bwd_kernel(RouterBwdArgs a) {
+  extern __shared__ float rb_smem[];
+  const int E = a.E, k = a.k;
+  float* gp = rb_smem + (size_t)threadIdx.x * (E + 1);
+  const int t = blockIdx.x * RB_ROWS + threadIdx.x;
+  if (t >= a.tokens) return;
+  float* gl = a.grad_logits + (size_t)t * E;
+  const int* sel = a.expert_of + (size_t)t * k;
+  if (sel[0] < 0) {
+    for (int e = 0; e < E; ++e) gl[e] = 0.f;
+    return;
+  }
+  const float* p = a.probs + (size_t)t * E;
+  const float* gg = a.grad_gates + (size_t)t * k;
+  for (int e = 0; e < E; ++e) gp[e] = 0.f;
+  float total = 0.f;
+  for (int j = 0; j < k; ++j) total = __fadd_rn(total, p[sel[j]]);
+  if (total > 0.f) {
+    float weighted = 0.f;
+    for (int j = 0; j < k; ++j) weighted = __fadd_rn(weighted, __fmul_rn(gg[j], p[sel[j]]));
+    for (int j = 0; j < k; ++j)
+      gp[sel[j]] = __fadd_rn(gp[sel[j]], __fsub_rn(__fdiv_rn(gg[j], total), __fdiv_rn(weighted, __fmul_rn(total, total))));
+  }
+  const float Vf = a.ext_stats ? a.ext_stats[E + 1] : (float)a.total[3];
+  if (a.aux_w != 0.f && Vf > 0.f) {
+    const float scale = __fdiv_rn(__fmul_rn(a.aux_w, (float)E), Vf);
+    const float slots = Vf * (float)k;
+    for (int e = 0; e < E; ++e) {
+      const float load = __fdiv_rn((float)(a.ext_counts ? a.ext_counts[e] : a.counts[e]), slots);
+      gp[e] = __fadd_rn(gp[e], __fmul_rn(scale, load));
+    }
+  }
+  float dot = 0.f;
+  for (int e = 0; e < E; ++e) dot = __fadd_rn(dot, __fmul_rn(p[e], gp[e]));
+  const float factor = a.z_w != 0.f ? __fdiv_rn(__fmul_rn(__fmul_rn(2.0f, a.z_w), a.lse[t]), fmaxf(Vf, 1.f)) : 0.f;
+  for (int e = 0; e < E; ++e) {
+    float v = __fmul_rn(p[e], __fsub_rn(gp[e], dot));
+    if (a.z_w != 0.f) v = __fadd_rn(v, __fmul_rn(factor, p[e]));
+    gl[e] = v;
+  }
+}
+
+cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  const size_t smem = sizeof(float) * (size_t)RB_ROWS * (a.E + 1);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(router_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  router_bwd_kernel<<<ceil_div(a.tokens, RB_ROWS), RB_ROWS, smem, stream>>>(a); count_launch();
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs a) {
+  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= a.tokens) return;
+  int pos[MAX_TOPK];
+  float unused[MAX_TOPK];
+  const int n = ordered_slots(a.expert_of, a.slot_pos, nullptr, t, a.k, pos, unused);
+  const int d = a.d, E = a.E;
+  const T* gp = (const T*)a.grad_x_perm;
+  const T* sh = (const T*)a.shared;
+  const float* gl = a.grad_logits + (size_t)t * E;
+  T* gx = (T*)a.grad_x + (size_t)t * d;
+  constexpr int V = Vec16<T>::N;
+  if (d % V == 0 && d % 4 == 0) {
+    for (int c = lane * V; c < d; c += 32 * V) {
+      float acc[V], r[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) { acc[i] = 0.f; r[i] = 0.f; }
+      if (sh) Vec16<T>::load(sh + (size_t)t * d + c, acc);
+      for (int j = 0; j < n; ++j) {
+        float v[V];
+        Vec16<T>::load(gp + (size_t)pos[j] * d + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+      }
+      for (int e = 0; e < E; ++e) {
+        const float g = gl[e];
+        const float* w = a.w_router + (size_t)e * d + c;
+#pragma unroll
+        for (int i = 0; i < V; i += 4) {
+          const float4 q = *reinterpret_cast<const float4*>(w + i);
+          r[i] = fmaf(g, q.x, r[i]); r[i + 1] = fmaf(g, q.y, r[i + 1]);
+          r[i + 2] = fmaf(g, q.z, r[i + 2]); r[i + 3] = fmaf(g, q.w, r[i + 3]);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+      if (a.accumulate) {
+        float v[V];
+        Vec16<T>::load(gx + c, v);
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(v[i], acc[i]);
+      }
+      Vec16<T>::store(gx + c, acc);
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) {
+      float acc = sh ? to_f32<T>(sh[(size_t)t * d + c]) : 0.f;
+      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, to_f32<T>(gp[(size_t)pos[j] * d + c]));
+      float r = 0.f;
+      for (int e = 0; e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
+      acc = __fadd_rn(acc, r);
+      if (a.accumulate) acc = __fadd_rn(to_f32<T>(gx[c]), acc);
+      gx[c] = from_f32<T>(acc);
+    }
+  }
+}
+
+cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  const int grid = ceil_div(a.tokens, CB_WARPS);
+  if (precision == PREC_BF16) { unpermute_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  else { unpermute_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  return cudaGetLastError();
+}
+
+// Stage 1: block (col chunk, split) accumulates its tokens; stage 2 adds the splits in order.
+constexpr int RW_COLS = 64;
+constexpr int RW_TOK = 32;
+
+template <typename T>
+__global__ void __launch_bounds__(256) router_wgrad_stage1(RouterWgradArgs a) {
+  extern __shared__ float rw_smem[];   // [RW_TOK][E] grad_logits chunk, [RW_TOK][RW_COLS] x chunk
+  const int E = a.E, d = a.d;
+  float* s_gl = rw_smem;
+  float* s_x = rw_smem + (size_t)RW_TOK * E;
+  const int c0 = blockIdx.x * RW_COLS;
+  const int per = ceil_div(a.tokens, a.splits);
+  const int tb = blockIdx.y * per, te = min(a.tokens, tb + per);
+  const int col = threadIdx.x % RW_COLS;
+  const int eg = threadIdx.x / RW_COLS;           // 4 expert groups
+  const int e_per = ceil_div(E, 4);
+  float acc[MAX_EXPERTS / 4];
+#pragma unroll
+  for (int i = 0; i < MAX_EXPERTS / 4; ++i) acc[i] = 0.f;
+  const T* x = (const T*)a.x;
+  for (int t0 = tb; t0 < te; t0 += RW_TOK) {
+    const int nt = min(RW_TOK, te - t0);
+    for (int i = threadIdx.x; i < RW_TOK * E; i += 256) {
+      const int r = i / E;
+      s_gl[i] = r < nt ? a.grad_logits[(size_t)(t0 + r) * E + (i - r * E)] : 0.f;
+    }
+    for (int i = threadIdx.x; i < RW_TOK * RW_COLS; i += 256) {
+      const int r = i / RW_COLS, c = i - r * RW_COLS;
+      s_x[i] = (r < nt && c0 + c < d) ? to_f32<T>(x[(size_t)(t0 + r) * d + c0 + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int r = 0; r < nt; ++r) {
+      const float xv = s_x[r * RW_COLS + col];
+#pragma unroll
+      for (int i = 0; i < MAX_EXPERTS / 4; ++i) {
+        const int e = eg * e_per + i;
+        if (i < e_per && e < E) acc[i] = fmaf(s_gl[r * E + e], xv, acc[i]);
+      }
+    }
+    __syncthreads();
+  }
+  if (c0 + col < d) {
+#pragma unroll
+    for (int i = 0; i < MAX_EXPERTS / 4; ++i) {
+      const int e = eg * e_per + i;
+      if (i < e_per && e < E) a.scratch[((size_t)blockIdx.y * E + e) * d + c0 + col] = acc[i];
+    }
+  }
+}
+
+__global__ void router_wgrad_stage2(RouterWgradArgs a) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long n = (long long)a.E * a.d;
+  if (i >= n) return;
+  float s = 0.f;
+  for (int sp = 0; sp < a.splits; ++sp) s += a.scratch[(size_t)sp * n + i];
+  a.grad_w[i] = a.accumulate ? a.grad_w[i] + s : s;
+}
+
+cudaError_t launch_router_wgrad(const RouterWgradArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) {
+    if (!a.accumulate) return cudaMemsetAsync(a.grad_w, 0, sizeof(float) * (size_t)a.E * a.d, stream);
+    return cudaSuccess;
+  }
+  const dim3 grid(ceil_div(a.d, RW_COLS), a.splits);
+  const size_t smem = sizeof(float) * ((size_t)RW_TOK * a.E + (size_t)RW_TOK * RW_COLS);
+  if (precision == PREC_BF16) { router_wgrad_stage1<bf16><<<grid, 256, smem, stream>>>(a); count_launch(); }
+  else { router_wgrad_stage1<float><<<grid, 256, smem, stream>>>(a); count_launch(); }
+  const long long n = (long long)a.E * a.d;
+  router_wgrad_stage2<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(a); count_launch();
+  return cudaGetLastError();
+}
+
+}  // namespace moe

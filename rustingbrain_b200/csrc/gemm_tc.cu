@@ -1,0 +1,571 @@
+// Grouped bf16 GEMMs on the Blackwell tensor cores (sm_100a): tcgen05.mma with
+// fp32 accumulators in tensor memory, operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), one persistent CTA per SM.
+//
+// Warp roles inside a CTA of 192 threads:
+//   warp 0, one lane : TMA producer (fills a 4-stage ring of A/B tiles)
+//   warp 1           : allocates tensor memory; one lane issues tcgen05.mma and
+//                      tcgen05.commit
+//   warps 2..5       : epilogue; each reads its quarter of the 128 TMEM lanes with
+//                      tcgen05.ld, applies the fused pointwise step, stores.
+// Two 128x256 fp32 accumulators (all 512 TMEM columns) are double buffered so the
+// epilogue of tile i overlaps the MMAs of tile i+1.
+//
+// The row groups (one per expert) are padded to multiples of 128 rows by the
+// dispatch step, so every M tile lies inside one group and the ragged sizes never
+// reach the tensor-core loop; only the tile schedule reads them, from device memory.
+//
+// Every wait on an mbarrier is bounded: after about a second it records an error
+// code in GemmArgs::error_flag, the CTA drains and frees its tensor memory, and
+// the host reports ST_TIMEOUT.
+
+#include "gemm_tc.cuh"
+
+#include <stdio.h>
+
+namespace moe {
+namespace tc {
+
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;           // 16 KiB
+constexpr int B_BYTES = BN * BK * 2;           // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES; // 48 KiB
+constexpr int BOX_BYTES = 64 * 64 * 2;         // one 64x64 box of an MN-major operand
+constexpr int MAX_GROUPS = MAX_EXPERTS + 1;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;  // ~1.5 s at 2 GHz
+
+struct __align__(8) SharedTail {
+  unsigned long long full[STAGES];
+  unsigned long long empty[STAGES];
+  unsigned long long tmem_full[2];
+  unsigned long long tmem_empty[2];
+  uint32_t tmem_base;
+  int dead;
+  int row0[MAX_GROUPS + 1];
+  int tstart[MAX_GROUPS + 1];
+};
+
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + (int)sizeof(SharedTail);
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false (and records `code`) when the limit passes or
+// another role of this grid has already reported a failure.
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 0xfff) == 0) {
+      if (*(volatile int*)error_flag != 0) return false;
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        atomicCAS(error_flag, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// D[tmem] (+)= A[smem] * B[smem], M=128, N=256, K=16, bf16 in, fp32 out.
+__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// The mbarrier gets one arrival once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives row
+// (lane quarter base + i), registers j = column (col0 + j).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and
+// stride byte offsets in 16-byte units, version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M=128, N=256.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+  return (1u << 4)                      // D format: f32
+         | (1u << 7)                    // A format: bf16
+         | (1u << 10)                   // B format: bf16
+         | ((a_mn ? 1u : 0u) << 15)     // A major: 0 = K, 1 = MN
+         | ((b_mn ? 1u : 0u) << 16)     // B major
+         | ((uint32_t)(BN >> 3) << 17)  // N / 8
+         | ((uint32_t)(BM >> 4) << 24); // M / 16
+}
+
+// ---------------------------------------------------------------------------
+// Tile schedule
+// ---------------------------------------------------------------------------
+struct Tile {
+  int group, row0 /*first row of the row-indexed operands*/, m0, n0, k_iters;
+};
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ int total_tiles(const SharedTail* st, const GemmArgs& p) {
+  const int nt = ceil_div(p.N, BN);
+  if (ROWS_ARE_K) return p.n_groups * ceil_div(p.M, BM) * nt;
+  return st->tstart[p.n_groups] * nt;
+}
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ Tile decode_tile(const SharedTail* st, const GemmArgs& p, int t) {
+  Tile tl;
+  const int nt = ceil_div(p.N, BN);
+  if (ROWS_ARE_K) {
+    const int mt = ceil_div(p.M, BM);
+    const int g = t / (mt * nt);
+    const int rem = t - g * mt * nt;
+    tl.group = g;
+    tl.n0 = (rem / mt) * BN;
+    tl.m0 = (rem % mt) * BM;
+    tl.row0 = st->row0[g];
+    tl.k_iters = (st->row0[g + 1] - st->row0[g]) / BK;
+  } else {
+    // tiles of group g occupy [tstart[g]*nt, tstart[g+1]*nt); m varies fastest so
+    // that neighbouring CTAs share the same weight tile in L2.
+    int lo = 0, hi = p.n_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (st->tstart[mid] * nt <= t) lo = mid; else hi = mid;
+    }
+    const int g = lo;
+    const int mt = st->tstart[g + 1] - st->tstart[g];
+    const int local = t - st->tstart[g] * nt;
+    tl.group = g;
+    tl.n0 = (local / mt) * BN;
+    tl.m0 = 0;
+    tl.row0 = st->row0[g] + (local % mt) * BM;
+    tl.k_iters = ceil_div(p.K, BK);
+  }
+  return tl;
+}
+
+// ---------------------------------------------------------------------------
+// Epilogues.  `v` holds 32 consecutive accumulator columns of one row.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void store32_bf16(bf16* dst, const float* v) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    d4[i] = make_uint4(pack2(v[8 * i], v[8 * i + 1]), pack2(v[8 * i + 2], v[8 * i + 3]),
+                       pack2(v[8 * i + 4], v[8 * i + 5]), pack2(v[8 * i + 6], v[8 * i + 7]));
+}
+__device__ __forceinline__ void load32_bf16(const bf16* src, float* v) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 q = s4[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+      v[8 * i + 2 * j] = __low2float(h);
+      v[8 * i + 2 * j + 1] = __high2float(h);
+    }
+  }
+}
+
+template <int EPI>
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl, uint32_t taddr, int row_in_tile,
+                                              bool have_acc) {
+  if (EPI == EPI_STORE) {
+    const long long row = (long long)tl.row0 + row_in_tile;
+    bf16* out = (bf16*)p.out0 + row * p.ld0;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      if (tl.n0 + c >= p.N) break;   // warp-uniform
+      float v[32];
+      tmem_ld32(taddr + c, v);
+      store32_bf16(out + tl.n0 + c, v);
+    }
+  } else if (EPI == EPI_SWIGLU) {
+    const long long row = (long long)tl.row0 + row_in_tile;
+    bf16* h_out = (bf16*)p.out0 + row * p.ld0;
+    bf16* gu_out = p.out1 ? (bf16*)p.out1 + row * p.ld1 : nullptr;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 2 * GU_BLOCK) {
+      if (tl.n0 + c >= p.N) break;
+      float g[32], u[32];
+      tmem_ld32(taddr + c, g);
+      tmem_ld32(taddr + c + GU_BLOCK, u);
+      if (gu_out) {
+        store32_bf16(gu_out + tl.n0 + c, g);
+        store32_bf16(gu_out + tl.n0 + c + GU_BLOCK, u);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
+      store32_bf16(h_out + (tl.n0 + c) / 2, g);
+    }
+  } else if (EPI == EPI_SWIGLU_BWD) {
+    // accumulator columns are logical hidden columns f; the saved (g|u) and the
+    // output (dg|du) use the interleaved layout: block f/32 -> columns [64b, 64b+64).
+    const long long row = (long long)tl.row0 + row_in_tile;
+    const bf16* gu = (const bf16*)p.aux + row * p.ldaux;
+    bf16* out = (bf16*)p.out0 + row * p.ld0;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      if (tl.n0 + c >= p.N) break;
+      float dh[32], g[32], u[32];
+      tmem_ld32(taddr + c, dh);
+      const int col = (tl.n0 + c) * 2;
+      load32_bf16(gu + col, g);
+      load32_bf16(gu + col + GU_BLOCK, u);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float s = sigmoidf_(g[i]);
+        const float dg = dh[i] * u[i] * (s * (1.0f + g[i] * (1.0f - s)));
+        u[i] = dh[i] * (g[i] * s);
+        g[i] = dg;
+      }
+      store32_bf16(out + col, g);
+      store32_bf16(out + col + GU_BLOCK, u);
+    }
+  } else {  // EPI_ACCUM_F32
+    const int m = tl.m0 + row_in_tile;
+    float* out = (float*)p.out0 + (long long)tl.group * p.group_stride0 + (long long)m * p.ld0;
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      if (tl.n0 + c >= p.N) break;
+      float v[32];
+      if (have_acc) {
+        tmem_ld32(taddr + c, v);   // every lane of the warp takes part in the load
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.f;
+      }
+      if (m < p.M) {
+        float4* o4 = reinterpret_cast<float4*>(out + tl.n0 + c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 r = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          if (p.accumulate) {
+            const float4 o = o4[i];
+            r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+          }
+          o4[i] = r;
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// The kernel
+// ---------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
+  SharedTail* st = reinterpret_cast<SharedTail*>(smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i <= p.n_groups; i += NUM_THREADS) {
+    st->row0[i] = p.group_row0[i];
+    st->tstart[i] = ROWS_ARE_K ? 0 : p.tile_start[i];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&st->full[s]), 1);
+      mbar_init(smem_u32(&st->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&st->tmem_full[a]), 1);
+      mbar_init(smem_u32(&st->tmem_empty[a]), 4);
+    }
+    st->dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&st->tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = st->tmem_base;
+
+  const int n_tiles = total_tiles<ROWS_ARE_K>(st, p);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&st->full[stage]);
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          if (ROWS_ARE_K) {
+            const int krow = tl.row0 + ki * BK;
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * BOX_BYTES, &map_a, bar, tl.m0 + 64 * j, krow);
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * BOX_BYTES, &map_b, bar, tl.n0 + 64 * j, krow);
+          } else {
+            tma_load_2d(sa, &map_a, bar, ki * BK, tl.row0);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * BOX_BYTES, &map_b, bar, tl.n0 + 64 * j, ki * BK, tl.group);
+            } else {
+              tma_load_3d(sb, &map_b, bar, ki * BK, tl.n0, tl.group);
+            }
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) st->dead = 1;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuer --------------------------------
+      constexpr uint32_t idesc = make_idesc(A_MN, B_MN);
+      // K-major tiles: rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart; one
+      // MMA (K=16) advances 32 bytes inside the 128-byte row.
+      // MN-major tiles: 64x64 boxes of 8 KiB; 64-element chunks of the M/N extent are
+      // 8192 bytes apart (leading offset), 8-row groups of K 1024 bytes apart; one MMA
+      // (16 rows of K) advances 2048 bytes.
+      constexpr uint32_t a_lbo = A_MN ? BOX_BYTES : 16, a_sbo = 1024, a_adv = A_MN ? 2048 : 32;
+      constexpr uint32_t b_lbo = B_MN ? BOX_BYTES : 16, b_sbo = 1024, b_adv = B_MN ? 2048 : 32;
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 102)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = tiles_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = make_desc(sa + kk * a_adv, a_lbo, a_sbo);
+            const uint64_t db = make_desc(sb + kk * b_adv, b_lbo, b_sbo);
+            umma_bf16(d_tmem, da, db, idesc, (ki | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(smem_u32(&st->empty[stage]));   // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (tl.k_iters > 0) umma_commit(smem_u32(&st->tmem_full[acc]));
+        else mbar_arrive(smem_u32(&st->tmem_full[acc]));   // empty group: nothing was accumulated
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) st->dead = 1;
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------- epilogue ----------------------------------
+    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      epilogue_tile<EPI>(p, tl, taddr, row_in_tile, tl.k_iters > 0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&st->tmem_empty[acc]));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (st->dead || *(volatile int*)p.error_flag != 0) {
+    // Failure path: give copies that may still be in flight time to land before the
+    // shared memory and tensor memory are released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: tensor maps and launches
+// ---------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// bf16 tensor [groups][rows][cols], cols contiguous; box = {box_cols, box_rows, 1}.
+static bool make_map(CUtensorMap* map, const Operand& op, int box_cols, int box_rows, bool three_d) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.groups};
+  cuuint64_t strides[2] = {(cuuint64_t)op.cols * 2, (cuuint64_t)op.cols * (cuuint64_t)op.rows * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, three_d ? 3 : 2, const_cast<void*>(op.ptr), dims,
+                        strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool operand_ok(const Operand& op) {
+  return op.ptr && ((uintptr_t)op.ptr & 15) == 0 && op.cols > 0 && (op.cols % 8) == 0 && op.rows > 0 && op.groups > 0;
+}
+
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
+                          cudaStream_t stream) {
+  auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kern<<<sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, args); count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
+                         cudaStream_t stream) {
+  if (!operand_ok(A) || !operand_ok(B) || A.cols != B.cols || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
+    return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, BN, true)) return cudaErrorInvalidValue;
+  switch (epilogue) {
+    case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, sm_count, stream);
+    case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, sm_count, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t gemm_rows_nn(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
+                         cudaStream_t stream) {
+  if (!operand_ok(A) || !operand_ok(B) || A.cols != B.rows || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
+    return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, 64, 64, true)) return cudaErrorInvalidValue;
+  switch (epilogue) {
+    case EPI_STORE: return launch<false, true, false, EPI_STORE>(ma, mb, args, sm_count, stream);
+    case EPI_SWIGLU_BWD: return launch<false, true, false, EPI_SWIGLU_BWD>(ma, mb, args, sm_count, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+cudaError_t gemm_rows_tn(const Operand& A, const Operand& B, const GemmArgs& args, int sm_count,
+                         cudaStream_t stream) {
+  if (!operand_ok(A) || !operand_ok(B) || A.rows != B.rows || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
+    return cudaErrorInvalidValue;
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, A, 64, 64, false) || !make_map(&mb, B, 64, 64, false)) return cudaErrorInvalidValue;
+  return launch<true, true, true, EPI_ACCUM_F32>(ma, mb, args, sm_count, stream);
+}
+
+}  // namespace tc
+}  // namespace moe

@@ -1,0 +1,56 @@
+// Host-side interface of the tcgen05 grouped GEMM family (gemm_tc.cu).
+#pragma once
+#include "common.cuh"
+
+namespace moe {
+namespace tc {
+
+constexpr int BM = 128;   // rows of one output tile (TMEM lanes)
+constexpr int BN = 256;   // columns of one output tile (TMEM columns, fp32)
+constexpr int BK = 64;    // reduction elements per pipeline stage (128 bytes of bf16)
+
+enum Epilogue {
+  EPI_STORE = 0,       // out0[row, col] = bf16(acc)
+  EPI_SWIGLU = 1,      // acc holds interleaved gate|up blocks: out0 = silu(g)*u, out1 = (g|u) if non-null
+  EPI_SWIGLU_BWD = 2,  // acc = dL/dh; aux = saved (g|u); out0 = (dg|du) in the same interleaved layout
+  EPI_ACCUM_F32 = 3,   // out0 (f32) = acc  or  += acc
+};
+
+struct GemmArgs {
+  // Schedule.  Row groups come from the dispatch metadata: group g owns rows
+  // [group_row0[g], group_row0[g+1]) of the row-indexed operands, a multiple of 128.
+  const int* group_row0;  // [n_groups+1], device
+  const int* tile_start;  // [n_groups+1], device: exclusive prefix of rows/128 (rows-as-M only)
+  int n_groups;
+  int N;                  // output columns
+  int K;                  // reduction length (rows-as-M); ignored when the rows are the reduction
+  int M;                  // output rows per group (rows-as-K only)
+  void* out0;
+  void* out1;
+  const void* aux;
+  long long ld0, ld1, ldaux;   // leading dimensions in elements
+  long long group_stride0;     // rows-as-K: elements between consecutive groups of out0
+  int accumulate;              // EPI_ACCUM_F32: add to out0 instead of overwriting
+  int* error_flag;             // device int, set non-zero when a bounded wait gives up
+};
+
+// Operand descriptions for tensor-map construction (bf16, row-major).
+struct Operand {
+  const void* ptr;
+  long long rows;      // rows per group (or total rows for row-indexed operands)
+  long long cols;      // contiguous dimension
+  long long groups;    // 1 for row-indexed operands
+};
+
+// y[rows, N] = A[rows, K] * B_g[N, K]^T            (forward projections)
+cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
+                         cudaStream_t stream);
+// y[rows, N] = A[rows, K] * B_g[K, N]              (input gradients; B is the [out,in] weight itself)
+cudaError_t gemm_rows_nn(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
+                         cudaStream_t stream);
+// C_g[M, N] (+)= A[rows_g, M]^T * B[rows_g, N]     (weight gradients; the ragged rows are the reduction)
+cudaError_t gemm_rows_tn(const Operand& A, const Operand& B, const GemmArgs& args, int sm_count,
+                         cudaStream_t stream);
+
+}  // namespace tc
+}  // namespace moe

@@ -1,0 +1,144 @@
+// Launchers of the non-tensor-core kernels (route.cu, combine.cu, gemm_simt.cu,
+// backward.cu, optim.cu).  `precision` selects the activation type: f32 or bf16.
+#pragma once
+#include "common.cuh"
+
+namespace moe {
+
+struct RouterArgs {
+  const void* x;            // [tokens, d] activations (f32 or bf16); unused when logits_in is set
+  const float* w_router;    // [E, d]
+  const float* logits_in;   // optional [tokens, E]: skip the projection (test hook)
+  const uint8_t* valid;     // optional [tokens] padding mask (0 = padding row)
+  int tokens, d, E, k;
+  float* logits_out;        // optional [tokens, E]
+  float* probs;             // [tokens, E]
+  float* lse;               // [tokens]
+  int* expert_of;           // [tokens*k], -1 on padding rows
+  float* gates;             // [tokens*k]
+  float* partial;           // [blocks, E+2]
+  int* hist;                // [blocks, E]; after finalize: padded-row write cursors
+};
+
+struct PermuteArgs {
+  const void* x;
+  const int* expert_of;
+  const float* gates;
+  const int* cursor;
+  RouteMeta meta;
+  int tokens, d, E, k;
+  void* x_perm;       // [padded rows, d]
+  int* slot_pos;      // [tokens*k] padded row of each slot, -1 when unrouted
+  int* row_token;     // [padded rows] token of each row, -1 for padding rows
+  float* row_gate;    // [padded rows] gate of each row
+  int* token_of;      // [R] compact, stable expert-major order (the reference's permutation)
+  int* slot_of;       // [R]
+};
+
+cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t stream);
+cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
+                            const float* ext_stats, const int* ext_counts, cudaStream_t stream);
+cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t stream);
+cudaError_t launch_pad_rows(void* buf, int d, RouteMeta meta, int E, int precision, cudaStream_t stream);
+
+// y[t] (+)= sum over the token's slots in ascending expert order of gate * y_perm[row] (+ shared[t]).
+struct CombineArgs {
+  const void* y_perm;       // [padded rows, d]
+  const void* shared;       // optional [tokens, d]
+  const int* expert_of;     // [tokens*k]
+  const float* gates;       // [tokens*k]
+  const int* slot_pos;      // [tokens*k]
+  void* y;                  // [tokens, d]
+  int tokens, d, k, accumulate;
+};
+cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t stream);
+
+// ----- f32 path: grouped SIMT GEMMs over the padded row groups -----
+struct SimtGemmArgs {
+  const float* A;
+  const float* B;
+  float* C;
+  const int* group_row0;   // [G+1] device
+  int n_groups;
+  int max_rows;            // capacity of the row-indexed operands (bounds the grid)
+  int a_rows, b_rows;      // readable rows of A (and of B when B is row-indexed); rows beyond read as zero
+  int N, K, M;
+  long long b_group_stride, c_group_stride;
+  int accumulate;
+};
+// C[row, n] = sum_k A[row,k] * B_g[n,k]
+cudaError_t simt_gemm_nt(const SimtGemmArgs& a, cudaStream_t stream);
+// C[row, n] = sum_k A[row,k] * B_g[k,n]
+cudaError_t simt_gemm_nn(const SimtGemmArgs& a, cudaStream_t stream);
+// C_g[m, n] (+)= sum_{row in g} A[row,m] * B[row,n]
+cudaError_t simt_gemm_tn(const SimtGemmArgs& a, cudaStream_t stream);
+
+// h[r, f] = silu(g) * u from the interleaved (g|u) rows; f32 path only (the bf16
+// path fuses this into the GEMM epilogue).
+cudaError_t launch_swiglu_fwd_f32(const float* gu, float* h, long long rows, int f_pad, cudaStream_t stream);
+cudaError_t launch_swiglu_bwd_f32(const float* dh, const float* gu, float* dgu, long long rows, int f_pad,
+                                  cudaStream_t stream);
+
+// ----- backward, non-GEMM -----
+struct GatherGradArgs {
+  const void* grad_y;     // [tokens, d]
+  const void* y_perm;     // [padded rows, d] pre-gate expert outputs
+  const int* slot_pos;    // [tokens*k]
+  const float* gates;     // [tokens*k]
+  void* grad_y_perm;      // [padded rows, d] = gate * grad_y[token]
+  float* grad_gates;      // [tokens*k] = <grad_y[token], y_perm[row]>
+  int tokens, d, k;
+};
+cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStream_t stream);
+
+struct RouterBwdArgs {
+  const float* probs;       // [tokens, E]
+  const float* lse;         // [tokens]
+  const int* expert_of;     // [tokens*k]
+  const float* grad_gates;  // [tokens*k]
+  const int* counts;        // [E]   (whole batch)
+  const int* total;         // meta.total ([3] = valid tokens) unless valid_override >= 0
+  const float* ext_stats;   // optional: whole-batch statistics (expert parallel), [E+1] = V
+  const int* ext_counts;
+  int tokens, E, k;
+  float aux_w, z_w;
+  float* grad_logits;       // [tokens, E]
+};
+cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream);
+
+// grad_x[t] (+)= sum over slots (ascending expert) grad_x_perm[row] (+ shared) + grad_logits[t] W_r
+struct UnpermuteArgs {
+  const void* grad_x_perm;   // [padded rows, d]
+  const void* shared;        // optional [tokens, d]
+  const float* grad_logits;  // [tokens, E]
+  const float* w_router;     // [E, d]
+  const int* expert_of;
+  const int* slot_pos;
+  void* grad_x;
+  int tokens, d, E, k, accumulate;
+};
+cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream);
+
+// dW_r[e, c] (+)= sum_t grad_logits[t,e] * x[t,c]; deterministic two-stage reduction.
+struct RouterWgradArgs {
+  const float* grad_logits;
+  const void* x;
+  float* grad_w;       // [E, d]
+  float* scratch;      // [splits, E, d]
+  int tokens, d, E, splits, accumulate;
+};
+cudaError_t launch_router_wgrad(const RouterWgradArgs& a, int precision, cudaStream_t stream);
+
+// ----- optimizer and casts -----
+struct AdamArgs {
+  float* w; float* g; float* m; float* v;
+  bf16* w_bf16;        // optional compute copy refreshed in the same pass
+  long long n;
+  float lr, beta1, beta2, eps, wd, c1, c2, scale;
+};
+cudaError_t launch_adam(const AdamArgs& a, cudaStream_t stream);
+cudaError_t launch_cast_f32_to_bf16(const float* src, bf16* dst, long long n, cudaStream_t stream);
+cudaError_t launch_cast_bf16_to_f32(const bf16* src, float* dst, long long n, cudaStream_t stream);
+cudaError_t launch_fill_f32(float* dst, float v, long long n, cudaStream_t stream);
+
+}  // namespace moe

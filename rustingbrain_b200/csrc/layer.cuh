@@ -1,0 +1,81 @@
+// The layer handle behind the C ABI: owned device memory and the per-pass plans.
+#pragma once
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "gemm_tc.cuh"
+#include "kernels.cuh"
+
+struct moe_layer {
+  // configuration
+  int d = 0, E = 0, k = 0, F = 0, F_pad = 0;
+  int E_local = 0, e0 = 0, ep_rank = 0, ep_size = 1;
+  bool shared = false, training = false;
+  float aux_w = 0.f, z_w = 0.f;
+  int precision = 0;       // moe_precision
+  int act = 0;             // moe::PREC_F32 or PREC_BF16: element type of activations
+  int max_tokens = 0, rows_cap = 0, shared_rows_cap = 0;
+  int device = 0, sm_count = 0;
+  size_t esz = 4;          // bytes per activation element
+
+  // error state (sticky, like the reference's poisoned context)
+  std::string err;
+  int status = 0;
+
+  // parameters: one arena per role so the optimizer is a single launch
+  long long n_params = 0;
+  long long off_router = 0, off_gu = 0, off_d = 0, off_sgu = 0, off_sd = 0;
+  float* w = nullptr;      // f32 master
+  float* g = nullptr;      // dL/dW
+  float* m = nullptr;
+  float* v = nullptr;
+  moe::bf16* wb = nullptr; // bf16 compute copy (bf16 precision)
+  bool grad_valid = false; // false: the next backward overwrites instead of accumulating
+  float* stage = nullptr;  // staging for weight upload / download (one matrix)
+  long long stage_elems = 0;
+
+  // int8 inference weights (Q8 precision)
+  int8_t* q_gu = nullptr; float* s_gu = nullptr;   // [E][2F_pad][d], [E][2F_pad]
+  int8_t* q_d = nullptr;  float* s_d = nullptr;    // [E][d][F_pad],  [E][d]
+  int8_t* q_sgu = nullptr; float* s_sgu = nullptr;
+  int8_t* q_sd = nullptr;  float* s_sd = nullptr;
+
+  // router cache
+  float *logits = nullptr, *probs = nullptr, *lse = nullptr, *gates = nullptr;
+  int* expert_of = nullptr;
+  float* partial = nullptr;
+  int* hist = nullptr;
+  moe::RouteMeta meta{};
+  int* meta_block = nullptr;
+  float *stats = nullptr, *losses = nullptr;
+  int *slot_pos = nullptr, *row_token = nullptr, *token_of = nullptr, *slot_of = nullptr;
+  float* row_gate = nullptr;
+  int* shared_meta = nullptr;   // [4]: row0[0..1], tstart[0..1] of the dense (shared expert) group
+  int* error_flag = nullptr;
+
+  // activations (element type `act`)
+  void *x_perm = nullptr, *gu = nullptr, *h = nullptr, *y_perm = nullptr;
+  void *dy_perm = nullptr, *dgu = nullptr, *dx_perm = nullptr, *dh = nullptr;
+  void *gu_s = nullptr, *h_s = nullptr, *y_s = nullptr, *dgu_s = nullptr, *dx_s = nullptr, *dh_s = nullptr;
+  float *grad_gates = nullptr, *grad_logits = nullptr, *rw_scratch = nullptr;
+  int rw_splits = 1;
+
+  // host-call staging
+  float* host_stage_f32 = nullptr;   // [max_tokens, d]
+  void* host_x = nullptr;            // [max_tokens, d] act type
+  void* host_y = nullptr;
+  void* host_gx = nullptr;
+  uint8_t* host_valid = nullptr;
+  void* pinned = nullptr;            // pinned bounce buffer, [max_tokens, d] f32
+  cudaStream_t own_stream = nullptr;
+
+  // last forward
+  int last_tokens = 0;
+  bool have_cache = false;
+  const void* last_x = nullptr;
+  cudaStream_t last_stream = nullptr;
+
+  std::vector<void*> allocations;
+  long long allocated_bytes = 0;
+};

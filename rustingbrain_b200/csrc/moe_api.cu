@@ -1,0 +1,797 @@
+// C ABI of the layer (declared in include/moe_b200.h): handle life cycle, weight
+// transfer, and the forward / backward / optimizer plans that sequence the kernels.
+// Nothing here falls back to the host: without a device every entry fails.
+
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <cmath>
+#include <new>
+
+#include "../../include/moe_b200.h"
+#include "layer.cuh"
+
+using namespace moe;
+
+namespace {
+
+int fail(moe_layer* L, int status, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  if (L) {
+    L->err = buf;
+    L->status = status;
+  }
+  return status;
+}
+
+#define CK(call)                                                                                   \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess)                                                                         \
+      return fail(L, e_ == cudaErrorMemoryAllocation ? MOE_OUT_OF_MEMORY : MOE_CUDA_ERROR,         \
+                  "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__);     \
+  } while (0)
+
+#define ENTER(L)                                                                                   \
+  do {                                                                                             \
+    if (!(L)) return MOE_INVALID_INPUT;                                                            \
+    if ((L)->status != MOE_OK) return MOE_POISONED;                                                \
+    cudaError_t e_ = cudaSetDevice((L)->device);                                                   \
+    if (e_ != cudaSuccess) return fail((L), MOE_CUDA_ERROR, "cudaSetDevice: %s", cudaGetErrorString(e_)); \
+  } while (0)
+
+long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
+
+int validate(const moe_config_t* c, char* msg, int len) {
+  auto say = [&](const char* fmt, ...) {
+    if (msg && len > 0) {
+      va_list ap;
+      va_start(ap, fmt);
+      vsnprintf(msg, len, fmt, ap);
+      va_end(ap);
+    }
+    return (int)MOE_INVALID_CONFIG;
+  };
+  if (!c) return say("null config");
+  // MoeConfig::validate, moe.rs:68-86
+  if (c->num_experts <= 0) return say("a MoE layer needs at least one expert");
+  if (c->experts_per_token <= 0 || c->experts_per_token > c->num_experts)
+    return say("experts_per_token must be between 1 and num_experts (%d), got %d", c->num_experts,
+               c->experts_per_token);
+  if (c->d_ff <= 0) return say("expert d_ff must be non-zero");
+  if (c->d_model <= 0) return say("d_model must be non-zero");
+  if (c->num_experts > MAX_EXPERTS) return say("at most %d experts are supported", MAX_EXPERTS);
+  if (c->experts_per_token > MAX_TOPK) return say("at most %d experts per token are supported", MAX_TOPK);
+  if (c->max_tokens <= 0) return say("max_tokens must be positive");
+  if (c->precision < MOE_PRECISION_F32 || c->precision > MOE_PRECISION_Q8) return say("unknown precision");
+  if (c->ep_size < 1 || c->ep_rank < 0 || c->ep_rank >= c->ep_size || c->num_experts % c->ep_size != 0)
+    return say("num_experts must divide evenly over ep_size ranks");
+  if (c->precision != MOE_PRECISION_F32 && c->d_model % 32 != 0)
+    return say("the bf16 and int8 paths need d_model to be a multiple of 32 (got %d); use MOE_PRECISION_F32",
+               c->d_model);
+  if (c->precision == MOE_PRECISION_Q8 && c->training) return say("a quantized layer cannot be trained");
+  if ((long long)c->max_tokens * c->experts_per_token > (1ll << 30)) return say("max_tokens * experts_per_token too large");
+  return MOE_OK;
+}
+
+struct Sizes {
+  int F_pad, E_local, rows_cap, shared_rows_cap;
+  long long off_router, off_gu, off_d, off_sgu, off_sd, n_params;
+};
+
+Sizes sizes_of(const moe_config_t* c) {
+  Sizes s;
+  s.F_pad = round_up(c->d_ff, GU_BLOCK);
+  s.E_local = c->num_experts / c->ep_size;
+  s.rows_cap = round_up(c->max_tokens * c->experts_per_token + c->num_experts * (GROUP_ALIGN - 1), GROUP_ALIGN);
+  s.shared_rows_cap = round_up(c->max_tokens, GROUP_ALIGN);
+  long long o = 0;
+  s.off_router = o; o = align_up(o + (long long)c->num_experts * c->d_model, 128);
+  s.off_gu = o;     o = align_up(o + (long long)s.E_local * 2 * s.F_pad * c->d_model, 128);
+  s.off_d = o;      o = align_up(o + (long long)s.E_local * c->d_model * s.F_pad, 128);
+  s.off_sgu = o;    if (c->shared_expert) o = align_up(o + 2ll * s.F_pad * c->d_model, 128);
+  s.off_sd = o;     if (c->shared_expert) o = align_up(o + (long long)c->d_model * s.F_pad, 128);
+  s.n_params = o;
+  return s;
+}
+
+long long workspace_bytes(const moe_config_t* c) {
+  const Sizes s = sizes_of(c);
+  const long long esz = c->precision == MOE_PRECISION_F32 ? 4 : 2;
+  const long long T = c->max_tokens, d = c->d_model, E = c->num_experts, k = c->experts_per_token;
+  long long b = 0;
+  if (c->precision == MOE_PRECISION_Q8) {
+    b += (long long)c->num_experts * d * 4;                          // router
+    b += (s.n_params - s.off_gu) + (s.E_local + 1ll) * (2 * s.F_pad + d) * 4;  // int8 values and scales
+  } else {
+    b += s.n_params * 4 * (c->training ? 4 : 1);
+    if (c->precision == MOE_PRECISION_BF16) b += s.n_params * 2;
+  }
+  const long long act_rows = (long long)s.rows_cap * (2 * d + 3 * s.F_pad) + (c->shared_expert ? (long long)s.shared_rows_cap * (d + 3 * s.F_pad) : 0);
+  b += act_rows * esz * (c->training ? 2 : 1);
+  b += T * E * 4 * 4 + T * k * 4 * 6 + (long long)s.rows_cap * 8;
+  return b;
+}
+
+int dalloc(moe_layer* L, void** p, long long bytes, bool zero) {
+  if (bytes <= 0) bytes = 16;
+  CK(cudaMalloc(p, (size_t)bytes));
+  L->allocations.push_back(*p);
+  L->allocated_bytes += bytes;
+  if (zero) CK(cudaMemset(*p, 0, (size_t)bytes));
+  return MOE_OK;
+}
+#define DA(ptr, bytes, zero)                                         \
+  do {                                                               \
+    int rc_ = dalloc(L, (void**)&(ptr), (long long)(bytes), (zero)); \
+    if (rc_ != MOE_OK) return rc_;                                   \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// weight packing
+// ---------------------------------------------------------------------------
+struct WeightSlot {
+  long long offset;     // into the parameter arenas
+  int rows, cols;       // caller's [out, in]
+  int ld;               // leading dimension inside the arena
+  int kind;             // 0 plain rows, 1 gate rows of the interleaved matrix, 2 up rows
+};
+
+int slot_of_weight(moe_layer* L, int which, int expert, WeightSlot* s) {
+  const int d = L->d, F = L->F, Fp = L->F_pad;
+  int le = expert - L->e0;
+  switch (which) {
+    case MOE_W_ROUTER: *s = {L->off_router, L->E, d, d, 0}; return MOE_OK;
+    case MOE_W_GATE:
+    case MOE_W_UP:
+      if (le < 0 || le >= L->E_local) return fail(L, MOE_INVALID_INPUT, "expert %d is not owned by this handle", expert);
+      *s = {L->off_gu + (long long)le * 2 * Fp * d, F, d, d, which == MOE_W_GATE ? 1 : 2};
+      return MOE_OK;
+    case MOE_W_DOWN:
+      if (le < 0 || le >= L->E_local) return fail(L, MOE_INVALID_INPUT, "expert %d is not owned by this handle", expert);
+      *s = {L->off_d + (long long)le * d * Fp, d, F, Fp, 0};
+      return MOE_OK;
+    case MOE_W_SHARED_GATE:
+    case MOE_W_SHARED_UP:
+      if (!L->shared) return fail(L, MOE_INVALID_INPUT, "the layer has no shared expert");
+      *s = {L->off_sgu, F, d, d, which == MOE_W_SHARED_GATE ? 1 : 2};
+      return MOE_OK;
+    case MOE_W_SHARED_DOWN:
+      if (!L->shared) return fail(L, MOE_INVALID_INPUT, "the layer has no shared expert");
+      *s = {L->off_sd, d, F, Fp, 0};
+      return MOE_OK;
+  }
+  return fail(L, MOE_INVALID_INPUT, "unknown weight id %d", which);
+}
+
+__global__ void pack_kernel(const float* __restrict__ src, float* __restrict__ dst, bf16* __restrict__ dst_bf16,
+                            int rows, int cols, int ld, int kind) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * cols) return;
+  const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+  const int pr = kind == 0 ? r : gu_row(kind - 1, r);
+  const float v = src[i];
+  dst[(long long)pr * ld + c] = v;
+  if (dst_bf16) dst_bf16[(long long)pr * ld + c] = __float2bfloat16_rn(v);
+}
+__global__ void unpack_kernel(const float* __restrict__ src, float* __restrict__ dst, int rows, int cols, int ld,
+                              int kind, int zero) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * cols) return;
+  const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+  const int pr = kind == 0 ? r : gu_row(kind - 1, r);
+  dst[i] = zero ? 0.f : src[(long long)pr * ld + c];
+}
+__global__ void pack_q8_kernel(const int8_t* __restrict__ src, const float* __restrict__ scale_src,
+                               int8_t* __restrict__ dst, float* __restrict__ scale_dst, int rows, int cols, int ld,
+                               int kind) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * cols) return;
+  const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
+  const int pr = kind == 0 ? r : gu_row(kind - 1, r);
+  dst[(long long)pr * ld + c] = src[i];
+  if (c == 0) scale_dst[pr] = scale_src[r];
+}
+__global__ void shared_meta_kernel(int* meta, int tokens) {
+  const int rows = round_up(tokens, GROUP_ALIGN);
+  meta[0] = 0; meta[1] = rows; meta[2] = 0; meta[3] = rows / GROUP_ALIGN;
+}
+
+bool is_device_pointer(const void* p) {
+  cudaPointerAttributes a;
+  if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
+}
+
+int check_flag(moe_layer* L) {
+  int flag = 0;
+  CK(cudaMemcpy(&flag, L->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
+  if (flag != 0) {
+    cudaMemset(L->error_flag, 0, sizeof(int));
+    return fail(L, MOE_TIMEOUT, "a bounded device-side wait gave up (code %d)", flag);
+  }
+  return MOE_OK;
+}
+
+// ---------------------------------------------------------------------------
+// expert stacks: one set of row groups through gate|up -> SwiGLU -> down
+// ---------------------------------------------------------------------------
+struct Groups {
+  const int* row0;
+  const int* tstart;
+  int n_groups;
+  int cap_rows;       // rows of the internal row-indexed buffers
+  int in_rows;        // readable rows of the external input operand
+};
+struct ExpertIO {
+  const void* x;          // input rows [*, d]
+  void *gu, *h, *y;       // [cap, 2Fp], [cap, Fp], [cap, d]
+  const void* dy;         // upstream gradient rows [*, d]
+  void *dgu, *dx, *dh;    // [cap, 2Fp], [cap, d], [cap, Fp] (dh: f32 path only)
+  long long w_gu, w_d;    // arena offsets
+};
+
+int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save, cudaStream_t st) {
+  const int d = L->d, Fp = L->F_pad;
+  if (L->act == PREC_BF16) {
+    tc::GemmArgs a{};
+    a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
+    a.N = 2 * Fp; a.K = d;
+    a.out0 = io.h; a.ld0 = Fp; a.out1 = save ? io.gu : nullptr; a.ld1 = 2 * Fp;
+    tc::Operand A{io.x, G.in_rows, d, 1};
+    tc::Operand B{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
+    CK(tc::gemm_rows_nt(A, B, a, tc::EPI_SWIGLU, L->sm_count, st));
+    tc::GemmArgs b{};
+    b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
+    b.N = d; b.K = Fp; b.out0 = io.y; b.ld0 = d;
+    tc::Operand A2{io.h, G.cap_rows, Fp, 1};
+    tc::Operand B2{L->wb + io.w_d, d, Fp, G.n_groups};
+    CK(tc::gemm_rows_nt(A2, B2, b, tc::EPI_STORE, L->sm_count, st));
+  } else {
+    SimtGemmArgs a{};
+    a.A = (const float*)io.x; a.B = L->w + io.w_gu; a.C = (float*)io.gu;
+    a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows; a.b_rows = 0;
+    a.N = 2 * Fp; a.K = d; a.b_group_stride = 2ll * Fp * d;
+    CK(simt_gemm_nt(a, st));
+    CK(launch_swiglu_fwd_f32((const float*)io.gu, (float*)io.h, G.cap_rows, Fp, st));
+    SimtGemmArgs b{};
+    b.A = (const float*)io.h; b.B = L->w + io.w_d; b.C = (float*)io.y;
+    b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
+    b.N = d; b.K = Fp; b.b_group_stride = (long long)d * Fp;
+    CK(simt_gemm_nt(b, st));
+  }
+  return MOE_OK;
+}
+
+int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st) {
+  const int d = L->d, Fp = L->F_pad;
+  const int acc = L->grad_valid ? 1 : 0;
+  if (L->act == PREC_BF16) {
+    // dgu = swiglu'(dy W_d) ; dW_d += dy^T h ; dx = dgu W_gu ; dW_gu += dgu^T x
+    tc::GemmArgs a{};
+    a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
+    a.N = Fp; a.K = d; a.out0 = io.dgu; a.ld0 = 2 * Fp; a.aux = io.gu; a.ldaux = 2 * Fp;
+    tc::Operand A{io.dy, G.in_rows, d, 1};
+    tc::Operand B{L->wb + io.w_d, d, Fp, G.n_groups};
+    CK(tc::gemm_rows_nn(A, B, a, tc::EPI_SWIGLU_BWD, L->sm_count, st));
+
+    tc::GemmArgs wd{};
+    wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.error_flag = L->error_flag;
+    wd.M = d; wd.N = Fp; wd.out0 = L->g + io.w_d; wd.ld0 = Fp; wd.group_stride0 = (long long)d * Fp; wd.accumulate = acc;
+    tc::Operand Ad{io.dy, G.in_rows, d, 1};
+    tc::Operand Bd{io.h, G.cap_rows, Fp, 1};
+    CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st));
+
+    tc::GemmArgs b{};
+    b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
+    b.N = d; b.K = 2 * Fp; b.out0 = io.dx; b.ld0 = d;
+    tc::Operand A2{io.dgu, G.cap_rows, 2 * Fp, 1};
+    tc::Operand B2{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
+    CK(tc::gemm_rows_nn(A2, B2, b, tc::EPI_STORE, L->sm_count, st));
+
+    tc::GemmArgs wg{};
+    wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.error_flag = L->error_flag;
+    wg.M = 2 * Fp; wg.N = d; wg.out0 = L->g + io.w_gu; wg.ld0 = d; wg.group_stride0 = 2ll * Fp * d; wg.accumulate = acc;
+    tc::Operand Ag{io.dgu, G.cap_rows, 2 * Fp, 1};
+    tc::Operand Bg{io.x, G.in_rows, d, 1};
+    CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st));
+  } else {
+    SimtGemmArgs a{};
+    a.A = (const float*)io.dy; a.B = L->w + io.w_d; a.C = (float*)io.dh;
+    a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows;
+    a.N = Fp; a.K = d; a.b_group_stride = (long long)d * Fp;
+    CK(simt_gemm_nn(a, st));
+    CK(launch_swiglu_bwd_f32((const float*)io.dh, (const float*)io.gu, (float*)io.dgu, G.cap_rows, Fp, st));
+    SimtGemmArgs wd{};
+    wd.A = (const float*)io.dy; wd.B = (const float*)io.h; wd.C = L->g + io.w_d;
+    wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.a_rows = G.in_rows; wd.b_rows = G.cap_rows;
+    wd.M = d; wd.N = Fp; wd.c_group_stride = (long long)d * Fp; wd.accumulate = acc;
+    CK(simt_gemm_tn(wd, st));
+    SimtGemmArgs b{};
+    b.A = (const float*)io.dgu; b.B = L->w + io.w_gu; b.C = (float*)io.dx;
+    b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
+    b.N = d; b.K = 2 * Fp; b.b_group_stride = 2ll * Fp * d;
+    CK(simt_gemm_nn(b, st));
+    SimtGemmArgs wg{};
+    wg.A = (const float*)io.dgu; wg.B = (const float*)io.x; wg.C = L->g + io.w_gu;
+    wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.a_rows = G.cap_rows; wg.b_rows = G.in_rows;
+    wg.M = 2 * Fp; wg.N = d; wg.c_group_stride = 2ll * Fp * d; wg.accumulate = acc;
+    CK(simt_gemm_tn(wg, st));
+  }
+  return MOE_OK;
+}
+
+int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens, int cols, const uint8_t* valid,
+                 void* y, int accumulate, int save, cudaStream_t st) {
+  if (cols != L->d) {   // moe.rs:248-253
+    L->err = "InvalidInput: expected " + std::to_string(L->d) + " columns, got " + std::to_string(cols);
+    return MOE_INVALID_INPUT;
+  }
+  if (tokens < 0 || tokens > L->max_tokens) {
+    L->err = "InvalidInput: " + std::to_string(tokens) + " tokens exceed max_tokens " + std::to_string(L->max_tokens);
+    return MOE_INVALID_INPUT;
+  }
+  if (tokens > 0 && (!x || !y)) { L->err = "InvalidInput: null activation pointer"; return MOE_INVALID_INPUT; }
+  if (L->precision == MOE_PRECISION_Q8) return fail(L, MOE_UNSUPPORTED, "the int8 decode path is not built into this library version");
+  if (save && !L->training) { L->err = "InvalidConfig: save_for_backward needs a handle created with training = 1"; return MOE_INVALID_CONFIG; }
+  L->have_cache = false;
+  L->last_tokens = tokens;
+  L->last_stream = st;
+  if (tokens == 0) return MOE_OK;
+
+  RouterArgs ra{};
+  ra.x = x; ra.w_router = L->w + L->off_router; ra.logits_in = logits_in; ra.valid = valid;
+  ra.tokens = tokens; ra.d = L->d; ra.E = L->E; ra.k = L->k;
+  ra.logits_out = L->logits; ra.probs = L->probs; ra.lse = L->lse; ra.expert_of = L->expert_of; ra.gates = L->gates;
+  ra.partial = L->partial; ra.hist = L->hist;
+  CK(launch_router(ra, L->act, st));
+  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, nullptr, nullptr, st));
+
+  PermuteArgs pa{};
+  pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
+  pa.tokens = tokens; pa.d = L->d; pa.E = L->E; pa.k = L->k;
+  pa.x_perm = L->x_perm; pa.slot_pos = L->slot_pos; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
+  pa.token_of = L->token_of; pa.slot_of = L->slot_of;
+  CK(launch_permute(pa, L->act, st));
+
+  Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+  ExpertIO io{};
+  io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.w_gu = L->off_gu; io.w_d = L->off_d;
+  int rc = experts_forward(L, G, io, save != 0, st);
+  if (rc != MOE_OK) return rc;
+
+  if (L->shared) {
+    shared_meta_kernel<<<1, 1, 0, st>>>(L->shared_meta, tokens); count_launch();
+    Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
+    ExpertIO sio{};
+    sio.x = x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
+    rc = experts_forward(L, S, sio, save != 0, st);
+    if (rc != MOE_OK) return rc;
+  }
+
+  CombineArgs ca{};
+  ca.y_perm = L->y_perm; ca.shared = L->shared ? L->y_s : nullptr; ca.expert_of = L->expert_of; ca.gates = L->gates;
+  ca.slot_pos = L->slot_pos; ca.y = y; ca.tokens = tokens; ca.d = L->d; ca.k = L->k; ca.accumulate = accumulate;
+  CK(launch_combine(ca, L->act, st));
+  CK(cudaGetLastError());
+  L->have_cache = save != 0;
+  L->last_x = x;
+  return MOE_OK;
+}
+
+int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaStream_t st) {
+  if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
+  if (!L->have_cache) { L->err = "InvalidInput: moe_backward needs a preceding moe_forward with save_for_backward"; return MOE_INVALID_INPUT; }
+  if (!gy || !gx) { L->err = "InvalidInput: null gradient pointer"; return MOE_INVALID_INPUT; }
+  const int tokens = L->last_tokens;
+  if (tokens == 0) return MOE_OK;
+
+  GatherGradArgs ga{};
+  ga.grad_y = gy; ga.y_perm = L->y_perm; ga.slot_pos = L->slot_pos; ga.gates = L->gates;
+  ga.grad_y_perm = L->dy_perm; ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
+  CK(launch_gather_grad(ga, L->act, st));
+  CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st));
+
+  Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+  ExpertIO io{};
+  io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
+  io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
+  int rc = experts_backward(L, G, io, st);
+  if (rc != MOE_OK) return rc;
+
+  if (L->shared) {
+    Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
+    ExpertIO sio{};
+    sio.x = L->last_x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.dy = gy; sio.dgu = L->dgu_s;
+    sio.dx = L->dx_s; sio.dh = L->dh_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
+    rc = experts_backward(L, S, sio, st);
+    if (rc != MOE_OK) return rc;
+  }
+
+  RouterBwdArgs rb{};
+  rb.probs = L->probs; rb.lse = L->lse; rb.expert_of = L->expert_of; rb.grad_gates = L->grad_gates;
+  rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
+  rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
+  CK(launch_router_bwd(rb, st));
+
+  UnpermuteArgs ua{};
+  ua.grad_x_perm = L->dx_perm; ua.shared = L->shared ? L->dx_s : nullptr; ua.grad_logits = L->grad_logits;
+  ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
+  ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
+  CK(launch_unpermute(ua, L->act, st));
+
+  RouterWgradArgs rw{};
+  rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
+  rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
+  CK(launch_router_wgrad(rw, L->act, st));
+  CK(cudaGetLastError());
+  L->grad_valid = true;
+  return MOE_OK;
+}
+
+int ensure_host_buffers(moe_layer* L) {
+  if (L->pinned) return MOE_OK;
+  const long long n = (long long)L->max_tokens * L->d;
+  CK(cudaMallocHost(&L->pinned, (size_t)n * 4));
+  DA(L->host_stage_f32, n * 4, false);
+  DA(L->host_x, n * L->esz, false);
+  DA(L->host_y, n * L->esz, false);
+  if (L->training) DA(L->host_gx, n * L->esz, false);
+  DA(L->host_valid, L->max_tokens, false);
+  CK(cudaStreamCreateWithFlags(&L->own_stream, cudaStreamNonBlocking));
+  return MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t moe_config_validate(const moe_config_t* cfg, char* message, int32_t message_len) {
+  if (message && message_len > 0) message[0] = 0;
+  return validate(cfg, message, message_len);
+}
+
+int64_t moe_workspace_bytes(const moe_config_t* cfg) {
+  if (validate(cfg, nullptr, 0) != MOE_OK) return -1;
+  return workspace_bytes(cfg);
+}
+
+int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
+  if (!out) return MOE_INVALID_INPUT;
+  *out = nullptr;
+  char msg[256];
+  if (validate(cfg, msg, sizeof(msg)) != MOE_OK) return MOE_INVALID_CONFIG;
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0 || cfg->device < 0 || cfg->device >= ndev) {
+    cudaGetLastError();
+    return MOE_UNSUPPORTED;   // no usable device: fail closed, never a host fallback
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess) return MOE_CUDA_ERROR;
+  if (prop.major != 10) return MOE_UNSUPPORTED;   // built for sm_100a only
+  moe_layer* L = new (std::nothrow) moe_layer;
+  if (!L) return MOE_OUT_OF_MEMORY;
+  *out = L;   // returned even on failure so the caller can read moe_last_error, then destroy
+  L->device = cfg->device;
+  L->sm_count = prop.multiProcessorCount;
+  CK(cudaSetDevice(cfg->device));
+
+  const Sizes s = sizes_of(cfg);
+  L->d = cfg->d_model; L->E = cfg->num_experts; L->k = cfg->experts_per_token; L->F = cfg->d_ff; L->F_pad = s.F_pad;
+  L->E_local = s.E_local; L->ep_rank = cfg->ep_rank; L->ep_size = cfg->ep_size; L->e0 = cfg->ep_rank * s.E_local;
+  L->shared = cfg->shared_expert != 0; L->training = cfg->training != 0;
+  L->aux_w = cfg->aux_loss_weight; L->z_w = cfg->router_z_loss_weight;
+  L->precision = cfg->precision; L->act = cfg->precision == MOE_PRECISION_F32 ? PREC_F32 : PREC_BF16;
+  L->esz = L->act == PREC_F32 ? 4 : 2;
+  L->max_tokens = cfg->max_tokens; L->rows_cap = s.rows_cap; L->shared_rows_cap = s.shared_rows_cap;
+  L->off_router = s.off_router; L->off_gu = s.off_gu; L->off_d = s.off_d; L->off_sgu = s.off_sgu; L->off_sd = s.off_sd;
+  L->n_params = s.n_params;
+  if (L->ep_size != 1) return fail(L, MOE_UNSUPPORTED, "expert-parallel handles are not built into this library version");
+
+  const long long T = L->max_tokens, d = L->d, E = L->E, k = L->k, Fp = L->F_pad;
+  if (L->precision == MOE_PRECISION_Q8) {
+    DA(L->w, (long long)E * d * 4, true);   // router only
+  } else {
+    DA(L->w, L->n_params * 4, true);
+    if (L->training) {
+      DA(L->g, L->n_params * 4, true);
+      DA(L->m, L->n_params * 4, true);
+      DA(L->v, L->n_params * 4, true);
+    }
+    if (L->act == PREC_BF16) DA(L->wb, L->n_params * 2, true);
+  }
+  L->stage_elems = std::max((long long)E * d, 2ll * Fp * d);
+  DA(L->stage, L->stage_elems * 4 * 2, false);
+
+  const int nb = ceil_div((int)T, ROUTER_ROWS);
+  DA(L->logits, T * E * 4, false); DA(L->probs, T * E * 4, false); DA(L->lse, T * 4, false);
+  DA(L->gates, T * k * 4, false); DA(L->expert_of, T * k * 4, false);
+  DA(L->partial, (long long)nb * (E + 2) * 4, false); DA(L->hist, (long long)nb * E * 4, false);
+  DA(L->meta_block, (4 * (E + 1) + 8) * 4, true);
+  L->meta.counts = L->meta_block; L->meta.offsets = L->meta_block + (E + 1); L->meta.pad_off = L->meta_block + 2 * (E + 1);
+  L->meta.tile_start = L->meta_block + 3 * (E + 1); L->meta.total = L->meta_block + 4 * (E + 1);
+  DA(L->stats, (E + 2) * 4, true); DA(L->losses, 2 * 4, true);
+  DA(L->slot_pos, T * k * 4, false); DA(L->token_of, T * k * 4, false); DA(L->slot_of, T * k * 4, false);
+  DA(L->row_token, (long long)L->rows_cap * 4, false); DA(L->row_gate, (long long)L->rows_cap * 4, false);
+  DA(L->shared_meta, 4 * 4, true); DA(L->error_flag, 4, true);
+
+  const long long rc = L->rows_cap, sc = L->shared_rows_cap, es = (long long)L->esz;
+  DA(L->x_perm, rc * d * es, true); DA(L->gu, rc * 2 * Fp * es, true); DA(L->h, rc * Fp * es, true);
+  DA(L->y_perm, rc * d * es, true);
+  if (L->shared) { DA(L->gu_s, sc * 2 * Fp * es, true); DA(L->h_s, sc * Fp * es, true); DA(L->y_s, sc * d * es, true); }
+  if (L->training) {
+    DA(L->dy_perm, rc * d * es, true); DA(L->dgu, rc * 2 * Fp * es, true); DA(L->dx_perm, rc * d * es, true);
+    if (L->act == PREC_F32) DA(L->dh, rc * Fp * es, true);
+    if (L->shared) {
+      DA(L->dgu_s, sc * 2 * Fp * es, true); DA(L->dx_s, sc * d * es, true);
+      if (L->act == PREC_F32) DA(L->dh_s, sc * Fp * es, true);
+    }
+    DA(L->grad_gates, T * k * 4, true); DA(L->grad_logits, T * E * 4, true);
+    L->rw_splits = (int)std::min<long long>(64, std::max<long long>(1, T / 256));
+    DA(L->rw_scratch, (long long)L->rw_splits * E * d * 4, false);
+  }
+  CK(cudaDeviceSynchronize());
+  return MOE_OK;
+}
+
+void moe_destroy(moe_layer_t* L) {
+  if (!L) return;
+  cudaSetDevice(L->device);
+  cudaDeviceSynchronize();
+  for (void* p : L->allocations) cudaFree(p);
+  if (L->pinned) cudaFreeHost(L->pinned);
+  if (L->own_stream) cudaStreamDestroy(L->own_stream);
+  delete L;
+}
+
+const char* moe_last_error(const moe_layer_t* L) { return L ? L->err.c_str() : "null handle"; }
+
+int32_t moe_clear_error(moe_layer_t* L) {
+  if (!L) return MOE_INVALID_INPUT;
+  L->status = MOE_OK;
+  L->err.clear();
+  cudaSetDevice(L->device);
+  cudaGetLastError();
+  if (L->error_flag) cudaMemset(L->error_flag, 0, sizeof(int));
+  return MOE_OK;
+}
+
+int32_t moe_set_weight_f32(moe_layer_t* L, int32_t which, int32_t expert, const float* src, int32_t rows, int32_t cols) {
+  ENTER(L);
+  if (L->precision == MOE_PRECISION_Q8 && which != MOE_W_ROUTER) { L->err = "InvalidInput: a quantized layer takes int8 expert weights"; return MOE_INVALID_INPUT; }
+  WeightSlot s;
+  int rc = slot_of_weight(L, which, expert, &s);
+  if (rc != MOE_OK) { L->status = MOE_OK; return rc; }
+  if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  const long long n = (long long)rows * cols;
+  const float* dev_src = src;
+  if (!is_device_pointer(src)) {
+    CK(cudaMemcpy(L->stage, src, (size_t)n * 4, cudaMemcpyHostToDevice));
+    dev_src = L->stage;
+  }
+  pack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(dev_src, L->w + s.offset, L->wb ? L->wb + s.offset : nullptr, rows, cols, s.ld, s.kind); count_launch();
+  CK(cudaGetLastError());
+  CK(cudaDeviceSynchronize());
+  return MOE_OK;
+}
+
+static int read_arena(moe_layer* L, const float* arena, int which, int expert, float* dst, int rows, int cols, bool zero) {
+  WeightSlot s;
+  int rc = slot_of_weight(L, which, expert, &s);
+  if (rc != MOE_OK) { L->status = MOE_OK; return rc; }
+  if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  if (!arena) { L->err = "InvalidConfig: the handle holds no such buffer (training = 0 or quantized)"; return MOE_INVALID_CONFIG; }
+  const long long n = (long long)rows * cols;
+  const bool dev = is_device_pointer(dst);
+  float* out = dev ? dst : L->stage;
+  unpack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(arena + s.offset, out, rows, cols, s.ld, s.kind, zero ? 1 : 0); count_launch();
+  CK(cudaGetLastError());
+  if (!dev) CK(cudaMemcpy(dst, L->stage, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  else CK(cudaDeviceSynchronize());
+  return MOE_OK;
+}
+
+int32_t moe_get_weight_f32(moe_layer_t* L, int32_t which, int32_t expert, float* dst, int32_t rows, int32_t cols) {
+  ENTER(L);
+  if (L->precision == MOE_PRECISION_Q8 && which != MOE_W_ROUTER) { L->err = "InvalidConfig: quantized weights are not readable as f32"; return MOE_INVALID_CONFIG; }
+  return read_arena(L, L->w, which, expert, dst, rows, cols, false);
+}
+int32_t moe_get_grad_f32(moe_layer_t* L, int32_t which, int32_t expert, float* dst, int32_t rows, int32_t cols) {
+  ENTER(L);
+  return read_arena(L, L->g, which, expert, dst, rows, cols, !L->grad_valid);
+}
+int32_t moe_get_moments_f32(moe_layer_t* L, int32_t which, int32_t expert, float* m, float* v, int32_t rows, int32_t cols) {
+  ENTER(L);
+  int rc = read_arena(L, L->m, which, expert, m, rows, cols, false);
+  if (rc != MOE_OK) return rc;
+  return read_arena(L, L->v, which, expert, v, rows, cols, false);
+}
+int32_t moe_set_moments_f32(moe_layer_t* L, int32_t which, int32_t expert, const float* m, const float* v, int32_t rows, int32_t cols) {
+  ENTER(L);
+  if (!L->m) { L->err = "InvalidConfig: the handle holds no optimizer state"; return MOE_INVALID_CONFIG; }
+  WeightSlot s;
+  int rc = slot_of_weight(L, which, expert, &s);
+  if (rc != MOE_OK) { L->status = MOE_OK; return rc; }
+  if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  const long long n = (long long)rows * cols;
+  const float* srcs[2] = {m, v};
+  float* dsts[2] = {L->m, L->v};
+  for (int i = 0; i < 2; ++i) {
+    const float* dev_src = srcs[i];
+    if (!is_device_pointer(srcs[i])) {
+      CK(cudaMemcpy(L->stage, srcs[i], (size_t)n * 4, cudaMemcpyHostToDevice));
+      dev_src = L->stage;
+    }
+    pack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(dev_src, dsts[i] + s.offset, nullptr, rows, cols, s.ld, s.kind); count_launch();
+    CK(cudaDeviceSynchronize());
+  }
+  return MOE_OK;
+}
+
+int32_t moe_set_weight_q8(moe_layer_t* L, int32_t, int32_t, const int8_t*, const float*, int32_t, int32_t) {
+  ENTER(L);
+  L->err = "Unsupported: the int8 decode path is not built into this library version";
+  return MOE_UNSUPPORTED;
+}
+
+int32_t moe_forward(moe_layer_t* L, const void* x, int32_t tokens, int32_t cols, const uint8_t* valid, void* y,
+                    int32_t accumulate, int32_t save, void* stream) {
+  ENTER(L);
+  return forward_impl(L, x, nullptr, tokens, cols, valid, y, accumulate, save, (cudaStream_t)stream);
+}
+
+int32_t moe_forward_from_logits(moe_layer_t* L, const void* x, const float* logits, int32_t tokens, int32_t cols,
+                                const uint8_t* valid, void* y, int32_t accumulate, int32_t save, void* stream) {
+  ENTER(L);
+  if (!logits) { L->err = "InvalidInput: null logits"; return MOE_INVALID_INPUT; }
+  return forward_impl(L, x, logits, tokens, cols, valid, y, accumulate, save, (cudaStream_t)stream);
+}
+
+int32_t moe_backward(moe_layer_t* L, const void* gy, void* gx, int32_t accumulate, void* stream) {
+  ENTER(L);
+  return backward_impl(L, gy, gx, accumulate, (cudaStream_t)stream);
+}
+
+int32_t moe_zero_grad(moe_layer_t* L, void*) {
+  ENTER(L);
+  L->grad_valid = false;   // a flag, as DeviceParam::zero_grad (gpu_transformer.rs:634-636)
+  return MOE_OK;
+}
+
+int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, float wd, int32_t step, float scale, void* stream) {
+  ENTER(L);
+  if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!L->grad_valid) CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
+  AdamArgs a{};
+  a.w = L->w; a.g = L->g; a.m = L->m; a.v = L->v; a.w_bf16 = L->wb; a.n = L->n_params;
+  a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
+  a.c1 = 1.0f - powf(b1, (float)step);
+  a.c2 = 1.0f - powf(b2, (float)step);
+  CK(launch_adam(a, st));
+  L->grad_valid = false;   // the kernel cleared the gradients
+  return MOE_OK;
+}
+
+int32_t moe_forward_host(moe_layer_t* L, const float* x, int32_t tokens, int32_t cols, const uint8_t* valid, float* y, int32_t save) {
+  ENTER(L);
+  if (cols != L->d || tokens < 0 || tokens > L->max_tokens || !x || !y) {
+    L->err = "InvalidInput: expected " + std::to_string(L->d) + " columns and at most " + std::to_string(L->max_tokens) + " tokens";
+    return MOE_INVALID_INPUT;
+  }
+  int rc = ensure_host_buffers(L);
+  if (rc != MOE_OK) return rc;
+  cudaStream_t st = L->own_stream;
+  const long long n = (long long)tokens * L->d;
+  if (tokens > 0) {
+    memcpy(L->pinned, x, (size_t)n * 4);
+    if (L->act == PREC_F32) {
+      CK(cudaMemcpyAsync(L->host_x, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    } else {
+      CK(cudaMemcpyAsync(L->host_stage_f32, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(launch_cast_f32_to_bf16(L->host_stage_f32, (bf16*)L->host_x, n, st));
+    }
+    if (valid) CK(cudaMemcpyAsync(L->host_valid, valid, (size_t)tokens, cudaMemcpyHostToDevice, st));
+  }
+  rc = forward_impl(L, L->host_x, nullptr, tokens, cols, valid ? L->host_valid : nullptr, L->host_y, 0, save, st);
+  if (rc != MOE_OK) return rc;
+  if (tokens > 0) {
+    if (L->act == PREC_F32) {
+      CK(cudaMemcpyAsync(L->pinned, L->host_y, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    } else {
+      CK(launch_cast_bf16_to_f32((const bf16*)L->host_y, L->host_stage_f32, n, st));
+      CK(cudaMemcpyAsync(L->pinned, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    }
+  }
+  CK(cudaStreamSynchronize(st));
+  if (tokens > 0) memcpy(y, L->pinned, (size_t)n * 4);
+  return check_flag(L);
+}
+
+int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
+  ENTER(L);
+  if (!gy || !gx) { L->err = "InvalidInput: null gradient pointer"; return MOE_INVALID_INPUT; }
+  if (!L->have_cache || L->last_x != L->host_x) { L->err = "InvalidInput: moe_backward_host needs a preceding moe_forward_host with save_for_backward"; return MOE_INVALID_INPUT; }
+  cudaStream_t st = L->own_stream;
+  const long long n = (long long)L->last_tokens * L->d;
+  if (n > 0) {
+    memcpy(L->pinned, gy, (size_t)n * 4);
+    // host_y is free once the forward result has been copied out: reuse it for the upstream gradient
+    if (L->act == PREC_F32) {
+      CK(cudaMemcpyAsync(L->host_y, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    } else {
+      CK(cudaMemcpyAsync(L->host_stage_f32, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(launch_cast_f32_to_bf16(L->host_stage_f32, (bf16*)L->host_y, n, st));
+    }
+  }
+  int rc = backward_impl(L, L->host_y, L->host_gx, 0, st);
+  if (rc != MOE_OK) return rc;
+  if (n > 0) {
+    if (L->act == PREC_F32) {
+      CK(cudaMemcpyAsync(L->pinned, L->host_gx, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    } else {
+      CK(launch_cast_bf16_to_f32((const bf16*)L->host_gx, L->host_stage_f32, n, st));
+      CK(cudaMemcpyAsync(L->pinned, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+    }
+  }
+  CK(cudaStreamSynchronize(st));
+  if (n > 0) memcpy(gx, L->pinned, (size_t)n * 4);
+  return check_flag(L);
+}
+
+int32_t moe_get_losses(moe_layer_t* L, float* aux, float* z) {
+  ENTER(L);
+  CK(cudaStreamSynchronize(L->last_stream));
+  float v[2] = {0.f, 0.f};
+  if (L->last_tokens > 0) CK(cudaMemcpy(v, L->losses, sizeof(v), cudaMemcpyDeviceToHost));
+  if (aux) *aux = v[0];
+  if (z) *z = v[1];
+  return check_flag(L);
+}
+
+int32_t moe_get_routing(moe_layer_t* L, int32_t* expert_of, float* gates, int32_t* counts, int32_t* token_of,
+                        int32_t* slot_of, int32_t* routed) {
+  ENTER(L);
+  CK(cudaStreamSynchronize(L->last_stream));
+  const long long tk = (long long)L->last_tokens * L->k;
+  int total[4] = {0, 0, 0, 0};
+  if (L->last_tokens > 0) CK(cudaMemcpy(total, L->meta.total, sizeof(total), cudaMemcpyDeviceToHost));
+  if (expert_of && tk > 0) CK(cudaMemcpy(expert_of, L->expert_of, (size_t)tk * 4, cudaMemcpyDeviceToHost));
+  if (gates && tk > 0) CK(cudaMemcpy(gates, L->gates, (size_t)tk * 4, cudaMemcpyDeviceToHost));
+  if (counts) {
+    if (L->last_tokens > 0) CK(cudaMemcpy(counts, L->meta.counts, (size_t)L->E * 4, cudaMemcpyDeviceToHost));
+    else memset(counts, 0, (size_t)L->E * 4);
+  }
+  if (token_of && total[0] > 0) CK(cudaMemcpy(token_of, L->token_of, (size_t)total[0] * 4, cudaMemcpyDeviceToHost));
+  if (slot_of && total[0] > 0) CK(cudaMemcpy(slot_of, L->slot_of, (size_t)total[0] * 4, cudaMemcpyDeviceToHost));
+  if (routed) *routed = total[0];
+  return check_flag(L);
+}
+
+int32_t moe_get_router_cache(moe_layer_t* L, float* logits, float* probs, float* lse) {
+  ENTER(L);
+  CK(cudaStreamSynchronize(L->last_stream));
+  const long long te = (long long)L->last_tokens * L->E;
+  if (te > 0) {
+    if (logits) CK(cudaMemcpy(logits, L->logits, (size_t)te * 4, cudaMemcpyDeviceToHost));
+    if (probs) CK(cudaMemcpy(probs, L->probs, (size_t)te * 4, cudaMemcpyDeviceToHost));
+    if (lse) CK(cudaMemcpy(lse, L->lse, (size_t)L->last_tokens * 4, cudaMemcpyDeviceToHost));
+  }
+  return MOE_OK;
+}
+
+int32_t moe_synchronize(moe_layer_t* L) {
+  ENTER(L);
+  CK(cudaDeviceSynchronize());
+  return check_flag(L);
+}
+
+}  // extern "C"

@@ -1,0 +1,414 @@
+// Fused router and device-side dispatch.
+//
+//   router_kernel   logits = x W_r^T, softmax + log-sum-exp, dropless top-k,
+//                   renormalised gates, and per-block partial sums for the Switch
+//                   load-balancing loss and the ST-MoE z-loss, plus the per-block
+//                   expert histogram the dispatch needs.
+//                   Replaces Router::forward + softmax_rows + route + the stats
+//                   half of auxiliary_losses (reference moe.rs:262-264, 553-593,
+//                   602-639; device kernels softmax_lse / topk_gate / moe_stats,
+//                   cuda_training.rs:291-292, 313).
+//   finalize_kernel reduces the partials in a fixed order (no float atomics), forms
+//                   the two losses, and scans the histogram into per-(block, expert)
+//                   write cursors, compact offsets and 128-row padded group offsets.
+//                   Replaces the host pass of gpu_model.rs:2474-2507.
+//   permute_kernel  stable counting-sort placement of every (token, rank) slot and
+//                   the row gather with 16-byte vector copies (moe.rs:266-279,
+//                   gather_rows in cuda_training.rs:70).
+//
+// Selection is done on probabilities with a strict '>' so ties go to the lowest
+// expert index, exactly as the reference.  The exponentials are evaluated in
+// double precision and rounded once to f32, and the row sum is accumulated
+// sequentially in expert order, so the probabilities (and therefore the chosen
+// experts) agree with a host libm evaluation of the same logits.
+
+#include "kernels.cuh"
+
+namespace moe {
+
+constexpr int RT_THREADS = 256;
+constexpr int RT_KC = 32;
+
+template <typename T, int EPT, bool FROM_LOGITS>
+__global__ void __launch_bounds__(RT_THREADS)
+router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ logits_in,
+              const uint8_t* __restrict__ valid, int tokens, int d, int E, int k, float* __restrict__ logits_out,
+              float* __restrict__ probs, float* __restrict__ lse, int* __restrict__ expert_of,
+              float* __restrict__ gates, float* __restrict__ partial /*[nb, E+2]*/, int* __restrict__ hist /*[nb,E]*/) {
+  extern __shared__ float rt_smem[];
+  const int ldl = E + 1;
+  float* lg = rt_smem;                          // [64][E+1] logits, then probabilities
+  float* xs = lg + ROUTER_ROWS * ldl;           // [64][KC+1]
+  float* ws = xs + ROUTER_ROWS * (RT_KC + 1);   // [E][KC+1]
+  int* sel = reinterpret_cast<int*>(ws + (size_t)E * (RT_KC + 1));   // [64][k]
+  float* row_lse = reinterpret_cast<float*>(sel + ROUTER_ROWS * k);  // [64]
+  int* row_valid = reinterpret_cast<int*>(row_lse + ROUTER_ROWS);    // [64]
+
+  const int t0 = blockIdx.x * ROUTER_ROWS;
+  const int rows = min(ROUTER_ROWS, tokens - t0);
+  const int tid = threadIdx.x;
+
+  if (FROM_LOGITS) {
+    for (int i = tid; i < ROUTER_ROWS * E; i += RT_THREADS) {
+      const int r = i / E, e = i - r * E;
+      lg[r * ldl + e] = r < rows ? logits_in[(size_t)(t0 + r) * E + e] : 0.f;
+    }
+  } else {
+    const int tx = tid & 15, ty = tid >> 4;  // 16 expert lanes x 16 row groups of 4
+    float acc[4][EPT];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < d; k0 += RT_KC) {
+      for (int i = tid; i < ROUTER_ROWS * RT_KC; i += RT_THREADS) {
+        const int r = i / RT_KC, c = i - r * RT_KC;
+        xs[r * (RT_KC + 1) + c] = (r < rows && k0 + c < d) ? to_f32<T>(x[(size_t)(t0 + r) * d + k0 + c]) : 0.f;
+      }
+      for (int i = tid; i < E * RT_KC; i += RT_THREADS) {
+        const int e = i / RT_KC, c = i - e * RT_KC;
+        ws[e * (RT_KC + 1) + c] = (k0 + c < d) ? w_router[(size_t)e * d + k0 + c] : 0.f;
+      }
+      __syncthreads();
+#pragma unroll 8
+      for (int c = 0; c < RT_KC; ++c) {
+        float xv[4], wv[EPT];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) xv[i] = xs[(ty * 4 + i) * (RT_KC + 1) + c];
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+          const int e = tx + 16 * j;
+          wv[j] = e < E ? ws[e * (RT_KC + 1) + c] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < EPT; ++j) acc[i][j] = fmaf(xv[i], wv[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < EPT; ++j) {
+        const int e = tx + 16 * j;
+        if (e < E) lg[(ty * 4 + i) * ldl + e] = acc[i][j];
+      }
+  }
+  __syncthreads();
+
+  // One thread per token row: softmax, log-sum-exp, top-k, gates.
+  if (tid < ROUTER_ROWS) {
+    const int r = tid;
+    int is_valid = 0;
+    if (r < rows) {
+      const int t = t0 + r;
+      float* row = lg + r * ldl;
+      if (logits_out)
+        for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = row[e];
+      float mx = -INFINITY;
+      for (int e = 0; e < E; ++e) mx = fmaxf(mx, row[e]);
+      float sum = 0.f;
+      for (int e = 0; e < E; ++e) {
+        const float ex = (float)exp((double)(row[e] - mx));
+        row[e] = ex;
+        sum = __fadd_rn(sum, ex);
+      }
+      const float l = mx + logf(sum);
+      if (sum > 0.f)
+        for (int e = 0; e < E; ++e) row[e] = __fdiv_rn(row[e], sum);
+      for (int e = 0; e < E; ++e) probs[(size_t)t * E + e] = row[e];
+      lse[t] = l;
+      row_lse[r] = l;
+      is_valid = (valid == nullptr || valid[t] != 0) ? 1 : 0;
+      int* s = sel + r * k;
+      if (!is_valid) {
+        for (int j = 0; j < k; ++j) {
+          s[j] = -1;
+          expert_of[(size_t)t * k + j] = -1;
+          gates[(size_t)t * k + j] = 0.f;
+        }
+      } else {
+        float total = 0.f;
+        for (int j = 0; j < k; ++j) {
+          int best = -1;
+          for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int q = 0; q < j; ++q) taken |= (s[q] == e);
+            if (taken) continue;
+            if (best < 0 || row[e] > row[best]) best = e;
+          }
+          s[j] = best;
+          total = __fadd_rn(total, row[best]);
+        }
+        for (int j = 0; j < k; ++j) {
+          const float p = row[s[j]];
+          expert_of[(size_t)t * k + j] = s[j];
+          gates[(size_t)t * k + j] = total > 0.f ? __fdiv_rn(p, total) : p;
+        }
+      }
+    } else {
+      for (int j = 0; j < k; ++j) sel[r * k + j] = -1;
+    }
+    row_valid[r] = is_valid;
+  }
+  __syncthreads();
+
+  // Per-block partials, rows in order (deterministic): column sums of the
+  // probabilities over valid rows, sum of lse^2, valid-row count, expert histogram.
+  float* part = partial + (size_t)blockIdx.x * (E + 2);
+  for (int e = tid; e < E; e += RT_THREADS) {
+    float s = 0.f;
+    int h = 0;
+    for (int r = 0; r < rows; ++r)
+      if (row_valid[r]) s += lg[r * ldl + e];
+    for (int i = 0; i < rows * k; ++i) h += (sel[i] == e) ? 1 : 0;
+    part[e] = s;
+    hist[(size_t)blockIdx.x * E + e] = h;
+  }
+  if (tid == RT_THREADS - 1) {
+    float s = 0.f;
+    int v = 0;
+    for (int r = 0; r < rows; ++r)
+      if (row_valid[r]) { s += row_lse[r] * row_lse[r]; ++v; }
+    part[E] = s;
+    part[E + 1] = (float)v;
+  }
+}
+
+// One block.  hist[b][e] becomes the padded-row write cursor of block b for expert e.
+__global__ void __launch_bounds__(256)
+finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int nb, int E, int k, float aux_w,
+                float z_w, RouteMeta meta, float* __restrict__ stats /*[E+2]: sums, lse2, V*/,
+                float* __restrict__ losses /*[2]*/, const float* __restrict__ ext_stats, const int* __restrict__ ext_counts) {
+  __shared__ int s_counts[MAX_EXPERTS];
+  __shared__ float s_sums[MAX_EXPERTS + 2];
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E + 2; e += blockDim.x) {
+    double s = 0.0;
+    for (int b = 0; b < nb; ++b) s += (double)partial[(size_t)b * (E + 2) + e];
+    s_sums[e] = (float)s;
+    stats[e] = (float)s;
+  }
+  for (int e = tid; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int b = 0; b < nb; ++b) {
+      const int h = hist[(size_t)b * E + e];
+      hist[(size_t)b * E + e] = run;
+      run += h;
+    }
+    s_counts[e] = run;
+    meta.counts[e] = run;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, pad = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      meta.offsets[e] = off;
+      meta.pad_off[e] = pad;
+      meta.tile_start[e] = tiles;
+      off += s_counts[e];
+      const int padded = round_up(s_counts[e], GROUP_ALIGN);
+      pad += padded;
+      tiles += padded / GROUP_ALIGN;
+    }
+    meta.offsets[E] = off;
+    meta.pad_off[E] = pad;
+    meta.tile_start[E] = tiles;
+    const int V = (int)s_sums[E + 1];
+    meta.total[0] = off;
+    meta.total[1] = pad;
+    meta.total[2] = tiles;
+    meta.total[3] = V;
+    // auxiliary_losses (moe.rs:602-639).  In an expert-parallel group the statistics
+    // of the whole batch (all ranks) are supplied through ext_stats / ext_counts.
+    const float* sums = ext_stats ? ext_stats : s_sums;
+    const float Vf = ext_stats ? ext_stats[E + 1] : (float)V;
+    float aux = 0.f, z = 0.f;
+    if (Vf > 0.f) {
+      const float slots = Vf * (float)k;
+      for (int e = 0; e < E; ++e) {
+        const float load = (float)(ext_counts ? ext_counts[e] : s_counts[e]) / slots;
+        const float mass = sums[e] / Vf;
+        aux += load * mass;
+      }
+      aux *= (float)E * aux_w;
+      z = z_w * sums[E] / Vf;
+    }
+    losses[0] = aux;
+    losses[1] = z;
+  }
+}
+
+// Adds the padded group base to the cursors once pad_off is known.
+__global__ void cursor_base_kernel(int* __restrict__ hist, int nb, int E, const int* __restrict__ pad_off) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < nb * E) hist[i] += pad_off[i % E];
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const float* __restrict__ gates,
+               const int* __restrict__ cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
+               T* __restrict__ x_perm, int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/,
+               float* __restrict__ row_gate /*[Rp]*/, int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of) {
+  extern __shared__ int pm_smem[];
+  int* cnt = pm_smem;        // [E] running cursors
+  int* spos = cnt + E;       // [64*k] padded row of every slot of this block
+  const int t0 = blockIdx.x * ROUTER_ROWS;
+  const int rows = min(ROUTER_ROWS, tokens - t0);
+  const int nslots = rows * k;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = cursor[(size_t)blockIdx.x * E + e];
+  __syncthreads();
+  if (warp == 0) {
+    // Slots in ascending order, 32 at a time; equal experts inside a chunk are ranked
+    // by lane, so the placement is the stable counting sort of the reference.
+    for (int base = 0; base < nslots; base += 32) {
+      const int i = base + lane;
+      const int slot = t0 * k + i;
+      const int e = i < nslots ? expert_of[slot] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      int pos = -1;
+      if (e >= 0) {
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        pos = cnt[e] + rank;
+      }
+      __syncwarp();
+      if (e >= 0 && lane == 31 - __clz(peers)) cnt[e] += __popc(peers);
+      __syncwarp();
+      if (i < nslots) {
+        spos[i] = pos;
+        slot_pos[slot] = pos;
+        if (pos >= 0) {
+          row_token[pos] = slot / k;
+          row_gate[pos] = gates[slot];
+          const int cpos = meta.offsets[e] + (pos - meta.pad_off[e]);
+          token_of[cpos] = slot / k;
+          slot_of[cpos] = slot;
+        }
+      }
+    }
+  }
+  __syncthreads();
+
+  constexpr int VEC = 16 / sizeof(T);
+  const bool vec_ok = (d % VEC) == 0;
+  for (int r = warp; r < rows; r += blockDim.x / 32) {
+    const T* src = x + (size_t)(t0 + r) * d;
+    const int* p = spos + r * k;
+    if (p[0] < 0) continue;   // padding row: routed nowhere
+    if (vec_ok) {
+      const uint4* s4 = reinterpret_cast<const uint4*>(src);
+      for (int c = lane; c < d / VEC; c += 32) {
+        const uint4 v = s4[c];
+        for (int j = 0; j < k; ++j) reinterpret_cast<uint4*>(x_perm + (size_t)p[j] * d)[c] = v;
+      }
+    } else {
+      for (int c = lane; c < d; c += 32) {
+        const T v = src[c];
+        for (int j = 0; j < k; ++j) x_perm[(size_t)p[j] * d + c] = v;
+      }
+    }
+  }
+}
+
+// Zeroes the padding rows at the end of every expert's group (they change place
+// every step) so the tensor-core reductions over padded groups stay exact.
+template <typename T>
+__global__ void pad_rows_kernel(T* __restrict__ buf, int d, RouteMeta meta, int* __restrict__ row_token,
+                                float* __restrict__ row_gate) {
+  const int e = blockIdx.x;
+  const int begin = meta.pad_off[e] + meta.counts[e];
+  const int end = meta.pad_off[e + 1];
+  for (int r = begin; r < end; ++r) {
+    for (int c = threadIdx.x; c < d; c += blockDim.x) buf[(size_t)r * d + c] = from_f32<T>(0.f);
+    if (row_token && threadIdx.x == 0) {
+      row_token[r] = -1;
+      row_gate[r] = 0.f;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host launchers
+// ---------------------------------------------------------------------------
+static size_t router_smem(int E, int k) {
+  return sizeof(float) * ((size_t)ROUTER_ROWS * (E + 1) + (size_t)ROUTER_ROWS * (RT_KC + 1) + (size_t)E * (RT_KC + 1)) +
+         sizeof(int) * (size_t)ROUTER_ROWS * k + sizeof(float) * ROUTER_ROWS + sizeof(int) * ROUTER_ROWS;
+}
+
+template <typename T, int EPT>
+static cudaError_t launch_router_ept(const RouterArgs& a, cudaStream_t stream) {
+  const int nb = ceil_div(a.tokens, ROUTER_ROWS);
+  const size_t smem = router_smem(a.E, a.k);
+  if (a.logits_in) {
+    auto kern = router_kernel<T, EPT, true>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
+                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist); count_launch();
+  } else {
+    auto kern = router_kernel<T, EPT, false>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
+                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist); count_launch();
+  }
+  return cudaGetLastError();
+}
+
+template <typename T>
+static cudaError_t launch_router_t(const RouterArgs& a, cudaStream_t stream) {
+  const int ept = ceil_div(a.E, 16);
+  if (ept <= 1) return launch_router_ept<T, 1>(a, stream);
+  if (ept <= 2) return launch_router_ept<T, 2>(a, stream);
+  if (ept <= 4) return launch_router_ept<T, 4>(a, stream);
+  if (ept <= 8) return launch_router_ept<T, 8>(a, stream);
+  return launch_router_ept<T, 16>(a, stream);
+}
+
+cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  return precision == PREC_BF16 ? launch_router_t<bf16>(a, stream) : launch_router_t<float>(a, stream);
+}
+
+cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
+                            const float* ext_stats, const int* ext_counts, cudaStream_t stream) {
+  const int nb = ceil_div(a.tokens, ROUTER_ROWS);
+  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, ext_stats,
+                                         ext_counts); count_launch();
+  if (nb > 0) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
+  return cudaGetLastError();
+}
+
+cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t stream) {
+  const int nb = ceil_div(a.tokens, ROUTER_ROWS);
+  const size_t smem = sizeof(int) * ((size_t)a.E + (size_t)ROUTER_ROWS * a.k);
+  if (nb > 0) {
+    if (precision == PREC_BF16) {
+      permute_kernel<bf16><<<nb, 256, smem, stream>>>((const bf16*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens,
+                                                      a.d, a.E, a.k, (bf16*)a.x_perm, a.slot_pos, a.row_token,
+                                                      a.row_gate, a.token_of, a.slot_of);
+    } else {
+      permute_kernel<float><<<nb, 256, smem, stream>>>((const float*)a.x, a.expert_of, a.gates, a.cursor, a.meta,
+                                                       a.tokens, a.d, a.E, a.k, (float*)a.x_perm, a.slot_pos,
+                                                       a.row_token, a.row_gate, a.token_of, a.slot_of);
+    }
+    count_launch();
+  }
+  if (precision == PREC_BF16) {
+    pad_rows_kernel<bf16><<<a.E, 256, 0, stream>>>((bf16*)a.x_perm, a.d, a.meta, a.row_token, a.row_gate);
+  } else {
+    pad_rows_kernel<float><<<a.E, 256, 0, stream>>>((float*)a.x_perm, a.d, a.meta, a.row_token, a.row_gate);
+  }
+  count_launch();
+  return cudaGetLastError();
+}
+
+cudaError_t launch_pad_rows(void* buf, int d, RouteMeta meta, int E, int precision, cudaStream_t stream) {
+  if (precision == PREC_BF16) { pad_rows_kernel<bf16><<<E, 256, 0, stream>>>((bf16*)buf, d, meta, nullptr, nullptr); count_launch(); }
+  else { pad_rows_kernel<float><<<E, 256, 0, stream>>>((float*)buf, d, meta, nullptr, nullptr); count_launch(); }
+  return cudaGetLastError();
+}
+
+}  // namespace moe

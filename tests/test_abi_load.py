@@ -1,0 +1,52 @@
+"""The C-ABI library loads and exports everything include/*.h declares (no GPU needed)."""
+import ctypes as C
+
+import pytest
+
+from rustingbrain_b200 import _lib, MoeConfig, InvalidConfig
+
+
+def test_library_exports_every_declared_symbol():
+    L = _lib.lib()
+    names = _lib.exported_symbols()
+    assert "moe_forward" in names and "moe_backward" in names and "moe_create" in names
+    for name in names:
+        assert hasattr(L, name), "libmoe_b200.so does not export " + name
+
+
+def _cfg(**kw):
+    base = dict(d_model=64, num_experts=4, experts_per_token=2, d_ff=32, shared_expert=0, aux_loss_weight=0.01,
+                router_z_loss_weight=1e-3, precision=_lib.PRECISION_F32, max_tokens=16, device=0, training=1,
+                ep_rank=0, ep_size=1)
+    base.update(kw)
+    return _lib.MoeConfigC(**base)
+
+
+def test_config_validation_follows_the_reference():  # moe.rs:68-86, 705-710
+    L = _lib.lib()
+    msg = C.create_string_buffer(256)
+    assert L.moe_config_validate(C.byref(_cfg()), msg, 256) == _lib.OK
+    for bad in (dict(experts_per_token=0), dict(experts_per_token=5), dict(num_experts=0), dict(d_ff=0)):
+        assert L.moe_config_validate(C.byref(_cfg(**bad)), msg, 256) == _lib.INVALID_CONFIG
+        assert msg.value
+    # shape rule of the tensor-core path is reported, not silently worked around
+    assert L.moe_config_validate(C.byref(_cfg(precision=_lib.PRECISION_BF16, d_model=40)), msg, 256) == _lib.INVALID_CONFIG
+    assert L.moe_workspace_bytes(C.byref(_cfg())) > 0
+    for k, e in ((0, 4), (5, 4), (1, 0)):
+        with pytest.raises(InvalidConfig):
+            MoeConfig(e, k, 6).validate()
+
+
+def test_builder_style_config_helpers():  # moe.rs:42-66
+    c = MoeConfig(8, 2, 1408).with_shared_expert(True).with_aux_loss_weight(0.0).with_router_z_loss_weight(0.5)
+    assert c.shared_expert and c.aux_loss_weight == 0.0 and c.router_z_loss_weight == 0.5
+    assert MoeConfig(8, 2, 1408).aux_loss_weight == 0.01 and MoeConfig(8, 2, 1408).router_z_loss_weight == 1e-3
+
+
+def test_create_fails_closed_without_a_device():  # lib.rs:72-76: never a silent CPU fallback
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a device is present")
+    h = C.c_void_p()
+    rc = _lib.lib().moe_create(C.byref(_cfg()), C.byref(h))
+    assert rc != _lib.OK
