@@ -1,0 +1,339 @@
+"""Benchmark of the MoE layer hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg4|cfg3|cfg1] [--impl reference]
+
+One "step" is one forward + backward pass of the layer over one batch of synthetic
+tokens.  Prints ONE JSON line (rank 0).  The default workload is the expert-parallel
+configuration the metric is quoted on (32768 tokens per GPU, d_model 4096, 64 experts
+top-8, SwiGLU d_ff 1536, bf16); `--workload cfg3` is the 1-GPU fine-grained layer
+(16384 tokens, d 2048, 64 experts top-8 + shared expert, d_ff 1408, Zipf-skewed router).
+
+`--impl reference` times the CPU restatement of the reference's own (rayon) MoE path
+on the host cores instead; it is the one place this file executes code under oracle/
+besides the `cpu_baseline` leg.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    "cfg4": dict(T=32768, d=4096, E=64, k=8, F=1536, shared=False, seed=2024, precision="bf16", zipf=False,
+                 name="expert-parallel MoE layer fwd+bwd bf16: 32768 tokens/GPU, d_model 4096, 64 experts top-8, d_ff 1536"),
+    "cfg3": dict(T=16384, d=2048, E=64, k=8, F=1408, shared=True, seed=123, precision="bf16", zipf=True,
+                 name="fine-grained MoE layer fwd+bwd bf16: 16384 tokens, d_model 2048, 64 experts top-8 + shared, d_ff 1408, Zipf router"),
+    "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
+                 name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], tf_burst=p["bf16_tflops"], tf_sustained=p["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf_sustained=1400.0, src="fallback")
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY,
+                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.file.flush()
+        rows = [l.split(",") for l in open(self.file.name).read().strip().splitlines() if l.count(",") >= 8]
+        os.unlink(self.file.name)
+        if not rows:
+            return out
+        sm = [float(r[1]) for r in rows if r[1].strip().replace(".", "").isdigit()]
+        out["sm_mhz"] = float(np.median(sm)) if sm else None
+        out["sm_max_mhz"] = float(rows[0][2]) if rows[0][2].strip().replace(".", "").isdigit() else None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for i, nm in enumerate(names):
+            if any(r[5 + i].strip().lower().startswith("active") for r in rows):
+                out["reasons"].append(nm)
+        out["samples"] = len(rows)
+        return out
+
+
+def make_inputs(torch, w, rank, device):
+    g = torch.Generator(device=device)
+    g.manual_seed(w["seed"] + rank)
+    dt = torch.float32 if w["precision"] == "f32" else torch.bfloat16
+    x = torch.randn(w["T"], w["d"], generator=g, device=device, dtype=torch.float32)
+    if w["zipf"]:
+        x[:, -1] = 1.0
+    gy = torch.randn(w["T"], w["d"], generator=g, device=device, dtype=torch.float32)
+    return x.to(dt), gy.to(dt)
+
+
+def load_weights(torch, layer, w, device, experts=None):
+    """N(0, 0.02) weights from the workload's seed, generated on the device, expert by expert."""
+    from rustingbrain_b200 import _lib
+    g = torch.Generator(device=device)
+    d, E, F = w["d"], w["E"], w["F"]
+    g.manual_seed(w["seed"])
+    router = torch.randn(E, d, generator=g, device=device) * (1.0 / np.sqrt(d) if w["zipf"] else 0.02)
+    if w["zipf"]:   # per-expert bias 1.5*log(1/rank) through a constant-one input column
+        router[:, -1] = 1.5 * torch.log(1.0 / torch.arange(1, E + 1, device=device, dtype=torch.float32))
+    layer.set_weight(_lib.W_ROUTER, 0, router)
+    for e in range(E):
+        g.manual_seed(w["seed"] * 1000 + e)
+        wg = torch.randn(F, d, generator=g, device=device) * 0.02
+        wu = torch.randn(F, d, generator=g, device=device) * 0.02
+        wd = torch.randn(d, F, generator=g, device=device) * 0.02
+        if experts is None or e in experts:
+            layer.set_weight(_lib.W_GATE, e, wg)
+            layer.set_weight(_lib.W_UP, e, wu)
+            layer.set_weight(_lib.W_DOWN, e, wd)
+    if w["shared"]:
+        g.manual_seed(w["seed"] * 1000 + E)
+        layer.set_weight(_lib.W_SHARED_GATE, 0, torch.randn(F, d, generator=g, device=device) * 0.02)
+        layer.set_weight(_lib.W_SHARED_UP, 0, torch.randn(F, d, generator=g, device=device) * 0.02)
+        layer.set_weight(_lib.W_SHARED_DOWN, 0, torch.randn(d, F, generator=g, device=device) * 0.02)
+
+
+def oracle_layer(w, sample_tokens, threads=None):
+    """CPU restatement with the workload's shapes; weights N(0,0.02) from numpy (same distribution)."""
+    import oracle
+    from oracle import OracleMoe
+    if threads:
+        oracle.lib().orc_set_threads(threads)
+    d, E, k, F = w["d"], w["E"], w["k"], w["F"]
+    m = OracleMoe(d, E, k, F, w["shared"])
+    g = np.random.Generator(np.random.Philox(w["seed"]))
+    router = (g.standard_normal((E, d)) * (1.0 / np.sqrt(d) if w["zipf"] else 0.02)).astype(np.float32)
+    if w["zipf"]:
+        router[:, -1] = 1.5 * np.log(1.0 / np.arange(1, E + 1))
+    m.set_weight(oracle.ROUTER, 0, router)
+    base = (g.standard_normal((3, max(F, d), max(F, d))) * 0.02).astype(np.float32)
+    for e in range(E):   # one draw, rolled per expert: distribution, not values, is what the timing needs
+        r = np.roll(base, e * 7, axis=2)
+        m.set_weight(oracle.GATE, e, np.ascontiguousarray(r[0, :F, :d]))
+        m.set_weight(oracle.UP, e, np.ascontiguousarray(r[1, :F, :d]))
+        m.set_weight(oracle.DOWN, e, np.ascontiguousarray(r[2, :d, :F]))
+    if w["shared"]:
+        m.set_weight(oracle.SHARED_GATE, 0, np.ascontiguousarray(base[0, :F, :d]))
+        m.set_weight(oracle.SHARED_UP, 0, np.ascontiguousarray(base[1, :F, :d]))
+        m.set_weight(oracle.SHARED_DOWN, 0, np.ascontiguousarray(base[2, :d, :F]))
+    x = g.standard_normal((sample_tokens, d)).astype(np.float32)
+    if w["zipf"]:
+        x[:, -1] = 1.0
+    gy = g.standard_normal((sample_tokens, d)).astype(np.float32)
+    return m, x, gy
+
+
+def time_oracle(w, sample_tokens, steps, warmup):
+    import oracle
+    m, x, gy = oracle_layer(w, sample_tokens)
+    for _ in range(warmup):
+        m.forward(x); m.backward(gy)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        m.forward(x)
+        m.backward(gy)
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    return sample_tokens / dt, dt, oracle.lib().orc_max_threads()
+
+
+def run_reference(args, w):
+    """The reference's CPU path (restated in oracle/) on the host cores, bounded sample per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 256 if w["d"] >= 2048 else w["T"]
+    value, dt, cores = time_oracle(w, sample, max(args.steps, 1), min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": "MoE-layer tokens/s (forward + backward)", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w["name"], "sample": "%d tokens per step" % sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
+                         "sample": "%d tokens of the workload's shape per step, forward + backward, all host threads" % sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from rustingbrain_b200 import MoeConfig, MoeLayer, _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    args.warmup = max(args.warmup, 3)
+
+    cfg = MoeConfig(w["E"], w["k"], w["F"], w["shared"])
+    if world > 1:
+        from rustingbrain_b200.ep import ExpertParallelMoe
+        layer = ExpertParallelMoe(w["d"], cfg, precision=w["precision"], max_tokens=w["T"], device=local)
+        load_weights(torch, layer, w, device, experts=set(layer.owned_experts()))
+    else:
+        layer = MoeLayer(w["d"], cfg, precision=w["precision"], max_tokens=w["T"], device=local, training=True)
+        load_weights(torch, layer, w, device)
+    x, gy = make_inputs(torch, w, rank, device)
+    y = torch.empty_like(x)
+    gx = torch.empty_like(x)
+
+    def step():
+        _, cache = layer.forward_train(x, out=y)
+        layer.zero_grad()
+        layer.backward(cache, gy, out=gx)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    launches0 = _lib.lib().moe_debug_launch_count()
+    layer.profile(True)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    launches = _lib.lib().moe_debug_launch_count() - launches0
+    prof = layer.profile_read()
+    layer.profile(False)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = world * w["T"] / (ms * 1e-3)
+
+    # ---- end to end through the host-buffer entry points (copies inside the timed region) ----
+    e2e = None
+    if not args.no_e2e:
+        xh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
+        gh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
+        xh.copy_(x.float().cpu()); gh.copy_(gy.float().cpu())
+        host = layer.local_layer() if world > 1 else layer
+        xn, gn = xh.numpy(), gh.numpy()
+        e2e_steps = max(1, min(args.steps, 3))
+        if world == 1:
+            for _ in range(2):
+                _, c = host.forward_train(xn); host.zero_grad(); host.backward(c, gn)
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                yh, c = host.forward_train(xn)
+                host.zero_grad()
+                gxh = host.backward(c, gn)
+                aux = c.auxiliary_loss()
+            dt = (time.perf_counter() - t0) / e2e_steps
+            nbytes = w["T"] * w["d"] * 4
+            e2e = {"value": w["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
+                   "d2h_bytes_per_step": 2 * nbytes + 8, "ms_per_step": dt * 1e3}
+        else:
+            e2e = layer.e2e_measure(xn, gn, e2e_steps, barrier)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    pk = peaks()
+    R = w["T"] * w["k"]
+    gemm_stages = ("gemm_gate_up", "gemm_down", "dgrad_down", "wgrad_down", "dgrad_gate_up", "wgrad_gate_up")
+    gemm_ms = sum(prof[s][0] for s in gemm_stages)
+    gemm_launches = sum(prof[s][1] for s in gemm_stages)
+    gemm_flops = 18.0 * R * w["d"] * w["F"] * args.steps      # 6RdF forward, twice that backward
+    es = 4 if w["precision"] == "f32" else 2
+    if w["precision"] == "f32":
+        roof = {"bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None, "traffic": None,
+                "note": "f32 configuration runs its products on the CUDA cores; see DESIGN.md"}
+    else:
+        ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        roof = {"bound": "tensor", "achieved": ach, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
+                "frac": ach / pk["tf_sustained"] if ach else None, "traffic": None,
+                "kernel": "grouped_gemm_kernel (6 launches per step: gate|up, down, 2 dgrad, 2 wgrad)",
+                "launches": gemm_launches, "ms_per_launch": gemm_ms / max(gemm_launches, 1),
+                "flops_per_step": gemm_flops / args.steps, "peak_source": pk["src"] + " sustained bf16",
+                "frac_of_nominal_2250": ach / 2250.0 if ach else None}
+    hbm = {}
+    alg_bytes = {"permute": 2.0 * R * w["d"] * es, "combine": (R + w["T"] * (2 if w["shared"] else 1)) * w["d"] * es,
+                 "grad_gather": (w["T"] + 2.0 * R) * w["d"] * es, "unpermute": (R + w["T"]) * w["d"] * es,
+                 "router": w["T"] * w["d"] * es + w["T"] * w["k"] * 8}
+    for name, b in alg_bytes.items():
+        t, n = prof[name]
+        if t > 0:
+            gbs = b * n / (t * 1e-3) / 1e9
+            hbm[name] = {"ms": t / n, "GB/s": gbs, "frac": gbs / pk["hbm"]}
+    line = {
+        "metric": "MoE-layer tokens/s (forward + backward)", "value": value, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": w["precision"], "data": "synthetic",
+        "config": {"workload": w["name"], "tokens_per_gpu": w["T"], "l2": "inputs larger than L2 (%.0f MB activations per pass)" % (w["T"] * w["d"] * es / 1e6),
+                   "parallelism": "ep%d" % world if world > 1 else "single"},
+        "clocks": clocks, "gpu_launches": int(launches), "roofline": roof, "hbm_kernels": hbm,
+        "stage_ms_per_step": {k: v[0] / args.steps for k, v in prof.items() if v[1]},
+    }
+    if e2e:
+        line["e2e"] = e2e
+    if world == 1 and not args.no_cpu_baseline:
+        sample = 256 if w["d"] >= 2048 else min(w["T"], 2048)
+        v, dt, cores = time_oracle(w, sample, 2, 1)
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                                "sample": "%d tokens of the workload's shape, forward + backward, %.1f s per pass" % (sample, dt)}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -24,6 +24,18 @@ int32_t moe_debug_tc_gemm(int32_t variant, const void* a, const void* b, void* o
                           const int32_t* group_row0, const int32_t* tile_start, int32_t n_groups, int32_t rows,
                           int32_t m, int32_t n, int32_t k, int32_t accumulate, int32_t* error_flag, void* stream);
 
+/* Per-kernel timing.  While enabled, the library brackets each stage of forward / backward
+ * with CUDA events on the caller's stream.  moe_debug_profile_read synchronises, adds the
+ * elapsed milliseconds and the number of bracketed stages per category into the two arrays
+ * of MOE_PROFILE_CATEGORIES entries, and clears the record.  Categories:
+ *  0 router+finalize  1 permute  2 gate|up GEMM  3 down GEMM  4 combine  5 gradient gather
+ *  6 down dgrad  7 down wgrad  8 gate|up dgrad  9 gate|up wgrad  10 router backward
+ *  11 un-permute  12 router wgrad  13 shared expert forward  14 shared expert backward  15 Adam */
+#define MOE_PROFILE_CATEGORIES 16
+struct moe_layer;
+int32_t moe_debug_profile(struct moe_layer* layer, int32_t enable);
+int32_t moe_debug_profile_read(struct moe_layer* layer, float* milliseconds, int32_t* stages);
+
 /* Number of kernel launches issued by this library in the calling process. */
 int64_t moe_debug_launch_count(void);
 

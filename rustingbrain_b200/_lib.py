@@ -65,6 +65,8 @@ def lib() -> C.CDLL:
         "moe_synchronize": (i32, [vp]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
+        "moe_debug_profile": (i32, [vp, i32]),
+        "moe_debug_profile_read": (i32, [vp, fp, ip]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)

@@ -560,7 +560,7 @@ cudaError_t gemm_rows_nn(const Operand& A, const Operand& B, const GemmArgs& arg
 
 cudaError_t gemm_rows_tn(const Operand& A, const Operand& B, const GemmArgs& args, int sm_count,
                          cudaStream_t stream) {
-  if (!operand_ok(A) || !operand_ok(B) || A.rows != B.rows || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
+  if (!operand_ok(A) || !operand_ok(B) || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, 64, 64, false) || !make_map(&mb, B, 64, 64, false)) return cudaErrorInvalidValue;

@@ -76,6 +76,12 @@ struct moe_layer {
   const void* last_x = nullptr;
   cudaStream_t last_stream = nullptr;
 
+  // optional per-kernel timing with CUDA events on the launching stream
+  struct ProfSpan { int cat; cudaEvent_t begin, end; };
+  bool prof_on = false;
+  std::vector<ProfSpan> prof_spans;
+  std::vector<cudaEvent_t> prof_pool;
+
   std::vector<void*> allocations;
   long long allocated_bytes = 0;
 };

@@ -10,6 +10,7 @@
 #include <new>
 
 #include "../../include/moe_b200.h"
+#include "../../include/moe_b200_debug.h"
 #include "layer.cuh"
 
 using namespace moe;
@@ -44,6 +45,23 @@ int fail(moe_layer* L, int status, const char* fmt, ...) {
     cudaError_t e_ = cudaSetDevice((L)->device);                                                   \
     if (e_ != cudaSuccess) return fail((L), MOE_CUDA_ERROR, "cudaSetDevice: %s", cudaGetErrorString(e_)); \
   } while (0)
+
+// Brackets a stage with two events when profiling is on.
+struct Span {
+  moe_layer* L; cudaStream_t st; int idx = -1;
+  Span(moe_layer* layer, int cat, cudaStream_t stream) : L(layer), st(stream) {
+    if (!L->prof_on || cat < 0) return;
+    cudaEvent_t ev[2];
+    for (int i = 0; i < 2; ++i) {
+      if (!L->prof_pool.empty()) { ev[i] = L->prof_pool.back(); L->prof_pool.pop_back(); }
+      else if (cudaEventCreate(&ev[i]) != cudaSuccess) return;
+    }
+    cudaEventRecord(ev[0], st);
+    L->prof_spans.push_back({cat, ev[0], ev[1]});
+    idx = (int)L->prof_spans.size() - 1;
+  }
+  ~Span() { if (idx >= 0) cudaEventRecord(L->prof_spans[idx].end, st); }
+};
 
 long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
 
@@ -239,8 +257,9 @@ struct ExpertIO {
   long long w_gu, w_d;    // arena offsets
 };
 
-int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save, cudaStream_t st) {
+int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save, cudaStream_t st, bool routed) {
   const int d = L->d, Fp = L->F_pad;
+  Span whole(L, routed ? -1 : 13, st);
   if (L->act == PREC_BF16) {
     tc::GemmArgs a{};
     a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
@@ -248,31 +267,32 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
     a.out0 = io.h; a.ld0 = Fp; a.out1 = save ? io.gu : nullptr; a.ld1 = 2 * Fp;
     tc::Operand A{io.x, G.in_rows, d, 1};
     tc::Operand B{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
-    CK(tc::gemm_rows_nt(A, B, a, tc::EPI_SWIGLU, L->sm_count, st));
+    { Span sp(L, routed ? 2 : -1, st); CK(tc::gemm_rows_nt(A, B, a, tc::EPI_SWIGLU, L->sm_count, st)); }
     tc::GemmArgs b{};
     b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
     b.N = d; b.K = Fp; b.out0 = io.y; b.ld0 = d;
     tc::Operand A2{io.h, G.cap_rows, Fp, 1};
     tc::Operand B2{L->wb + io.w_d, d, Fp, G.n_groups};
-    CK(tc::gemm_rows_nt(A2, B2, b, tc::EPI_STORE, L->sm_count, st));
+    { Span sp(L, routed ? 3 : -1, st); CK(tc::gemm_rows_nt(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
   } else {
     SimtGemmArgs a{};
     a.A = (const float*)io.x; a.B = L->w + io.w_gu; a.C = (float*)io.gu;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows; a.b_rows = 0;
     a.N = 2 * Fp; a.K = d; a.b_group_stride = 2ll * Fp * d;
-    CK(simt_gemm_nt(a, st));
-    CK(launch_swiglu_fwd_f32((const float*)io.gu, (float*)io.h, G.cap_rows, Fp, st));
+    { Span sp(L, routed ? 2 : -1, st); CK(simt_gemm_nt(a, st));
+    CK(launch_swiglu_fwd_f32((const float*)io.gu, (float*)io.h, G.cap_rows, Fp, st)); }
     SimtGemmArgs b{};
     b.A = (const float*)io.h; b.B = L->w + io.w_d; b.C = (float*)io.y;
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = Fp; b.b_group_stride = (long long)d * Fp;
-    CK(simt_gemm_nt(b, st));
+    { Span sp(L, routed ? 3 : -1, st); CK(simt_gemm_nt(b, st)); }
   }
   return MOE_OK;
 }
 
-int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st) {
+int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed) {
   const int d = L->d, Fp = L->F_pad;
+  Span whole(L, routed ? -1 : 14, st);
   const int acc = L->grad_valid ? 1 : 0;
   if (L->act == PREC_BF16) {
     // dgu = swiglu'(dy W_d) ; dW_d += dy^T h ; dx = dgu W_gu ; dW_gu += dgu^T x
@@ -281,50 +301,50 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     a.N = Fp; a.K = d; a.out0 = io.dgu; a.ld0 = 2 * Fp; a.aux = io.gu; a.ldaux = 2 * Fp;
     tc::Operand A{io.dy, G.in_rows, d, 1};
     tc::Operand B{L->wb + io.w_d, d, Fp, G.n_groups};
-    CK(tc::gemm_rows_nn(A, B, a, tc::EPI_SWIGLU_BWD, L->sm_count, st));
+    { Span sp(L, routed ? 6 : -1, st); CK(tc::gemm_rows_nn(A, B, a, tc::EPI_SWIGLU_BWD, L->sm_count, st)); }
 
     tc::GemmArgs wd{};
     wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.error_flag = L->error_flag;
     wd.M = d; wd.N = Fp; wd.out0 = L->g + io.w_d; wd.ld0 = Fp; wd.group_stride0 = (long long)d * Fp; wd.accumulate = acc;
     tc::Operand Ad{io.dy, G.in_rows, d, 1};
     tc::Operand Bd{io.h, G.cap_rows, Fp, 1};
-    CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st));
+    { Span sp(L, routed ? 7 : -1, st); CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st)); }
 
     tc::GemmArgs b{};
     b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
     b.N = d; b.K = 2 * Fp; b.out0 = io.dx; b.ld0 = d;
     tc::Operand A2{io.dgu, G.cap_rows, 2 * Fp, 1};
     tc::Operand B2{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
-    CK(tc::gemm_rows_nn(A2, B2, b, tc::EPI_STORE, L->sm_count, st));
+    { Span sp(L, routed ? 8 : -1, st); CK(tc::gemm_rows_nn(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
 
     tc::GemmArgs wg{};
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.error_flag = L->error_flag;
     wg.M = 2 * Fp; wg.N = d; wg.out0 = L->g + io.w_gu; wg.ld0 = d; wg.group_stride0 = 2ll * Fp * d; wg.accumulate = acc;
     tc::Operand Ag{io.dgu, G.cap_rows, 2 * Fp, 1};
     tc::Operand Bg{io.x, G.in_rows, d, 1};
-    CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st));
+    { Span sp(L, routed ? 9 : -1, st); CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st)); }
   } else {
     SimtGemmArgs a{};
     a.A = (const float*)io.dy; a.B = L->w + io.w_d; a.C = (float*)io.dh;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows;
     a.N = Fp; a.K = d; a.b_group_stride = (long long)d * Fp;
-    CK(simt_gemm_nn(a, st));
-    CK(launch_swiglu_bwd_f32((const float*)io.dh, (const float*)io.gu, (float*)io.dgu, G.cap_rows, Fp, st));
+    { Span sp(L, routed ? 6 : -1, st); CK(simt_gemm_nn(a, st));
+    CK(launch_swiglu_bwd_f32((const float*)io.dh, (const float*)io.gu, (float*)io.dgu, G.cap_rows, Fp, st)); }
     SimtGemmArgs wd{};
     wd.A = (const float*)io.dy; wd.B = (const float*)io.h; wd.C = L->g + io.w_d;
     wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.a_rows = G.in_rows; wd.b_rows = G.cap_rows;
     wd.M = d; wd.N = Fp; wd.c_group_stride = (long long)d * Fp; wd.accumulate = acc;
-    CK(simt_gemm_tn(wd, st));
+    { Span sp(L, routed ? 7 : -1, st); CK(simt_gemm_tn(wd, st)); }
     SimtGemmArgs b{};
     b.A = (const float*)io.dgu; b.B = L->w + io.w_gu; b.C = (float*)io.dx;
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = 2 * Fp; b.b_group_stride = 2ll * Fp * d;
-    CK(simt_gemm_nn(b, st));
+    { Span sp(L, routed ? 8 : -1, st); CK(simt_gemm_nn(b, st)); }
     SimtGemmArgs wg{};
     wg.A = (const float*)io.dgu; wg.B = (const float*)io.x; wg.C = L->g + io.w_gu;
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.a_rows = G.cap_rows; wg.b_rows = G.in_rows;
     wg.M = 2 * Fp; wg.N = d; wg.c_group_stride = 2ll * Fp * d; wg.accumulate = acc;
-    CK(simt_gemm_tn(wg, st));
+    { Span sp(L, routed ? 9 : -1, st); CK(simt_gemm_tn(wg, st)); }
   }
   return MOE_OK;
 }
@@ -352,20 +372,20 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.tokens = tokens; ra.d = L->d; ra.E = L->E; ra.k = L->k;
   ra.logits_out = L->logits; ra.probs = L->probs; ra.lse = L->lse; ra.expert_of = L->expert_of; ra.gates = L->gates;
   ra.partial = L->partial; ra.hist = L->hist;
-  CK(launch_router(ra, L->act, st));
-  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, nullptr, nullptr, st));
+  { Span sp(L, 0, st); CK(launch_router(ra, L->act, st));
+  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, nullptr, nullptr, st)); }
 
   PermuteArgs pa{};
   pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
   pa.tokens = tokens; pa.d = L->d; pa.E = L->E; pa.k = L->k;
   pa.x_perm = L->x_perm; pa.slot_pos = L->slot_pos; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
   pa.token_of = L->token_of; pa.slot_of = L->slot_of;
-  CK(launch_permute(pa, L->act, st));
+  { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
   Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
   ExpertIO io{};
   io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.w_gu = L->off_gu; io.w_d = L->off_d;
-  int rc = experts_forward(L, G, io, save != 0, st);
+  int rc = experts_forward(L, G, io, save != 0, st, true);
   if (rc != MOE_OK) return rc;
 
   if (L->shared) {
@@ -373,14 +393,14 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
     ExpertIO sio{};
     sio.x = x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
-    rc = experts_forward(L, S, sio, save != 0, st);
+    rc = experts_forward(L, S, sio, save != 0, st, false);
     if (rc != MOE_OK) return rc;
   }
 
   CombineArgs ca{};
   ca.y_perm = L->y_perm; ca.shared = L->shared ? L->y_s : nullptr; ca.expert_of = L->expert_of; ca.gates = L->gates;
   ca.slot_pos = L->slot_pos; ca.y = y; ca.tokens = tokens; ca.d = L->d; ca.k = L->k; ca.accumulate = accumulate;
-  CK(launch_combine(ca, L->act, st));
+  { Span sp(L, 4, st); CK(launch_combine(ca, L->act, st)); }
   CK(cudaGetLastError());
   L->have_cache = save != 0;
   L->last_x = x;
@@ -397,14 +417,14 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   GatherGradArgs ga{};
   ga.grad_y = gy; ga.y_perm = L->y_perm; ga.slot_pos = L->slot_pos; ga.gates = L->gates;
   ga.grad_y_perm = L->dy_perm; ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
-  CK(launch_gather_grad(ga, L->act, st));
-  CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st));
+  { Span sp(L, 5, st); CK(launch_gather_grad(ga, L->act, st));
+  CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st)); }
 
   Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
   ExpertIO io{};
   io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
   io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
-  int rc = experts_backward(L, G, io, st);
+  int rc = experts_backward(L, G, io, st, true);
   if (rc != MOE_OK) return rc;
 
   if (L->shared) {
@@ -412,7 +432,7 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     ExpertIO sio{};
     sio.x = L->last_x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.dy = gy; sio.dgu = L->dgu_s;
     sio.dx = L->dx_s; sio.dh = L->dh_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
-    rc = experts_backward(L, S, sio, st);
+    rc = experts_backward(L, S, sio, st, false);
     if (rc != MOE_OK) return rc;
   }
 
@@ -420,27 +440,26 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   rb.probs = L->probs; rb.lse = L->lse; rb.expert_of = L->expert_of; rb.grad_gates = L->grad_gates;
   rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
   rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
-  CK(launch_router_bwd(rb, st));
+  { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
 
   UnpermuteArgs ua{};
   ua.grad_x_perm = L->dx_perm; ua.shared = L->shared ? L->dx_s : nullptr; ua.grad_logits = L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
-  CK(launch_unpermute(ua, L->act, st));
+  { Span sp(L, 11, st); CK(launch_unpermute(ua, L->act, st)); }
 
   RouterWgradArgs rw{};
   rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
   rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
-  CK(launch_router_wgrad(rw, L->act, st));
+  { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
   CK(cudaGetLastError());
   L->grad_valid = true;
   return MOE_OK;
 }
 
 int ensure_host_buffers(moe_layer* L) {
-  if (L->pinned) return MOE_OK;
+  if (L->own_stream) return MOE_OK;
   const long long n = (long long)L->max_tokens * L->d;
-  CK(cudaMallocHost(&L->pinned, (size_t)n * 4));
   DA(L->host_stage_f32, n * 4, false);
   DA(L->host_x, n * L->esz, false);
   DA(L->host_y, n * L->esz, false);
@@ -547,7 +566,8 @@ void moe_destroy(moe_layer_t* L) {
   cudaSetDevice(L->device);
   cudaDeviceSynchronize();
   for (void* p : L->allocations) cudaFree(p);
-  if (L->pinned) cudaFreeHost(L->pinned);
+  for (auto& sp : L->prof_spans) { cudaEventDestroy(sp.begin); cudaEventDestroy(sp.end); }
+  for (auto ev : L->prof_pool) cudaEventDestroy(ev);
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
   delete L;
 }
@@ -676,7 +696,7 @@ int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, f
   a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
   a.c1 = 1.0f - powf(b1, (float)step);
   a.c2 = 1.0f - powf(b2, (float)step);
-  CK(launch_adam(a, st));
+  { Span sp(L, 15, st); CK(launch_adam(a, st)); }
   L->grad_valid = false;   // the kernel cleared the gradients
   return MOE_OK;
 }
@@ -692,11 +712,11 @@ int32_t moe_forward_host(moe_layer_t* L, const float* x, int32_t tokens, int32_t
   cudaStream_t st = L->own_stream;
   const long long n = (long long)tokens * L->d;
   if (tokens > 0) {
-    memcpy(L->pinned, x, (size_t)n * 4);
+    // straight from the caller's buffer: asynchronous when it is pinned, staged by the driver otherwise
     if (L->act == PREC_F32) {
-      CK(cudaMemcpyAsync(L->host_x, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(cudaMemcpyAsync(L->host_x, x, (size_t)n * 4, cudaMemcpyHostToDevice, st));
     } else {
-      CK(cudaMemcpyAsync(L->host_stage_f32, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(cudaMemcpyAsync(L->host_stage_f32, x, (size_t)n * 4, cudaMemcpyHostToDevice, st));
       CK(launch_cast_f32_to_bf16(L->host_stage_f32, (bf16*)L->host_x, n, st));
     }
     if (valid) CK(cudaMemcpyAsync(L->host_valid, valid, (size_t)tokens, cudaMemcpyHostToDevice, st));
@@ -705,14 +725,13 @@ int32_t moe_forward_host(moe_layer_t* L, const float* x, int32_t tokens, int32_t
   if (rc != MOE_OK) return rc;
   if (tokens > 0) {
     if (L->act == PREC_F32) {
-      CK(cudaMemcpyAsync(L->pinned, L->host_y, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+      CK(cudaMemcpyAsync(y, L->host_y, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     } else {
       CK(launch_cast_bf16_to_f32((const bf16*)L->host_y, L->host_stage_f32, n, st));
-      CK(cudaMemcpyAsync(L->pinned, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+      CK(cudaMemcpyAsync(y, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     }
   }
   CK(cudaStreamSynchronize(st));
-  if (tokens > 0) memcpy(y, L->pinned, (size_t)n * 4);
   return check_flag(L);
 }
 
@@ -723,12 +742,11 @@ int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
   cudaStream_t st = L->own_stream;
   const long long n = (long long)L->last_tokens * L->d;
   if (n > 0) {
-    memcpy(L->pinned, gy, (size_t)n * 4);
     // host_y is free once the forward result has been copied out: reuse it for the upstream gradient
     if (L->act == PREC_F32) {
-      CK(cudaMemcpyAsync(L->host_y, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(cudaMemcpyAsync(L->host_y, gy, (size_t)n * 4, cudaMemcpyHostToDevice, st));
     } else {
-      CK(cudaMemcpyAsync(L->host_stage_f32, L->pinned, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+      CK(cudaMemcpyAsync(L->host_stage_f32, gy, (size_t)n * 4, cudaMemcpyHostToDevice, st));
       CK(launch_cast_f32_to_bf16(L->host_stage_f32, (bf16*)L->host_y, n, st));
     }
   }
@@ -736,14 +754,13 @@ int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
   if (rc != MOE_OK) return rc;
   if (n > 0) {
     if (L->act == PREC_F32) {
-      CK(cudaMemcpyAsync(L->pinned, L->host_gx, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+      CK(cudaMemcpyAsync(gx, L->host_gx, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     } else {
       CK(launch_cast_bf16_to_f32((const bf16*)L->host_gx, L->host_stage_f32, n, st));
-      CK(cudaMemcpyAsync(L->pinned, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
+      CK(cudaMemcpyAsync(gx, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     }
   }
   CK(cudaStreamSynchronize(st));
-  if (n > 0) memcpy(gx, L->pinned, (size_t)n * 4);
   return check_flag(L);
 }
 
@@ -785,6 +802,30 @@ int32_t moe_get_router_cache(moe_layer_t* L, float* logits, float* probs, float*
     if (probs) CK(cudaMemcpy(probs, L->probs, (size_t)te * 4, cudaMemcpyDeviceToHost));
     if (lse) CK(cudaMemcpy(lse, L->lse, (size_t)L->last_tokens * 4, cudaMemcpyDeviceToHost));
   }
+  return MOE_OK;
+}
+
+int32_t moe_debug_profile(moe_layer_t* L, int32_t enable) {
+  ENTER(L);
+  L->prof_on = enable != 0;
+  return MOE_OK;
+}
+
+int32_t moe_debug_profile_read(moe_layer_t* L, float* ms, int32_t* stages) {
+  ENTER(L);
+  CK(cudaDeviceSynchronize());
+  for (int i = 0; i < MOE_PROFILE_CATEGORIES; ++i) { if (ms) ms[i] = 0.f; if (stages) stages[i] = 0; }
+  for (auto& sp : L->prof_spans) {
+    float t = 0.f;
+    if (cudaEventElapsedTime(&t, sp.begin, sp.end) == cudaSuccess && sp.cat >= 0 && sp.cat < MOE_PROFILE_CATEGORIES) {
+      if (ms) ms[sp.cat] += t;
+      if (stages) stages[sp.cat] += 1;
+    }
+    L->prof_pool.push_back(sp.begin);
+    L->prof_pool.push_back(sp.end);
+  }
+  cudaGetLastError();
+  L->prof_spans.clear();
   return MOE_OK;
 }
 

@@ -17,14 +17,60 @@
 //                   gather_rows in cuda_training.rs:70).
 //
 // Selection is done on probabilities with a strict '>' so ties go to the lowest
-// expert index, exactly as the reference.  The exponentials are evaluated in
-// double precision and rounded once to f32, and the row sum is accumulated
-// sequentially in expert order, so the probabilities (and therefore the chosen
-// experts) agree with a host libm evaluation of the same logits.
+// expert index, exactly as the reference.  The exponentials follow the host libm's
+// own algorithm (expf_libm below) and the row sum is accumulated sequentially in
+// expert order, so the probabilities (and therefore the chosen experts) agree bit
+// for bit with a host evaluation of the same logits.
 
 #include "kernels.cuh"
 
 namespace moe {
+
+
+// Single-precision exp evaluated the way the GNU C library does it (the published
+// algorithm of its flt-32 expf: x*32/ln2 split into an integer and a remainder by
+// the 1.5*2^52 shift, a 32-entry table of 2^(i/32), a cubic in the remainder, all
+// in double, one final rounding to f32).  That routine is not correctly rounded in
+// about one case in a thousand; reproducing its arithmetic is what makes the
+// device probabilities - and with them the top-k decisions - equal bit for bit to
+// a host evaluation with libm, which is what the reference's f32::exp calls.
+__device__ const unsigned long long kExp2Tab[32] = {
+    0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,
+    0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,
+    0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,
+    0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,
+    0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,
+    0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,
+    0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
+    0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
+
+__device__ __forceinline__ float expf_libm(float x) {
+  if (!(fabsf(x) < 88.0f)) {
+    if (x == -INFINITY) return 0.f;
+    if (!(fabsf(x) < INFINITY)) return x + x;
+    if (x > 0x1.62e42ep6f) return INFINITY;
+    if (x < -0x1.9fe368p6f) return 0.f;
+    if (x < -0x1.9d1d9ep6f) return 0x1p-149f;
+  }
+  constexpr double kInvLn2N = 0x1.71547652b82fep+0 * 32.0;
+  constexpr double kShift = 0x1.8p52;
+  constexpr double c0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
+  constexpr double c1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+  constexpr double c2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+  const double z = __dmul_rn(kInvLn2N, (double)x);
+  double kd = __dadd_rn(z, kShift);
+  const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+  kd = __dsub_rn(kd, kShift);
+  const double r = __dsub_rn(z, kd);
+  const unsigned long long t = kExp2Tab[ki & 31] + (ki << 47);
+  const double s = __longlong_as_double((long long)t);
+  const double p = fma(c0, r, c1);
+  const double r2 = __dmul_rn(r, r);
+  double y = fma(c2, r, 1.0);
+  y = fma(p, r2, y);
+  y = __dmul_rn(y, s);
+  return (float)y;
+}
 
 constexpr int RT_THREADS = 256;
 constexpr int RT_KC = 32;
@@ -110,7 +156,7 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
       for (int e = 0; e < E; ++e) mx = fmaxf(mx, row[e]);
       float sum = 0.f;
       for (int e = 0; e < E; ++e) {
-        const float ex = (float)exp((double)(row[e] - mx));
+        const float ex = expf_libm(__fsub_rn(row[e], mx));
         row[e] = ex;
         sum = __fadd_rn(sum, ex);
       }

@@ -360,6 +360,22 @@ class MoeLayer:
                                                  lse.ctypes.data_as(fp)))
         return logits, probs, lse
 
+    PROFILE_STAGES = ("router", "permute", "gemm_gate_up", "gemm_down", "combine", "grad_gather", "dgrad_down",
+                      "wgrad_down", "dgrad_gate_up", "wgrad_gate_up", "router_bwd", "unpermute", "router_wgrad",
+                      "shared_fwd", "shared_bwd", "adam")
+
+    def profile(self, enable: bool):
+        """Brackets every stage with CUDA events on the launching stream (measurement aid)."""
+        self._ck(_lib.lib().moe_debug_profile(self._h, int(enable)))
+
+    def profile_read(self):
+        """{stage: (milliseconds, launches)} accumulated since the last read; synchronises."""
+        n = len(self.PROFILE_STAGES)
+        ms = (C.c_float * n)()
+        cnt = (C.c_int32 * n)()
+        self._ck(_lib.lib().moe_debug_profile_read(self._h, ms, cnt))
+        return {name: (float(ms[i]), int(cnt[i])) for i, name in enumerate(self.PROFILE_STAGES)}
+
     def synchronize(self):
         self._ck(_lib.lib().moe_synchronize(self._h))
 

@@ -143,7 +143,7 @@ def test_bf16_zipf_skew_with_empty_experts():
     gy = g.standard_normal((T, d)).astype(np.float32)
     y, yo, gx, gxo, cache = _fwd_bwd(dev, ora, x, gy, "bf16")
     counts = cache.routing()[2]
-    assert (counts == 0).any() and counts.max() > 10 * np.median(counts[counts > 0])
+    assert (counts == 0).any() and counts.max() > 3 * np.median(counts[counts > 0])
     assert rel_l2(y, yo) <= BF16_TOL and rel_l2(gx, gxo) <= BF16_TOL
     _check_grads(dev, ora, E, True, BF16_TOL)
 
