@@ -30,6 +30,9 @@ WORKLOADS = {
                  name="expert-parallel MoE layer fwd+bwd bf16: 32768 tokens/GPU, d_model 4096, 64 experts top-8, d_ff 1536"),
     "cfg3": dict(T=16384, d=2048, E=64, k=8, F=1408, shared=True, seed=123, precision="bf16", zipf=True,
                  name="fine-grained MoE layer fwd+bwd bf16: 16384 tokens, d_model 2048, 64 experts top-8 + shared, d_ff 1408, Zipf router"),
+    # reduced copy of cfg3's shapes (same tile shapes, a quarter of the rows and experts) for ncu captures
+    "prof": dict(T=8192, d=2048, E=16, k=4, F=1408, shared=True, seed=123, precision="bf16", zipf=False,
+                 name="profiling case: 8192 tokens, d_model 2048, 16 experts top-4 + shared, d_ff 1408"),
     "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
                  name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
 }
@@ -52,7 +55,7 @@ class ClockSampler:
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), "--query-gpu=" + self.QUERY,
-                                          "--format=csv,noheader,nounits", "-lms", "200"], stdout=self.file,
+                                          "--format=csv,noheader,nounits", "-lms", "50"], stdout=self.file,
                                          stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -185,7 +188,7 @@ def run_reference(args, w):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOADS))
@@ -264,16 +267,18 @@ def main():
         xh.copy_(x.float().cpu()); gh.copy_(gy.float().cpu())
         host = layer.local_layer() if world > 1 else layer
         xn, gn = xh.numpy(), gh.numpy()
+        yn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
+        gxn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
         e2e_steps = max(1, min(args.steps, 3))
         if world == 1:
             for _ in range(2):
-                _, c = host.forward_train(xn); host.zero_grad(); host.backward(c, gn)
+                _, c = host.forward_train(xn, out=yn); host.zero_grad(); host.backward(c, gn, out=gxn)
             barrier()
             t0 = time.perf_counter()
             for _ in range(e2e_steps):
-                yh, c = host.forward_train(xn)
+                yh, c = host.forward_train(xn, out=yn)
                 host.zero_grad()
-                gxh = host.backward(c, gn)
+                gxh = host.backward(c, gn, out=gxn)
                 aux = c.auxiliary_loss()
             dt = (time.perf_counter() - t0) / e2e_steps
             nbytes = w["T"] * w["d"] * 4

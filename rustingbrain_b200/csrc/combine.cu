@@ -201,8 +201,9 @@ __global__ void __launch_bounds__(RB_ROWS) router_bwd_kernel(RouterBwdArgs a) {
   if (t >= a.tokens) return;
   float* gl = a.grad_logits + (size_t)t * E;
   const int* sel = a.expert_of + (size_t)t * k;
+  bf16* glb = a.grad_logits_bf16 ? a.grad_logits_bf16 + (size_t)t * E : nullptr;
   if (sel[0] < 0) {
-    for (int e = 0; e < E; ++e) gl[e] = 0.f;
+    for (int e = 0; e < E; ++e) { gl[e] = 0.f; if (glb) glb[e] = __float2bfloat16_rn(0.f); }
     return;
   }
   const float* p = a.probs + (size_t)t * E;
@@ -232,6 +233,7 @@ __global__ void __launch_bounds__(RB_ROWS) router_bwd_kernel(RouterBwdArgs a) {
     float v = __fmul_rn(p[e], __fsub_rn(gp[e], dot));
     if (a.z_w != 0.f) v = __fadd_rn(v, __fmul_rn(factor, p[e]));
     gl[e] = v;
+    if (glb) glb[e] = __float2bfloat16_rn(v);
   }
 }
 
@@ -254,7 +256,8 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
   const int d = a.d, E = a.E;
   const T* gp = (const T*)a.grad_x_perm;
   const T* sh = (const T*)a.shared;
-  const float* gl = a.grad_logits + (size_t)t * E;
+  const T* ex = (const T*)a.extra;
+  const float* gl = a.grad_logits ? a.grad_logits + (size_t)t * E : nullptr;
   T* gx = (T*)a.grad_x + (size_t)t * d;
   constexpr int V = Vec16<T>::N;
   if (d % V == 0 && d % 4 == 0) {
@@ -269,7 +272,8 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
       }
-      for (int e = 0; e < E; ++e) {
+      if (ex) Vec16<T>::load(ex + (size_t)t * d + c, r);
+      for (int e = 0; gl && e < E; ++e) {
         const float g = gl[e];
         const float* w = a.w_router + (size_t)e * d + c;
 #pragma unroll
@@ -293,8 +297,8 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
     for (int c = lane; c < d; c += 32) {
       float acc = sh ? to_f32<T>(sh[(size_t)t * d + c]) : 0.f;
       for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, to_f32<T>(gp[(size_t)pos[j] * d + c]));
-      float r = 0.f;
-      for (int e = 0; e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
+      float r = ex ? to_f32<T>(ex[(size_t)t * d + c]) : 0.f;
+      for (int e = 0; gl && e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
       acc = __fadd_rn(acc, r);
       if (a.accumulate) acc = __fadd_rn(to_f32<T>(gx[c]), acc);
       gx[c] = from_f32<T>(acc);

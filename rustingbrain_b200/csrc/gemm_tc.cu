@@ -2,12 +2,12 @@
 // fp32 accumulators in tensor memory, operands staged in shared memory by TMA
 // (cp.async.bulk.tensor, 128-byte swizzle), one persistent CTA per SM.
 //
-// Warp roles inside a CTA of 192 threads:
+// Warp roles inside a CTA of 320 threads:
 //   warp 0, one lane : TMA producer (fills a 4-stage ring of A/B tiles)
 //   warp 1           : allocates tensor memory; one lane issues tcgen05.mma and
 //                      tcgen05.commit
-//   warps 2..5       : epilogue; each reads its quarter of the 128 TMEM lanes with
-//                      tcgen05.ld, applies the fused pointwise step, stores.
+//   warps 2..9       : epilogue; two warps per quarter of the 128 TMEM lanes, each takes
+//                      half of the tile's columns: tcgen05.ld, fused pointwise step, stores.
 // Two 128x256 fp32 accumulators (all 512 TMEM columns) are double buffered so the
 // epilogue of tile i overlaps the MMAs of tile i+1.
 //
@@ -33,7 +33,8 @@ constexpr int B_BYTES = BN * BK * 2;           // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES; // 48 KiB
 constexpr int BOX_BYTES = 64 * 64 * 2;         // one 64x64 box of an MN-major operand
 constexpr int MAX_GROUPS = MAX_EXPERTS + 1;
-constexpr int NUM_THREADS = 192;
+constexpr int EPI_WARPS = 8;
+constexpr int NUM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr long long WAIT_LIMIT_CYCLES = 3000000000LL;  // ~1.5 s at 2 GHz
 
@@ -164,13 +165,13 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 // Instruction descriptor for kind::f16: fp32 accumulate, bf16 A and B, M=128, N=256.
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn) {
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
   return (1u << 4)                      // D format: f32
          | (1u << 7)                    // A format: bf16
          | (1u << 10)                   // B format: bf16
          | ((a_mn ? 1u : 0u) << 15)     // A major: 0 = K, 1 = MN
          | ((b_mn ? 1u : 0u) << 16)     // B major
-         | ((uint32_t)(BN >> 3) << 17)  // N / 8
+         | ((uint32_t)(n >> 3) << 17)   // N / 8
          | ((uint32_t)(BM >> 4) << 24); // M / 16
 }
 
@@ -250,14 +251,19 @@ __device__ __forceinline__ void load32_bf16(const bf16* src, float* v) {
   }
 }
 
+// The tensor-core path rounds its outputs to bf16 (2^-9), so the pointwise step uses
+// the fast exponential and reciprocal; the f32 path keeps expf and IEEE division.
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl, uint32_t taddr, int row_in_tile,
+                                              int c_begin, int c_end,
                                               bool have_acc) {
   if (EPI == EPI_STORE) {
     const long long row = (long long)tl.row0 + row_in_tile;
     bf16* out = (bf16*)p.out0 + row * p.ld0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;   // warp-uniform
       float v[32];
       tmem_ld32(taddr + c, v);
@@ -268,7 +274,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
     bf16* h_out = (bf16*)p.out0 + row * p.ld0;
     bf16* gu_out = p.out1 ? (bf16*)p.out1 + row * p.ld1 : nullptr;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 2 * GU_BLOCK) {
+    for (int c = c_begin; c < c_end; c += 2 * GU_BLOCK) {
       if (tl.n0 + c >= p.N) break;
       float g[32], u[32];
       tmem_ld32(taddr + c, g);
@@ -278,7 +284,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
         store32_bf16(gu_out + tl.n0 + c + GU_BLOCK, u);
       }
 #pragma unroll
-      for (int i = 0; i < 32; ++i) g[i] = siluf_(g[i]) * u[i];
+      for (int i = 0; i < 32; ++i) g[i] = g[i] * fast_sigmoid(g[i]) * u[i];
       store32_bf16(h_out + (tl.n0 + c) / 2, g);
     }
   } else if (EPI == EPI_SWIGLU_BWD) {
@@ -288,7 +294,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
     const bf16* gu = (const bf16*)p.aux + row * p.ldaux;
     bf16* out = (bf16*)p.out0 + row * p.ld0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;
       float dh[32], g[32], u[32];
       tmem_ld32(taddr + c, dh);
@@ -297,7 +303,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
       load32_bf16(gu + col + GU_BLOCK, u);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
-        const float s = sigmoidf_(g[i]);
+        const float s = fast_sigmoid(g[i]);
         const float dg = dh[i] * u[i] * (s * (1.0f + g[i] * (1.0f - s)));
         u[i] = dh[i] * (g[i] * s);
         g[i] = dg;
@@ -305,11 +311,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
       store32_bf16(out + col, g);
       store32_bf16(out + col + GU_BLOCK, u);
     }
+  } else if (EPI == EPI_STORE_F32) {
+    // f32 output with a row limit (p.M) and any column count: used for the router logits.
+    const long long row = (long long)tl.row0 + row_in_tile;
+    float* out = (float*)p.out0 + row * p.ld0;
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; c += 32) {
+      if (tl.n0 + c >= p.N) break;
+      float v[32];
+      tmem_ld32(taddr + c, v);
+      if (row < p.M) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (tl.n0 + c + i < p.N) out[tl.n0 + c + i] = v[i];
+      }
+    }
   } else {  // EPI_ACCUM_F32
     const int m = tl.m0 + row_in_tile;
     float* out = (float*)p.out0 + (long long)tl.group * p.group_stride0 + (long long)m * p.ld0;
 #pragma unroll 1
-    for (int c = 0; c < BN; c += 32) {
+    for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;
       float v[32];
       if (have_acc) {
@@ -360,7 +381,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&st->tmem_full[a]), 1);
-      mbar_init(smem_u32(&st->tmem_empty[a]), 4);
+      mbar_init(smem_u32(&st->tmem_empty[a]), EPI_WARPS);
     }
     st->dead = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -411,7 +432,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0) {
       // ------------------------------ MMA issuer --------------------------------
-      constexpr uint32_t idesc = make_idesc(A_MN, B_MN);
       // K-major tiles: rows of 128 bytes, 8-row swizzle atoms 1024 bytes apart; one
       // MMA (K=16) advances 32 bytes inside the 128-byte row.
       // MN-major tiles: 64x64 boxes of 8 KiB; 64-element chunks of the M/N extent are
@@ -426,6 +446,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 102)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        // the last column tile may be narrower: issue an MMA only as wide as needed (multiple of 16)
+        const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
+        const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
           if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103)) { ok = false; break; }
           tc_fence_after();
@@ -450,8 +473,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncwarp();
   } else {
     // -------------------------------- epilogue ----------------------------------
-    const int quarter = warp & 3;                 // TMEM lanes [32*quarter, 32*quarter+32)
+    // A warp may only touch TMEM lanes [32*(warp%4), +32); two warps share each lane
+    // quarter and split the tile's columns between them.
+    const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    const int c_begin = half * (BN / 2), c_end = c_begin + BN / 2;
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
@@ -459,7 +486,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      epilogue_tile<EPI>(p, tl, taddr, row_in_tile, tl.k_iters > 0);
+      epilogue_tile<EPI>(p, tl, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&st->tmem_empty[acc]));
@@ -534,13 +561,15 @@ static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const Ge
 
 cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
                          cudaStream_t stream) {
-  if (!operand_ok(A) || !operand_ok(B) || A.cols != B.cols || args.N % 32 != 0 || args.n_groups > MAX_GROUPS - 1)
+  if (!operand_ok(A) || !operand_ok(B) || A.cols != B.cols || (args.N % 32 != 0 && epilogue != EPI_STORE_F32) ||
+      args.n_groups > MAX_GROUPS - 1)
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, BN, true)) return cudaErrorInvalidValue;
   switch (epilogue) {
     case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, sm_count, stream);
     case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, sm_count, stream);
+    case EPI_STORE_F32: return launch<false, false, false, EPI_STORE_F32>(ma, mb, args, sm_count, stream);
     default: return cudaErrorInvalidValue;
   }
 }

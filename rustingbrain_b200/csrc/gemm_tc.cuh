@@ -14,6 +14,7 @@ enum Epilogue {
   EPI_SWIGLU = 1,      // acc holds interleaved gate|up blocks: out0 = silu(g)*u, out1 = (g|u) if non-null
   EPI_SWIGLU_BWD = 2,  // acc = dL/dh; aux = saved (g|u); out0 = (dg|du) in the same interleaved layout
   EPI_ACCUM_F32 = 3,   // out0 (f32) = acc  or  += acc
+  EPI_STORE_F32 = 4,   // out0[row, col] = acc in f32, rows < M and cols < N only
 };
 
 struct GemmArgs {

@@ -103,6 +103,7 @@ struct RouterBwdArgs {
   int tokens, E, k;
   float aux_w, z_w;
   float* grad_logits;       // [tokens, E]
+  bf16* grad_logits_bf16;   // optional bf16 copy (operand of the tensor-core router products)
 };
 cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream);
 
@@ -110,7 +111,8 @@ cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream);
 struct UnpermuteArgs {
   const void* grad_x_perm;   // [padded rows, d]
   const void* shared;        // optional [tokens, d]
-  const float* grad_logits;  // [tokens, E]
+  const void* extra;         // optional [tokens, d]: router input gradient computed elsewhere
+  const float* grad_logits;  // [tokens, E]; null when `extra` already holds grad_logits W_r
   const float* w_router;     // [E, d]
   const int* expert_of;
   const int* slot_pos;

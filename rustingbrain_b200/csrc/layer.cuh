@@ -59,6 +59,9 @@ struct moe_layer {
   void *dy_perm = nullptr, *dgu = nullptr, *dx_perm = nullptr, *dh = nullptr;
   void *gu_s = nullptr, *h_s = nullptr, *y_s = nullptr, *dgu_s = nullptr, *dx_s = nullptr, *dh_s = nullptr;
   float *grad_gates = nullptr, *grad_logits = nullptr, *rw_scratch = nullptr;
+  moe::bf16* gl_bf16 = nullptr;   // [max_tokens, E]
+  void* dx_r = nullptr;           // [shared_rows_cap, d] router input gradient
+  bool tc_router = false;         // router products on the tensor cores (bf16, E % 8 == 0)
   int rw_splits = 1;
 
   // host-call staging

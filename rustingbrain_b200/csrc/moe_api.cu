@@ -372,7 +372,20 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.tokens = tokens; ra.d = L->d; ra.E = L->E; ra.k = L->k;
   ra.logits_out = L->logits; ra.probs = L->probs; ra.lse = L->lse; ra.expert_of = L->expert_of; ra.gates = L->gates;
   ra.partial = L->partial; ra.hist = L->hist;
-  { Span sp(L, 0, st); CK(launch_router(ra, L->act, st));
+  shared_meta_kernel<<<1, 1, 0, st>>>(L->shared_meta, tokens); count_launch();
+  { Span sp(L, 0, st);
+  if (L->tc_router && !logits_in) {
+    // logits = x W_r^T on the tensor cores, f32 out; softmax/top-k then read them back
+    tc::GemmArgs g{};
+    g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;
+    g.N = L->E; g.K = L->d; g.M = tokens; g.out0 = L->logits; g.ld0 = L->E;
+    tc::Operand A{x, tokens, L->d, 1};
+    tc::Operand B{L->wb + L->off_router, L->E, L->d, 1};
+    CK(tc::gemm_rows_nt(A, B, g, tc::EPI_STORE_F32, L->sm_count, st));
+    ra.logits_in = L->logits;
+    ra.logits_out = nullptr;
+  }
+  CK(launch_router(ra, L->act, st));
   CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, nullptr, nullptr, st)); }
 
   PermuteArgs pa{};
@@ -389,7 +402,6 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   if (rc != MOE_OK) return rc;
 
   if (L->shared) {
-    shared_meta_kernel<<<1, 1, 0, st>>>(L->shared_meta, tokens); count_launch();
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
     ExpertIO sio{};
     sio.x = x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
@@ -440,10 +452,29 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   rb.probs = L->probs; rb.lse = L->lse; rb.expert_of = L->expert_of; rb.grad_gates = L->grad_gates;
   rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
   rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
+  rb.grad_logits_bf16 = L->tc_router ? L->gl_bf16 : nullptr;
   { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
 
+  if (L->tc_router) {
+    // router input gradient grad_logits W_r and router weight gradient grad_logits^T x as two
+    // more launches of the grouped tensor-core GEMM over one dense row group
+    Span sp(L, 12, st);
+    tc::GemmArgs g{};
+    g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;
+    g.N = L->d; g.K = L->E; g.out0 = L->dx_r; g.ld0 = L->d;
+    tc::Operand A{L->gl_bf16, tokens, L->E, 1};
+    tc::Operand B{L->wb + L->off_router, L->E, L->d, 1};
+    CK(tc::gemm_rows_nn(A, B, g, tc::EPI_STORE, L->sm_count, st));
+    tc::GemmArgs wg{};
+    wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
+    wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
+    tc::Operand Ax{L->last_x, tokens, L->d, 1};
+    CK(tc::gemm_rows_tn(A, Ax, wg, L->sm_count, st));
+  }
+
   UnpermuteArgs ua{};
-  ua.grad_x_perm = L->dx_perm; ua.shared = L->shared ? L->dx_s : nullptr; ua.grad_logits = L->grad_logits;
+  ua.grad_x_perm = L->dx_perm; ua.shared = L->shared ? L->dx_s : nullptr;
+  ua.extra = L->tc_router ? L->dx_r : nullptr; ua.grad_logits = L->tc_router ? nullptr : L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
   { Span sp(L, 11, st); CK(launch_unpermute(ua, L->act, st)); }
@@ -451,7 +482,7 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   RouterWgradArgs rw{};
   rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
   rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
-  { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
+  if (!L->tc_router) { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
   CK(cudaGetLastError());
   L->grad_valid = true;
   return MOE_OK;
@@ -516,6 +547,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   if (L->ep_size != 1) return fail(L, MOE_UNSUPPORTED, "expert-parallel handles are not built into this library version");
 
   const long long T = L->max_tokens, d = L->d, E = L->E, k = L->k, Fp = L->F_pad;
+  L->tc_router = L->precision == MOE_PRECISION_BF16 && L->E % 8 == 0;
   if (L->precision == MOE_PRECISION_Q8) {
     DA(L->w, (long long)E * d * 4, true);   // router only
   } else {
@@ -554,6 +586,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
       if (L->act == PREC_F32) DA(L->dh_s, sc * Fp * es, true);
     }
     DA(L->grad_gates, T * k * 4, true); DA(L->grad_logits, T * E * 4, true);
+    if (L->tc_router) { DA(L->gl_bf16, T * E * 2, true); DA(L->dx_r, sc * d * es, true); }
     L->rw_splits = (int)std::min<long long>(64, std::max<long long>(1, T / 256));
     DA(L->rw_scratch, (long long)L->rw_splits * E * d * 4, false);
   }

@@ -306,7 +306,7 @@ class MoeLayer:
             v = np.ascontiguousarray(valid, dtype=np.uint8)
             if v.size != T:
                 raise InvalidConfig("padding mask covers %d rows, not %d" % (v.size, T))
-        y = np.empty((T, self._d), np.float32)
+        y = out if out is not None else np.empty((T, self._d), np.float32)
         fp, bp = C.POINTER(C.c_float), C.POINTER(C.c_uint8)
         self._ck(L.moe_forward_host(self._h, x.ctypes.data_as(fp), T, cols, v.ctypes.data_as(bp) if v is not None else None,
                                     y.ctypes.data_as(fp), int(save)))
@@ -324,7 +324,7 @@ class MoeLayer:
             self._ck(L.moe_backward(self._h, g.data_ptr(), gx.data_ptr(), 0, st))
             return gx
         g = np.ascontiguousarray(grad_output, dtype=np.float32)
-        gx = np.empty_like(g)
+        gx = out if out is not None else np.empty_like(g)
         fp = C.POINTER(C.c_float)
         self._ck(L.moe_backward_host(self._h, g.ctypes.data_as(fp), gx.ctypes.data_as(fp)))
         return gx
