@@ -265,27 +265,29 @@ def main():
         xh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
         gh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
         xh.copy_(x.float().cpu()); gh.copy_(gy.float().cpu())
-        host = layer.local_layer() if world > 1 else layer
+        host = layer
         xn, gn = xh.numpy(), gh.numpy()
         yn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
         gxn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
         e2e_steps = max(1, min(args.steps, 3))
-        if world == 1:
-            for _ in range(2):
-                _, c = host.forward_train(xn, out=yn); host.zero_grad(); host.backward(c, gn, out=gxn)
-            barrier()
-            t0 = time.perf_counter()
-            for _ in range(e2e_steps):
-                yh, c = host.forward_train(xn, out=yn)
-                host.zero_grad()
-                gxh = host.backward(c, gn, out=gxn)
-                aux = c.auxiliary_loss()
-            dt = (time.perf_counter() - t0) / e2e_steps
-            nbytes = w["T"] * w["d"] * 4
-            e2e = {"value": w["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
-                   "d2h_bytes_per_step": 2 * nbytes + 8, "ms_per_step": dt * 1e3}
-        else:
-            e2e = layer.e2e_measure(xn, gn, e2e_steps, barrier)
+        for _ in range(2):
+            _, c = host.forward_train(xn, out=yn); host.zero_grad(); host.backward(c, gn, out=gxn)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            yh, c = host.forward_train(xn, out=yn)
+            host.zero_grad()
+            gxh = host.backward(c, gn, out=gxn)
+            aux = c.auxiliary_loss()
+        barrier()
+        dt = (time.perf_counter() - t0) / e2e_steps
+        if world > 1:
+            t = torch.tensor([dt], device=device, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        nbytes = w["T"] * w["d"] * 4
+        e2e = {"value": world * w["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
+               "d2h_bytes_per_step": 2 * nbytes + 8, "ms_per_step": dt * 1e3}
 
     if rank != 0:
         if world > 1:

@@ -79,6 +79,10 @@ typedef struct {
    * ep_size = 1 is the single-device layer. */
   int32_t ep_rank;
   int32_t ep_size;
+  /* Receive-buffer rows of an expert-parallel rank as a multiple of max_tokens * experts_per_token
+   * (its share under uniform routing); 0 selects 1.25.  Routing is dropless, so a pass that sends
+   * a rank more rows than this fails with MOE_INVALID_INPUT instead of dropping tokens. */
+  float ep_capacity_factor;
 } moe_config_t;
 
 /* MoeConfig::validate (moe.rs:68-86) and the shape rules of the chosen precision. */
@@ -149,6 +153,21 @@ int32_t moe_get_routing(moe_layer_t* layer, int32_t* expert_of, float* gates, in
                         int32_t* slot_of, int32_t* routed);
 /* logits / probabilities [tokens, E] and log-sum-exp [tokens] of the last forward. */
 int32_t moe_get_router_cache(moe_layer_t* layer, float* logits, float* probabilities, float* log_sum_exp);
+
+/* Expert parallelism (no counterpart in the reference, which is single-device; README.md:29-31).
+ * Rank r of ep_size owns experts [r*E/ep_size, (r+1)*E/ep_size); router and shared expert are
+ * replicated.  One rank obtains an id with moe_ep_unique_id and passes it to the others by any
+ * host channel; every rank then calls moe_ep_init (collective).  After that moe_forward /
+ * moe_backward on these handles are collectives: every rank must call them in the same order.
+ * The row exchange is NCCL send/recv on the caller's stream. */
+#define MOE_EP_UNIQUE_ID_BYTES 128
+int32_t moe_ep_unique_id(void* out, int32_t len);
+int32_t moe_ep_init(moe_layer_t* layer, const void* unique_id, int32_t len);
+/* Host-only helper (no device needed): the exchange plan of `rank` from the gathered
+ * count matrix counts_all[ranks][num_experts].  Outputs: send_off[E+1], recv_row[ranks*E/ranks],
+ * local_row0 / local_tiles / local_counts [E/ranks + 1].  Returns the padded local row total, -1 on bad arguments. */
+int32_t moe_ep_plan(const int32_t* counts_all, int32_t ranks, int32_t num_experts, int32_t rank, int32_t* send_off,
+                    int32_t* recv_row, int32_t* local_row0, int32_t* local_tiles, int32_t* local_counts);
 
 /* Device synchronisation for timing (TransformerLm::synchronize, transformer.rs:1323-1334). */
 int32_t moe_synchronize(moe_layer_t* layer);

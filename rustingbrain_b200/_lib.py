@@ -21,7 +21,7 @@ class MoeConfigC(C.Structure):
         ("d_model", C.c_int32), ("num_experts", C.c_int32), ("experts_per_token", C.c_int32), ("d_ff", C.c_int32),
         ("shared_expert", C.c_int32), ("aux_loss_weight", C.c_float), ("router_z_loss_weight", C.c_float),
         ("precision", C.c_int32), ("max_tokens", C.c_int32), ("device", C.c_int32), ("training", C.c_int32),
-        ("ep_rank", C.c_int32), ("ep_size", C.c_int32),
+        ("ep_rank", C.c_int32), ("ep_size", C.c_int32), ("ep_capacity_factor", C.c_float),
     ]
 
 
@@ -63,6 +63,9 @@ def lib() -> C.CDLL:
         "moe_get_routing": (i32, [vp, ip, fp, ip, ip, ip, ip]),
         "moe_get_router_cache": (i32, [vp, fp, fp, fp]),
         "moe_synchronize": (i32, [vp]),
+        "moe_ep_unique_id": (i32, [vp, i32]),
+        "moe_ep_init": (i32, [vp, vp, i32]),
+        "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
         "moe_debug_profile": (i32, [vp, i32]),

@@ -20,7 +20,7 @@ def sources():
 
 
 def _newest_header():
-    hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
     hdrs.append(os.path.join(HERE, "..", "include", "moe_b200.h"))
     return max(os.path.getmtime(h) for h in hdrs if os.path.exists(h))
 
@@ -48,7 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 raise RuntimeError("nvcc failed for " + cmd[-3])
     objs = [os.path.join(OBJ, src[:-3] + ".o") for src in sources()]
     if jobs or not os.path.exists(LIB):
-        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart", "-ccbin", "/usr/bin/g++"]
+        cmd = [NVCC, "-shared", "-o", LIB] + objs + ["-lcudart", "-lnccl", "-ccbin", "/usr/bin/g++"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)

@@ -36,8 +36,13 @@ struct PermuteArgs {
 };
 
 cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t stream);
+// `align`: every expert's row group starts at a multiple of this many rows (128 for the
+// local expert GEMMs, 1 for the compact send layout of an expert-parallel rank).
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
-                            const float* ext_stats, const int* ext_counts, cudaStream_t stream);
+                            int align, cudaStream_t stream);
+cudaError_t launch_ep_pack_stats(const float* stats, const int* counts, int E, int* out, cudaStream_t stream);
+cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float aux_w, float z_w, float* ext_stats,
+                             int* ext_counts, float* losses, cudaStream_t stream);
 cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t stream);
 cudaError_t launch_pad_rows(void* buf, int d, RouteMeta meta, int E, int precision, cudaStream_t stream);
 

@@ -64,6 +64,20 @@ struct moe_layer {
   bool tc_router = false;         // router products on the tensor cores (bf16, E % 8 == 0)
   int rw_splits = 1;
 
+  // expert parallelism (ep_size > 1): the send side keeps the compact expert-major
+  // layout in x_perm / y_perm / dy_perm / dx_perm; rows received for the local experts
+  // live in the *_recv buffers in the padded layout the grouped GEMMs want.
+  void* comm = nullptr;            // ncclComm_t
+  bool ep_ready = false;
+  float ep_capacity = 1.25f;
+  int rows_cap_l = 0;              // capacity (rows) of the local-expert buffers
+  int *ep_pack = nullptr, *ep_gathered = nullptr, *ep_gathered_host = nullptr;
+  float* ext_stats = nullptr;      // whole-batch sum p[e], sum lse^2, valid tokens
+  int* ext_counts = nullptr;       // whole-batch rows per expert
+  int *local_meta = nullptr, *local_meta_host = nullptr;   // row0[El+1], tiles[El+1], counts[El+1]
+  std::vector<int> cnt_all, send_off, recv_row;
+  void *x_recv = nullptr, *y_recv = nullptr, *dy_recv = nullptr, *dx_recv = nullptr;
+
   // host-call staging
   float* host_stage_f32 = nullptr;   // [max_tokens, d]
   void* host_x = nullptr;            // [max_tokens, d] act type

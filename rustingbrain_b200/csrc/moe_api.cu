@@ -11,6 +11,8 @@
 
 #include "../../include/moe_b200.h"
 #include "../../include/moe_b200_debug.h"
+#include <nccl.h>
+
 #include "layer.cuh"
 
 using namespace moe;
@@ -349,6 +351,8 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
   return MOE_OK;
 }
 
+#include "ep_impl.inc"
+
 int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens, int cols, const uint8_t* valid,
                  void* y, int accumulate, int save, cudaStream_t st) {
   if (cols != L->d) {   // moe.rs:248-253
@@ -362,10 +366,12 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   if (tokens > 0 && (!x || !y)) { L->err = "InvalidInput: null activation pointer"; return MOE_INVALID_INPUT; }
   if (L->precision == MOE_PRECISION_Q8) return fail(L, MOE_UNSUPPORTED, "the int8 decode path is not built into this library version");
   if (save && !L->training) { L->err = "InvalidConfig: save_for_backward needs a handle created with training = 1"; return MOE_INVALID_CONFIG; }
+  const bool ep = L->ep_size > 1;
+  if (ep && !L->ep_ready) { L->err = "InvalidConfig: expert-parallel handle without a communicator (call moe_ep_init)"; return MOE_INVALID_CONFIG; }
   L->have_cache = false;
   L->last_tokens = tokens;
   L->last_stream = st;
-  if (tokens == 0) return MOE_OK;
+  if (tokens == 0 && !ep) return MOE_OK;   // an expert-parallel rank with no tokens still serves its experts
 
   RouterArgs ra{};
   ra.x = x; ra.w_router = L->w + L->off_router; ra.logits_in = logits_in; ra.valid = valid;
@@ -386,7 +392,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     ra.logits_out = nullptr;
   }
   CK(launch_router(ra, L->act, st));
-  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, nullptr, nullptr, st)); }
+  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, ep ? 1 : GROUP_ALIGN, st)); }
 
   PermuteArgs pa{};
   pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
@@ -395,13 +401,18 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   pa.token_of = L->token_of; pa.slot_of = L->slot_of;
   { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
-  Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
-  ExpertIO io{};
-  io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.w_gu = L->off_gu; io.w_d = L->off_d;
-  int rc = experts_forward(L, G, io, save != 0, st, true);
+  int rc;
+  if (ep) {
+    rc = ep_forward_experts(L, save != 0, st);
+  } else {
+    Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+    ExpertIO io{};
+    io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.w_gu = L->off_gu; io.w_d = L->off_d;
+    rc = experts_forward(L, G, io, save != 0, st, true);
+  }
   if (rc != MOE_OK) return rc;
 
-  if (L->shared) {
+  if (L->shared && tokens > 0) {
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
     ExpertIO sio{};
     sio.x = x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
@@ -424,7 +435,12 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   if (!L->have_cache) { L->err = "InvalidInput: moe_backward needs a preceding moe_forward with save_for_backward"; return MOE_INVALID_INPUT; }
   if (!gy || !gx) { L->err = "InvalidInput: null gradient pointer"; return MOE_INVALID_INPUT; }
   const int tokens = L->last_tokens;
-  if (tokens == 0) return MOE_OK;
+  const bool ep = L->ep_size > 1;
+  if (tokens == 0 && !ep) return MOE_OK;
+  if (ep && L->grad_valid) {
+    L->err = "Unsupported: an expert-parallel handle does not accumulate gradients over several backward passes; call moe_zero_grad between them";
+    return MOE_UNSUPPORTED;
+  }
 
   GatherGradArgs ga{};
   ga.grad_y = gy; ga.y_perm = L->y_perm; ga.slot_pos = L->slot_pos; ga.gates = L->gates;
@@ -432,14 +448,19 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   { Span sp(L, 5, st); CK(launch_gather_grad(ga, L->act, st));
   CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st)); }
 
-  Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
-  ExpertIO io{};
-  io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
-  io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
-  int rc = experts_backward(L, G, io, st, true);
+  int rc;
+  if (ep) {
+    rc = ep_backward_experts(L, st);
+  } else {
+    Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+    ExpertIO io{};
+    io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
+    io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
+    rc = experts_backward(L, G, io, st, true);
+  }
   if (rc != MOE_OK) return rc;
 
-  if (L->shared) {
+  if (L->shared && tokens > 0) {
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
     ExpertIO sio{};
     sio.x = L->last_x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.dy = gy; sio.dgu = L->dgu_s;
@@ -453,9 +474,10 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
   rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
   rb.grad_logits_bf16 = L->tc_router ? L->gl_bf16 : nullptr;
+  if (ep) { rb.ext_stats = L->ext_stats; rb.ext_counts = L->ext_counts; }
   { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
 
-  if (L->tc_router) {
+  if (L->tc_router && tokens > 0) {
     // router input gradient grad_logits W_r and router weight gradient grad_logits^T x as two
     // more launches of the grouped tensor-core GEMM over one dense row group
     Span sp(L, 12, st);
@@ -482,7 +504,12 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   RouterWgradArgs rw{};
   rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
   rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
-  if (!L->tc_router) { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
+  if (!L->tc_router || tokens == 0) { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
+  if (ep) {
+    Span sp(L, 12, st);
+    rc = ep_allreduce_replicated(L, st);
+    if (rc != MOE_OK) return rc;
+  }
   CK(cudaGetLastError());
   L->grad_valid = true;
   return MOE_OK;
@@ -544,7 +571,6 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   L->max_tokens = cfg->max_tokens; L->rows_cap = s.rows_cap; L->shared_rows_cap = s.shared_rows_cap;
   L->off_router = s.off_router; L->off_gu = s.off_gu; L->off_d = s.off_d; L->off_sgu = s.off_sgu; L->off_sd = s.off_sd;
   L->n_params = s.n_params;
-  if (L->ep_size != 1) return fail(L, MOE_UNSUPPORTED, "expert-parallel handles are not built into this library version");
 
   const long long T = L->max_tokens, d = L->d, E = L->E, k = L->k, Fp = L->F_pad;
   L->tc_router = L->precision == MOE_PRECISION_BF16 && L->E % 8 == 0;
@@ -574,13 +600,30 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   DA(L->row_token, (long long)L->rows_cap * 4, false); DA(L->row_gate, (long long)L->rows_cap * 4, false);
   DA(L->shared_meta, 4 * 4, true); DA(L->error_flag, 4, true);
 
+  const bool ep = L->ep_size > 1;
+  if (ep) {
+    L->ep_capacity = cfg->ep_capacity_factor > 0.f ? cfg->ep_capacity_factor : 1.25f;
+    const long long want = (long long)std::ceil((double)L->ep_capacity * (double)T * (double)k) + (long long)L->E_local * (GROUP_ALIGN - 1);
+    L->rows_cap_l = (int)std::min<long long>(round_up((int)std::min<long long>(want, 1ll << 30), GROUP_ALIGN),
+                                             (long long)round_up((int)(T * k) * L->ep_size + L->E_local * (GROUP_ALIGN - 1), GROUP_ALIGN));
+    const int El = L->E_local, N = L->ep_size, words = 2 * (int)E + 2;
+    DA(L->ep_pack, words * 4, true); DA(L->ep_gathered, (long long)N * words * 4, true);
+    DA(L->ext_stats, (E + 2) * 4, true); DA(L->ext_counts, E * 4, true);
+    DA(L->local_meta, 3 * (El + 1) * 4, true);
+    CK(cudaMallocHost((void**)&L->ep_gathered_host, (size_t)N * words * 4));
+    CK(cudaMallocHost((void**)&L->local_meta_host, (size_t)3 * (El + 1) * 4));
+    L->cnt_all.assign((size_t)N * E, 0); L->send_off.assign(E + 1, 0); L->recv_row.assign((size_t)N * El, 0);
+  }
   const long long rc = L->rows_cap, sc = L->shared_rows_cap, es = (long long)L->esz;
-  DA(L->x_perm, rc * d * es, true); DA(L->gu, rc * 2 * Fp * es, true); DA(L->h, rc * Fp * es, true);
+  const long long rl = ep ? L->rows_cap_l : rc;   // rows of the buffers the expert GEMMs work on
+  DA(L->x_perm, rc * d * es, true); DA(L->gu, rl * 2 * Fp * es, true); DA(L->h, rl * Fp * es, true);
+  if (ep) { DA(L->x_recv, rl * d * es, true); DA(L->y_recv, rl * d * es, true); }
   DA(L->y_perm, rc * d * es, true);
   if (L->shared) { DA(L->gu_s, sc * 2 * Fp * es, true); DA(L->h_s, sc * Fp * es, true); DA(L->y_s, sc * d * es, true); }
   if (L->training) {
-    DA(L->dy_perm, rc * d * es, true); DA(L->dgu, rc * 2 * Fp * es, true); DA(L->dx_perm, rc * d * es, true);
-    if (L->act == PREC_F32) DA(L->dh, rc * Fp * es, true);
+    DA(L->dy_perm, rc * d * es, true); DA(L->dgu, rl * 2 * Fp * es, true); DA(L->dx_perm, rc * d * es, true);
+    if (L->act == PREC_F32) DA(L->dh, rl * Fp * es, true);
+    if (ep) { DA(L->dy_recv, rl * d * es, true); DA(L->dx_recv, rl * d * es, true); }
     if (L->shared) {
       DA(L->dgu_s, sc * 2 * Fp * es, true); DA(L->dx_s, sc * d * es, true);
       if (L->act == PREC_F32) DA(L->dh_s, sc * Fp * es, true);
@@ -598,6 +641,9 @@ void moe_destroy(moe_layer_t* L) {
   if (!L) return;
   cudaSetDevice(L->device);
   cudaDeviceSynchronize();
+  if (L->comm) ncclCommDestroy((ncclComm_t)L->comm);
+  if (L->ep_gathered_host) cudaFreeHost(L->ep_gathered_host);
+  if (L->local_meta_host) cudaFreeHost(L->local_meta_host);
   for (void* p : L->allocations) cudaFree(p);
   for (auto& sp : L->prof_spans) { cudaEventDestroy(sp.begin); cudaEventDestroy(sp.end); }
   for (auto ev : L->prof_pool) cudaEventDestroy(ev);
@@ -860,6 +906,33 @@ int32_t moe_debug_profile_read(moe_layer_t* L, float* ms, int32_t* stages) {
   cudaGetLastError();
   L->prof_spans.clear();
   return MOE_OK;
+}
+
+int32_t moe_ep_unique_id(void* out, int32_t len) {
+  if (!out || len < (int32_t)sizeof(ncclUniqueId)) return MOE_INVALID_INPUT;
+  ncclUniqueId id;
+  if (ncclGetUniqueId(&id) != ncclSuccess) return MOE_COMM_ERROR;
+  memcpy(out, &id, sizeof(id));
+  return MOE_OK;
+}
+
+int32_t moe_ep_init(moe_layer_t* L, const void* unique_id, int32_t len) {
+  ENTER(L);
+  if (L->ep_size <= 1) { L->err = "InvalidConfig: the handle was created with ep_size = 1"; return MOE_INVALID_CONFIG; }
+  if (!unique_id || len < (int32_t)sizeof(ncclUniqueId)) { L->err = "InvalidInput: bad unique id"; return MOE_INVALID_INPUT; }
+  ncclUniqueId id;
+  memcpy(&id, unique_id, sizeof(id));
+  ncclComm_t comm = nullptr;
+  NCK(ncclCommInitRank(&comm, L->ep_size, id, L->ep_rank));
+  L->comm = comm;
+  L->ep_ready = true;
+  return MOE_OK;
+}
+
+int32_t moe_ep_plan(const int32_t* counts_all, int32_t ranks, int32_t num_experts, int32_t rank, int32_t* send_off,
+                    int32_t* recv_row, int32_t* local_row0, int32_t* local_tiles, int32_t* local_counts) {
+  if (!counts_all || ranks <= 0 || num_experts <= 0 || num_experts % ranks != 0 || rank < 0 || rank >= ranks) return -1;
+  return ep_plan(counts_all, ranks, num_experts, rank, send_off, recv_row, local_row0, local_tiles, local_counts);
 }
 
 int32_t moe_synchronize(moe_layer_t* L) {

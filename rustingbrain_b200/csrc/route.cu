@@ -226,7 +226,7 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
 __global__ void __launch_bounds__(256)
 finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int nb, int E, int k, float aux_w,
                 float z_w, RouteMeta meta, float* __restrict__ stats /*[E+2]: sums, lse2, V*/,
-                float* __restrict__ losses /*[2]*/, const float* __restrict__ ext_stats, const int* __restrict__ ext_counts) {
+                float* __restrict__ losses /*[2]*/, int align) {
   __shared__ int s_counts[MAX_EXPERTS];
   __shared__ float s_sums[MAX_EXPERTS + 2];
   const int tid = threadIdx.x;
@@ -254,9 +254,9 @@ finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int n
       meta.pad_off[e] = pad;
       meta.tile_start[e] = tiles;
       off += s_counts[e];
-      const int padded = round_up(s_counts[e], GROUP_ALIGN);
+      const int padded = round_up(s_counts[e], align);
       pad += padded;
-      tiles += padded / GROUP_ALIGN;
+      tiles += ceil_div(padded, GROUP_ALIGN);
     }
     meta.offsets[E] = off;
     meta.pad_off[E] = pad;
@@ -266,15 +266,14 @@ finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int n
     meta.total[1] = pad;
     meta.total[2] = tiles;
     meta.total[3] = V;
-    // auxiliary_losses (moe.rs:602-639).  In an expert-parallel group the statistics
-    // of the whole batch (all ranks) are supplied through ext_stats / ext_counts.
-    const float* sums = ext_stats ? ext_stats : s_sums;
-    const float Vf = ext_stats ? ext_stats[E + 1] : (float)V;
+    // auxiliary_losses (moe.rs:602-639) over the rows this device saw.
+    const float* sums = s_sums;
+    const float Vf = (float)V;
     float aux = 0.f, z = 0.f;
     if (Vf > 0.f) {
       const float slots = Vf * (float)k;
       for (int e = 0; e < E; ++e) {
-        const float load = (float)(ext_counts ? ext_counts[e] : s_counts[e]) / slots;
+        const float load = (float)s_counts[e] / slots;
         const float mass = sums[e] / Vf;
         aux += load * mass;
       }
@@ -284,6 +283,42 @@ finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int n
     losses[0] = aux;
     losses[1] = z;
   }
+}
+
+// Expert parallelism: every rank contributed {stats[E+2] as floats, counts[E] as ints};
+// the statistics of the whole batch are their sums in rank order, and the two losses
+// follow from them exactly as on one device (moe.rs:602-639 over the concatenated batch).
+__global__ void ep_losses_kernel(const int* __restrict__ gathered, int ranks, int E, int k, float aux_w, float z_w,
+                                 float* __restrict__ ext_stats, int* __restrict__ ext_counts, float* __restrict__ losses) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int stride = 2 * E + 2;
+  for (int e = 0; e < E + 2; ++e) {
+    float s = 0.f;
+    for (int r = 0; r < ranks; ++r) s += __int_as_float(gathered[(size_t)r * stride + e]);
+    ext_stats[e] = s;
+  }
+  for (int e = 0; e < E; ++e) {
+    int c = 0;
+    for (int r = 0; r < ranks; ++r) c += gathered[(size_t)r * stride + E + 2 + e];
+    ext_counts[e] = c;
+  }
+  const float Vf = ext_stats[E + 1];
+  float aux = 0.f, z = 0.f;
+  if (Vf > 0.f) {
+    const float slots = Vf * (float)k;
+    for (int e = 0; e < E; ++e) aux += ((float)ext_counts[e] / slots) * (ext_stats[e] / Vf);
+    aux *= (float)E * aux_w;
+    z = z_w * ext_stats[E] / Vf;
+  }
+  losses[0] = aux;
+  losses[1] = z;
+}
+
+// Packs this rank's contribution to the exchange above: stats as float bits, then counts.
+__global__ void ep_pack_stats_kernel(const float* __restrict__ stats, const int* __restrict__ counts, int E,
+                                     int* __restrict__ out) {
+  for (int i = threadIdx.x; i < 2 * E + 2; i += blockDim.x)
+    out[i] = i < E + 2 ? __float_as_int(stats[i]) : counts[i - (E + 2)];
 }
 
 // Adds the padded group base to the cursors once pad_off is known.
@@ -418,11 +453,20 @@ cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t strea
   return precision == PREC_BF16 ? launch_router_t<bf16>(a, stream) : launch_router_t<float>(a, stream);
 }
 
+cudaError_t launch_ep_pack_stats(const float* stats, const int* counts, int E, int* out, cudaStream_t stream) {
+  ep_pack_stats_kernel<<<1, 256, 0, stream>>>(stats, counts, E, out); count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float aux_w, float z_w, float* ext_stats,
+                             int* ext_counts, float* losses, cudaStream_t stream) {
+  ep_losses_kernel<<<1, 32, 0, stream>>>(gathered, ranks, E, k, aux_w, z_w, ext_stats, ext_counts, losses); count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
-                            const float* ext_stats, const int* ext_counts, cudaStream_t stream) {
+                            int align, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
-  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, ext_stats,
-                                         ext_counts); count_launch();
+  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align); count_launch();
   if (nb > 0) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
   return cudaGetLastError();
 }

@@ -141,7 +141,8 @@ class MoeLayer:
     """
 
     def __init__(self, d_model: int, config: MoeConfig, *, precision: str = "bf16", max_tokens: int = 4096,
-                 device: int = 0, training: bool = True, ep_rank: int = 0, ep_size: int = 1):
+                 device: int = 0, training: bool = True, ep_rank: int = 0, ep_size: int = 1,
+                 ep_capacity_factor: float = 0.0):
         config.validate()
         if precision not in _PRECISIONS:
             raise InvalidConfig("precision must be one of %s" % sorted(_PRECISIONS))
@@ -156,7 +157,8 @@ class MoeLayer:
         self._keep = None
         c = _lib.MoeConfigC(self._d, config.num_experts, config.experts_per_token, config.d_ff,
                             int(config.shared_expert), config.aux_loss_weight, config.router_z_loss_weight,
-                            _PRECISIONS[precision], self.max_tokens, self.device, int(self.training), ep_rank, ep_size)
+                            _PRECISIONS[precision], self.max_tokens, self.device, int(self.training), ep_rank, ep_size,
+                            ep_capacity_factor)
         self._cfg = c
         L = _lib.lib()
         msg = C.create_string_buffer(256)
@@ -191,7 +193,7 @@ class MoeLayer:
     def workspace_bytes(d_model, config: MoeConfig, precision="bf16", max_tokens=4096, training=True) -> int:
         c = _lib.MoeConfigC(d_model, config.num_experts, config.experts_per_token, config.d_ff,
                             int(config.shared_expert), config.aux_loss_weight, config.router_z_loss_weight,
-                            _PRECISIONS[precision], max_tokens, 0, int(training), 0, 1)
+                            _PRECISIONS[precision], max_tokens, 0, int(training), 0, 1, 0.0)
         return int(_lib.lib().moe_workspace_bytes(C.byref(c)))
 
     def d_model(self) -> int:

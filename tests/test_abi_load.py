@@ -17,7 +17,7 @@ def test_library_exports_every_declared_symbol():
 def _cfg(**kw):
     base = dict(d_model=64, num_experts=4, experts_per_token=2, d_ff=32, shared_expert=0, aux_loss_weight=0.01,
                 router_z_loss_weight=1e-3, precision=_lib.PRECISION_F32, max_tokens=16, device=0, training=1,
-                ep_rank=0, ep_size=1)
+                ep_rank=0, ep_size=1, ep_capacity_factor=0.0)
     base.update(kw)
     return _lib.MoeConfigC(**base)
 

@@ -1,0 +1,89 @@
+"""Expert parallelism on real GPUs: N ranks against one CPU checker over the concatenated batch."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, precision, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from oracle import OracleMoe, ROUTER, GATE, UP, DOWN, SHARED_GATE
+        from helpers import seeded_weights, rel_l2
+        from rustingbrain_b200 import MoeConfig
+        from rustingbrain_b200.ep import ExpertParallelMoe
+        d, E, k, F = 256, 8, 2, 96
+        Ts = [200 + 56 * r for r in range(world)]
+        tol = 1e-5 if precision == "f32" else 2e-2
+        w = seeded_weights(d, E, F, True, 21, std=0.05, router_std=0.05)
+        if precision != "f32":
+            rb = lambda a: torch.from_numpy(a).bfloat16().float().numpy()
+            w = dict(w, gate=rb(w["gate"]), up=rb(w["up"]), down=rb(w["down"]), shared=tuple(rb(s) for s in w["shared"]))
+        layer = ExpertParallelMoe(d, MoeConfig(E, k, F, True), precision=precision, max_tokens=max(Ts), device=rank,
+                                  capacity_factor=2.0)
+        layer.set_weight(ROUTER, 0, w["router"])
+        for e in layer.owned_experts():
+            layer.set_weight(GATE, e, w["gate"][e]); layer.set_weight(UP, e, w["up"][e]); layer.set_weight(DOWN, e, w["down"][e])
+        for i, s in enumerate(w["shared"]):
+            layer.set_weight(SHARED_GATE + i, 0, s)
+        gens = [np.random.Generator(np.random.Philox(50 + r)) for r in range(world)]
+        xs = [g.standard_normal((T, d)).astype(np.float32) for g, T in zip(gens, Ts)]
+        gys = [g.standard_normal((T, d)).astype(np.float32) for g, T in zip(gens, Ts)]
+        dt = torch.float32 if precision == "f32" else torch.bfloat16
+        x = torch.from_numpy(xs[rank]).cuda().to(dt)
+        gy = torch.from_numpy(gys[rank]).cuda().to(dt)
+        y, cache = layer.forward_train(x)
+        layer.zero_grad()
+        gx = layer.backward(cache, gy)
+        logits = layer.router_cache(Ts[rank])[0]
+        all_logits = [None] * world
+        dist.all_gather_object(all_logits, logits)
+        # single-device checker over the concatenated batch, fed the devices' own logits
+        rnd = (lambda a: torch.from_numpy(a).to(dt).float().numpy())
+        ora = OracleMoe(d, E, k, F, True)
+        ora.set_weights(w["router"], w["gate"], w["up"], w["down"], w["shared"])
+        yo = ora.forward(rnd(np.concatenate(xs)), logits=np.concatenate(all_logits))
+        gxo = ora.backward(rnd(np.concatenate(gys)))
+        lo, hi = sum(Ts[:rank]), sum(Ts[:rank + 1])
+        ok = True
+        e_dev = cache.routing()[0]
+        ok &= np.array_equal(e_dev, ora.routing()[0][lo:hi])
+        ok &= rel_l2(y.float().cpu().numpy(), yo[lo:hi]) <= tol
+        ok &= rel_l2(gx.float().cpu().numpy(), gxo[lo:hi]) <= tol
+        a, z = ora.losses()
+        ok &= abs(cache.aux_loss() - a) <= 1e-4 * abs(a) and abs(cache.z_loss() - z) <= 1e-4 * abs(z)
+        for e in layer.owned_experts():
+            for which in (GATE, UP, DOWN):
+                ok &= rel_l2(layer.get_grad(which, e), ora.get_grad(which, e)) <= tol
+        ok &= rel_l2(layer.get_grad(ROUTER), ora.get_grad(ROUTER)) <= max(tol, 1e-4)
+        ok &= rel_l2(layer.get_grad(SHARED_GATE), ora.get_grad(SHARED_GATE)) <= tol
+        ret[rank] = bool(ok)
+        layer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("precision", ["f32", "bf16"])
+def test_expert_parallel_matches_single_device(precision):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    if world == 3:
+        world = 2
+    port = 29700 + (os.getpid() % 2000)
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_worker, args=(world, port, precision, ret), nprocs=world, join=True)
+        assert dict(ret) == {r: True for r in range(world)}
