@@ -163,6 +163,14 @@ int32_t moe_get_router_cache(moe_layer_t* layer, float* logits, float* probabili
 #define MOE_EP_UNIQUE_ID_BYTES 128
 int32_t moe_ep_unique_id(void* out, int32_t len);
 int32_t moe_ep_init(moe_layer_t* layer, const void* unique_id, int32_t len);
+/* Optional peer transport.  Each rank exports CUDA IPC handles of its four receive buffers
+ * (MOE_EP_EXPORT_BYTES bytes); every rank imports the handles of every rank, its own included.
+ * Once all are imported, the dispatch kernels store rows straight into the owner's buffer and the
+ * combine kernels load rows straight from it over NVLink, with NCCL only for the count exchange,
+ * the barriers and the gradient all-reduce.  Without it the rows travel by ncclSend/ncclRecv. */
+#define MOE_EP_EXPORT_BYTES 256
+int32_t moe_ep_export_buffers(moe_layer_t* layer, void* out, int32_t len);
+int32_t moe_ep_import_buffers(moe_layer_t* layer, int32_t rank, const void* handles, int32_t len);
 /* Host-only helper (no device needed): the exchange plan of `rank` from the gathered
  * count matrix counts_all[ranks][num_experts].  Outputs: send_off[E+1], recv_row[ranks*E/ranks],
  * local_row0 / local_tiles / local_counts [E/ranks + 1].  Returns the padded local row total, -1 on bad arguments. */

@@ -65,6 +65,8 @@ def lib() -> C.CDLL:
         "moe_synchronize": (i32, [vp]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),
+        "moe_ep_export_buffers": (i32, [vp, vp, i32]),
+        "moe_ep_import_buffers": (i32, [vp, i32, vp, i32]),
         "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),

@@ -85,7 +85,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   int pos[MAX_TOPK];
   float gate[MAX_TOPK];
   const int n = ordered_slots(a.expert_of, a.slot_pos, a.gates, t, a.k, pos, gate);
-  const T* yp = (const T*)a.y_perm;
+  const size_t rb = (size_t)a.d * sizeof(T);
   const T* sh = (const T*)a.shared;
   T* y = (T*)a.y + (size_t)t * a.d;
   constexpr int V = Vec16<T>::N;
@@ -97,7 +97,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
       for (int i = 0; i < V; ++i) acc[i] = 0.f;
       for (int j = 0; j < n; ++j) {
         float v[V];
-        Vec16<T>::load(yp + (size_t)pos[j] * d + c, v);
+        Vec16<T>::load((const T*)row_ptr(a.y_perm, pos[j], rb) + c, v);
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j], v[i]));
       }
@@ -118,7 +118,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   } else {
     for (int c = lane; c < d; c += 32) {
       float acc = 0.f;
-      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, __fmul_rn(gate[j], to_f32<T>(yp[(size_t)pos[j] * d + c])));
+      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, __fmul_rn(gate[j], to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c])));
       if (sh) acc = __fadd_rn(acc, to_f32<T>(sh[(size_t)t * d + c]));
       if (a.accumulate) acc = __fadd_rn(to_f32<T>(y[c]), acc);
       y[c] = from_f32<T>(acc);
@@ -148,8 +148,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradAr
     dot[j] = 0.f;
   }
   const T* gy = (const T*)a.grad_y + (size_t)t * d;
-  const T* yp = (const T*)a.y_perm;
-  T* gyp = (T*)a.grad_y_perm;
+  const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
   if (d % V == 0) {
     for (int c = lane * V; c < d; c += 32 * V) {
@@ -158,13 +157,13 @@ __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradAr
       for (int j = 0; j < k; ++j) {
         if (pos[j] < 0) continue;
         float o[V], s[V];
-        Vec16<T>::load(yp + (size_t)pos[j] * d + c, o);
+        Vec16<T>::load((const T*)row_ptr(a.y_perm, pos[j], rb) + c, o);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
           dot[j] = fmaf(g[i], o[i], dot[j]);
           s[i] = gate[j] * g[i];
         }
-        Vec16<T>::store(gyp + (size_t)pos[j] * d + c, s);
+        Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j], rb) + c, s);
       }
     }
   } else {
@@ -172,8 +171,8 @@ __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradAr
       const float g = to_f32<T>(gy[c]);
       for (int j = 0; j < k; ++j) {
         if (pos[j] < 0) continue;
-        dot[j] = fmaf(g, to_f32<T>(yp[(size_t)pos[j] * d + c]), dot[j]);
-        gyp[(size_t)pos[j] * d + c] = from_f32<T>(gate[j] * g);
+        dot[j] = fmaf(g, to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c]), dot[j]);
+        ((T*)row_ptr(a.grad_y_perm, pos[j], rb))[c] = from_f32<T>(gate[j] * g);
       }
     }
   }
@@ -254,7 +253,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
   float unused[MAX_TOPK];
   const int n = ordered_slots(a.expert_of, a.slot_pos, nullptr, t, a.k, pos, unused);
   const int d = a.d, E = a.E;
-  const T* gp = (const T*)a.grad_x_perm;
+  const size_t rb = (size_t)a.d * sizeof(T);
   const T* sh = (const T*)a.shared;
   const T* ex = (const T*)a.extra;
   const float* gl = a.grad_logits ? a.grad_logits + (size_t)t * E : nullptr;
@@ -268,7 +267,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
       if (sh) Vec16<T>::load(sh + (size_t)t * d + c, acc);
       for (int j = 0; j < n; ++j) {
         float v[V];
-        Vec16<T>::load(gp + (size_t)pos[j] * d + c, v);
+        Vec16<T>::load((const T*)row_ptr(a.grad_x_perm, pos[j], rb) + c, v);
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
       }
@@ -296,7 +295,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
   } else {
     for (int c = lane; c < d; c += 32) {
       float acc = sh ? to_f32<T>(sh[(size_t)t * d + c]) : 0.f;
-      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, to_f32<T>(gp[(size_t)pos[j] * d + c]));
+      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, to_f32<T>(((const T*)row_ptr(a.grad_x_perm, pos[j], rb))[c]));
       float r = ex ? to_f32<T>(ex[(size_t)t * d + c]) : 0.f;
       for (int e = 0; gl && e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
       acc = __fadd_rn(acc, r);

@@ -65,6 +65,27 @@ __device__ inline float silu_grad_(float x) {
   return s * (1.0f + x * (1.0f - s));
 }
 
+// Where the expert-major rows live.  On one GPU that is a single local buffer (n = 1 and a
+// row id is the row).  In an expert-parallel group every rank exposes its receive buffer to
+// its peers (CUDA IPC over NVLink); a row id is then rank * cap + row and the kernels store
+// to / load from the owner's memory directly.
+constexpr int MAX_RANKS = 8;
+struct RowSpace {
+  void* base[MAX_RANKS];
+  int cap;   // rows per rank
+  int n;     // ranks
+};
+__host__ __device__ inline RowSpace local_rows(void* p) {
+  RowSpace s{};
+  s.base[0] = p; s.cap = 0x7fffffff; s.n = 1;
+  return s;
+}
+__device__ inline char* row_ptr(const RowSpace& s, int id, size_t row_bytes) {
+  if (s.n == 1) return (char*)s.base[0] + (size_t)id * row_bytes;
+  const int r = id / s.cap;
+  return (char*)s.base[r] + (size_t)(id - r * s.cap) * row_bytes;
+}
+
 // Device-resident routing metadata, rebuilt by every forward pass.
 struct RouteMeta {
   int* counts;       // [E]   rows routed to each expert

@@ -27,8 +27,9 @@ struct PermuteArgs {
   const int* cursor;
   RouteMeta meta;
   int tokens, d, E, k;
-  void* x_perm;       // [padded rows, d]
-  int* slot_pos;      // [tokens*k] padded row of each slot, -1 when unrouted
+  RowSpace x_perm;    // destination rows (local buffer, or the owners' receive buffers)
+  const int* dest_base;  // optional [E]: row id of this rank's first row of each expert (expert parallel)
+  int* slot_pos;      // [tokens*k] row id of each slot, -1 when unrouted
   int* row_token;     // [padded rows] token of each row, -1 for padding rows
   float* row_gate;    // [padded rows] gate of each row
   int* token_of;      // [R] compact, stable expert-major order (the reference's permutation)
@@ -48,7 +49,7 @@ cudaError_t launch_pad_rows(void* buf, int d, RouteMeta meta, int E, int precisi
 
 // y[t] (+)= sum over the token's slots in ascending expert order of gate * y_perm[row] (+ shared[t]).
 struct CombineArgs {
-  const void* y_perm;       // [padded rows, d]
+  RowSpace y_perm;          // expert output rows
   const void* shared;       // optional [tokens, d]
   const int* expert_of;     // [tokens*k]
   const float* gates;       // [tokens*k]
@@ -87,10 +88,10 @@ cudaError_t launch_swiglu_bwd_f32(const float* dh, const float* gu, float* dgu, 
 // ----- backward, non-GEMM -----
 struct GatherGradArgs {
   const void* grad_y;     // [tokens, d]
-  const void* y_perm;     // [padded rows, d] pre-gate expert outputs
+  RowSpace y_perm;        // pre-gate expert output rows
   const int* slot_pos;    // [tokens*k]
   const float* gates;     // [tokens*k]
-  void* grad_y_perm;      // [padded rows, d] = gate * grad_y[token]
+  RowSpace grad_y_perm;   // rows receiving gate * grad_y[token]
   float* grad_gates;      // [tokens*k] = <grad_y[token], y_perm[row]>
   int tokens, d, k;
 };
@@ -114,7 +115,7 @@ cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream);
 
 // grad_x[t] (+)= sum over slots (ascending expert) grad_x_perm[row] (+ shared) + grad_logits[t] W_r
 struct UnpermuteArgs {
-  const void* grad_x_perm;   // [padded rows, d]
+  RowSpace grad_x_perm;      // expert input-gradient rows
   const void* shared;        // optional [tokens, d]
   const void* extra;         // optional [tokens, d]: router input gradient computed elsewhere
   const float* grad_logits;  // [tokens, E]; null when `extra` already holds grad_logits W_r

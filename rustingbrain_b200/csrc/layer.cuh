@@ -77,6 +77,13 @@ struct moe_layer {
   int *local_meta = nullptr, *local_meta_host = nullptr;   // row0[El+1], tiles[El+1], counts[El+1]
   std::vector<int> cnt_all, send_off, recv_row;
   void *x_recv = nullptr, *y_recv = nullptr, *dy_recv = nullptr, *dx_recv = nullptr;
+  // peer transport: every rank's four receive buffers mapped into this process (CUDA IPC);
+  // dispatch pushes rows straight into the owner's x_recv / dy_recv and combine / un-permute
+  // pull rows straight from the owner's y_recv / dx_recv over NVLink.
+  void* peer_base[4][moe::MAX_RANKS] = {};   // [x, y, dy, dx][rank]
+  bool peer_ready = false;
+  int *dest_base = nullptr, *dest_base_host = nullptr;   // [E] first row id (rank*cap+row) of my rows per expert
+  int* barrier_word = nullptr;
 
   // host-call staging
   float* host_stage_f32 = nullptr;   // [max_tokens, d]

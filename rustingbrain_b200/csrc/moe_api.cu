@@ -394,10 +394,16 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   CK(launch_router(ra, L->act, st));
   CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, ep ? 1 : GROUP_ALIGN, st)); }
 
+  if (ep) {
+    Span sp(L, 1, st);
+    int rc0 = ep_dispatch(L, st);
+    if (rc0 != MOE_OK) return rc0;
+  }
   PermuteArgs pa{};
   pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
   pa.tokens = tokens; pa.d = L->d; pa.E = L->E; pa.k = L->k;
-  pa.x_perm = L->x_perm; pa.slot_pos = L->slot_pos; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
+  pa.x_perm = ep ? ep_rows(L, 0, L->x_perm) : local_rows(L->x_perm); pa.slot_pos = L->slot_pos;
+  pa.dest_base = (ep && L->peer_ready) ? L->dest_base : nullptr; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
   pa.token_of = L->token_of; pa.slot_of = L->slot_of;
   { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
@@ -421,7 +427,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   }
 
   CombineArgs ca{};
-  ca.y_perm = L->y_perm; ca.shared = L->shared ? L->y_s : nullptr; ca.expert_of = L->expert_of; ca.gates = L->gates;
+  ca.y_perm = ep ? ep_rows(L, 1, L->y_perm) : local_rows(L->y_perm); ca.shared = L->shared ? L->y_s : nullptr; ca.expert_of = L->expert_of; ca.gates = L->gates;
   ca.slot_pos = L->slot_pos; ca.y = y; ca.tokens = tokens; ca.d = L->d; ca.k = L->k; ca.accumulate = accumulate;
   { Span sp(L, 4, st); CK(launch_combine(ca, L->act, st)); }
   CK(cudaGetLastError());
@@ -443,10 +449,10 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   }
 
   GatherGradArgs ga{};
-  ga.grad_y = gy; ga.y_perm = L->y_perm; ga.slot_pos = L->slot_pos; ga.gates = L->gates;
-  ga.grad_y_perm = L->dy_perm; ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
+  ga.grad_y = gy; ga.y_perm = ep ? ep_rows(L, 1, L->y_perm) : local_rows(L->y_perm); ga.slot_pos = L->slot_pos; ga.gates = L->gates;
+  ga.grad_y_perm = ep ? ep_rows(L, 2, L->dy_perm) : local_rows(L->dy_perm); ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
   { Span sp(L, 5, st); CK(launch_gather_grad(ga, L->act, st));
-  CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st)); }
+  if (!ep) CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st)); }
 
   int rc;
   if (ep) {
@@ -495,7 +501,7 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   }
 
   UnpermuteArgs ua{};
-  ua.grad_x_perm = L->dx_perm; ua.shared = L->shared ? L->dx_s : nullptr;
+  ua.grad_x_perm = ep ? ep_rows(L, 3, L->dx_perm) : local_rows(L->dx_perm); ua.shared = L->shared ? L->dx_s : nullptr;
   ua.extra = L->tc_router ? L->dx_r : nullptr; ua.grad_logits = L->tc_router ? nullptr : L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
@@ -610,6 +616,9 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     DA(L->ep_pack, words * 4, true); DA(L->ep_gathered, (long long)N * words * 4, true);
     DA(L->ext_stats, (E + 2) * 4, true); DA(L->ext_counts, E * 4, true);
     DA(L->local_meta, 3 * (El + 1) * 4, true);
+    DA(L->dest_base, E * 4, true); DA(L->barrier_word, 4, true);
+    CK(cudaMallocHost((void**)&L->dest_base_host, (size_t)E * 4));
+    if (L->ep_size > MAX_RANKS) return fail(L, MOE_INVALID_CONFIG, "at most %d expert-parallel ranks", MAX_RANKS);
     CK(cudaMallocHost((void**)&L->ep_gathered_host, (size_t)N * words * 4));
     CK(cudaMallocHost((void**)&L->local_meta_host, (size_t)3 * (El + 1) * 4));
     L->cnt_all.assign((size_t)N * E, 0); L->send_off.assign(E + 1, 0); L->recv_row.assign((size_t)N * El, 0);
@@ -644,6 +653,11 @@ void moe_destroy(moe_layer_t* L) {
   if (L->comm) ncclCommDestroy((ncclComm_t)L->comm);
   if (L->ep_gathered_host) cudaFreeHost(L->ep_gathered_host);
   if (L->local_meta_host) cudaFreeHost(L->local_meta_host);
+  if (L->dest_base_host) cudaFreeHost(L->dest_base_host);
+  if (L->peer_ready)
+    for (int b = 0; b < 4; ++b)
+      for (int r = 0; r < L->ep_size; ++r)
+        if (r != L->ep_rank && L->peer_base[b][r]) cudaIpcCloseMemHandle(L->peer_base[b][r]);
   for (void* p : L->allocations) cudaFree(p);
   for (auto& sp : L->prof_spans) { cudaEventDestroy(sp.begin); cudaEventDestroy(sp.end); }
   for (auto ev : L->prof_pool) cudaEventDestroy(ev);
@@ -926,6 +940,34 @@ int32_t moe_ep_init(moe_layer_t* L, const void* unique_id, int32_t len) {
   NCK(ncclCommInitRank(&comm, L->ep_size, id, L->ep_rank));
   L->comm = comm;
   L->ep_ready = true;
+  return MOE_OK;
+}
+
+int32_t moe_ep_export_buffers(moe_layer_t* L, void* out, int32_t len) {
+  ENTER(L);
+  if (L->ep_size <= 1 || !out || len < (int32_t)(4 * sizeof(cudaIpcMemHandle_t))) { L->err = "InvalidInput: bad export request"; return MOE_INVALID_INPUT; }
+  void* bufs[4] = {L->x_recv, L->y_recv, L->training ? L->dy_recv : L->x_recv, L->training ? L->dx_recv : L->y_recv};
+  cudaIpcMemHandle_t* h = (cudaIpcMemHandle_t*)out;
+  for (int b = 0; b < 4; ++b) CK(cudaIpcGetMemHandle(&h[b], bufs[b]));
+  return MOE_OK;
+}
+
+int32_t moe_ep_import_buffers(moe_layer_t* L, int32_t rank, const void* handles, int32_t len) {
+  ENTER(L);
+  if (L->ep_size <= 1 || rank < 0 || rank >= L->ep_size || !handles || len < (int32_t)(4 * sizeof(cudaIpcMemHandle_t))) { L->err = "InvalidInput: bad import request"; return MOE_INVALID_INPUT; }
+  if (rank == L->ep_rank) {
+    L->peer_base[0][rank] = L->x_recv; L->peer_base[1][rank] = L->y_recv;
+    L->peer_base[2][rank] = L->dy_recv; L->peer_base[3][rank] = L->dx_recv;
+  } else {
+    const cudaIpcMemHandle_t* h = (const cudaIpcMemHandle_t*)handles;
+    for (int b = 0; b < 4; ++b) {
+      if (!L->training && b >= 2) { L->peer_base[b][rank] = nullptr; continue; }
+      CK(cudaIpcOpenMemHandle(&L->peer_base[b][rank], h[b], cudaIpcMemLazyEnablePeerAccess));
+    }
+  }
+  bool all = true;
+  for (int r = 0; r < L->ep_size; ++r) all = all && L->peer_base[0][r] != nullptr;
+  L->peer_ready = all;
   return MOE_OK;
 }
 

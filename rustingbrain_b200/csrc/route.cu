@@ -331,7 +331,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const float* __restrict__ gates,
                const int* __restrict__ cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
-               T* __restrict__ x_perm, int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/,
+               const RowSpace x_perm, const int* __restrict__ dest_base, int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/,
                float* __restrict__ row_gate /*[Rp]*/, int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of) {
   extern __shared__ int pm_smem[];
   int* cnt = pm_smem;        // [E] running cursors
@@ -360,15 +360,20 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       if (e >= 0 && lane == 31 - __clz(peers)) cnt[e] += __popc(peers);
       __syncwarp();
       if (i < nslots) {
-        spos[i] = pos;
-        slot_pos[slot] = pos;
+        int dest = pos;
         if (pos >= 0) {
-          row_token[pos] = slot / k;
-          row_gate[pos] = gates[slot];
           const int cpos = meta.offsets[e] + (pos - meta.pad_off[e]);
           token_of[cpos] = slot / k;
           slot_of[cpos] = slot;
+          if (dest_base) {
+            dest = dest_base[e] + (pos - meta.pad_off[e]);   // a row of the expert's owner
+          } else {
+            row_token[pos] = slot / k;
+            row_gate[pos] = gates[slot];
+          }
         }
+        spos[i] = dest;
+        slot_pos[slot] = dest;
       }
     }
   }
@@ -376,6 +381,7 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
 
   constexpr int VEC = 16 / sizeof(T);
   const bool vec_ok = (d % VEC) == 0;
+  const size_t row_bytes = (size_t)d * sizeof(T);
   for (int r = warp; r < rows; r += blockDim.x / 32) {
     const T* src = x + (size_t)(t0 + r) * d;
     const int* p = spos + r * k;
@@ -384,12 +390,12 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       const uint4* s4 = reinterpret_cast<const uint4*>(src);
       for (int c = lane; c < d / VEC; c += 32) {
         const uint4 v = s4[c];
-        for (int j = 0; j < k; ++j) reinterpret_cast<uint4*>(x_perm + (size_t)p[j] * d)[c] = v;
+        for (int j = 0; j < k; ++j) reinterpret_cast<uint4*>(row_ptr(x_perm, p[j], row_bytes))[c] = v;
       }
     } else {
       for (int c = lane; c < d; c += 32) {
         const T v = src[c];
-        for (int j = 0; j < k; ++j) x_perm[(size_t)p[j] * d + c] = v;
+        for (int j = 0; j < k; ++j) reinterpret_cast<T*>(row_ptr(x_perm, p[j], row_bytes))[c] = v;
       }
     }
   }
@@ -477,19 +483,20 @@ cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t str
   if (nb > 0) {
     if (precision == PREC_BF16) {
       permute_kernel<bf16><<<nb, 256, smem, stream>>>((const bf16*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens,
-                                                      a.d, a.E, a.k, (bf16*)a.x_perm, a.slot_pos, a.row_token,
+                                                      a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token,
                                                       a.row_gate, a.token_of, a.slot_of);
     } else {
       permute_kernel<float><<<nb, 256, smem, stream>>>((const float*)a.x, a.expert_of, a.gates, a.cursor, a.meta,
-                                                       a.tokens, a.d, a.E, a.k, (float*)a.x_perm, a.slot_pos,
+                                                       a.tokens, a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos,
                                                        a.row_token, a.row_gate, a.token_of, a.slot_of);
     }
     count_launch();
   }
+  if (a.dest_base) return cudaGetLastError();   // remote rows: the owners zero their own padding
   if (precision == PREC_BF16) {
-    pad_rows_kernel<bf16><<<a.E, 256, 0, stream>>>((bf16*)a.x_perm, a.d, a.meta, a.row_token, a.row_gate);
+    pad_rows_kernel<bf16><<<a.E, 256, 0, stream>>>((bf16*)a.x_perm.base[0], a.d, a.meta, a.row_token, a.row_gate);
   } else {
-    pad_rows_kernel<float><<<a.E, 256, 0, stream>>>((float*)a.x_perm, a.d, a.meta, a.row_token, a.row_gate);
+    pad_rows_kernel<float><<<a.E, 256, 0, stream>>>((float*)a.x_perm.base[0], a.d, a.meta, a.row_token, a.row_gate);
   }
   count_launch();
   return cudaGetLastError();

@@ -53,7 +53,7 @@ class ExpertParallelMoe(MoeLayer):
     """
 
     def __init__(self, d_model: int, config: MoeConfig, *, precision: str = "bf16", max_tokens: int = 4096,
-                 device: int = 0, training: bool = True, capacity_factor: float = 0.0):
+                 device: int = 0, training: bool = True, capacity_factor: float = 0.0, transport: str = "peer"):
         import torch
         import torch.distributed as dist
         if not dist.is_initialized():
@@ -70,6 +70,18 @@ class ExpertParallelMoe(MoeLayer):
         dist.broadcast(t, 0)
         raw = bytes(t.cpu().tolist())
         self._ck(_lib.lib().moe_ep_init(self._h, raw, n))
+        self.transport = transport
+        if transport == "peer":
+            # map every rank's receive buffers into this process (CUDA IPC); rows then move by
+            # direct stores / loads over NVLink inside the dispatch and combine kernels
+            hb = (C.c_uint8 * 256)()
+            self._ck(_lib.lib().moe_ep_export_buffers(self._h, hb, 256))
+            all_handles = [None] * self.world
+            dist.all_gather_object(all_handles, bytes(hb))
+            for r, h in enumerate(all_handles):
+                self._ck(_lib.lib().moe_ep_import_buffers(self._h, r, h, 256))
+        elif transport != "nccl":
+            raise ValueError("transport must be 'peer' or 'nccl'")
 
     def owned_experts(self):
         el = self.config.num_experts // self.world

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _worker(rank, world, port, precision, ret):
+def _worker(rank, world, port, precision, transport, ret):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
@@ -32,7 +32,7 @@ def _worker(rank, world, port, precision, ret):
             rb = lambda a: torch.from_numpy(a).bfloat16().float().numpy()
             w = dict(w, gate=rb(w["gate"]), up=rb(w["up"]), down=rb(w["down"]), shared=tuple(rb(s) for s in w["shared"]))
         layer = ExpertParallelMoe(d, MoeConfig(E, k, F, True), precision=precision, max_tokens=max(Ts), device=rank,
-                                  capacity_factor=2.0)
+                                  capacity_factor=2.0, transport=transport)
         layer.set_weight(ROUTER, 0, w["router"])
         for e in layer.owned_experts():
             layer.set_weight(GATE, e, w["gate"][e]); layer.set_weight(UP, e, w["up"][e]); layer.set_weight(DOWN, e, w["down"][e])
@@ -75,8 +75,8 @@ def _worker(rank, world, port, precision, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("precision", ["f32", "bf16"])
-def test_expert_parallel_matches_single_device(precision):
+@pytest.mark.parametrize("precision,transport", [("f32", "nccl"), ("bf16", "nccl"), ("f32", "peer"), ("bf16", "peer")])
+def test_expert_parallel_matches_single_device(precision, transport):
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
@@ -85,5 +85,5 @@ def test_expert_parallel_matches_single_device(precision):
     port = 29700 + (os.getpid() % 2000)
     with mp.Manager() as mgr:
         ret = mgr.dict()
-        mp.spawn(_worker, args=(world, port, precision, ret), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, port, precision, transport, ret), nprocs=world, join=True)
         assert dict(ret) == {r: True for r in range(world)}
