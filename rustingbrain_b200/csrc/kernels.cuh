@@ -137,6 +137,24 @@ struct RouterWgradArgs {
 };
 cudaError_t launch_router_wgrad(const RouterWgradArgs& a, int precision, cudaStream_t stream);
 
+// ----- int8 expert weights for decode-sized batches (decode_q8.cu) -----
+// out[row, n] = (sum_k x[row,k] * q_g[n,k]) * scale_g[n], rows of group g < E taken from the
+// padded expert-major buffers, group E (optional) = the shared expert over every token row.
+// swiglu: q holds the interleaved gate|up rows [2N, K]; out = silu(gate) * up, N hidden columns.
+struct Q8Args {
+  const bf16* x_rows;      // [padded rows, K]
+  const bf16* x_shared;    // optional [tokens, K]
+  bf16* out_rows;          // [padded rows, ldo]
+  bf16* out_shared;        // [tokens, ldo]
+  const int8_t* w;         // [groups][rows][K]
+  const float* scale;      // [groups][rows]
+  const int* counts;       // [E]
+  const int* pad_off;      // [E+1]
+  long long w_group_stride, s_group_stride;
+  int E, tokens, K, N, ldo;
+};
+cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream);
+
 // ----- optimizer and casts -----
 struct AdamArgs {
   float* w; float* g; float* m; float* v;

@@ -95,6 +95,8 @@ int validate(const moe_config_t* c, char* msg, int len) {
     return say("the bf16 and int8 paths need d_model to be a multiple of 32 (got %d); use MOE_PRECISION_F32",
                c->d_model);
   if (c->precision == MOE_PRECISION_Q8 && c->training) return say("a quantized layer cannot be trained");
+  if (c->precision == MOE_PRECISION_Q8 && c->d_model % 64 != 0) return say("the int8 path needs d_model to be a multiple of 64");
+  if (c->precision == MOE_PRECISION_Q8 && c->ep_size != 1) return say("the int8 path is single-device");
   if ((long long)c->max_tokens * c->experts_per_token > (1ll << 30)) return say("max_tokens * experts_per_token too large");
   return MOE_OK;
 }
@@ -106,7 +108,7 @@ struct Sizes {
 
 Sizes sizes_of(const moe_config_t* c) {
   Sizes s;
-  s.F_pad = round_up(c->d_ff, GU_BLOCK);
+  s.F_pad = round_up(c->d_ff, c->precision == MOE_PRECISION_Q8 ? 2 * GU_BLOCK : GU_BLOCK);
   s.E_local = c->num_experts / c->ep_size;
   s.rows_cap = round_up(c->max_tokens * c->experts_per_token + c->num_experts * (GROUP_ALIGN - 1), GROUP_ALIGN);
   s.shared_rows_cap = round_up(c->max_tokens, GROUP_ALIGN);
@@ -364,7 +366,6 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     return MOE_INVALID_INPUT;
   }
   if (tokens > 0 && (!x || !y)) { L->err = "InvalidInput: null activation pointer"; return MOE_INVALID_INPUT; }
-  if (L->precision == MOE_PRECISION_Q8) return fail(L, MOE_UNSUPPORTED, "the int8 decode path is not built into this library version");
   if (save && !L->training) { L->err = "InvalidConfig: save_for_backward needs a handle created with training = 1"; return MOE_INVALID_CONFIG; }
   const bool ep = L->ep_size > 1;
   if (ep && !L->ep_ready) { L->err = "InvalidConfig: expert-parallel handle without a communicator (call moe_ep_init)"; return MOE_INVALID_CONFIG; }
@@ -408,7 +409,26 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
   int rc;
-  if (ep) {
+  if (L->precision == MOE_PRECISION_Q8) {
+    // decode: stream each active expert's int8 rows once; the shared expert rides along as group E
+    Span sp(L, 2, st);
+    const int d = L->d, Fp = L->F_pad;
+    Q8Args qa{};
+    qa.x_rows = (const bf16*)L->x_perm; qa.x_shared = L->shared ? (const bf16*)x : nullptr;
+    qa.out_rows = (bf16*)L->h; qa.out_shared = (bf16*)L->h_s;
+    qa.w = L->q_gu; qa.scale = L->s_gu; qa.counts = L->meta.counts; qa.pad_off = L->meta.pad_off;
+    qa.w_group_stride = 2ll * Fp * d; qa.s_group_stride = 2ll * Fp;
+    qa.E = L->E; qa.tokens = tokens; qa.K = d; qa.N = Fp; qa.ldo = Fp;
+    CK(launch_q8_rows(qa, true, st));
+    Q8Args qb{};
+    qb.x_rows = (const bf16*)L->h; qb.x_shared = L->shared ? (const bf16*)L->h_s : nullptr;
+    qb.out_rows = (bf16*)L->y_perm; qb.out_shared = (bf16*)L->y_s;
+    qb.w = L->q_d; qb.scale = L->s_d; qb.counts = L->meta.counts; qb.pad_off = L->meta.pad_off;
+    qb.w_group_stride = (long long)d * Fp; qb.s_group_stride = d;
+    qb.E = L->E; qb.tokens = tokens; qb.K = Fp; qb.N = d; qb.ldo = d;
+    CK(launch_q8_rows(qb, false, st));
+    rc = MOE_OK;
+  } else if (ep) {
     rc = ep_forward_experts(L, save != 0, st);
   } else {
     Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
@@ -418,7 +438,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   }
   if (rc != MOE_OK) return rc;
 
-  if (L->shared && tokens > 0) {
+  if (L->shared && tokens > 0 && L->precision != MOE_PRECISION_Q8) {
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
     ExpertIO sio{};
     sio.x = x; sio.gu = L->gu_s; sio.h = L->h_s; sio.y = L->y_s; sio.w_gu = L->off_sgu; sio.w_d = L->off_sd;
@@ -582,6 +602,9 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   L->tc_router = L->precision == MOE_PRECISION_BF16 && L->E % 8 == 0;
   if (L->precision == MOE_PRECISION_Q8) {
     DA(L->w, (long long)E * d * 4, true);   // router only
+    const long long G = E + 1;   // the shared expert is stored as group E
+    DA(L->q_gu, G * 2 * Fp * d, true); DA(L->s_gu, G * 2 * Fp * 4, true);
+    DA(L->q_d, G * d * Fp, true); DA(L->s_d, G * d * 4, true);
   } else {
     DA(L->w, L->n_params * 4, true);
     if (L->training) {
@@ -749,10 +772,35 @@ int32_t moe_set_moments_f32(moe_layer_t* L, int32_t which, int32_t expert, const
   return MOE_OK;
 }
 
-int32_t moe_set_weight_q8(moe_layer_t* L, int32_t, int32_t, const int8_t*, const float*, int32_t, int32_t) {
+int32_t moe_set_weight_q8(moe_layer_t* L, int32_t which, int32_t expert, const int8_t* q, const float* scale, int32_t rows, int32_t cols) {
   ENTER(L);
-  L->err = "Unsupported: the int8 decode path is not built into this library version";
-  return MOE_UNSUPPORTED;
+  if (L->precision != MOE_PRECISION_Q8) { L->err = "InvalidConfig: int8 weights need a MOE_PRECISION_Q8 handle"; return MOE_INVALID_CONFIG; }
+  if (!q || !scale) { L->err = "InvalidInput: null weight pointer"; return MOE_INVALID_INPUT; }
+  const int d = L->d, F = L->F, Fp = L->F_pad;
+  int group = expert, kind = 0, ld = d;
+  bool down = false;
+  switch (which) {
+    case MOE_W_GATE: kind = 1; break;
+    case MOE_W_UP: kind = 2; break;
+    case MOE_W_DOWN: down = true; ld = Fp; break;
+    case MOE_W_SHARED_GATE: kind = 1; group = L->E; break;
+    case MOE_W_SHARED_UP: kind = 2; group = L->E; break;
+    case MOE_W_SHARED_DOWN: down = true; ld = Fp; group = L->E; break;
+    default: L->err = "InvalidInput: the router of a quantized layer stays f32 (moe_set_weight_f32)"; return MOE_INVALID_INPUT;
+  }
+  if (group < 0 || group > L->E || (group == L->E && !L->shared)) { L->err = "InvalidInput: no such expert"; return MOE_INVALID_INPUT; }
+  if ((!down && (rows != F || cols != d)) || (down && (rows != d || cols != F))) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  const long long n = (long long)rows * cols;
+  int8_t* qs = reinterpret_cast<int8_t*>(L->stage);
+  float* ss = L->stage + L->stage_elems;   // second half of the staging buffer
+  CK(cudaMemcpy(qs, q, (size_t)n, is_device_pointer(q) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(ss, scale, (size_t)rows * 4, is_device_pointer(scale) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+  int8_t* dst = down ? L->q_d + (long long)group * d * Fp : L->q_gu + (long long)group * 2 * Fp * d;
+  float* sdst = down ? L->s_d + (long long)group * d : L->s_gu + (long long)group * 2 * Fp;
+  pack_q8_kernel<<<(unsigned)((n + 255) / 256), 256>>>(qs, ss, dst, sdst, rows, cols, ld, kind);
+  CK(cudaGetLastError());
+  CK(cudaDeviceSynchronize());
+  return MOE_OK;
 }
 
 int32_t moe_forward(moe_layer_t* L, const void* x, int32_t tokens, int32_t cols, const uint8_t* valid, void* y,

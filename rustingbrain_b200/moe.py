@@ -222,6 +222,16 @@ class MoeLayer:
             ptr = w.ctypes.data
         self._ck(_lib.lib().moe_set_weight_f32(self._h, which, expert, ptr, rows, cols))
 
+    def set_weight_q8(self, which: int, expert: int, q, scales):
+        """Uploads one int8 projection: values ``[out, in]`` and one f32 scale per output row
+        (``Quantized``, quantized.rs:17-24).  Only for ``precision="q8"`` layers."""
+        rows, cols = self._shape(which)
+        q = np.ascontiguousarray(q, dtype=np.int8)
+        scales = np.ascontiguousarray(scales, dtype=np.float32)
+        if q.shape != (rows, cols) or scales.shape != (rows,):
+            raise InvalidInput("int8 weight shape %s / %s, expected %s" % (q.shape, scales.shape, (rows, cols)))
+        self._ck(_lib.lib().moe_set_weight_q8(self._h, which, expert, q.ctypes.data, scales.ctypes.data, rows, cols))
+
     def set_weights(self, router, gate, up, down, shared=None):
         """router [E,d]; gate/up [E,F,d]; down [E,d,F]; shared = (gate, up, down) of one expert."""
         self.set_weight(W_ROUTER, 0, router)

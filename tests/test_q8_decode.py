@@ -1,0 +1,53 @@
+"""int8 expert weights on the decode path against the checker's Quantized restatement."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+from helpers import rel_l2
+from oracle import OracleMoe, ROUTER, GATE, UP, DOWN, SHARED_GATE, SHARED_UP, SHARED_DOWN
+from rustingbrain_b200 import MoeConfig, MoeLayer, InvalidConfig
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(T, d, E, k, F, shared, seed):
+    g = np.random.Generator(np.random.Philox(seed))
+    dev = MoeLayer(d, MoeConfig(E, k, F, shared), precision="q8", max_tokens=T, training=False)
+    ora = OracleMoe(d, E, k, F, shared)
+    router = (g.standard_normal((E, d)) * 0.05).astype(np.float32)
+    dev.set_weight(ROUTER, 0, router)
+    ora.set_weight(ROUTER, 0, router)
+
+    def put(which, expert, rows, cols):
+        q = g.integers(-127, 128, (rows, cols)).astype(np.int8)      # BASELINE config 5: uniform in [-127, 127]
+        s = g.uniform(1e-3, 4e-3, rows).astype(np.float32)           # scales uniform in [1e-3, 4e-3]
+        dev.set_weight_q8(which, expert, q, s)
+        ora.set_weight_q8(which, expert, q, s)
+
+    for e in range(E):
+        put(GATE, e, F, d); put(UP, e, F, d); put(DOWN, e, d, F)
+    if shared:
+        put(SHARED_GATE, 0, F, d); put(SHARED_UP, 0, F, d); put(SHARED_DOWN, 0, d, F)
+    x = g.standard_normal((T, d)).astype(np.float32)
+    return dev, ora, x
+
+
+@pytest.mark.parametrize("T,d,E,k,F,shared", [(64, 1024, 16, 2, 2816, True),   # BASELINE config 5
+                                              (200, 128, 4, 2, 96, True),      # many rows per expert, padded d_ff
+                                              (5, 64, 8, 1, 64, False)])       # most experts empty
+def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
+    dev, ora, x = _pair(T, d, E, k, F, shared, seed=9)
+    xd = torch.from_numpy(x).cuda().bfloat16()
+    y, cache = dev.forward_train(xd)
+    logits = dev.router_cache(T)[0]
+    yo = ora.forward(xd.float().cpu().numpy(), logits=logits)
+    assert np.array_equal(cache.routing()[0], ora.routing()[0])
+    assert np.array_equal(cache.routing()[2], ora.routing()[2])
+    assert rel_l2(y.float().cpu().numpy(), yo) <= 2e-2
+    y2 = dev.forward(xd)
+    assert torch.equal(y, y2)
+
+
+def test_a_quantized_layer_refuses_to_train():  # transformer.rs:2202-2280: quantizing is one-way
+    with pytest.raises(InvalidConfig):
+        MoeLayer(64, MoeConfig(4, 2, 64), precision="q8", max_tokens=8, training=True)
