@@ -36,6 +36,9 @@ struct moe_layer;
 int32_t moe_debug_profile(struct moe_layer* layer, int32_t enable);
 int32_t moe_debug_profile_read(struct moe_layer* layer, float* milliseconds, int32_t* stages);
 
+/* Selects the two-SM (cta_group::2) variant of the grouped tensor-core GEMM for later launches. */
+int32_t moe_debug_set_tc_pair(int32_t on);
+
 /* Number of kernel launches issued by this library in the calling process. */
 int64_t moe_debug_launch_count(void);
 

@@ -31,6 +31,11 @@ int32_t moe_debug_tc_gemm(int32_t variant, const void* a, const void* b, void* o
   return e == cudaSuccess ? 0 : 3;
 }
 
+int32_t moe_debug_set_tc_pair(int32_t on) {
+  tc::set_pair_mode(on);
+  return 0;
+}
+
 int64_t moe_debug_launch_count(void) { return moe::g_launch_count; }
 
 }  // extern "C"

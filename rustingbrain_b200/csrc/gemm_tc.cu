@@ -22,6 +22,7 @@
 #include "gemm_tc.cuh"
 
 #include <stdio.h>
+#include <stdlib.h>
 
 namespace moe {
 namespace tc {
@@ -508,6 +509,301 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Two-SM variant: a cluster of two CTAs computes one 256x256 tile with
+// tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows of A and HALF of the B tile
+// (128 of the 256 columns); the tensor cores of both SMs read both halves.  Per SM and
+// K-stage that is 32 KiB of shared memory instead of 48, so the ring holds 6 stages
+// instead of 4 (longer latency cover for the same 192 KiB) and the L2 -> SM traffic per
+// FLOP drops by a third.  CTA 0 of the pair issues the MMAs; both run their epilogue on
+// their own 128 TMEM lanes.  No load is multicast: every CTA fetches what it stores.
+//
+//   full[s]      (leader's)  one arrive.expect_tx by the leader for BOTH CTAs' bytes; the
+//                            peer's TMA completes its bytes on the leader's barrier
+//   empty[s]     (each CTA)  one tcgen05.commit per CTA after the stage's MMAs
+//   tmem_full[a] (each CTA)  one tcgen05.commit per CTA after the tile's last MMA
+//   tmem_empty[a](leader's)  one arrival per epilogue warp of both CTAs
+// ---------------------------------------------------------------------------
+constexpr int P_STAGES = 6;
+constexpr int P_B_BYTES = (BN / 2) * BK * 2;            // 16 KiB: this CTA's half of B
+constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;      // 32 KiB
+
+struct __align__(8) PairTail {
+  unsigned long long full[P_STAGES];
+  unsigned long long empty[P_STAGES];
+  unsigned long long tmem_full[2];
+  unsigned long long tmem_empty[2];
+  uint32_t tmem_base;
+  int dead;
+  int row0[MAX_GROUPS + 1];
+  int pstart[MAX_GROUPS + 1];   // exclusive prefix of ceil(m-tiles / 2) per group
+  int mtiles[MAX_GROUPS + 1];
+};
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + (int)sizeof(PairTail);
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of the same shared-memory object in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_pair_2d(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_pair_3d(uint32_t dst, const CUtensorMap* map, uint32_t leader_bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B with M = 256 (128 rows per CTA), K = 16.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc_pair(bool a_mn, bool b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+}
+
+struct PairTile {
+  int group, row0, m0, n0, k_iters, skip;   // skip: this CTA repeats a neighbour's rows and stores nothing
+};
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ int pair_total(const PairTail* st, const GemmArgs& p) {
+  const int nt = ceil_div(p.N, BN);
+  if (ROWS_ARE_K) return p.n_groups * ceil_div(ceil_div(p.M, BM), 2) * nt;
+  return st->pstart[p.n_groups] * nt;
+}
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ PairTile pair_decode(const PairTail* st, const GemmArgs& p, int t, int rank) {
+  PairTile tl;
+  const int nt = ceil_div(p.N, BN);
+  tl.skip = 0;
+  if (ROWS_ARE_K) {
+    const int pt = ceil_div(ceil_div(p.M, BM), 2);
+    const int g = t / (pt * nt);
+    const int rem = t - g * pt * nt;
+    tl.group = g;
+    tl.n0 = (rem / pt) * BN;
+    tl.m0 = ((rem % pt) * 2 + rank) * BM;     // rows past M load zeros and are masked on store
+    tl.row0 = st->row0[g];
+    tl.k_iters = (st->row0[g + 1] - st->row0[g]) / BK;
+  } else {
+    int lo = 0, hi = p.n_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (st->pstart[mid] * nt <= t) lo = mid; else hi = mid;
+    }
+    const int g = lo;
+    const int pt = st->pstart[g + 1] - st->pstart[g];
+    const int local = t - st->pstart[g] * nt;
+    int mtile = (local % pt) * 2 + rank;
+    if (mtile >= st->mtiles[g]) { mtile = st->mtiles[g] - 1; tl.skip = 1; }
+    tl.group = g;
+    tl.n0 = (local / pt) * BN;
+    tl.m0 = 0;
+    tl.row0 = st->row0[g] + mtile * BM;
+    tl.k_iters = ceil_div(p.K, BK);
+  }
+  return tl;
+}
+
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  PairTail* st = reinterpret_cast<PairTail*>(smem_raw + (tiles_base - raw) + P_STAGES * P_STAGE_BYTES);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0 = leader (issues the MMAs)
+  const int cluster_id = blockIdx.x >> 1;
+  const int n_clusters = gridDim.x >> 1;
+
+  for (int i = threadIdx.x; i <= p.n_groups; i += NUM_THREADS) st->row0[i] = p.group_row0[i];
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int g = 0; g < p.n_groups; ++g) {
+      const int mt = ROWS_ARE_K ? 0 : p.tile_start[g + 1] - p.tile_start[g];
+      st->mtiles[g] = mt;
+      st->pstart[g] = run;
+      run += (mt + 1) >> 1;
+    }
+    st->pstart[p.n_groups] = run;
+    for (int s = 0; s < P_STAGES; ++s) {
+      mbar_init(smem_u32(&st->full[s]), 1);
+      mbar_init(smem_u32(&st->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&st->tmem_full[a]), 1);
+      mbar_init(smem_u32(&st->tmem_empty[a]), 2 * EPI_WARPS);
+    }
+    st->dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(&st->tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers exist before anything is signalled across the pair
+  tc_fence_after();
+  const uint32_t tmem_base = st->tmem_base;
+  const int n_tiles = pair_total<ROWS_ARE_K>(st, p);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer (both CTAs) ------------------------------
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+        const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, (int)rank);
+        // this CTA's half of the B tile; a narrower last column tile is split in the middle
+        const int n_live = min(BN, ((p.N - tl.n0) + 31) & ~31);
+        const int nb0 = tl.n0 + (int)rank * (n_live / 2);
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 201)) { ok = false; break; }
+          const uint32_t leader_bar = map_to_cta(smem_u32(&st->full[stage]), 0);
+          const uint32_t sa = tiles_base + stage * P_STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          if (rank == 0) mbar_expect_tx(smem_u32(&st->full[stage]), 2 * P_STAGE_BYTES);
+          if (ROWS_ARE_K) {
+            const int krow = tl.row0 + ki * BK;
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_pair_2d(sa + j * BOX_BYTES, &map_a, leader_bar, tl.m0 + 64 * j, krow);
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) tma_pair_2d(sb + j * BOX_BYTES, &map_b, leader_bar, nb0 + 64 * j, krow);
+          } else {
+            tma_pair_2d(sa, &map_a, leader_bar, ki * BK, tl.row0);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                tma_pair_3d(sb + j * BOX_BYTES, &map_b, leader_bar, nb0 + 64 * j, ki * BK, tl.group);
+            } else {
+              tma_pair_3d(sb, &map_b, leader_bar, ki * BK, nb0, tl.group);
+            }
+          }
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) st->dead = 1;
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ------------------------------ MMA issuer (leader CTA only) ------------------------------
+      constexpr uint32_t a_lbo = A_MN ? BOX_BYTES : 16, a_sbo = 1024, a_adv = A_MN ? 2048 : 32;
+      constexpr uint32_t b_lbo = B_MN ? BOX_BYTES : 16, b_sbo = 1024, b_adv = B_MN ? 2048 : 32;
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+        const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, 0);
+        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 202)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        const int n_live = min(BN, ((p.N - tl.n0) + 31) & ~31);
+        const uint32_t idesc = make_idesc_pair(A_MN, B_MN, n_live);
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 203)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = tiles_base + stage * P_STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = make_desc(sa + kk * a_adv, a_lbo, a_sbo);
+            const uint64_t db = make_desc(sb + kk * b_adv, b_lbo, b_sbo);
+            umma_bf16_pair(d_tmem, da, db, idesc, (ki | kk) != 0 ? 1u : 0u);
+          }
+          // the stage is free in BOTH CTAs once these MMAs have read it
+          umma_commit_pair(smem_u32(&st->empty[stage]));
+          umma_commit_pair(map_to_cta(smem_u32(&st->empty[stage]), 1));
+          if (++stage == P_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (tl.k_iters > 0) {
+          umma_commit_pair(smem_u32(&st->tmem_full[acc]));
+          umma_commit_pair(map_to_cta(smem_u32(&st->tmem_full[acc]), 1));
+        } else {
+          mbar_arrive(smem_u32(&st->tmem_full[acc]));
+          mbar_arrive_cluster(map_to_cta(smem_u32(&st->tmem_full[acc]), 1));
+        }
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) st->dead = 1;
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------- epilogue (both CTAs) ----------------------------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    const int c_begin = half * (BN / 2), c_end = c_begin + BN / 2;
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+      const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, (int)rank);
+      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 204)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
+      if (!tl.skip) {
+        Tile one;
+        one.group = tl.group; one.row0 = tl.row0; one.m0 = tl.m0; one.n0 = tl.n0; one.k_iters = tl.k_iters;
+        epilogue_tile<EPI>(p, one, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&st->tmem_empty[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  __syncthreads();
+  if (st->dead || *(volatile int*)p.error_flag != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) __nanosleep(1000);
+    __syncthreads();
+  }
+  cluster_sync_all();   // neither CTA leaves while its partner may still signal or read it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Host side: tensor maps and launches
 // ---------------------------------------------------------------------------
@@ -545,9 +841,45 @@ static bool operand_ok(const Operand& op) {
   return op.ptr && ((uintptr_t)op.ptr & 15) == 0 && op.cols > 0 && (op.cols % 8) == 0 && op.rows > 0 && op.groups > 0;
 }
 
+static int g_pair_mode = -1;   // -1: read MOE_B200_TC_PAIR from the environment on first use
+void set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
+bool pair_mode() {
+  if (g_pair_mode < 0) {
+    const char* e = getenv("MOE_B200_TC_PAIR");
+    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+  }
+  return g_pair_mode == 1;
+}
+
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+static cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
+                               cudaStream_t stream) {
+  auto kern = grouped_gemm_pair_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)(sm_count & ~1));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = P_SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, ma, mb, args);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
 static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
                           cudaStream_t stream) {
+  if (pair_mode()) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
   auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
   static bool configured = false;
   if (!configured) {
@@ -565,7 +897,7 @@ cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& arg
       args.n_groups > MAX_GROUPS - 1)
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
-  if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, BN, true)) return cudaErrorInvalidValue;
+  if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, pair_mode() ? BN / 2 : BN, true)) return cudaErrorInvalidValue;
   switch (epilogue) {
     case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, sm_count, stream);
     case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, sm_count, stream);

@@ -43,6 +43,10 @@ struct Operand {
   long long groups;    // 1 for row-indexed operands
 };
 
+// Two-SM tiles (cta_group::2, clusters of two CTAs) instead of one-SM tiles; also MOE_B200_TC_PAIR=1.
+void set_pair_mode(int on);
+bool pair_mode();
+
 // y[rows, N] = A[rows, K] * B_g[N, K]^T            (forward projections)
 cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,
                          cudaStream_t stream);

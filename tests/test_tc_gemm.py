@@ -10,6 +10,14 @@ from rustingbrain_b200 import _lib
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[0, 1], ids=["one_sm", "two_sm"], autouse=True)
+def tc_variant(request):
+    """Every case runs on the one-SM tiles and on the two-SM (cta_group::2) tiles."""
+    _lib.lib().moe_debug_set_tc_pair(request.param)
+    yield request.param
+    _lib.lib().moe_debug_set_tc_pair(0)
+
+
 def _groups(rows_per_group):
     row0 = np.concatenate([[0], np.cumsum(rows_per_group)]).astype(np.int32)
     assert np.all(row0 % 128 == 0)
