@@ -177,6 +177,29 @@ int32_t moe_ep_import_buffers(moe_layer_t* layer, int32_t rank, const void* hand
 int32_t moe_ep_plan(const int32_t* counts_all, int32_t ranks, int32_t num_experts, int32_t rank, int32_t* send_off,
                     int32_t* recv_row, int32_t* local_row0, int32_t* local_tiles, int32_t* local_counts);
 
+/* Routing without allocation.  This entry has no counterpart in the reference; it exists for
+ * callers that may not let a library allocate device memory: a runtime that gave the whole device
+ * to its own arena and works under a fixed budget, or a serving loop that cannot afford the
+ * device-wide synchronisation a cudaMalloc implies.  It performs the routing step only, from given
+ * router logits: softmax + log-sum-exp, dropless top-k with renormalised gates, per-expert counts,
+ * and the weighted load-balancing and z losses (same results as moe_forward_from_logits followed by
+ * moe_get_routing / moe_get_losses).  Every input and output is a caller-owned device buffer:
+ *   logits [tokens, E] f32, valid optional [tokens] bytes;
+ *   probabilities [tokens, E], log_sum_exp [tokens], expert_of / gates [tokens*k], counts [E], losses [2].
+ * The scratch between its two kernels is a static array inside the library image (about 134 KB on
+ * every GPU that loads the library, until the process exits), hence the limits below; a larger
+ * problem is rejected with MOE_INVALID_INPUT.  It calls no allocation routine.  The first call on a
+ * device looks up the array's device address (cudaGetSymbolAddress); make that call before any
+ * stream capture begins.  All calls on one device share the array: two calls that overlap on the GPU
+ * (different streams, no dependency) race on it.  Nothing in it has to be cleared between calls,
+ * because each call writes every word it later reads.  `message` (optional) receives the error text. */
+#define MOE_ROUTE_NOALLOC_MAX_TOKENS 16384
+#define MOE_ROUTE_NOALLOC_MAX_EXPERTS 64
+int32_t moe_route_noalloc(const float* logits_dev, const uint8_t* valid_dev, int32_t tokens, int32_t num_experts,
+                          int32_t experts_per_token, float aux_loss_weight, float router_z_loss_weight,
+                          float* probabilities_dev, float* log_sum_exp_dev, int32_t* expert_of_dev, float* gates_dev,
+                          int32_t* counts_dev, float* losses_dev, void* stream, char* message, int32_t message_len);
+
 /* Device synchronisation for timing (TransformerLm::synchronize, transformer.rs:1323-1334). */
 int32_t moe_synchronize(moe_layer_t* layer);
 

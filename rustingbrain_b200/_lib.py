@@ -63,6 +63,7 @@ def lib() -> C.CDLL:
         "moe_get_routing": (i32, [vp, ip, fp, ip, ip, ip, ip]),
         "moe_get_router_cache": (i32, [vp, fp, fp, fp]),
         "moe_synchronize": (i32, [vp]),
+        "moe_route_noalloc": (i32, [vp, vp, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, C.c_char_p, i32]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),
         "moe_ep_export_buffers": (i32, [vp, vp, i32]),
@@ -70,6 +71,7 @@ def lib() -> C.CDLL:
         "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
+        "moe_debug_set_tc_pair": (i32, [i32]),
         "moe_debug_profile": (i32, [vp, i32]),
         "moe_debug_profile_read": (i32, [vp, fp, ip]),
     }
