@@ -27,7 +27,13 @@
 namespace moe {
 namespace tc {
 
-constexpr int STAGES = 4;
+#ifndef TC_STAGES
+#define TC_STAGES 4
+#endif
+#ifndef TC_PAIR_STAGES
+#define TC_PAIR_STAGES 6
+#endif
+constexpr int STAGES = TC_STAGES;
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;           // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;           // 32 KiB
@@ -260,6 +266,9 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl, uint32_t taddr, int row_in_tile,
                                               int c_begin, int c_end,
                                               bool have_acc) {
+#ifdef TC_EXP_NOEPI
+  return;
+#endif
   if (EPI == EPI_STORE) {
     const long long row = (long long)tl.row0 + row_in_tile;
     bf16* out = (bf16*)p.out0 + row * p.ld0;
@@ -404,6 +413,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
+#ifdef TC_EXP_NOLOAD
+          break;
+#endif
           if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101)) { ok = false; break; }
           const uint32_t bar = smem_u32(&st->full[stage]);
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -451,10 +463,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
         const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
+#ifndef TC_EXP_NOLOAD
           if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103)) { ok = false; break; }
+#endif
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
+#ifndef TC_EXP_NOMMA
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = make_desc(sa + kk * a_adv, a_lbo, a_sbo);
@@ -462,11 +477,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             umma_bf16(d_tmem, da, db, idesc, (ki | kk) != 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&st->empty[stage]));   // frees the stage once these MMAs have read it
+#else
+          mbar_arrive(smem_u32(&st->empty[stage]));
+#endif
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
+#ifdef TC_EXP_NOMMA
+        mbar_arrive(smem_u32(&st->tmem_full[acc]));
+#else
         if (tl.k_iters > 0) umma_commit(smem_u32(&st->tmem_full[acc]));
         else mbar_arrive(smem_u32(&st->tmem_full[acc]));   // empty group: nothing was accumulated
+#endif
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) st->dead = 1;
@@ -525,7 +547,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //   tmem_full[a] (each CTA)  one tcgen05.commit per CTA after the tile's last MMA
 //   tmem_empty[a](leader's)  one arrival per epilogue warp of both CTAs
 // ---------------------------------------------------------------------------
-constexpr int P_STAGES = 6;
+constexpr int P_STAGES = TC_PAIR_STAGES;
 constexpr int P_B_BYTES = (BN / 2) * BK * 2;            // 16 KiB: this CTA's half of B
 constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;      // 32 KiB
 
