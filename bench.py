@@ -33,6 +33,9 @@ WORKLOADS = {
     # reduced copy of cfg3's shapes (same tile shapes, a quarter of the rows and experts) for ncu captures
     "prof": dict(T=8192, d=2048, E=16, k=4, F=1408, shared=True, seed=123, precision="bf16", zipf=False,
                  name="profiling case: 8192 tokens, d_model 2048, 16 experts top-4 + shared, d_ff 1408"),
+    # cfg3's token rows (16384 x top-8, d 2048) with few narrow experts: same dispatch/combine traffic, ~3 GB on the device
+    "hbm": dict(T=16384, d=2048, E=8, k=8, F=256, shared=False, seed=123, precision="bf16", zipf=False,
+                name="HBM-kernel profiling case: 16384 tokens, d_model 2048, 8 experts top-8, d_ff 256"),
     "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
                  name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
 }
@@ -313,8 +316,8 @@ def main():
                 "flops_per_step": gemm_flops / args.steps, "peak_source": pk["src"] + " sustained bf16",
                 "frac_of_nominal_2250": ach / 2250.0 if ach else None}
     hbm = {}
-    alg_bytes = {"permute": 2.0 * R * w["d"] * es, "combine": (R + w["T"] * (2 if w["shared"] else 1)) * w["d"] * es,
-                 "grad_gather": (w["T"] + 2.0 * R) * w["d"] * es, "unpermute": (R + w["T"]) * w["d"] * es,
+    alg_bytes = {"permute": (w["T"] + 1.0 * R) * w["d"] * es, "combine": (R + w["T"] * (2 if w["shared"] else 1)) * w["d"] * es,
+                 "grad_gather": (w["T"] + 2.0 * R) * w["d"] * es, "unpermute": (R + w["T"] * (3 if w["shared"] else 2)) * w["d"] * es,
                  "router": w["T"] * w["d"] * es + w["T"] * w["k"] * 8}
     for name, b in alg_bytes.items():
         t, n = prof[name]

@@ -56,6 +56,14 @@ template <> __device__ inline void Vec16<bf16>::store(bf16* p, const float* v) {
   *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Four independent 16-byte row loads in flight per lane before any of them is consumed: the
+// rows of one token live in unrelated places, so the loads do not depend on each other.
+constexpr int ROW_BATCH = 4;
+template <typename T>
+__device__ inline void unpack16(const uint4& q, float* v) {
+  Vec16<T>::load(reinterpret_cast<const T*>(&q), v);
+}
+
 // The token's routed slots in ascending expert order (the order in which the
 // reference accumulates a token's contributions).  Returns the count.
 __device__ inline int ordered_slots(const int* expert_of, const int* slot_pos, const float* gates, int t, int k,
@@ -95,11 +103,19 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
       float acc[V];
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = 0.f;
-      for (int j = 0; j < n; ++j) {
-        float v[V];
-        Vec16<T>::load((const T*)row_ptr(a.y_perm, pos[j], rb) + c, v);
+      for (int j0 = 0; j0 < n; j0 += ROW_BATCH) {
+        uint4 raw[ROW_BATCH];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j], v[i]));
+        for (int b = 0; b < ROW_BATCH; ++b)
+          if (j0 + b < n) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
+#pragma unroll
+        for (int b = 0; b < ROW_BATCH; ++b) {
+          if (j0 + b >= n) break;
+          float v[V];
+          unpack16<T>(raw[b], v);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j0 + b], v[i]));
+        }
       }
       if (sh) {
         float v[V];
@@ -154,16 +170,26 @@ __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradAr
     for (int c = lane * V; c < d; c += 32 * V) {
       float g[V];
       Vec16<T>::load(gy + c, g);
-      for (int j = 0; j < k; ++j) {
-        if (pos[j] < 0) continue;
-        float o[V], s[V];
-        Vec16<T>::load((const T*)row_ptr(a.y_perm, pos[j], rb) + c, o);
+      for (int j0 = 0; j0 < k; j0 += ROW_BATCH) {
+        uint4 raw[ROW_BATCH];
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          dot[j] = fmaf(g[i], o[i], dot[j]);
-          s[i] = gate[j] * g[i];
+        for (int b = 0; b < ROW_BATCH; ++b)
+          if (j0 + b < k && pos[j0 + b] >= 0)
+            raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
+#pragma unroll
+        for (int b = 0; b < ROW_BATCH; ++b) {
+          const int j = j0 + b;
+          if (j >= k) break;
+          if (pos[j] < 0) continue;
+          float o[V], s[V];
+          unpack16<T>(raw[b], o);
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            dot[j] = fmaf(g[i], o[i], dot[j]);
+            s[i] = gate[j] * g[i];
+          }
+          Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j], rb) + c, s);
         }
-        Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j], rb) + c, s);
       }
     }
   } else {
@@ -265,11 +291,19 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
 #pragma unroll
       for (int i = 0; i < V; ++i) { acc[i] = 0.f; r[i] = 0.f; }
       if (sh) Vec16<T>::load(sh + (size_t)t * d + c, acc);
-      for (int j = 0; j < n; ++j) {
-        float v[V];
-        Vec16<T>::load((const T*)row_ptr(a.grad_x_perm, pos[j], rb) + c, v);
+      for (int j0 = 0; j0 < n; j0 += ROW_BATCH) {
+        uint4 raw[ROW_BATCH];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+        for (int b = 0; b < ROW_BATCH; ++b)
+          if (j0 + b < n) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.grad_x_perm, pos[j0 + b], rb) + c);
+#pragma unroll
+        for (int b = 0; b < ROW_BATCH; ++b) {
+          if (j0 + b >= n) break;
+          float v[V];
+          unpack16<T>(raw[b], v);
+#pragma unroll
+          for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+        }
       }
       if (ex) Vec16<T>::load(ex + (size_t)t * d + c, r);
       for (int e = 0; gl && e < E; ++e) {
