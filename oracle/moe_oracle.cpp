@@ -239,9 +239,12 @@ struct Weight {
   void resize(int r, int c) {
     rows = r; cols = c;
     value.assign((size_t)r * c, 0.f);
-    grad.assign((size_t)r * c, 0.f);
-    m.assign((size_t)r * c, 0.f);
-    v.assign((size_t)r * c, 0.f);
+  }
+  // gradient and Adam state are created on first use (a forward-only timing run of a large
+  // layer should not hold four copies of every weight)
+  void need_grad() { if (grad.size() != value.size()) grad.assign(value.size(), 0.f); }
+  void need_moments() {
+    if (m.size() != value.size()) { m.assign(value.size(), 0.f); v.assign(value.size(), 0.f); }
   }
 };
 
@@ -548,6 +551,7 @@ int orc_get_weight(void* h, int which, int expert, float* dst) {
 int orc_get_grad(void* h, int which, int expert, float* dst) {
   Weight* w = pick(*(Layer*)h, which, expert);
   if (!w) return 1;
+  w->need_grad();
   std::memcpy(dst, w->grad.data(), sizeof(float) * w->grad.size());
   return 0;
 }
@@ -555,6 +559,7 @@ int orc_get_grad(void* h, int which, int expert, float* dst) {
 int orc_get_moments(void* h, int which, int expert, float* m, float* v) {
   Weight* w = pick(*(Layer*)h, which, expert);
   if (!w) return 1;
+  w->need_moments();
   std::memcpy(m, w->m.data(), sizeof(float) * w->m.size());
   std::memcpy(v, w->v.data(), sizeof(float) * w->v.size());
   return 0;
@@ -728,13 +733,14 @@ void orc_get_expert_rows(void* h, float* hidden, float* outputs) {
 }
 
 void orc_zero_grad(void* h) {
-  for_each_weight(*(Layer*)h, [](Weight& w, void*) { std::fill(w.grad.begin(), w.grad.end(), 0.f); }, nullptr);
+  for_each_weight(*(Layer*)h, [](Weight& w, void*) { w.need_grad(); std::fill(w.grad.begin(), w.grad.end(), 0.f); }, nullptr);
 }
 
 // MoeLayer::backward (moe.rs:348-489).  Weight gradients accumulate.
 int orc_backward(void* h, const float* grad_out, float* grad_in) {
   Layer& L = *(Layer*)h;
   const int T = L.T, d = L.d, E = L.E, k = L.k, F = L.F;
+  for_each_weight(L, [](Weight& w, void*) { w.need_grad(); }, nullptr);
   std::fill(grad_in, grad_in + (size_t)T * d, 0.f);
 
   if (L.has_shared) {  // :356-361
@@ -847,6 +853,8 @@ void orc_adam_step(void* h, float lr, float beta1, float beta2, float eps, float
       lr, beta1, beta2, eps, wd, 1.0f - std::pow(beta1, (float)step), 1.0f - std::pow(beta2, (float)step), scale};
   for_each_weight(*(Layer*)h, [](Weight& w, void* p) {
     const Ctx& c = *(const Ctx*)p;
+    w.need_grad();
+    w.need_moments();
     for (size_t i = 0; i < w.value.size(); ++i) {
       const float g = w.grad[i] * c.scale;
       w.m[i] = c.b1 * w.m[i] + (1.0f - c.b1) * g;

@@ -56,7 +56,8 @@ struct __align__(8) SharedTail {
   int tstart[MAX_GROUPS + 1];
 };
 
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + (int)sizeof(SharedTail);
+constexpr int STG_TOTAL = 8 * 32 * 80;   // epilogue staging, see STG_* below
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_TOTAL + 1024 /*alignment slack*/ + (int)sizeof(SharedTail);
 
 // ---------------------------------------------------------------------------
 // PTX wrappers
@@ -258,6 +259,45 @@ __device__ __forceinline__ void load32_bf16(const bf16* src, float* v) {
   }
 }
 
+// Coalescing through shared memory.  tcgen05.ld hands every lane one ROW (32 columns = 64 bytes
+// of bf16); storing that directly makes each warp-wide 16-byte store touch 32 different rows.
+// Each epilogue warp therefore owns a 32 x 64-byte staging tile (80-byte row pitch, conflict
+// free): lanes drop their row there, and the warp writes it out 8 rows x 64 contiguous bytes per
+// instruction (4x fewer L1/L2 request cycles, which the TMA loads share).  Loads of the saved
+// g|u rows take the same path in reverse.
+constexpr int STG_PITCH = 80;
+constexpr int STG_BYTES_PER_WARP = 32 * STG_PITCH;      // 2560
+constexpr int STG_BYTES = EPI_WARPS * STG_BYTES_PER_WARP;
+
+__device__ __forceinline__ void store32_bf16_staged(bf16* warp_row0_ptr, long long ld, const float* v, uint8_t* stg,
+                                                    int lane) {
+  uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    mine[i] = make_uint4(pack2(v[8 * i], v[8 * i + 1]), pack2(v[8 * i + 2], v[8 * i + 3]),
+                         pack2(v[8 * i + 4], v[8 * i + 5]), pack2(v[8 * i + 6], v[8 * i + 7]));
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int row = it * 8 + (lane >> 2), ch = lane & 3;
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + row * STG_PITCH + ch * 16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(warp_row0_ptr + (long long)row * ld) + ch * 16) = q;
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void load32_bf16_staged(const bf16* warp_row0_ptr, long long ld, float* v, uint8_t* stg,
+                                                   int lane) {
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int row = it * 8 + (lane >> 2), ch = lane & 3;
+    const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(warp_row0_ptr + (long long)row * ld) + ch * 16);
+    *reinterpret_cast<uint4*>(stg + row * STG_PITCH + ch * 16) = q;
+  }
+  __syncwarp();
+  load32_bf16(reinterpret_cast<const bf16*>(stg + lane * STG_PITCH), v);
+  __syncwarp();
+}
+
 // The tensor-core path rounds its outputs to bf16 (2^-9), so the pointwise step uses
 // the fast exponential and reciprocal; the f32 path keeps expf and IEEE division.
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
@@ -265,24 +305,24 @@ __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f,
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl, uint32_t taddr, int row_in_tile,
                                               int c_begin, int c_end,
-                                              bool have_acc) {
+                                              bool have_acc, uint8_t* stg) {
+  const int lane = row_in_tile & 31;
+  const long long wrow = (long long)tl.row0 + (row_in_tile & ~31);   // first row of this warp
 #ifdef TC_EXP_NOEPI
   return;
 #endif
   if (EPI == EPI_STORE) {
-    const long long row = (long long)tl.row0 + row_in_tile;
-    bf16* out = (bf16*)p.out0 + row * p.ld0;
+    bf16* out = (bf16*)p.out0 + wrow * p.ld0;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;   // warp-uniform
       float v[32];
       tmem_ld32(taddr + c, v);
-      store32_bf16(out + tl.n0 + c, v);
+      store32_bf16_staged(out + tl.n0 + c, p.ld0, v, stg, lane);
     }
   } else if (EPI == EPI_SWIGLU) {
-    const long long row = (long long)tl.row0 + row_in_tile;
-    bf16* h_out = (bf16*)p.out0 + row * p.ld0;
-    bf16* gu_out = p.out1 ? (bf16*)p.out1 + row * p.ld1 : nullptr;
+    bf16* h_out = (bf16*)p.out0 + wrow * p.ld0;
+    bf16* gu_out = p.out1 ? (bf16*)p.out1 + wrow * p.ld1 : nullptr;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; c += 2 * GU_BLOCK) {
       if (tl.n0 + c >= p.N) break;
@@ -290,27 +330,26 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
       tmem_ld32(taddr + c, g);
       tmem_ld32(taddr + c + GU_BLOCK, u);
       if (gu_out) {
-        store32_bf16(gu_out + tl.n0 + c, g);
-        store32_bf16(gu_out + tl.n0 + c + GU_BLOCK, u);
+        store32_bf16_staged(gu_out + tl.n0 + c, p.ld1, g, stg, lane);
+        store32_bf16_staged(gu_out + tl.n0 + c + GU_BLOCK, p.ld1, u, stg, lane);
       }
 #pragma unroll
       for (int i = 0; i < 32; ++i) g[i] = g[i] * fast_sigmoid(g[i]) * u[i];
-      store32_bf16(h_out + (tl.n0 + c) / 2, g);
+      store32_bf16_staged(h_out + (tl.n0 + c) / 2, p.ld0, g, stg, lane);
     }
   } else if (EPI == EPI_SWIGLU_BWD) {
     // accumulator columns are logical hidden columns f; the saved (g|u) and the
     // output (dg|du) use the interleaved layout: block f/32 -> columns [64b, 64b+64).
-    const long long row = (long long)tl.row0 + row_in_tile;
-    const bf16* gu = (const bf16*)p.aux + row * p.ldaux;
-    bf16* out = (bf16*)p.out0 + row * p.ld0;
+    const bf16* gu = (const bf16*)p.aux + wrow * p.ldaux;
+    bf16* out = (bf16*)p.out0 + wrow * p.ld0;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;
       float dh[32], g[32], u[32];
       tmem_ld32(taddr + c, dh);
       const int col = (tl.n0 + c) * 2;
-      load32_bf16(gu + col, g);
-      load32_bf16(gu + col + GU_BLOCK, u);
+      load32_bf16_staged(gu + col, p.ldaux, g, stg, lane);
+      load32_bf16_staged(gu + col + GU_BLOCK, p.ldaux, u, stg, lane);
 #pragma unroll
       for (int i = 0; i < 32; ++i) {
         const float s = fast_sigmoid(g[i]);
@@ -318,8 +357,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
         u[i] = dh[i] * (g[i] * s);
         g[i] = dg;
       }
-      store32_bf16(out + col, g);
-      store32_bf16(out + col + GU_BLOCK, u);
+      store32_bf16_staged(out + col, p.ld0, g, stg, lane);
+      store32_bf16_staged(out + col + GU_BLOCK, p.ld0, u, stg, lane);
     }
   } else if (EPI == EPI_STORE_F32) {
     // f32 output with a row limit (p.M) and any column count: used for the router logits.
@@ -375,7 +414,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;   // swizzle atoms need 1024-byte alignment
-  SharedTail* st = reinterpret_cast<SharedTail*>(smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES);
+  uint8_t* stg_all = smem_raw + (tiles_base - raw) + STAGES * STAGE_BYTES;
+  SharedTail* st = reinterpret_cast<SharedTail*>(stg_all + STG_TOTAL);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -509,7 +549,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
-      epilogue_tile<EPI>(p, tl, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0);
+      epilogue_tile<EPI>(p, tl, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0, stg_all + (warp - 2) * STG_BYTES_PER_WARP);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&st->tmem_empty[acc]));
@@ -562,7 +602,7 @@ struct __align__(8) PairTail {
   int pstart[MAX_GROUPS + 1];   // exclusive prefix of ceil(m-tiles / 2) per group
   int mtiles[MAX_GROUPS + 1];
 };
-constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + 1024 + (int)sizeof(PairTail);
+constexpr int P_SMEM_BYTES = P_STAGES * P_STAGE_BYTES + STG_TOTAL + 1024 + (int)sizeof(PairTail);
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -670,7 +710,8 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t tiles_base = (raw + 1023u) & ~1023u;
-  PairTail* st = reinterpret_cast<PairTail*>(smem_raw + (tiles_base - raw) + P_STAGES * P_STAGE_BYTES);
+  uint8_t* stg_all = smem_raw + (tiles_base - raw) + P_STAGES * P_STAGE_BYTES;
+  PairTail* st = reinterpret_cast<PairTail*>(stg_all + STG_TOTAL);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -804,7 +845,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       if (!tl.skip) {
         Tile one;
         one.group = tl.group; one.row0 = tl.row0; one.m0 = tl.m0; one.n0 = tl.n0; one.k_iters = tl.k_iters;
-        epilogue_tile<EPI>(p, one, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0);
+        epilogue_tile<EPI>(p, one, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0, stg_all + (warp - 2) * STG_BYTES_PER_WARP);
       }
       tc_fence_before();
       __syncwarp();
