@@ -36,6 +36,8 @@ WORKLOADS = {
     # cfg3's token rows (16384 x top-8, d 2048) with few narrow experts: same dispatch/combine traffic, ~3 GB on the device
     "hbm": dict(T=16384, d=2048, E=8, k=8, F=256, shared=False, seed=123, precision="bf16", zipf=False,
                 name="HBM-kernel profiling case: 16384 tokens, d_model 2048, 8 experts top-8, d_ff 256"),
+    "cfg5": dict(T=64, d=1024, E=16, k=2, F=2816, shared=True, seed=9, precision="q8", zipf=False,
+                 name="KV-cached decode step through a quantized MoE layer: 64 sequences x 1 token, d_model 1024, 16 experts top-2 + shared, d_ff 2816, int8 weights"),
     "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
                  name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
 }
@@ -156,16 +158,30 @@ def oracle_layer(w, sample_tokens, threads=None):
 
 
 def time_oracle(w, sample_tokens, steps, warmup):
+    """Times forward + backward of the CPU restatement on `sample_tokens` tokens of the workload's shape.
+
+    With sample_tokens = None the sample is sized from a 128-token probe so that the whole call
+    (warm-up included) stays near 90 s: between 128 and 4096 tokens, a multiple of 128.
+    """
     import oracle
-    m, x, gy = oracle_layer(w, sample_tokens)
+    probe = 128 if sample_tokens is None else sample_tokens
+    m, x, gy = oracle_layer(w, max(probe, 4096 if sample_tokens is None else probe))
+    m.forward(x[:probe]); m.backward(gy[:probe])            # first touch: page in weights, allocate gradients
+    if sample_tokens is None:
+        t0 = time.perf_counter()
+        m.forward(x[:probe]); m.backward(gy[:probe])
+        per_token = (time.perf_counter() - t0) / probe
+        budget = 90.0 / max(steps + warmup, 1)
+        sample_tokens = int(min(4096, max(128, (budget / per_token) // 128 * 128)))
+    xs, gs = x[:sample_tokens], gy[:sample_tokens]
     for _ in range(warmup):
-        m.forward(x); m.backward(gy)
+        m.forward(xs); m.backward(gs)
     t0 = time.perf_counter()
     for _ in range(steps):
-        m.forward(x)
-        m.backward(gy)
+        m.forward(xs)
+        m.backward(gs)
     dt = (time.perf_counter() - t0) / max(steps, 1)
-    return sample_tokens / dt, dt, oracle.lib().orc_max_threads()
+    return sample_tokens / dt, dt, oracle.lib().orc_max_threads(), sample_tokens
 
 
 def run_reference(args, w):
@@ -173,8 +189,7 @@ def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 256 if w["d"] >= 2048 else w["T"]
-    value, dt, cores = time_oracle(w, sample, max(args.steps, 1), min(args.warmup, 1))
+    value, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else w["T"], max(args.steps, 1), min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "MoE-layer tokens/s (forward + backward)", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
@@ -185,6 +200,67 @@ def run_reference(args, w):
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    print(json.dumps(line))
+
+
+def run_decode(args, w):
+    """BASELINE config 5: latency of one quantized MoE layer on a decode-sized batch (p50 over graph replays)."""
+    import torch
+    from rustingbrain_b200 import MoeConfig, MoeLayer, _lib
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    T, d, E, F = w["T"], w["d"], w["E"], w["F"]
+    layer = MoeLayer(d, MoeConfig(E, w["k"], F, w["shared"]), precision="q8", max_tokens=T, training=False)
+    g = np.random.Generator(np.random.Philox(w["seed"]))
+    layer.set_weight(_lib.W_ROUTER, 0, (g.standard_normal((E, d)) * 0.02).astype(np.float32))
+
+    def put(which, e, rows, cols):
+        layer.set_weight_q8(which, e, g.integers(-127, 128, (rows, cols)).astype(np.int8),
+                            g.uniform(1e-3, 4e-3, rows).astype(np.float32))
+    for e in range(E):
+        put(_lib.W_GATE, e, F, d); put(_lib.W_UP, e, F, d); put(_lib.W_DOWN, e, d, F)
+    put(_lib.W_SHARED_GATE, 0, F, d); put(_lib.W_SHARED_UP, 0, F, d); put(_lib.W_SHARED_DOWN, 0, d, F)
+    x = torch.from_numpy(g.standard_normal((T, d)).astype(np.float32)).to(dev).bfloat16()
+    y = torch.empty_like(x)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(5):
+            layer.forward(x, out=y)
+    torch.cuda.synchronize()
+    counts = layer._routing(T)[2]
+    l0 = _lib.lib().moe_debug_launch_count()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        layer.forward(x, out=y)
+    per_layer = _lib.lib().moe_debug_launch_count() - l0
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than L2: weights come from HBM each time
+    reps = max(args.steps, 20) * 50
+    times = []
+    for _ in range(max(args.warmup, 3) * 10):
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    for _ in range(reps):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); graph.replay(); e1.record()
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    clocks = sampler.stop()
+    times = np.array(times)
+    p50 = float(np.percentile(times, 50))
+    active = int((counts > 0).sum()) + 1
+    wbytes = active * 3 * d * F                  # int8 weights of the active experts + shared
+    pk = peaks()
+    line = {"metric": "p50 microseconds per quantized MoE layer (decode, 64 rows)", "value": p50, "unit": "us",
+            "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3) * 10, "ms_per_step": p50 / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "int8 weights, bf16 activations",
+            "data": "synthetic", "config": {"workload": w["name"], "l2": "256 MB buffer written between replays",
+                                            "graph": "one CUDA graph per layer, %d kernels" % per_layer},
+            "clocks": clocks, "gpu_launches": int(per_layer * reps), "p90_us": float(np.percentile(times, 90)),
+            "roofline": {"bound": "hbm", "achieved": wbytes / (p50 * 1e-6) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                         "frac": wbytes / (p50 * 1e-6) / 1e9 / pk["hbm"], "traffic": None,
+                         "note": "int8 weight bytes of the %d active experts + shared (%.0f MB) / whole-layer p50" % (active - 1, wbytes / 1e6)}}
     print(json.dumps(line))
 
 
@@ -201,6 +277,9 @@ def main():
     w = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference(args, w)
+        return
+    if w["precision"] == "q8":
+        run_decode(args, w)
         return
 
     import torch
@@ -336,8 +415,7 @@ def main():
     if e2e:
         line["e2e"] = e2e
     if world == 1 and not args.no_cpu_baseline:
-        sample = 256 if w["d"] >= 2048 else min(w["T"], 2048)
-        v, dt, cores = time_oracle(w, sample, 2, 1)
+        v, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else min(w["T"], 2048), 2, 0)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
                                 "sample": "%d tokens of the workload's shape, forward + backward, %.1f s per pass" % (sample, dt)}
     print(json.dumps(line))
