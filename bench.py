@@ -286,6 +286,10 @@ def main():
     import torch.distributed as dist
     from rustingbrain_b200 import MoeConfig, MoeLayer, _lib
 
+    # libraries (NCCL) may print banners on stdout; keep it clean for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -418,8 +422,11 @@ def main():
         v, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else min(w["T"], 2048), 2, 0)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
                                 "sample": "%d tokens of the workload's shape, forward + backward, %.1f s per pass" % (sample, dt)}
-    print(json.dumps(line))
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    print(json.dumps(line), flush=True)
     if world > 1:
+        os.dup2(2, 1)
         dist.destroy_process_group()
 
 

@@ -74,6 +74,7 @@ __device__ inline int ordered_slots(const int* expert_of, const int* slot_pos, c
     const int e = expert_of[(size_t)t * k + j];
     if (e < 0) continue;
     const int p = slot_pos[(size_t)t * k + j];
+    if (p < 0) continue;
     const float g = gates ? gates[(size_t)t * k + j] : 1.f;
     int i = n++;
     while (i > 0 && ex[i - 1] > e) {

@@ -34,6 +34,7 @@ struct PermuteArgs {
   float* row_gate;    // [padded rows] gate of each row
   int* token_of;      // [R] compact, stable expert-major order (the reference's permutation)
   int* slot_of;       // [R]
+  int skip_pad;       // do not zero the padding rows at the end of each expert's group
 };
 
 cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t stream);
@@ -41,6 +42,8 @@ cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t strea
 // local expert GEMMs, 1 for the compact send layout of an expert-parallel rank).
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
                             int align, cudaStream_t stream);
+cudaError_t launch_ep_plan(const int* gathered, int ranks, int E, int rank, int cap, int* dest_base, int* local_meta,
+                           int* error_flag, cudaStream_t stream);
 cudaError_t launch_ep_pack_stats(const float* stats, const int* counts, int E, int* out, cudaStream_t stream);
 cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float aux_w, float z_w, float* ext_stats,
                              int* ext_counts, float* losses, cudaStream_t stream);

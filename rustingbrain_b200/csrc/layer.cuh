@@ -93,6 +93,8 @@ struct moe_layer {
   uint8_t* host_valid = nullptr;
   void* pinned = nullptr;            // pinned bounce buffer, [max_tokens, d] f32
   cudaStream_t own_stream = nullptr;
+  cudaStream_t side_stream = nullptr;   // runs the un-permute beside the last weight-gradient GEMM
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 
   // last forward
   int last_tokens = 0;

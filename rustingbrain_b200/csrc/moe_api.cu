@@ -238,6 +238,10 @@ int check_flag(moe_layer* L) {
   CK(cudaMemcpy(&flag, L->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
   if (flag != 0) {
     cudaMemset(L->error_flag, 0, sizeof(int));
+    if (flag == 300) {
+      L->err = "InvalidInput: more rows were routed to one rank's experts than its receive buffers hold; raise ep_capacity_factor (nothing was sent)";
+      return MOE_INVALID_INPUT;
+    }
     return fail(L, MOE_TIMEOUT, "a bounded device-side wait gave up (code %d)", flag);
   }
   return MOE_OK;
@@ -294,11 +298,14 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
   return MOE_OK;
 }
 
-int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed) {
+// phase 0: everything; 1: everything except the gate|up weight gradient; 2: only that gradient
+// (it does not feed the input gradient, so the un-permute can run beside it).
+int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed, int phase = 0) {
   const int d = L->d, Fp = L->F_pad;
   Span whole(L, routed ? -1 : 14, st);
   const int acc = L->grad_valid ? 1 : 0;
   if (L->act == PREC_BF16) {
+    if (phase != 2) {
     // dgu = swiglu'(dy W_d) ; dW_d += dy^T h ; dx = dgu W_gu ; dW_gu += dgu^T x
     tc::GemmArgs a{};
     a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
@@ -321,13 +328,17 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     tc::Operand B2{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
     { Span sp(L, routed ? 8 : -1, st); CK(tc::gemm_rows_nn(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
 
+    }
+    if (phase != 1) {
     tc::GemmArgs wg{};
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.error_flag = L->error_flag;
     wg.M = 2 * Fp; wg.N = d; wg.out0 = L->g + io.w_gu; wg.ld0 = d; wg.group_stride0 = 2ll * Fp * d; wg.accumulate = acc;
     tc::Operand Ag{io.dgu, G.cap_rows, 2 * Fp, 1};
     tc::Operand Bg{io.x, G.in_rows, d, 1};
     { Span sp(L, routed ? 9 : -1, st); CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st)); }
+    }
   } else {
+    if (phase != 2) {
     SimtGemmArgs a{};
     a.A = (const float*)io.dy; a.B = L->w + io.w_d; a.C = (float*)io.dh;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows;
@@ -344,11 +355,14 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = 2 * Fp; b.b_group_stride = 2ll * Fp * d;
     { Span sp(L, routed ? 8 : -1, st); CK(simt_gemm_nn(b, st)); }
+    }
+    if (phase != 1) {
     SimtGemmArgs wg{};
     wg.A = (const float*)io.dgu; wg.B = (const float*)io.x; wg.C = L->g + io.w_gu;
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.a_rows = G.cap_rows; wg.b_rows = G.in_rows;
     wg.M = 2 * Fp; wg.N = d; wg.c_group_stride = 2ll * Fp * d; wg.accumulate = acc;
     { Span sp(L, routed ? 9 : -1, st); CK(simt_gemm_tn(wg, st)); }
+    }
   }
   return MOE_OK;
 }
@@ -406,6 +420,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   pa.x_perm = ep ? ep_rows(L, 0, L->x_perm) : local_rows(L->x_perm); pa.slot_pos = L->slot_pos;
   pa.dest_base = (ep && L->peer_ready) ? L->dest_base : nullptr; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
   pa.token_of = L->token_of; pa.slot_of = L->slot_of;
+  pa.skip_pad = L->precision == MOE_PRECISION_Q8 ? 1 : 0;   // the int8 kernels never read padding rows
   { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
   int rc;
@@ -476,13 +491,13 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
 
   int rc;
   if (ep) {
-    rc = ep_backward_experts(L, st);
+    rc = ep_backward_experts(L, st, 1);
   } else {
     Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
     ExpertIO io{};
     io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
     io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
-    rc = experts_backward(L, G, io, st, true);
+    rc = experts_backward(L, G, io, st, true, 1);
   }
   if (rc != MOE_OK) return rc;
 
@@ -503,30 +518,49 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   if (ep) { rb.ext_stats = L->ext_stats; rb.ext_counts = L->ext_counts; }
   { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
 
+  tc::Operand RA{L->gl_bf16, tokens, L->E, 1};
   if (L->tc_router && tokens > 0) {
-    // router input gradient grad_logits W_r and router weight gradient grad_logits^T x as two
-    // more launches of the grouped tensor-core GEMM over one dense row group
+    // router input gradient grad_logits W_r: one more launch of the grouped tensor-core GEMM
     Span sp(L, 12, st);
     tc::GemmArgs g{};
     g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;
     g.N = L->d; g.K = L->E; g.out0 = L->dx_r; g.ld0 = L->d;
-    tc::Operand A{L->gl_bf16, tokens, L->E, 1};
     tc::Operand B{L->wb + L->off_router, L->E, L->d, 1};
-    CK(tc::gemm_rows_nn(A, B, g, tc::EPI_STORE, L->sm_count, st));
-    tc::GemmArgs wg{};
-    wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
-    wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
-    tc::Operand Ax{L->last_x, tokens, L->d, 1};
-    CK(tc::gemm_rows_tn(A, Ax, wg, L->sm_count, st));
+    CK(tc::gemm_rows_nn(RA, B, g, tc::EPI_STORE, L->sm_count, st));
   }
 
+  // Everything the input gradient needs exists now.  The un-permute (HBM / NVLink bound, a few
+  // warps per SM) runs on a side stream next to the deferred gate|up weight gradient, which
+  // keeps the tensor cores busy and does not feed grad_x.
+  CK(cudaEventRecord(L->ev_fork, st));
+  CK(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
   UnpermuteArgs ua{};
   ua.grad_x_perm = ep ? ep_rows(L, 3, L->dx_perm) : local_rows(L->dx_perm); ua.shared = L->shared ? L->dx_s : nullptr;
   ua.extra = L->tc_router ? L->dx_r : nullptr; ua.grad_logits = L->tc_router ? nullptr : L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
-  { Span sp(L, 11, st); CK(launch_unpermute(ua, L->act, st)); }
+  { Span sp(L, 11, L->side_stream); CK(launch_unpermute(ua, L->act, L->side_stream)); }
+  CK(cudaEventRecord(L->ev_join, L->side_stream));
 
+  if (ep) {
+    rc = ep_backward_experts(L, st, 2);
+  } else {
+    Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+    ExpertIO io{};
+    io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
+    io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
+    rc = experts_backward(L, G, io, st, true, 2);
+  }
+  if (rc != MOE_OK) return rc;
+
+  if (L->tc_router && tokens > 0) {
+    Span sp(L, 12, st);
+    tc::GemmArgs wg{};
+    wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
+    wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
+    tc::Operand Ax{L->last_x, tokens, L->d, 1};
+    CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, st));
+  }
   RouterWgradArgs rw{};
   rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
   rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
@@ -536,6 +570,7 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     rc = ep_allreduce_replicated(L, st);
     if (rc != MOE_OK) return rc;
   }
+  CK(cudaStreamWaitEvent(st, L->ev_join, 0));
   CK(cudaGetLastError());
   L->grad_valid = true;
   return MOE_OK;
@@ -599,9 +634,10 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   L->n_params = s.n_params;
 
   const long long T = L->max_tokens, d = L->d, E = L->E, k = L->k, Fp = L->F_pad;
-  L->tc_router = L->precision == MOE_PRECISION_BF16 && L->E % 8 == 0;
+  L->tc_router = L->precision != MOE_PRECISION_F32 && L->E % 8 == 0;
   if (L->precision == MOE_PRECISION_Q8) {
     DA(L->w, (long long)E * d * 4, true);   // router only
+    DA(L->wb, (long long)E * d * 2, true);  // its bf16 copy for the tensor-core logits product
     const long long G = E + 1;   // the shared expert is stored as group E
     DA(L->q_gu, G * 2 * Fp * d, true); DA(L->s_gu, G * 2 * Fp * 4, true);
     DA(L->q_d, G * d * Fp, true); DA(L->s_d, G * d * 4, true);
@@ -665,6 +701,9 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     L->rw_splits = (int)std::min<long long>(64, std::max<long long>(1, T / 256));
     DA(L->rw_scratch, (long long)L->rw_splits * E * d * 4, false);
   }
+  CK(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
+  CK(cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming));
+  CK(cudaEventCreateWithFlags(&L->ev_join, cudaEventDisableTiming));
   CK(cudaDeviceSynchronize());
   return MOE_OK;
 }
@@ -685,6 +724,9 @@ void moe_destroy(moe_layer_t* L) {
   for (auto& sp : L->prof_spans) { cudaEventDestroy(sp.begin); cudaEventDestroy(sp.end); }
   for (auto ev : L->prof_pool) cudaEventDestroy(ev);
   if (L->own_stream) cudaStreamDestroy(L->own_stream);
+  if (L->side_stream) cudaStreamDestroy(L->side_stream);
+  if (L->ev_fork) cudaEventDestroy(L->ev_fork);
+  if (L->ev_join) cudaEventDestroy(L->ev_join);
   delete L;
 }
 

@@ -314,6 +314,52 @@ __global__ void ep_losses_kernel(const int* __restrict__ gathered, int ranks, in
   losses[1] = z;
 }
 
+// Expert parallelism, peer transport: the exchange plan of this rank, computed on the device from
+// the gathered counts so that the pass needs no host round trip.
+//   dest_base[e]  row id (owner * cap + row) of this rank's first row of global expert e
+//   local_meta    row0[El+1], m-tile prefix[El+1], counts[El+1] of the experts this rank owns
+// If any rank would receive more rows than its buffers hold, every rank sees the same counts and
+// takes the same decision: nothing is sent (all destinations negative, empty local groups) and
+// the error flag is set.
+__global__ void ep_plan_kernel(const int* __restrict__ gathered, int ranks, int E, int rank, int cap,
+                               int* __restrict__ dest_base, int* __restrict__ local_meta, int* __restrict__ error_flag) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int El = E / ranks, stride = 2 * E + 2;
+  bool overflow = false;
+  for (int p = 0; p < ranks; ++p) {
+    int row = 0, tiles = 0;
+    for (int l = 0; l < El; ++l) {
+      const int e = p * El + l;
+      int total = 0, before_me = 0;
+      for (int s = 0; s < ranks; ++s) {
+        const int c = gathered[(size_t)s * stride + E + 2 + e];
+        if (s < rank) before_me += c;
+        total += c;
+      }
+      dest_base[e] = p * cap + row + before_me;
+      if (p == rank) {
+        local_meta[l] = row;
+        local_meta[(El + 1) + l] = tiles;
+        local_meta[2 * (El + 1) + l] = total;
+      }
+      const int padded = round_up(total, GROUP_ALIGN);
+      row += padded;
+      tiles += padded / GROUP_ALIGN;
+    }
+    if (p == rank) {
+      local_meta[El] = row;
+      local_meta[(El + 1) + El] = tiles;
+      local_meta[2 * (El + 1) + El] = 0;
+    }
+    overflow |= row > cap;
+  }
+  if (overflow) {
+    for (int e = 0; e < E; ++e) dest_base[e] = -(1 << 30);
+    for (int i = 0; i < 3 * (El + 1); ++i) local_meta[i] = 0;
+    atomicCAS(error_flag, 0, 300);
+  }
+}
+
 // Packs this rank's contribution to the exchange above: stats as float bits, then counts.
 __global__ void ep_pack_stats_kernel(const float* __restrict__ stats, const int* __restrict__ counts, int E,
                                      int* __restrict__ out) {
@@ -361,19 +407,23 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       __syncwarp();
       if (i < nslots) {
         int dest = pos;
-        if (pos >= 0) {
+        if (pos >= 0 && blockIdx.y != 0) {
+          if (dest_base) dest = dest_base[e] + (pos - meta.pad_off[e]);
+          if (dest < 0) dest = -1;
+        } else if (pos >= 0) {
           const int cpos = meta.offsets[e] + (pos - meta.pad_off[e]);
           token_of[cpos] = slot / k;
           slot_of[cpos] = slot;
           if (dest_base) {
             dest = dest_base[e] + (pos - meta.pad_off[e]);   // a row of the expert's owner
+            if (dest < 0) dest = -1;                          // plan refused (a receive buffer would overflow)
           } else {
             row_token[pos] = slot / k;
             row_gate[pos] = gates[slot];
           }
         }
         spos[i] = dest;
-        slot_pos[slot] = dest;
+        if (blockIdx.y == 0) slot_pos[slot] = dest;
       }
     }
   }
@@ -382,20 +432,46 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
   constexpr int VEC = 16 / sizeof(T);
   const bool vec_ok = (d % VEC) == 0;
   const size_t row_bytes = (size_t)d * sizeof(T);
-  for (int r = warp; r < rows; r += blockDim.x / 32) {
-    const T* src = x + (size_t)(t0 + r) * d;
-    const int* p = spos + r * k;
-    if (p[0] < 0) continue;   // padding row: routed nowhere
-    if (vec_ok) {
-      const uint4* s4 = reinterpret_cast<const uint4*>(src);
-      for (int c = lane; c < d / VEC; c += 32) {
-        const uint4 v = s4[c];
-        for (int j = 0; j < k; ++j) reinterpret_cast<uint4*>(row_ptr(x_perm, p[j], row_bytes))[c] = v;
+  if (vec_ok) {
+    // flat over (row, 16-byte chunk): neighbouring threads take neighbouring chunks of one row,
+    // and each thread keeps four independent loads in flight
+    const int cpr = d / VEC;                 // chunks per row
+    // small batches: gridDim.y blocks share one 64-token group; each repeats the (cheap) ranking
+    // and copies its own slice of the rows, so the copy is not one block's latency chain
+    const int slice = ceil_div(rows, (int)gridDim.y);
+    const int r_begin = min(rows, (int)blockIdx.y * slice), r_end = min(rows, r_begin + slice);
+    const int total = r_end * cpr;
+    constexpr int U = 4;
+    for (int base = r_begin * cpr + tid; base < total; base += blockDim.x * U) {
+      uint4 v[U];
+      int rr[U], cc[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int idx = base + u * blockDim.x;
+        rr[u] = -1;
+        if (idx < total) {
+          rr[u] = idx / cpr; cc[u] = idx - rr[u] * cpr;
+          if (spos[rr[u] * k] < 0) rr[u] = -1;   // padding row: routed nowhere
+          else v[u] = reinterpret_cast<const uint4*>(x + (size_t)(t0 + rr[u]) * d)[cc[u]];
+        }
       }
-    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (rr[u] < 0) continue;
+        const int* p = spos + rr[u] * k;
+        for (int j = 0; j < k; ++j)
+          if (p[j] >= 0) reinterpret_cast<uint4*>(row_ptr(x_perm, p[j], row_bytes))[cc[u]] = v[u];
+      }
+    }
+  } else {
+    for (int r = warp + (int)blockIdx.y * (blockDim.x / 32); r < rows; r += (blockDim.x / 32) * gridDim.y) {
+      const T* src = x + (size_t)(t0 + r) * d;
+      const int* p = spos + r * k;
+      if (p[0] < 0) continue;
       for (int c = lane; c < d; c += 32) {
         const T v = src[c];
-        for (int j = 0; j < k; ++j) reinterpret_cast<T*>(row_ptr(x_perm, p[j], row_bytes))[c] = v;
+        for (int j = 0; j < k; ++j)
+          if (p[j] >= 0) reinterpret_cast<T*>(row_ptr(x_perm, p[j], row_bytes))[c] = v;
       }
     }
   }
@@ -409,13 +485,20 @@ __global__ void pad_rows_kernel(T* __restrict__ buf, int d, RouteMeta meta, int*
   const int e = blockIdx.x;
   const int begin = meta.pad_off[e] + meta.counts[e];
   const int end = meta.pad_off[e + 1];
-  for (int r = begin; r < end; ++r) {
-    for (int c = threadIdx.x; c < d; c += blockDim.x) buf[(size_t)r * d + c] = from_f32<T>(0.f);
-    if (row_token && threadIdx.x == 0) {
+  constexpr int VEC = 16 / sizeof(T);
+  if (d % VEC == 0) {
+    const int cpr = d / VEC;
+    uint4* base = reinterpret_cast<uint4*>(buf + (size_t)begin * d);   // rows are contiguous
+    for (int i = threadIdx.x; i < (end - begin) * cpr; i += blockDim.x) base[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    for (int r = begin; r < end; ++r)
+      for (int c = threadIdx.x; c < d; c += blockDim.x) buf[(size_t)r * d + c] = from_f32<T>(0.f);
+  }
+  if (row_token)
+    for (int r = begin + threadIdx.x; r < end; r += blockDim.x) {
       row_token[r] = -1;
       row_gate[r] = 0.f;
     }
-  }
 }
 
 // ---------------------------------------------------------------------------
@@ -459,6 +542,11 @@ cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t strea
   return precision == PREC_BF16 ? launch_router_t<bf16>(a, stream) : launch_router_t<float>(a, stream);
 }
 
+cudaError_t launch_ep_plan(const int* gathered, int ranks, int E, int rank, int cap, int* dest_base, int* local_meta,
+                           int* error_flag, cudaStream_t stream) {
+  ep_plan_kernel<<<1, 32, 0, stream>>>(gathered, ranks, E, rank, cap, dest_base, local_meta, error_flag); count_launch();
+  return cudaGetLastError();
+}
 cudaError_t launch_ep_pack_stats(const float* stats, const int* counts, int E, int* out, cudaStream_t stream) {
   ep_pack_stats_kernel<<<1, 256, 0, stream>>>(stats, counts, E, out); count_launch();
   return cudaGetLastError();
@@ -480,19 +568,20 @@ cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, fl
 cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
   const size_t smem = sizeof(int) * ((size_t)a.E + (size_t)ROUTER_ROWS * a.k);
+  const dim3 pgrid(nb, nb <= 16 ? 8 : 1);
   if (nb > 0) {
     if (precision == PREC_BF16) {
-      permute_kernel<bf16><<<nb, 256, smem, stream>>>((const bf16*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens,
+      permute_kernel<bf16><<<pgrid, 256, smem, stream>>>((const bf16*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens,
                                                       a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token,
                                                       a.row_gate, a.token_of, a.slot_of);
     } else {
-      permute_kernel<float><<<nb, 256, smem, stream>>>((const float*)a.x, a.expert_of, a.gates, a.cursor, a.meta,
+      permute_kernel<float><<<pgrid, 256, smem, stream>>>((const float*)a.x, a.expert_of, a.gates, a.cursor, a.meta,
                                                        a.tokens, a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos,
                                                        a.row_token, a.row_gate, a.token_of, a.slot_of);
     }
     count_launch();
   }
-  if (a.dest_base) return cudaGetLastError();   // remote rows: the owners zero their own padding
+  if (a.dest_base || a.skip_pad) return cudaGetLastError();   // remote rows: the owners zero their own padding
   if (precision == PREC_BF16) {
     pad_rows_kernel<bf16><<<a.E, 256, 0, stream>>>((bf16*)a.x_perm.base[0], a.d, a.meta, a.row_token, a.row_gate);
   } else {
