@@ -234,7 +234,7 @@ def run_decode(args, w):
         layer.forward(x, out=y)
     per_layer = _lib.lib().moe_debug_launch_count() - l0
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # larger than L2: weights come from HBM each time
-    reps = max(args.steps, 20) * 50
+    reps = max(args.steps, 1) * 50
     times = []
     for _ in range(max(args.warmup, 3) * 10):
         graph.replay()
@@ -392,8 +392,19 @@ def main():
                 "note": "f32 configuration runs its products on the CUDA cores; see DESIGN.md"}
     else:
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+        # Operand and result bytes of the six launches (every matrix once): activations R x {d, F, 2F} in
+        # bf16, weights in bf16, weight gradients in f32.  The ncu capture of the reduced case measured
+        # DRAM read+write at 0.95 of these bytes (profiles/grouped_gemm_prof_case.md); traffic scales with
+        # rows and experts, so the full-size figure is that ratio times the bytes below.
+        d_, F_, E_ = w["d"], w["F"], w["E"] // world
+        Rl = R   # rows per rank (balanced routing: every rank serves as many rows as it sends)
+        gemm_bytes = (2 * (Rl * d_ + E_ * 2 * F_ * d_ + Rl * 3 * F_) + 2 * (Rl * F_ + E_ * d_ * F_ + Rl * d_)
+                      + 2 * (Rl * d_ + E_ * d_ * F_ + Rl * 4 * F_) + 2 * (Rl * d_ + Rl * F_) + 4 * E_ * d_ * F_
+                      + 2 * (Rl * 2 * F_ + E_ * 2 * F_ * d_ + Rl * d_) + 2 * (Rl * 2 * F_ + Rl * d_) + 4 * E_ * 2 * F_ * d_)
         roof = {"bound": "tensor", "achieved": ach, "peak": pk["tf_sustained"], "unit": "TFLOP/s",
-                "frac": ach / pk["tf_sustained"] if ach else None, "traffic": None,
+                "frac": ach / pk["tf_sustained"] if ach else None, "traffic": 0.95 * gemm_bytes / 6.0,
+                "traffic_unit": "bytes per launch (mean of the 6), ncu DRAM bytes of the reduced case scaled by rows",
+                "algorithmic_bytes_per_launch": gemm_bytes / 6.0,
                 "kernel": "grouped_gemm_kernel (6 launches per step: gate|up, down, 2 dgrad, 2 wgrad)",
                 "launches": gemm_launches, "ms_per_launch": gemm_ms / max(gemm_launches, 1),
                 "flops_per_step": gemm_flops / args.steps, "peak_source": pk["src"] + " sustained bf16",

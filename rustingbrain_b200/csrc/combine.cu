@@ -217,6 +217,120 @@ cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStrea
   return cudaGetLastError();
 }
 
+// ---------------------------------------------------------------------------
+// Expert-parallel peer transport: the gate gradient is computed where the expert output lives.
+//   push_grad_kernel   (token owner)  stores grad_y[token] unscaled into the expert owner's row and the
+//                                      slot's gate beside it: one NVLink crossing per row instead of two
+//   scale_dot_kernel   (expert owner) dot[row] = <grad_y row, y row>; grad_y row *= gate (in place);
+//                                      zeroes the padding rows of each group
+//   pull_dots_kernel   (token owner)  grad_gate[slot] = dot[row] read back from the owner (4 bytes per slot)
+// The lane-to-column mapping and the reduction order equal gather_grad_kernel's, so do the results.
+// ---------------------------------------------------------------------------
+__device__ inline float* aux_ptr(const RowSpace& s, int id, size_t aux_off, int which) {
+  const int r = s.n == 1 ? 0 : id / s.cap;
+  const int row = id - r * s.cap;
+  return reinterpret_cast<float*>((char*)s.base[r] + aux_off) + (size_t)which * s.cap + row;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a) {
+  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= a.tokens) return;
+  const int k = a.k, d = a.d;
+  int pos[MAX_TOPK];
+  for (int j = 0; j < k; ++j) pos[j] = a.slot_pos[(size_t)t * k + j];
+  if (lane < k && pos[lane] >= 0) *aux_ptr(a.rows, pos[lane], a.aux_off, 0) = a.gates[(size_t)t * k + lane];
+  const T* gy = (const T*)a.grad_y + (size_t)t * d;
+  const size_t rb = (size_t)d * sizeof(T);
+  constexpr int V = Vec16<T>::N;
+  if (d % V == 0) {
+    for (int c = lane * V; c < d; c += 32 * V) {
+      const uint4 q = *reinterpret_cast<const uint4*>(gy + c);
+      for (int j = 0; j < k; ++j)
+        if (pos[j] >= 0) *reinterpret_cast<uint4*>((T*)row_ptr(a.rows, pos[j], rb) + c) = q;
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) {
+      const T g = gy[c];
+      for (int j = 0; j < k; ++j)
+        if (pos[j] >= 0) ((T*)row_ptr(a.rows, pos[j], rb))[c] = g;
+    }
+  }
+}
+
+cudaError_t launch_push_grad(const PushGradArgs& a, int precision, cudaStream_t stream) {
+  if (a.tokens <= 0) return cudaSuccess;
+  const int grid = ceil_div(a.tokens, CB_WARPS);
+  if (precision == PREC_BF16) { push_grad_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  else { push_grad_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  return cudaGetLastError();
+}
+
+template <typename T>
+__global__ void __launch_bounds__(CB_WARPS * 32) scale_dot_kernel(ScaleDotArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int d = a.d;
+  const int total = a.row0[a.groups];
+  constexpr int V = Vec16<T>::N;
+  for (int row = blockIdx.x * CB_WARPS + (threadIdx.x >> 5); row < total; row += gridDim.x * CB_WARPS) {
+    int g = 0;
+    while (g + 1 < a.groups && a.row0[g + 1] <= row) ++g;
+    const bool live = row - a.row0[g] < a.counts[g];
+    T* gy = (T*)a.grad_y + (size_t)row * d;
+    const T* y = (const T*)a.y + (size_t)row * d;
+    if (!live) {
+      if (d % V == 0) for (int c = lane * V; c < d; c += 32 * V) *reinterpret_cast<uint4*>(gy + c) = make_uint4(0, 0, 0, 0);
+      else for (int c = lane; c < d; c += 32) gy[c] = from_f32<T>(0.f);
+      continue;
+    }
+    const float gate = a.gate_in[row];
+    float dot = 0.f;
+    if (d % V == 0) {
+      for (int c = lane * V; c < d; c += 32 * V) {
+        float gv[V], o[V], s[V];
+        Vec16<T>::load(gy + c, gv);
+        Vec16<T>::load(y + c, o);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          dot = fmaf(gv[i], o[i], dot);
+          s[i] = gate * gv[i];
+        }
+        Vec16<T>::store(gy + c, s);
+      }
+    } else {
+      for (int c = lane; c < d; c += 32) {
+        const float gv = to_f32<T>(gy[c]);
+        dot = fmaf(gv, to_f32<T>(y[c]), dot);
+        gy[c] = from_f32<T>(gate * gv);
+      }
+    }
+    dot = warp_sum(dot);
+    if (lane == 0) a.dot_out[row] = dot;
+  }
+}
+
+cudaError_t launch_scale_dot(const ScaleDotArgs& a, int precision, int sm_count, cudaStream_t stream) {
+  const int grid = sm_count * 8;
+  if (precision == PREC_BF16) { scale_dot_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  else { scale_dot_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  return cudaGetLastError();
+}
+
+__global__ void pull_dots_kernel(PullDotsArgs a) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= a.slots) return;
+  const int pos = a.slot_pos[i];
+  a.grad_gates[i] = pos < 0 ? 0.f : *aux_ptr(a.rows, pos, a.aux_off, 1);
+}
+
+cudaError_t launch_pull_dots(const PullDotsArgs& a, cudaStream_t stream) {
+  if (a.slots <= 0) return cudaSuccess;
+  pull_dots_kernel<<<ceil_div(a.slots, 256), 256, 0, stream>>>(a);
+  count_launch();
+  return cudaGetLastError();
+}
+
 constexpr int RB_ROWS = 64;
 
 __global__ void __launch_bounds__(RB_ROWS) router_bwd_kernel(RouterBwdArgs a) {

@@ -51,11 +51,19 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <bool SWIGLU>
+// A warp owns two 8-column MMA tiles that share the token fragments: for the fused pass the gate
+// rows of 8 hidden columns and the matching up rows, otherwise 16 adjacent output columns.
+// U = 16-byte loads per lane and tile in one chunk of 64 U reduction values; K is a multiple of 64 U.
+template <bool SWIGLU, int U>
 __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
   extern __shared__ __align__(16) unsigned char q8_smem[];
-  bf16* xs = reinterpret_cast<bf16*>(q8_smem);
-  const int K = a.K, ldx = K + 8;
+  // Token tile in MMA-fragment order: rows r and r + 8 are interleaved so that one 16-byte unit holds
+  // the four A registers of a lane, {x[r][k..k+1], x[r+8][k..k+1], x[r][k+2..k+3], x[r+8][k+2..k+3]} for a
+  // group of four reduction values.  Row pair r has K/4 units plus one unit of padding, and units 8..15 of
+  // every 16 swap their 2-unit halves: the four quarter-chunks a quarter-warp reads then fall into
+  // different banks.
+  const int K = a.K;
+  const int pitch = (K / 4 + 1) * 16;   // bytes per row pair
   const int g = blockIdx.z, m0 = blockIdx.y * Q8_ROWS;
   int rows;
   const bf16* xin;
@@ -73,116 +81,157 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
   if (m0 >= rows) return;
   const int mrows = min(Q8_ROWS, rows - m0);
   const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
+
+  constexpr int COLS = SWIGLU ? 8 : 16;               // output columns per warp
+  constexpr int STEP = Q8_CHUNK * U;                  // reduction values per chunk
+  const int chunks = K / STEP;
+  const int n_blocks = ceil_div(a.N, COLS * Q8_WARPS);
+  const int8_t* wbase = a.w + (size_t)g * a.w_group_stride + 16 * q;
+  const size_t tile1 = (size_t)(SWIGLU ? GU_BLOCK : 8) * K;   // second tile's rows relative to the first
+  // first weight row of this lane in column block nb (nullptr when the warp has no columns there)
+  auto row_ptr0 = [&](int nb) -> const int8_t* {
+    const int n0 = (nb * Q8_WARPS + warp) * COLS;
+    if (nb >= n_blocks || n0 >= a.N) return nullptr;
+    return wbase + (size_t)(SWIGLU ? gu_row(0, n0 + gq) : n0 + gq) * K;
+  };
+  struct Chunk { uint4 w[U], u[U]; };
+  // The weight stream does not depend on the tokens: two register sets alternate so that the loads
+  // of the next chunk are in flight while this one is multiplied, and the first chunk is requested
+  // before the token tile is staged.
+  const int8_t* fp = row_ptr0(blockIdx.x);   // fetch cursor
+  int f_nb = blockIdx.x, f_c = 0;
+  auto fetch = [&](Chunk& ch) {
+    if (fp) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        ch.w[u] = __ldg(reinterpret_cast<const uint4*>(fp + Q8_CHUNK * u));
+        ch.u[u] = __ldg(reinterpret_cast<const uint4*>(fp + tile1 + Q8_CHUNK * u));
+      }
+      fp += STEP;
+    }
+    if (++f_c == chunks) { f_c = 0; f_nb += gridDim.x; fp = row_ptr0(f_nb); }
+  };
+  Chunk ca, cb;
+  fetch(ca);
+
   {
-    // the token rows of this tile, eight independent 16-byte loads in flight per thread
+    // the token rows of this tile as f16, eight independent 16-byte loads in flight per thread
     constexpr int SU = 8;
     const int cpr = K / 8, total = Q8_ROWS * cpr;
+    int r = tid / cpr, c = tid - r * cpr;             // (row, 16-byte column) of this thread's first element
+    const int dr = (Q8_WARPS * 32) / cpr, dc = (Q8_WARPS * 32) - dr * cpr;
     for (int base = tid; base < total; base += Q8_WARPS * 32 * SU) {
       uint4 v[SU];
+      int rr[SU], cc[SU];
 #pragma unroll
       for (int u = 0; u < SU; ++u) {
-        const int i = base + u * Q8_WARPS * 32;
+        rr[u] = r; cc[u] = c;
         v[u] = make_uint4(0, 0, 0, 0);
-        if (i < total) {
-          const int r = i / cpr, c = i - r * cpr;
-          if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(m0 + r) * K + c * 8);
-        }
+        if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(m0 + r) * K + c * 8);
+        r += dr; c += dc;
+        if (c >= cpr) { c -= cpr; ++r; }
       }
 #pragma unroll
       for (int u = 0; u < SU; ++u) {
-        const int i = base + u * Q8_WARPS * 32;
-        if (i < total) {
-          const int r = i / cpr, c = i - r * cpr;
-          *reinterpret_cast<uint4*>(xs + r * ldx + c * 8) =
-              make_uint4(bf16x2_to_f16x2(v[u].x), bf16x2_to_f16x2(v[u].y), bf16x2_to_f16x2(v[u].z), bf16x2_to_f16x2(v[u].w));
+        if (rr[u] < Q8_ROWS) {
+          // eight values = two groups of four; row half (r / 8) selects the 4-byte slot inside a unit
+          unsigned char* row = q8_smem + (rr[u] & 7) * pitch + (rr[u] >> 3) * 4;
+          const int kg = cc[u] * 2;
+          unsigned char* u0 = row + (kg ^ ((kg >> 2) & 2)) * 16;
+          unsigned char* u1 = row + ((kg + 1) ^ (((kg + 1) >> 2) & 2)) * 16;
+          *reinterpret_cast<uint32_t*>(u0) = bf16x2_to_f16x2(v[u].x);
+          *reinterpret_cast<uint32_t*>(u0 + 8) = bf16x2_to_f16x2(v[u].y);
+          *reinterpret_cast<uint32_t*>(u1) = bf16x2_to_f16x2(v[u].z);
+          *reinterpret_cast<uint32_t*>(u1 + 8) = bf16x2_to_f16x2(v[u].w);
         }
       }
     }
   }
   __syncthreads();
 
-  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
   const float* sc = a.scale + (size_t)g * a.s_group_stride;
-  const bf16* xa = xs + gq * ldx;
-  const bf16* xb = xs + (gq + 8) * ldx;
-  // a CTA keeps its token tile and walks over column blocks (64 columns each, 8 per warp)
-  for (int nb = blockIdx.x; nb * 8 * Q8_WARPS < a.N; nb += gridDim.x) {
-  const int n0 = (nb * Q8_WARPS + warp) * 8;    // first output column of this warp
-  if (n0 >= a.N) continue;
-  // weight row of the column this lane streams (column n0 + gq)
-  const int wrow = SWIGLU ? gu_row(0, n0 + gq) : n0 + gq;
-  const int8_t* w0 = a.w + (size_t)g * a.w_group_stride + (size_t)wrow * K;
-  const int8_t* w1 = w0 + (size_t)GU_BLOCK * K;          // matching up row (SWIGLU only)
+  // this lane's fragments: unit (k / 4) of row pair gq; for quarter-chunks 2 and 3 the halves are swapped
+  const unsigned char* xa0 = q8_smem + gq * pitch + (4 * q) * 16;
+  const int sw = (q & 2) ? 32 : 0;
+  const unsigned char* xa = xa0;              // compute cursor into the token tile
+  int m_nb = blockIdx.x, m_c = 0;
   float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
 
-  constexpr int UNROLL = SWIGLU ? 4 : 11;  // 16-byte weight loads in flight per lane and matrix (2816 = 4 x 11 x 64)
-  for (int c0 = 0; c0 < K; c0 += Q8_CHUNK * UNROLL) {
-    uint4 wq[UNROLL], uq[UNROLL];
+  auto multiply = [&](const Chunk& ch) {
+    const int n0 = (m_nb * Q8_WARPS + warp) * COLS;
+    const bool live = n0 < a.N;              // warp-uniform
+    if (live) {
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int kc = c0 + Q8_CHUNK * u;      // warp-uniform: K is a multiple of 64
-      const int k = kc + 16 * q;
-      wq[u] = make_uint4(0, 0, 0, 0);
-      uq[u] = make_uint4(0, 0, 0, 0);
-      if (kc < K) {
-        wq[u] = __ldg(reinterpret_cast<const uint4*>(w0 + k));
-        if (SWIGLU) uq[u] = __ldg(reinterpret_cast<const uint4*>(w1 + k));
+      for (int u = 0; u < U; ++u) {
+        const uint32_t ww[4] = {ch.w[u].x ^ 0x80808080u, ch.w[u].y ^ 0x80808080u, ch.w[u].z ^ 0x80808080u, ch.w[u].w ^ 0x80808080u};
+        const uint32_t uu[4] = {ch.u[u].x ^ 0x80808080u, ch.u[u].y ^ 0x80808080u, ch.u[u].z ^ 0x80808080u, ch.u[u].w ^ 0x80808080u};
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          // reduction slots of this MMA: (2q, 2q+1) <- k+4s+{0,1}, (2q+8, 2q+9) <- k+4s+{2,3}
+          // the A registers of reduction values k + 4s .. k + 4s + 3, rows gq and gq + 8, in one load
+          const uint4 f = *reinterpret_cast<const uint4*>((s < 2 ? xa + sw : xa + (32 - sw)) + u * (Q8_CHUNK * 4) + (s & 1) * 16);
+          mma_f16_16816(acc0, f.x, f.y, f.z, f.w, s8x2_to_f16x2(ww[s], 0), s8x2_to_f16x2(ww[s], 2));
+          mma_f16_16816(acc1, f.x, f.y, f.z, f.w, s8x2_to_f16x2(uu[s], 0), s8x2_to_f16x2(uu[s], 2));
+        }
+      }
+    }
+    xa += STEP * 4;   // 16 bytes per four reduction values
+    if (++m_c < chunks) return;
+    // last chunk of a column block: scale, activate, store.
+    // accumulator layout: c[0], c[1] -> row gq, columns 2q, 2q+1; c[2], c[3] -> row gq+8
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int col = n0 + 2 * q + j;
+        const float s0 = SWIGLU ? sc[gu_row(0, col)] : sc[col];
+        const float s1 = SWIGLU ? sc[gu_row(1, col)] : sc[col + 8];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = gq + 8 * half;
+          if (r >= mrows) continue;
+          bf16* o = out + (size_t)(m0 + r) * a.ldo + col;
+          const float v0 = acc0[2 * half + j] * s0, v1 = acc1[2 * half + j] * s1;
+          if (SWIGLU) { o[0] = __float2bfloat16_rn(siluf_(v0) * v1); }
+          else { o[0] = __float2bfloat16_rn(v0); o[8] = __float2bfloat16_rn(v1); }
+        }
       }
     }
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u) {
-      const int kc = c0 + Q8_CHUNK * u;
-      if (kc >= K) continue;                 // uniform over the warp: every lane joins every MMA
-      const int k = kc + 16 * q;
-      const uint32_t ww[4] = {wq[u].x ^ 0x80808080u, wq[u].y ^ 0x80808080u, wq[u].z ^ 0x80808080u, wq[u].w ^ 0x80808080u};
-      const uint32_t uu[4] = {uq[u].x ^ 0x80808080u, uq[u].y ^ 0x80808080u, uq[u].z ^ 0x80808080u, uq[u].w ^ 0x80808080u};
-#pragma unroll
-      for (int s = 0; s < 4; ++s) {
-        // reduction slots of this MMA: (2q, 2q+1) <- k+4s+{0,1}, (2q+8, 2q+9) <- k+4s+{2,3}
-        const uint2 lo = *reinterpret_cast<const uint2*>(xa + k + 4 * s);
-        const uint2 hi = *reinterpret_cast<const uint2*>(xb + k + 4 * s);
-        mma_f16_16816(acc0, lo.x, hi.x, lo.y, hi.y, s8x2_to_f16x2(ww[s], 0), s8x2_to_f16x2(ww[s], 2));
-        if (SWIGLU) mma_f16_16816(acc1, lo.x, hi.x, lo.y, hi.y, s8x2_to_f16x2(uu[s], 0), s8x2_to_f16x2(uu[s], 2));
-      }
-    }
-  }
+    for (int i = 0; i < 4; ++i) { acc0[i] = 0.f; acc1[i] = 0.f; }
+    m_c = 0; m_nb += gridDim.x; xa = xa0;
+  };
 
-  // accumulator layout: c[0], c[1] -> row gq, columns 2q, 2q+1; c[2], c[3] -> row gq+8
-#pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    const int col = n0 + 2 * q + j;
-    if (col >= a.N) continue;
-    float s0, s1 = 0.f;
-    if (SWIGLU) { s0 = sc[gu_row(0, col)]; s1 = sc[gu_row(1, col)]; } else { s0 = sc[col]; }
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int r = gq + 8 * half;
-      if (r >= mrows) continue;
-      float v = acc0[2 * half + j] * s0;
-      if (SWIGLU) v = siluf_(v) * (acc1[2 * half + j] * s1);
-      out[(size_t)(m0 + r) * a.ldo + col] = __float2bfloat16_rn(v);
-    }
+  const int my_blocks = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int iters = my_blocks * chunks;
+  for (int it = 0; it < iters; it += 2) {
+    fetch(cb);
+    multiply(ca);
+    if (it + 1 >= iters) break;
+    fetch(ca);
+    multiply(cb);
   }
-  }   // column blocks
+}
+
+template <bool SWIGLU, int U>
+static cudaError_t launch_q8_variant(const Q8Args& a, dim3 grid, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  q8_rows_kernel<SWIGLU, U><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
+  count_launch();
+  return cudaGetLastError();
 }
 
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
   const int groups = a.E + (a.x_shared ? 1 : 0);
-  // gate|up: two column blocks per CTA (the token tile is staged once for twice the weight stream);
-  // the narrower down projection needs every CTA it can get
-  const int nblocks = ceil_div(a.N, 8 * Q8_WARPS);
+  // gate|up: two column blocks (of 64 hidden columns) per CTA, so the token tile is staged once for
+  // twice the weight stream; the down projection has 128 output columns per block and few blocks
+  const int nblocks = ceil_div(a.N, (swiglu ? 8 : 16) * Q8_WARPS);
   const dim3 grid(swiglu ? ceil_div(nblocks, 2) : nblocks, ceil_div(a.tokens, Q8_ROWS), groups);
-  const size_t smem = (size_t)Q8_ROWS * (a.K + 8) * sizeof(bf16);
-  if (swiglu) {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    q8_rows_kernel<true><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
-  } else {
-    if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    q8_rows_kernel<false><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
-  }
-  count_launch();
-  return cudaGetLastError();
+  const size_t smem = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
+  const bool deep = a.K % (Q8_CHUNK * 4) == 0;   // K is always a multiple of 64
+  if (swiglu) return deep ? launch_q8_variant<true, 4>(a, grid, smem, stream) : launch_q8_variant<true, 1>(a, grid, smem, stream);
+  return deep ? launch_q8_variant<false, 4>(a, grid, smem, stream) : launch_q8_variant<false, 1>(a, grid, smem, stream);
 }
 
 }  // namespace moe

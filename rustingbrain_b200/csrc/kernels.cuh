@@ -100,6 +100,37 @@ struct GatherGradArgs {
 };
 cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStream_t stream);
 
+// Expert-parallel peer transport: gate gradient computed on the expert owner.  `aux_off` is the byte
+// offset, inside every rank's gradient receive buffer, of two float arrays of `rows.cap` entries:
+// the gates pushed with the rows, then the dots the owner computes.
+struct PushGradArgs {
+  const void* grad_y;     // [tokens, d]
+  RowSpace rows;          // the owners' gradient receive buffers
+  const int* slot_pos;    // [tokens*k]
+  const float* gates;     // [tokens*k]
+  size_t aux_off;
+  int tokens, d, k;
+};
+cudaError_t launch_push_grad(const PushGradArgs& a, int precision, cudaStream_t stream);
+struct ScaleDotArgs {
+  void* grad_y;           // local receive buffer, scaled in place
+  const void* y;          // local pre-gate expert outputs, same row layout
+  const float* gate_in;   // [rows]
+  float* dot_out;         // [rows]
+  const int* row0;        // [groups+1] padded group starts
+  const int* counts;      // [groups]
+  int groups, d;
+};
+cudaError_t launch_scale_dot(const ScaleDotArgs& a, int precision, int sm_count, cudaStream_t stream);
+struct PullDotsArgs {
+  RowSpace rows;
+  size_t aux_off;
+  const int* slot_pos;
+  float* grad_gates;
+  int slots;
+};
+cudaError_t launch_pull_dots(const PullDotsArgs& a, cudaStream_t stream);
+
 struct RouterBwdArgs {
   const float* probs;       // [tokens, E]
   const float* lse;         // [tokens]

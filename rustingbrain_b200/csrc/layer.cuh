@@ -93,8 +93,18 @@ struct moe_layer {
   uint8_t* host_valid = nullptr;
   void* pinned = nullptr;            // pinned bounce buffer, [max_tokens, d] f32
   cudaStream_t own_stream = nullptr;
-  cudaStream_t side_stream = nullptr;   // runs the un-permute beside the last weight-gradient GEMM
+  // The routed experts' weight-gradient GEMMs feed nothing else in the pass, so backward leaves them
+  // on a side stream and returns; the HBM/NVLink-bound tail of backward and the router + dispatch of
+  // the next forward run beside them.  Whatever they read that the next forward rewrites before its
+  // first expert GEMM is double-buffered (dispatched rows, group tables), selected by `parity`.
+  cudaStream_t side_stream = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  bool side_pending = false;            // deferred work not yet joined by a later call
+  int parity = 0;
+  void* x_perm2[2] = {nullptr, nullptr};
+  void* x_recv2[2] = {nullptr, nullptr};
+  int* meta_block2[2] = {nullptr, nullptr};
+  int* local_meta2[2] = {nullptr, nullptr};
 
   // last forward
   int last_tokens = 0;

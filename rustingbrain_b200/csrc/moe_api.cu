@@ -67,6 +67,37 @@ struct Span {
 
 long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
 
+// How backward overlaps its HBM-bound tail with the tensor-core work (MOE_B200_OVERLAP):
+//   0 (default) none; 1 un-permute on a side stream beside the gate|up weight gradient;
+//   2 both routed weight-gradient GEMMs deferred to the side stream past the end of the call.
+// Measured on cfg 4 at 1, 2 and 8 GPUs the three modes give the same step time: the step runs at the
+// board's power cap, and work that overlaps the GEMMs slows them by what it saves.
+int overlap_mode() {
+  static const int mode = [] {
+    const char* e = getenv("MOE_B200_OVERLAP");
+    return e && *e >= '0' && *e <= '2' ? *e - '0' : 0;
+  }();
+  return mode;
+}
+
+// Makes `st` wait for weight gradients still running on the side stream.
+int join_side(moe_layer* L, cudaStream_t st) {
+  if (!L->side_pending) return MOE_OK;
+  CK(cudaStreamWaitEvent(st, L->ev_join, 0));
+  L->side_pending = false;
+  return MOE_OK;
+}
+
+void select_parity(moe_layer* L, int p) {
+  const long long E = L->E;
+  L->parity = p;
+  L->meta_block = L->meta_block2[p];
+  L->meta.counts = L->meta_block; L->meta.offsets = L->meta_block + (E + 1); L->meta.pad_off = L->meta_block + 2 * (E + 1);
+  L->meta.tile_start = L->meta_block + 3 * (E + 1); L->meta.total = L->meta_block + 4 * (E + 1);
+  L->x_perm = L->x_perm2[p];
+  if (L->ep_size > 1) { L->x_recv = L->x_recv2[p]; L->local_meta = L->local_meta2[p]; }
+}
+
 int validate(const moe_config_t* c, char* msg, int len) {
   auto say = [&](const char* fmt, ...) {
     if (msg && len > 0) {
@@ -136,6 +167,7 @@ long long workspace_bytes(const moe_config_t* c) {
   }
   const long long act_rows = (long long)s.rows_cap * (2 * d + 3 * s.F_pad) + (c->shared_expert ? (long long)s.shared_rows_cap * (d + 3 * s.F_pad) : 0);
   b += act_rows * esz * (c->training ? 2 : 1);
+  if (c->training && overlap_mode() == 2) b += (long long)s.rows_cap * d * esz;   // second half of the double-buffered dispatched rows
   b += T * E * 4 * 4 + T * k * 4 * 6 + (long long)s.rows_cap * 8;
   return b;
 }
@@ -300,36 +332,38 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
 
 // phase 0: everything; 1: everything except the gate|up weight gradient; 2: only that gradient
 // (it does not feed the input gradient, so the un-permute can run beside it).
-int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed, int phase = 0) {
+// parts: 1 = the input-gradient chain (dgrad down + SwiGLU backward, dgrad gate|up), 2 = dW_down, 4 = dW_gate|up
+int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed, int parts = 7) {
   const int d = L->d, Fp = L->F_pad;
   Span whole(L, routed ? -1 : 14, st);
   const int acc = L->grad_valid ? 1 : 0;
   if (L->act == PREC_BF16) {
-    if (phase != 2) {
     // dgu = swiglu'(dy W_d) ; dW_d += dy^T h ; dx = dgu W_gu ; dW_gu += dgu^T x
+    if (parts & 1) {
     tc::GemmArgs a{};
     a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
     a.N = Fp; a.K = d; a.out0 = io.dgu; a.ld0 = 2 * Fp; a.aux = io.gu; a.ldaux = 2 * Fp;
     tc::Operand A{io.dy, G.in_rows, d, 1};
     tc::Operand B{L->wb + io.w_d, d, Fp, G.n_groups};
     { Span sp(L, routed ? 6 : -1, st); CK(tc::gemm_rows_nn(A, B, a, tc::EPI_SWIGLU_BWD, L->sm_count, st)); }
-
+    }
+    if (parts & 2) {
     tc::GemmArgs wd{};
     wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.error_flag = L->error_flag;
     wd.M = d; wd.N = Fp; wd.out0 = L->g + io.w_d; wd.ld0 = Fp; wd.group_stride0 = (long long)d * Fp; wd.accumulate = acc;
     tc::Operand Ad{io.dy, G.in_rows, d, 1};
     tc::Operand Bd{io.h, G.cap_rows, Fp, 1};
     { Span sp(L, routed ? 7 : -1, st); CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st)); }
-
+    }
+    if (parts & 1) {
     tc::GemmArgs b{};
     b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
     b.N = d; b.K = 2 * Fp; b.out0 = io.dx; b.ld0 = d;
     tc::Operand A2{io.dgu, G.cap_rows, 2 * Fp, 1};
     tc::Operand B2{L->wb + io.w_gu, 2 * Fp, d, G.n_groups};
     { Span sp(L, routed ? 8 : -1, st); CK(tc::gemm_rows_nn(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
-
     }
-    if (phase != 1) {
+    if (parts & 4) {
     tc::GemmArgs wg{};
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.error_flag = L->error_flag;
     wg.M = 2 * Fp; wg.N = d; wg.out0 = L->g + io.w_gu; wg.ld0 = d; wg.group_stride0 = 2ll * Fp * d; wg.accumulate = acc;
@@ -338,25 +372,29 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     { Span sp(L, routed ? 9 : -1, st); CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st)); }
     }
   } else {
-    if (phase != 2) {
+    if (parts & 1) {
     SimtGemmArgs a{};
     a.A = (const float*)io.dy; a.B = L->w + io.w_d; a.C = (float*)io.dh;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows;
     a.N = Fp; a.K = d; a.b_group_stride = (long long)d * Fp;
     { Span sp(L, routed ? 6 : -1, st); CK(simt_gemm_nn(a, st));
     CK(launch_swiglu_bwd_f32((const float*)io.dh, (const float*)io.gu, (float*)io.dgu, G.cap_rows, Fp, st)); }
+    }
+    if (parts & 2) {
     SimtGemmArgs wd{};
     wd.A = (const float*)io.dy; wd.B = (const float*)io.h; wd.C = L->g + io.w_d;
     wd.group_row0 = G.row0; wd.n_groups = G.n_groups; wd.a_rows = G.in_rows; wd.b_rows = G.cap_rows;
     wd.M = d; wd.N = Fp; wd.c_group_stride = (long long)d * Fp; wd.accumulate = acc;
     { Span sp(L, routed ? 7 : -1, st); CK(simt_gemm_tn(wd, st)); }
+    }
+    if (parts & 1) {
     SimtGemmArgs b{};
     b.A = (const float*)io.dgu; b.B = L->w + io.w_gu; b.C = (float*)io.dx;
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = 2 * Fp; b.b_group_stride = 2ll * Fp * d;
     { Span sp(L, routed ? 8 : -1, st); CK(simt_gemm_nn(b, st)); }
     }
-    if (phase != 1) {
+    if (parts & 4) {
     SimtGemmArgs wg{};
     wg.A = (const float*)io.dgu; wg.B = (const float*)io.x; wg.C = L->g + io.w_gu;
     wg.group_row0 = G.row0; wg.n_groups = G.n_groups; wg.a_rows = G.cap_rows; wg.b_rows = G.in_rows;
@@ -387,6 +425,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   L->last_tokens = tokens;
   L->last_stream = st;
   if (tokens == 0 && !ep) return MOE_OK;   // an expert-parallel rank with no tokens still serves its experts
+  if (L->training && overlap_mode() == 2) select_parity(L, L->parity ^ 1);   // deferred weight gradients may still read the other half
 
   RouterArgs ra{};
   ra.x = x; ra.w_router = L->w + L->off_router; ra.logits_in = logits_in; ra.valid = valid;
@@ -446,6 +485,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   } else if (ep) {
     rc = ep_forward_experts(L, save != 0, st);
   } else {
+    if ((rc = join_side(L, st)) != MOE_OK) return rc;   // the expert GEMMs rewrite what deferred gradients read
     Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
     ExpertIO io{};
     io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.w_gu = L->off_gu; io.w_d = L->off_d;
@@ -483,23 +523,48 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     return MOE_UNSUPPORTED;
   }
 
-  GatherGradArgs ga{};
-  ga.grad_y = gy; ga.y_perm = ep ? ep_rows(L, 1, L->y_perm) : local_rows(L->y_perm); ga.slot_pos = L->slot_pos; ga.gates = L->gates;
-  ga.grad_y_perm = ep ? ep_rows(L, 2, L->dy_perm) : local_rows(L->dy_perm); ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
-  { Span sp(L, 5, st); CK(launch_gather_grad(ga, L->act, st));
-  if (!ep) CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st)); }
-
-  int rc;
-  if (ep) {
-    rc = ep_backward_experts(L, st, 1);
+  const bool owner_dots = ep && L->peer_ready;   // gate gradient computed where the expert output lives
+  const size_t aux_off = (size_t)L->rows_cap_l * L->d * L->esz;
+  if (owner_dots) {
+    PushGradArgs pa{};
+    pa.grad_y = gy; pa.rows = ep_rows(L, 2, L->dy_perm); pa.slot_pos = L->slot_pos; pa.gates = L->gates;
+    pa.aux_off = aux_off; pa.tokens = tokens; pa.d = L->d; pa.k = L->k;
+    Span sp(L, 5, st); CK(launch_push_grad(pa, L->act, st));
   } else {
-    Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
-    ExpertIO io{};
-    io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
-    io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
-    rc = experts_backward(L, G, io, st, true, 1);
+    GatherGradArgs ga{};
+    ga.grad_y = gy; ga.y_perm = ep ? ep_rows(L, 1, L->y_perm) : local_rows(L->y_perm); ga.slot_pos = L->slot_pos; ga.gates = L->gates;
+    ga.grad_y_perm = ep ? ep_rows(L, 2, L->dy_perm) : local_rows(L->dy_perm); ga.grad_gates = L->grad_gates; ga.tokens = tokens; ga.d = L->d; ga.k = L->k;
+    Span sp(L, 5, st); CK(launch_gather_grad(ga, L->act, st));
+    if (!ep) CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st));
+  }
+
+  // mode 2: only the input-gradient chain stays on the caller's stream; both routed weight gradients
+  // go to the side stream and are joined by whichever later call needs their inputs or outputs
+  const int mode = L->prof_on ? 0 : overlap_mode();
+  const int first_parts = mode == 2 ? 1 : 3;
+  Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
+  ExpertIO io{};
+  io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
+  io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
+  int rc = join_side(L, st);
+  if (rc != MOE_OK) return rc;
+  rc = ep ? ep_backward_experts(L, st, first_parts) : experts_backward(L, G, io, st, true, first_parts);
+  if (rc != MOE_OK) return rc;
+  if (mode == 2) {
+    CK(cudaEventRecord(L->ev_fork, st));
+    CK(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
+    rc = ep ? ep_backward_experts(L, L->side_stream, 6) : experts_backward(L, G, io, L->side_stream, true, 6);
+    if (rc != MOE_OK) return rc;
+    CK(cudaEventRecord(L->ev_join, L->side_stream));
+    L->side_pending = true;
   }
   if (rc != MOE_OK) return rc;
+  if (owner_dots) {
+    PullDotsArgs pd{};
+    pd.rows = ep_rows(L, 2, L->dy_perm); pd.aux_off = aux_off; pd.slot_pos = L->slot_pos; pd.grad_gates = L->grad_gates;
+    pd.slots = tokens * L->k;
+    Span sp(L, 5, st); CK(launch_pull_dots(pd, st));
+  }
 
   if (L->shared && tokens > 0) {
     Groups S{L->shared_meta, L->shared_meta + 2, 1, L->shared_rows_cap, tokens};
@@ -529,29 +594,25 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     CK(tc::gemm_rows_nn(RA, B, g, tc::EPI_STORE, L->sm_count, st));
   }
 
-  // Everything the input gradient needs exists now.  The un-permute (HBM / NVLink bound, a few
-  // warps per SM) runs on a side stream next to the deferred gate|up weight gradient, which
-  // keeps the tensor cores busy and does not feed grad_x.
-  CK(cudaEventRecord(L->ev_fork, st));
-  CK(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
+  // Everything the input gradient needs exists now.  Mode 1: the un-permute (HBM / NVLink bound, a
+  // few warps per SM) runs on the side stream next to the gate|up weight gradient.
+  const cudaStream_t ust = mode == 1 ? L->side_stream : st;
+  if (mode == 1) {
+    CK(cudaEventRecord(L->ev_fork, st));
+    CK(cudaStreamWaitEvent(ust, L->ev_fork, 0));
+  }
   UnpermuteArgs ua{};
   ua.grad_x_perm = ep ? ep_rows(L, 3, L->dx_perm) : local_rows(L->dx_perm); ua.shared = L->shared ? L->dx_s : nullptr;
   ua.extra = L->tc_router ? L->dx_r : nullptr; ua.grad_logits = L->tc_router ? nullptr : L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
-  { Span sp(L, 11, L->side_stream); CK(launch_unpermute(ua, L->act, L->side_stream)); }
-  CK(cudaEventRecord(L->ev_join, L->side_stream));
+  { Span sp(L, 11, ust); CK(launch_unpermute(ua, L->act, ust)); }
+  if (mode == 1) CK(cudaEventRecord(L->ev_join, ust));
 
-  if (ep) {
-    rc = ep_backward_experts(L, st, 2);
-  } else {
-    Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
-    ExpertIO io{};
-    io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
-    io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
-    rc = experts_backward(L, G, io, st, true, 2);
+  if (mode != 2) {
+    rc = ep ? ep_backward_experts(L, st, 4) : experts_backward(L, G, io, st, true, 4);
+    if (rc != MOE_OK) return rc;
   }
-  if (rc != MOE_OK) return rc;
 
   if (L->tc_router && tokens > 0) {
     Span sp(L, 12, st);
@@ -570,7 +631,7 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     rc = ep_allreduce_replicated(L, st);
     if (rc != MOE_OK) return rc;
   }
-  CK(cudaStreamWaitEvent(st, L->ev_join, 0));
+  if (mode == 1) CK(cudaStreamWaitEvent(st, L->ev_join, 0));
   CK(cudaGetLastError());
   L->grad_valid = true;
   return MOE_OK;
@@ -657,9 +718,11 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   DA(L->logits, T * E * 4, false); DA(L->probs, T * E * 4, false); DA(L->lse, T * 4, false);
   DA(L->gates, T * k * 4, false); DA(L->expert_of, T * k * 4, false);
   DA(L->partial, (long long)nb * (E + 2) * 4, false); DA(L->hist, (long long)nb * E * 4, false);
-  DA(L->meta_block, (4 * (E + 1) + 8) * 4, true);
-  L->meta.counts = L->meta_block; L->meta.offsets = L->meta_block + (E + 1); L->meta.pad_off = L->meta_block + 2 * (E + 1);
-  L->meta.tile_start = L->meta_block + 3 * (E + 1); L->meta.total = L->meta_block + 4 * (E + 1);
+  const int halves = L->training && overlap_mode() == 2 ? 2 : 1;   // see moe_layer::parity
+  for (int h = 0; h < 2; ++h) {
+    if (h < halves) DA(L->meta_block2[h], (4 * (E + 1) + 8) * 4, true);
+    else L->meta_block2[h] = L->meta_block2[0];
+  }
   DA(L->stats, (E + 2) * 4, true); DA(L->losses, 2 * 4, true);
   DA(L->slot_pos, T * k * 4, false); DA(L->token_of, T * k * 4, false); DA(L->slot_of, T * k * 4, false);
   DA(L->row_token, (long long)L->rows_cap * 4, false); DA(L->row_gate, (long long)L->rows_cap * 4, false);
@@ -674,7 +737,10 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     const int El = L->E_local, N = L->ep_size, words = 2 * (int)E + 2;
     DA(L->ep_pack, words * 4, true); DA(L->ep_gathered, (long long)N * words * 4, true);
     DA(L->ext_stats, (E + 2) * 4, true); DA(L->ext_counts, E * 4, true);
-    DA(L->local_meta, 3 * (El + 1) * 4, true);
+    for (int h = 0; h < 2; ++h) {
+      if (h < halves) DA(L->local_meta2[h], 3 * (El + 1) * 4, true);
+      else L->local_meta2[h] = L->local_meta2[0];
+    }
     DA(L->dest_base, E * 4, true); DA(L->barrier_word, 4, true);
     CK(cudaMallocHost((void**)&L->dest_base_host, (size_t)E * 4));
     if (L->ep_size > MAX_RANKS) return fail(L, MOE_INVALID_CONFIG, "at most %d expert-parallel ranks", MAX_RANKS);
@@ -684,14 +750,22 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   }
   const long long rc = L->rows_cap, sc = L->shared_rows_cap, es = (long long)L->esz;
   const long long rl = ep ? L->rows_cap_l : rc;   // rows of the buffers the expert GEMMs work on
-  DA(L->x_perm, rc * d * es, true); DA(L->gu, rl * 2 * Fp * es, true); DA(L->h, rl * Fp * es, true);
-  if (ep) { DA(L->x_recv, rl * d * es, true); DA(L->y_recv, rl * d * es, true); }
+  DA(L->x_perm2[0], rc * d * es, true);
+  if (halves == 2 && !ep) DA(L->x_perm2[1], rc * d * es, true); else L->x_perm2[1] = L->x_perm2[0];
+  DA(L->gu, rl * 2 * Fp * es, true); DA(L->h, rl * Fp * es, true);
+  if (ep) {
+    DA(L->x_recv2[0], halves * rl * d * es, true);   // one allocation: it is exported to the peers as a whole
+    L->x_recv2[1] = (char*)L->x_recv2[0] + (halves - 1) * rl * d * es;
+    DA(L->y_recv, rl * d * es, true);
+  }
+  select_parity(L, 0);
   DA(L->y_perm, rc * d * es, true);
   if (L->shared) { DA(L->gu_s, sc * 2 * Fp * es, true); DA(L->h_s, sc * Fp * es, true); DA(L->y_s, sc * d * es, true); }
   if (L->training) {
     DA(L->dy_perm, rc * d * es, true); DA(L->dgu, rl * 2 * Fp * es, true); DA(L->dx_perm, rc * d * es, true);
     if (L->act == PREC_F32) DA(L->dh, rl * Fp * es, true);
-    if (ep) { DA(L->dy_recv, rl * d * es, true); DA(L->dx_recv, rl * d * es, true); }
+    // behind the gradient rows: the gates pushed with them and the dots computed from them (peer transport)
+    if (ep) { DA(L->dy_recv, rl * d * es + rl * 8, true); DA(L->dx_recv, rl * d * es, true); }
     if (L->shared) {
       DA(L->dgu_s, sc * 2 * Fp * es, true); DA(L->dx_s, sc * d * es, true);
       if (L->act == PREC_F32) DA(L->dh_s, sc * Fp * es, true);
@@ -770,6 +844,7 @@ static int read_arena(moe_layer* L, const float* arena, int which, int expert, f
   const long long n = (long long)rows * cols;
   const bool dev = is_device_pointer(dst);
   float* out = dev ? dst : L->stage;
+  if (L->side_pending) { CK(cudaStreamSynchronize(L->side_stream)); L->side_pending = false; }   // deferred weight gradients
   unpack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(arena + s.offset, out, rows, cols, s.ld, s.kind, zero ? 1 : 0); count_launch();
   CK(cudaGetLastError());
   if (!dev) CK(cudaMemcpy(dst, L->stage, (size_t)n * 4, cudaMemcpyDeviceToHost));
@@ -873,6 +948,7 @@ int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, f
   ENTER(L);
   if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
   cudaStream_t st = (cudaStream_t)stream;
+  { const int jr = join_side(L, st); if (jr != MOE_OK) return jr; }
   if (!L->grad_valid) CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
   AdamArgs a{};
   a.w = L->w; a.g = L->g; a.m = L->m; a.v = L->v; a.w_bf16 = L->wb; a.n = L->n_params;
@@ -1036,7 +1112,7 @@ int32_t moe_ep_init(moe_layer_t* L, const void* unique_id, int32_t len) {
 int32_t moe_ep_export_buffers(moe_layer_t* L, void* out, int32_t len) {
   ENTER(L);
   if (L->ep_size <= 1 || !out || len < (int32_t)(4 * sizeof(cudaIpcMemHandle_t))) { L->err = "InvalidInput: bad export request"; return MOE_INVALID_INPUT; }
-  void* bufs[4] = {L->x_recv, L->y_recv, L->training ? L->dy_recv : L->x_recv, L->training ? L->dx_recv : L->y_recv};
+  void* bufs[4] = {L->x_recv2[0], L->y_recv, L->training ? L->dy_recv : L->x_recv, L->training ? L->dx_recv : L->y_recv};
   cudaIpcMemHandle_t* h = (cudaIpcMemHandle_t*)out;
   for (int b = 0; b < 4; ++b) CK(cudaIpcGetMemHandle(&h[b], bufs[b]));
   return MOE_OK;
@@ -1046,7 +1122,7 @@ int32_t moe_ep_import_buffers(moe_layer_t* L, int32_t rank, const void* handles,
   ENTER(L);
   if (L->ep_size <= 1 || rank < 0 || rank >= L->ep_size || !handles || len < (int32_t)(4 * sizeof(cudaIpcMemHandle_t))) { L->err = "InvalidInput: bad import request"; return MOE_INVALID_INPUT; }
   if (rank == L->ep_rank) {
-    L->peer_base[0][rank] = L->x_recv; L->peer_base[1][rank] = L->y_recv;
+    L->peer_base[0][rank] = L->x_recv2[0]; L->peer_base[1][rank] = L->y_recv;
     L->peer_base[2][rank] = L->dy_recv; L->peer_base[3][rank] = L->dx_recv;
   } else {
     const cudaIpcMemHandle_t* h = (const cudaIpcMemHandle_t*)handles;

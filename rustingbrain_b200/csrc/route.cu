@@ -143,60 +143,88 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
   }
   __syncthreads();
 
-  // One thread per token row: softmax, log-sum-exp, top-k, gates.
-  if (tid < ROUTER_ROWS) {
-    const int r = tid;
+  // Four adjacent lanes per token row.  Everything that has an order in the reference keeps it: the
+  // denominator is summed by one lane in expert order, and the top-k scan (strict `>`, lowest index
+  // on ties, moe.rs:549-574) is split into four contiguous index ranges whose winners are merged in
+  // range order, which selects the same expert as one scan over all of them.
+  {
+    const int r = tid >> 2, part = tid & 3;
+    const int lane = tid & 31, lead = lane & ~3;
+    const unsigned gmask = 0xFu << lead;
     int is_valid = 0;
     if (r < rows) {
       const int t = t0 + r;
       float* row = lg + r * ldl;
       if (logits_out)
-        for (int e = 0; e < E; ++e) logits_out[(size_t)t * E + e] = row[e];
+        for (int e = part; e < E; e += 4) logits_out[(size_t)t * E + e] = row[e];
       float mx = -INFINITY;
-      for (int e = 0; e < E; ++e) mx = fmaxf(mx, row[e]);
+      for (int e = part; e < E; e += 4) mx = fmaxf(mx, row[e]);
+      mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(gmask, mx, 2));
+      for (int e = part; e < E; e += 4) row[e] = expf_libm(__fsub_rn(row[e], mx));
+      __syncwarp(gmask);
       float sum = 0.f;
-      for (int e = 0; e < E; ++e) {
-        const float ex = expf_libm(__fsub_rn(row[e], mx));
-        row[e] = ex;
-        sum = __fadd_rn(sum, ex);
-      }
+      if (part == 0)
+        for (int e = 0; e < E; ++e) sum = __fadd_rn(sum, row[e]);
+      sum = __shfl_sync(gmask, sum, lead);
       const float l = mx + logf(sum);
-      if (sum > 0.f)
-        for (int e = 0; e < E; ++e) row[e] = __fdiv_rn(row[e], sum);
-      for (int e = 0; e < E; ++e) probs[(size_t)t * E + e] = row[e];
-      lse[t] = l;
-      row_lse[r] = l;
+      for (int e = part; e < E; e += 4) {
+        const float p = sum > 0.f ? __fdiv_rn(row[e], sum) : row[e];
+        row[e] = p;
+        probs[(size_t)t * E + e] = p;
+      }
+      __syncwarp(gmask);
       is_valid = (valid == nullptr || valid[t] != 0) ? 1 : 0;
       int* s = sel + r * k;
+      if (part == 0) { lse[t] = l; row_lse[r] = l; }
       if (!is_valid) {
-        for (int j = 0; j < k; ++j) {
+        for (int j = part; j < k; j += 4) {
           s[j] = -1;
           expert_of[(size_t)t * k + j] = -1;
           gates[(size_t)t * k + j] = 0.f;
         }
       } else {
+        const int span = (E + 3) / 4;                 // <= 64: one bit per expert of this lane's range
+        const int q0 = min(E, part * span), q1 = min(E, q0 + span);
+        unsigned long long taken = 0ull;
         float total = 0.f;
         for (int j = 0; j < k; ++j) {
-          int best = -1;
-          for (int e = 0; e < E; ++e) {
-            bool taken = false;
-            for (int q = 0; q < j; ++q) taken |= (s[q] == e);
-            if (taken) continue;
-            if (best < 0 || row[e] > row[best]) best = e;
+          int best = -1, first = -1;
+          float bv = 0.f;
+          for (int e = q0; e < q1; ++e) {
+            if ((taken >> (e - q0)) & 1ull) continue;
+            if (first < 0) first = e;
+            const float v = row[e];
+            if (v != v) continue;                     // a NaN never compares greater
+            if (best < 0 || v > bv) { best = e; bv = v; }
           }
-          s[j] = best;
-          total = __fadd_rn(total, row[best]);
+          int gb = -1, gfirst = -1;
+          float gv = 0.f;
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int b = __shfl_sync(gmask, best, lead + p);
+            const float v = __shfl_sync(gmask, bv, lead + p);
+            const int f = __shfl_sync(gmask, first, lead + p);
+            if (gfirst < 0 && f >= 0) gfirst = f;
+            if (b >= 0 && (gb < 0 || v > gv)) { gb = b; gv = v; }
+          }
+          // the scan starts from the first free expert; if that one is NaN nothing replaces it
+          if (gfirst >= 0 && (gb < 0 || row[gfirst] != row[gfirst])) gb = gfirst;
+          if (gb >= q0 && gb < q1) taken |= 1ull << (gb - q0);
+          if (part == 0) s[j] = gb;
+          total = __fadd_rn(total, row[gb]);
         }
-        for (int j = 0; j < k; ++j) {
+        __syncwarp(gmask);
+        for (int j = part; j < k; j += 4) {
           const float p = row[s[j]];
           expert_of[(size_t)t * k + j] = s[j];
           gates[(size_t)t * k + j] = total > 0.f ? __fdiv_rn(p, total) : p;
         }
       }
-    } else {
+    } else if (part == 0) {
       for (int j = 0; j < k; ++j) sel[r * k + j] = -1;
     }
-    row_valid[r] = is_valid;
+    if (part == 0) row_valid[r] = is_valid;
   }
   __syncthreads();
 
@@ -232,16 +260,27 @@ finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int n
   const int tid = threadIdx.x;
   for (int e = tid; e < E + 2; e += blockDim.x) {
     double s = 0.0;
-    for (int b = 0; b < nb; ++b) s += (double)partial[(size_t)b * (E + 2) + e];
+    for (int b0 = 0; b0 < nb; b0 += 8) {            // eight independent loads, then the ordered sum
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = b0 + i < nb ? partial[(size_t)(b0 + i) * (E + 2) + e] : 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) if (b0 + i < nb) s += (double)v[i];
+    }
     s_sums[e] = (float)s;
     stats[e] = (float)s;
   }
   for (int e = tid; e < E; e += blockDim.x) {
     int run = 0;
-    for (int b = 0; b < nb; ++b) {
-      const int h = hist[(size_t)b * E + e];
-      hist[(size_t)b * E + e] = run;
-      run += h;
+    for (int b0 = 0; b0 < nb; b0 += 8) {
+      int h[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = b0 + i < nb ? hist[(size_t)(b0 + i) * E + e] : 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (b0 + i < nb) hist[(size_t)(b0 + i) * E + e] = run;
+        run += h[i];
+      }
     }
     s_counts[e] = run;
     meta.counts[e] = run;
