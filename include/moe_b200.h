@@ -203,6 +203,54 @@ int32_t moe_route_noalloc(const float* logits_dev, const uint8_t* valid_dev, int
 /* Device synchronisation for timing (TransformerLm::synchronize, transformer.rs:1323-1334). */
 int32_t moe_synchronize(moe_layer_t* layer);
 
+/* ---- binary snapshots -------------------------------------------------------------------------
+ * Readers for the two files the reference writes beside a model, so that a MoE layer can be filled
+ * straight from them (no whole-model load, no dequantize-then-requantize detour for int8 files):
+ *   weights   "RBWTS001"  TransformerLm::save_bin / load_bin (transformer.rs:1809-1932):
+ *             magic, u64 header length, JSON header {config, optimizer, optimizer_step, precision},
+ *             u64 parameter count, then per parameter u64 rows, u64 cols and either rows*cols f32
+ *             (precision "F32") or, per row, an f32 scale followed by `cols` int8 values ("Q8");
+ *   moments   "RBOPT001"  save_optimizer_state / load_optimizer_state (transformer.rs:1675-1753):
+ *             magic, u64 parameter count, u64 step, then per parameter u64 rows, u64 cols and the
+ *             first and second Adam moment as f32 (a frozen parameter is written as 0 x 0).
+ * All integers and floats are little endian.  Parameters come in TransformerLm::params_mut order
+ * (transformer.rs:1620-1630): embedding; per block attention norm, query, key, value, output,
+ * feed-forward norm, then the feed-forward (dense: gate, up, down — or up, down for the GELU
+ * variant; MoE: router, every expert's gate, up, down, then the shared expert's); final norm;
+ * the LM head unless the embeddings are tied.  Files of a model with LoRA adapters attached
+ * (config.lora set: two more parameters per projection) are refused with MOE_UNSUPPORTED. */
+typedef struct moe_snapshot_info {
+  int64_t vocab_size, d_model, n_layers, n_heads, n_kv_heads, head_dim, d_ff, moe_d_ff;
+  int64_t num_experts, experts_per_token, max_seq_len;
+  int32_t shared_expert, tie_embeddings, causal;
+  float aux_loss_weight, router_z_loss_weight, rope_base, rmsnorm_eps;
+  int32_t precision;            /* MOE_PRECISION_F32 or MOE_PRECISION_Q8: how the file stores weights */
+  int32_t n_moe_layers;         /* entries used in moe_layers */
+  int32_t moe_layers[256];      /* block indices with a MoE feed-forward, ascending */
+  int64_t optimizer_step;
+  int64_t parameter_count;      /* as written in the file */
+  int32_t dense_ffn_params;     /* 3 (SwiGLU) or 2 (GELU) parameters per dense feed-forward, 0 if none */
+} moe_snapshot_info_t;
+
+/* Parses the header of a weight file.  Host only (no GPU needed).  `message` (optional) receives
+ * the error text: InvalidSnapshot for a wrong magic, truncated file or inconsistent counts. */
+int32_t moe_snapshot_info(const char* weights_path, moe_snapshot_info_t* out, char* message, int32_t message_len);
+
+/* Fills the layer from block `block_index` of a weight file.  The handle's shape (d_model, experts,
+ * d_ff, shared expert) must match the file's configuration.  Any combination of file precision and
+ * handle precision works: an int8 file feeds an int8 handle row for row (scales and bytes as stored;
+ * the router, which stays f32 in an int8 handle, is dequantized), an int8 file is dequantized for an
+ * f32 / bf16 handle exactly as load_bin does (value = int8 * scale), an f32 file is quantized for an
+ * int8 handle on the reference's grid (scale = max|row| / 127, round half away from zero, clamp to
+ * +-127; transformer.rs:514-519, quantized.rs:8-12).  An expert-parallel handle takes its own experts only. */
+int32_t moe_load_snapshot_layer(moe_layer_t* layer, const char* weights_path, int32_t block_index);
+
+/* Restores the Adam moments of block `block_index` from a moments file; `info` is the configuration
+ * of the matching weight file (the moments file has no header of its own).  Returns the file's step
+ * counter in *step (optional). */
+int32_t moe_load_optimizer_layer(moe_layer_t* layer, const char* moments_path, const moe_snapshot_info_t* info,
+                                 int32_t block_index, int64_t* step);
+
 #ifdef __cplusplus
 }
 #endif

@@ -8,5 +8,8 @@ interface over that ABI.
 from .moe import (CudaError, InvalidConfig, InvalidInput, MoeCache, MoeConfig, MoeLayer, NetworkError,
                   DEFAULT_AUX_LOSS_WEIGHT, DEFAULT_ROUTER_Z_LOSS_WEIGHT)
 
-__all__ = ["MoeConfig", "MoeLayer", "MoeCache", "NetworkError", "InvalidConfig", "InvalidInput", "CudaError",
+from .snapshot import InvalidSnapshot, SnapshotInfo, snapshot_info, write_optimizer_state, write_snapshot
+
+__all__ = ["InvalidSnapshot", "SnapshotInfo", "snapshot_info", "write_snapshot", "write_optimizer_state",
+           "MoeConfig", "MoeLayer", "MoeCache", "NetworkError", "InvalidConfig", "InvalidInput", "CudaError",
            "DEFAULT_AUX_LOSS_WEIGHT", "DEFAULT_ROUTER_Z_LOSS_WEIGHT"]

@@ -25,6 +25,19 @@ class MoeConfigC(C.Structure):
     ]
 
 
+class SnapshotInfoC(C.Structure):
+    """moe_snapshot_info_t of include/moe_b200.h."""
+    _fields_ = [(n, C.c_int64) for n in (
+        "vocab_size", "d_model", "n_layers", "n_heads", "n_kv_heads", "head_dim", "d_ff", "moe_d_ff",
+        "num_experts", "experts_per_token", "max_seq_len")] + [
+        ("shared_expert", C.c_int32), ("tie_embeddings", C.c_int32), ("causal", C.c_int32),
+        ("aux_loss_weight", C.c_float), ("router_z_loss_weight", C.c_float), ("rope_base", C.c_float),
+        ("rmsnorm_eps", C.c_float), ("precision", C.c_int32), ("n_moe_layers", C.c_int32),
+        ("moe_layers", C.c_int32 * 256), ("optimizer_step", C.c_int64), ("parameter_count", C.c_int64),
+        ("dense_ffn_params", C.c_int32),
+    ]
+
+
 _lib = None
 
 
@@ -63,6 +76,9 @@ def lib() -> C.CDLL:
         "moe_get_routing": (i32, [vp, ip, fp, ip, ip, ip, ip]),
         "moe_get_router_cache": (i32, [vp, fp, fp, fp]),
         "moe_synchronize": (i32, [vp]),
+        "moe_snapshot_info": (i32, [C.c_char_p, C.POINTER(SnapshotInfoC), C.c_char_p, i32]),
+        "moe_load_snapshot_layer": (i32, [vp, C.c_char_p, i32]),
+        "moe_load_optimizer_layer": (i32, [vp, C.c_char_p, C.POINTER(SnapshotInfoC), i32, C.POINTER(C.c_int64)]),
         "moe_route_noalloc": (i32, [vp, vp, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, C.c_char_p, i32]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),

@@ -387,9 +387,10 @@ cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream) {
 
 template <typename T>
 __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs a) {
-  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (t >= a.tokens) return;
+  // grid-stride over tokens: the launcher may cap the grid so that the kernel fits beside a
+  // persistent GEMM on every SM
+  for (int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5); t < a.tokens; t += gridDim.x * CB_WARPS) {
   int pos[MAX_TOPK];
   float unused[MAX_TOPK];
   const int n = ordered_slots(a.expert_of, a.slot_pos, nullptr, t, a.k, pos, unused);
@@ -452,11 +453,13 @@ __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs 
       gx[c] = from_f32<T>(acc);
     }
   }
+  }   // tokens
 }
 
-cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream) {
+cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream, int max_blocks) {
   if (a.tokens <= 0) return cudaSuccess;
-  const int grid = ceil_div(a.tokens, CB_WARPS);
+  int grid = ceil_div(a.tokens, CB_WARPS);
+  if (max_blocks > 0) grid = min(grid, max_blocks);
   if (precision == PREC_BF16) { unpermute_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
   else { unpermute_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
   return cudaGetLastError();

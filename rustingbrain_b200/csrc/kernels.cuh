@@ -159,7 +159,8 @@ struct UnpermuteArgs {
   void* grad_x;
   int tokens, d, E, k, accumulate;
 };
-cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream);
+// max_blocks > 0 caps the grid (the kernel strides over the tokens)
+cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t stream, int max_blocks = 0);
 
 // dW_r[e, c] (+)= sum_t grad_logits[t,e] * x[t,c]; deterministic two-stage reduction.
 struct RouterWgradArgs {

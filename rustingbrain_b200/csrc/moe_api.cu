@@ -594,24 +594,29 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     CK(tc::gemm_rows_nn(RA, B, g, tc::EPI_STORE, L->sm_count, st));
   }
 
-  // Everything the input gradient needs exists now.  Mode 1: the un-permute (HBM / NVLink bound, a
-  // few warps per SM) runs on the side stream next to the gate|up weight gradient.
-  const cudaStream_t ust = mode == 1 ? L->side_stream : st;
-  if (mode == 1) {
-    CK(cudaEventRecord(L->ev_fork, st));
-    CK(cudaStreamWaitEvent(ust, L->ev_fork, 0));
-  }
+  // Everything the input gradient needs exists now.
   UnpermuteArgs ua{};
   ua.grad_x_perm = ep ? ep_rows(L, 3, L->dx_perm) : local_rows(L->dx_perm); ua.shared = L->shared ? L->dx_s : nullptr;
   ua.extra = L->tc_router ? L->dx_r : nullptr; ua.grad_logits = L->tc_router ? nullptr : L->grad_logits;
   ua.w_router = L->w + L->off_router; ua.expert_of = L->expert_of; ua.slot_pos = L->slot_pos; ua.grad_x = gx;
   ua.tokens = tokens; ua.d = L->d; ua.E = L->E; ua.k = L->k; ua.accumulate = accumulate;
-  { Span sp(L, 11, ust); CK(launch_unpermute(ua, L->act, ust)); }
-  if (mode == 1) CK(cudaEventRecord(L->ev_join, ust));
-
-  if (mode != 2) {
+  if (mode == 1) {
+    // The gate|up weight gradient goes first so that its persistent CTAs are resident on every SM;
+    // the un-permute (HBM / NVLink bound) follows on the side stream with two CTAs per SM, which fit
+    // in the registers and shared memory the GEMM leaves free.  The other order lets the un-permute's
+    // thousands of small CTAs fill the SMs and the GEMM waits for all of them.
+    CK(cudaEventRecord(L->ev_fork, st));
     rc = ep ? ep_backward_experts(L, st, 4) : experts_backward(L, G, io, st, true, 4);
     if (rc != MOE_OK) return rc;
+    CK(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
+    CK(launch_unpermute(ua, L->act, L->side_stream, 2 * L->sm_count));
+    CK(cudaEventRecord(L->ev_join, L->side_stream));
+  } else {
+    { Span sp(L, 11, st); CK(launch_unpermute(ua, L->act, st)); }
+    if (mode != 2) {
+      rc = ep ? ep_backward_experts(L, st, 4) : experts_backward(L, G, io, st, true, 4);
+      if (rc != MOE_OK) return rc;
+    }
   }
 
   if (L->tc_router && tokens > 0) {

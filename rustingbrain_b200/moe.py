@@ -232,6 +232,20 @@ class MoeLayer:
             raise InvalidInput("int8 weight shape %s / %s, expected %s" % (q.shape, scales.shape, (rows, cols)))
         self._ck(_lib.lib().moe_set_weight_q8(self._h, which, expert, q.ctypes.data, scales.ctypes.data, rows, cols))
 
+    def load_snapshot(self, path, block: int):
+        """Fills the layer from MoE block ``block`` of a weight file written by the reference's
+        ``save_bin`` (transformer.rs:1809-1860), f32 or int8, whatever this layer's precision."""
+        self._ck(_lib.lib().moe_load_snapshot_layer(self._h, str(path).encode(), int(block)))
+
+    def load_optimizer_state(self, path, info, block: int) -> int:
+        """Restores the Adam moments of MoE block ``block`` from a ``save_optimizer_state`` file
+        (transformer.rs:1675-1696); ``info`` is `snapshot.snapshot_info` of the matching weight file.
+        Returns the file's step counter."""
+        step = C.c_int64(0)
+        self._ck(_lib.lib().moe_load_optimizer_layer(self._h, str(path).encode(), C.byref(info._c), int(block),
+                                                     C.byref(step)))
+        return int(step.value)
+
     def set_weights(self, router, gate, up, down, shared=None):
         """router [E,d]; gate/up [E,F,d]; down [E,d,F]; shared = (gate, up, down) of one expert."""
         self.set_weight(W_ROUTER, 0, router)
