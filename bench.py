@@ -38,6 +38,11 @@ WORKLOADS = {
                 name="HBM-kernel profiling case: 16384 tokens, d_model 2048, 8 experts top-8, d_ff 256"),
     "cfg5": dict(T=64, d=1024, E=16, k=2, F=2816, shared=True, seed=9, precision="q8", zipf=False,
                  name="KV-cached decode step through a quantized MoE layer: 64 sequences x 1 token, d_model 1024, 16 experts top-2 + shared, d_ff 2816, int8 weights"),
+    # BASELINE config 2 is a whole-model train_step; only its MoE layers are on this path.  One of its
+    # six MoE blocks (layers 2..7: 8 experts top-2, expert d_ff 352 + shared, 8 x 1024 tokens), forward +
+    # backward + Adam, bf16 GEMMs over f32 master weights.
+    "cfg2": dict(T=8192, d=512, E=8, k=2, F=352, shared=True, seed=42, precision="bf16", zipf=False, adam=True,
+                 name="one MoE block of the 55M language model, fwd+bwd+Adam bf16: 8192 tokens, d_model 512, 8 experts top-2 + shared, d_ff 352"),
     "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
                  name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
 }
@@ -315,6 +320,11 @@ def main():
         _, cache = layer.forward_train(x, out=y)
         layer.zero_grad()
         layer.backward(cache, gy, out=gx)
+        if w.get("adam"):
+            step.n += 1
+            layer.step_adam(lr=3e-4, step=step.n)
+
+    step.n = 0
 
     def barrier():
         torch.cuda.synchronize()
