@@ -44,6 +44,13 @@ def _worker(rank, world, port, precision, transport, ret):
         dt = torch.float32 if precision == "f32" else torch.bfloat16
         x = torch.from_numpy(xs[rank]).cuda().to(dt)
         gy = torch.from_numpy(gys[rank]).cuda().to(dt)
+        if os.environ.get("MOE_B200_OVERLAP", "0") != "0":
+            # passes on other data first: with overlap their weight gradients may still run while the
+            # checked pass dispatches, and the double-buffered halves alternate
+            for scale in (0.5, -1.5):
+                _, c0 = layer.forward_train(x * scale)
+                layer.zero_grad()
+                layer.backward(c0, gy * scale)
         y, cache = layer.forward_train(x)
         layer.zero_grad()
         gx = layer.backward(cache, gy)
@@ -75,8 +82,11 @@ def _worker(rank, world, port, precision, transport, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("precision,transport", [("f32", "nccl"), ("bf16", "nccl"), ("f32", "peer"), ("bf16", "peer")])
-def test_expert_parallel_matches_single_device(precision, transport):
+@pytest.mark.parametrize("precision,transport,overlap", [
+    ("f32", "nccl", "0"), ("bf16", "nccl", "0"), ("f32", "peer", "0"), ("bf16", "peer", "0"),
+    ("bf16", "peer", "1"), ("bf16", "peer", "2"), ("bf16", "nccl", "2")])
+def test_expert_parallel_matches_single_device(precision, transport, overlap, monkeypatch):
+    monkeypatch.setenv("MOE_B200_OVERLAP", overlap)   # read by the spawned ranks' copy of the library
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
