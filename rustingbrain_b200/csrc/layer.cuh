@@ -51,7 +51,8 @@ struct moe_layer {
   float *stats = nullptr, *losses = nullptr;
   int *slot_pos = nullptr, *row_token = nullptr, *token_of = nullptr, *slot_of = nullptr;
   float* row_gate = nullptr;
-  int* shared_meta = nullptr;   // [4]: row0[0..1], tstart[0..1] of the dense (shared expert) group
+  int* shared_meta = nullptr;   // [4]: row0[0..1], tstart[0..1] of the dense (shared expert) group: entry `tokens` of the table
+  int* shared_meta_table = nullptr;   // [max_tokens + 1][4]
   int* error_flag = nullptr;
 
   // activations (element type `act`)

@@ -251,9 +251,14 @@ __global__ void pack_q8_kernel(const int8_t* __restrict__ src, const float* __re
   dst[(long long)pr * ld + c] = src[i];
   if (c == 0) scale_dst[pr] = scale_src[r];
 }
-__global__ void shared_meta_kernel(int* meta, int tokens) {
-  const int rows = round_up(tokens, GROUP_ALIGN);
-  meta[0] = 0; meta[1] = rows; meta[2] = 0; meta[3] = rows / GROUP_ALIGN;
+// Group table of the dense (shared expert, router) GEMMs for every possible token count: entry t is
+// {row0[0], row0[1], tile_start[0], tile_start[1]} of one group of t rows.  Filled once, so a pass only
+// picks a pointer instead of launching a kernel.
+__global__ void shared_meta_table_kernel(int* table, int max_tokens) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t > max_tokens) return;
+  const int rows = round_up(t, GROUP_ALIGN);
+  table[4 * t] = 0; table[4 * t + 1] = rows; table[4 * t + 2] = 0; table[4 * t + 3] = rows / GROUP_ALIGN;
 }
 
 bool is_device_pointer(const void* p) {
@@ -432,7 +437,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.tokens = tokens; ra.d = L->d; ra.E = L->E; ra.k = L->k;
   ra.logits_out = L->logits; ra.probs = L->probs; ra.lse = L->lse; ra.expert_of = L->expert_of; ra.gates = L->gates;
   ra.partial = L->partial; ra.hist = L->hist;
-  shared_meta_kernel<<<1, 1, 0, st>>>(L->shared_meta, tokens); count_launch();
+  L->shared_meta = L->shared_meta_table + 4 * tokens;
   { Span sp(L, 0, st);
   if (L->tc_router && !logits_in) {
     // logits = x W_r^T on the tensor cores, f32 out; softmax/top-k then read them back
@@ -731,7 +736,10 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   DA(L->stats, (E + 2) * 4, true); DA(L->losses, 2 * 4, true);
   DA(L->slot_pos, T * k * 4, false); DA(L->token_of, T * k * 4, false); DA(L->slot_of, T * k * 4, false);
   DA(L->row_token, (long long)L->rows_cap * 4, false); DA(L->row_gate, (long long)L->rows_cap * 4, false);
-  DA(L->shared_meta, 4 * 4, true); DA(L->error_flag, 4, true);
+  DA(L->shared_meta_table, (T + 1) * 16, false); DA(L->error_flag, 4, true);
+  shared_meta_table_kernel<<<(unsigned)((T + 256) / 256), 256>>>(L->shared_meta_table, (int)T);
+  CK(cudaGetLastError());
+  L->shared_meta = L->shared_meta_table;
 
   const bool ep = L->ep_size > 1;
   if (ep) {

@@ -254,7 +254,7 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
 __global__ void __launch_bounds__(256)
 finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int nb, int E, int k, float aux_w,
                 float z_w, RouteMeta meta, float* __restrict__ stats /*[E+2]: sums, lse2, V*/,
-                float* __restrict__ losses /*[2]*/, int align) {
+                float* __restrict__ losses /*[2]*/, int align, int add_base) {
   __shared__ int s_counts[MAX_EXPERTS];
   __shared__ float s_sums[MAX_EXPERTS + 2];
   const int tid = threadIdx.x;
@@ -321,6 +321,10 @@ finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int n
     }
     losses[0] = aux;
     losses[1] = z;
+  }
+  if (add_base) {   // few blocks: the cursors get their group base here instead of in a second launch
+    __syncthreads();
+    for (int i = tid; i < nb * E; i += blockDim.x) hist[i] += meta.pad_off[i % E];
   }
 }
 
@@ -599,8 +603,9 @@ cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
                             int align, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
-  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align); count_launch();
-  if (nb > 0) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
+  const int fold = nb <= 16 ? 1 : 0;
+  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align, fold); count_launch();
+  if (nb > 0 && !fold) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
   return cudaGetLastError();
 }
 
