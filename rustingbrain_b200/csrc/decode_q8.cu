@@ -51,12 +51,18 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 
+// Work list.  An item is one 16-row token tile of one group (an expert, or the shared expert over
+// all tokens) times one block of output columns; items are numbered tile-major, so neighbours share
+// their token tile.  The grid is two CTAs per SM whatever the routing turned out to be; CTA c takes
+// the contiguous item range [c n / grid, (c + 1) n / grid) and stages a token tile only when it changes.
+//
 // A warp owns two 8-column MMA tiles that share the token fragments: for the fused pass the gate
 // rows of 8 hidden columns and the matching up rows, otherwise 16 adjacent output columns.
 // U = 16-byte loads per lane and tile in one chunk of 64 U reduction values; K is a multiple of 64 U.
 template <bool SWIGLU, int U>
-__global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
+__global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
   extern __shared__ __align__(16) unsigned char q8_smem[];
+  __shared__ int tile_start[MAX_EXPERTS + 2];   // first token tile of every group
   // Token tile in MMA-fragment order: rows r and r + 8 are interleaved so that one 16-byte unit holds
   // the four A registers of a lane, {x[r][k..k+1], x[r+8][k..k+1], x[r][k+2..k+3], x[r+8][k+2..k+3]} for a
   // group of four reduction values.  Row pair r has K/4 units plus one unit of padding, and units 8..15 of
@@ -64,60 +70,99 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
   // different banks.
   const int K = a.K;
   const int pitch = (K / 4 + 1) * 16;   // bytes per row pair
-  const int g = blockIdx.z, m0 = blockIdx.y * Q8_ROWS;
-  int rows;
-  const bf16* xin;
-  bf16* out;
-  if (g < a.E) {
-    rows = a.counts[g];
-    const size_t base = (size_t)a.pad_off[g];
-    xin = a.x_rows + base * K;
-    out = a.out_rows + base * a.ldo;
-  } else {
-    rows = a.tokens;
-    xin = a.x_shared;
-    out = a.out_shared;
-  }
-  if (m0 >= rows) return;
-  const int mrows = min(Q8_ROWS, rows - m0);
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
+  const int G = a.E + (a.x_shared ? 1 : 0);
+  if (tid == 0) {
+    int run = 0;
+    for (int g = 0; g < G; ++g) {
+      tile_start[g] = run;
+      run += ceil_div(g < a.E ? a.counts[g] : a.tokens, Q8_ROWS);
+    }
+    tile_start[G] = run;
+  }
+  __syncthreads();
 
   constexpr int COLS = SWIGLU ? 8 : 16;               // output columns per warp
   constexpr int STEP = Q8_CHUNK * U;                  // reduction values per chunk
   const int chunks = K / STEP;
   const int n_blocks = ceil_div(a.N, COLS * Q8_WARPS);
-  const int8_t* wbase = a.w + (size_t)g * a.w_group_stride + 16 * q;
+  const long long n_items = (long long)tile_start[G] * n_blocks;
+  const int i0 = (int)(n_items * blockIdx.x / gridDim.x), i1 = (int)(n_items * (blockIdx.x + 1) / gridDim.x);
+  if (i0 >= i1) return;
+  const int n0_warp = warp * COLS;
   const size_t tile1 = (size_t)(SWIGLU ? GU_BLOCK : 8) * K;   // second tile's rows relative to the first
-  // first weight row of this lane in column block nb (nullptr when the warp has no columns there)
-  auto row_ptr0 = [&](int nb) -> const int8_t* {
-    const int n0 = (nb * Q8_WARPS + warp) * COLS;
-    if (nb >= n_blocks || n0 >= a.N) return nullptr;
-    return wbase + (size_t)(SWIGLU ? gu_row(0, n0 + gq) : n0 + gq) * K;
+
+  // A cursor walks the items of this CTA: (token tile, its group, column block).
+  struct Cursor { int item, tile, g, nb, c; };
+  auto seek = [&](Cursor& cu, int item) {
+    cu.item = item;
+    cu.c = 0;
+    if (item >= i1) return;
+    cu.tile = item / n_blocks;
+    cu.nb = item - cu.tile * n_blocks;
+    while (tile_start[cu.g + 1] <= cu.tile) ++cu.g;   // items only move forward
+  };
+  // weights are stored in blocks of 8 rows x 64 reduction values (512 contiguous bytes): lane l reads
+  // bytes [16 l, 16 l + 16) of a block = row l / 4, reduction values 16 (l % 4) .. + 15
+  auto stripe = [&](const Cursor& cu) -> const int8_t* {
+    const int n0 = cu.nb * Q8_WARPS * COLS + n0_warp;
+    if (cu.item >= i1 || n0 >= a.N) return nullptr;   // warp-uniform
+    return a.w + (size_t)cu.g * a.w_group_stride + (size_t)(SWIGLU ? gu_row(0, n0) : n0) * K + 16 * lane;
   };
   struct Chunk { uint4 w[U], u[U]; };
   // The weight stream does not depend on the tokens: two register sets alternate so that the loads
-  // of the next chunk are in flight while this one is multiplied, and the first chunk is requested
-  // before the token tile is staged.
-  const int8_t* fp = row_ptr0(blockIdx.x);   // fetch cursor
-  int f_nb = blockIdx.x, f_c = 0;
+  // of the next chunk are in flight while this one is multiplied, across item boundaries too, and the
+  // first chunk is requested before the first token tile is staged.
+  Cursor fc{0, 0, 0, 0, 0};
+  seek(fc, i0);
+  const int8_t* fp = stripe(fc);
   auto fetch = [&](Chunk& ch) {
     if (fp) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        ch.w[u] = __ldg(reinterpret_cast<const uint4*>(fp + Q8_CHUNK * u));
-        ch.u[u] = __ldg(reinterpret_cast<const uint4*>(fp + tile1 + Q8_CHUNK * u));
+        ch.w[u] = __ldg(reinterpret_cast<const uint4*>(fp + 512 * u));
+        ch.u[u] = __ldg(reinterpret_cast<const uint4*>(fp + tile1 + 512 * u));
       }
-      fp += STEP;
+      fp += 512 * U;
     }
-    if (++f_c == chunks) { f_c = 0; f_nb += gridDim.x; fp = row_ptr0(f_nb); }
+    if (++fc.c == chunks) { seek(fc, fc.item + 1); fp = stripe(fc); }
   };
   Chunk ca, cb;
   fetch(ca);
 
-  {
-    // the token rows of this tile as f16, eight independent 16-byte loads in flight per thread
-    constexpr int SU = 8;
+  Cursor mc{0, 0, 0, 0, 0};
+  seek(mc, i0);
+  int staged_tile = -1, mrows = 0;
+  bf16* out = nullptr;
+  const float* sc = nullptr;
+  // this lane's fragments: unit (k / 4) of row pair gq; for quarter-chunks 2 and 3 the halves are swapped
+  const unsigned char* xa0 = q8_smem + gq * pitch + (4 * q) * 16;
+  const int sw = (q & 2) ? 32 : 0;
+  const unsigned char* xa = xa0;              // compute cursor into the token tile
+  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+
+  // Stages the token tile of the compute cursor (all threads; only when the tile changes).
+  auto stage_tile = [&]() {
+    const int g = mc.g, m0 = (mc.tile - tile_start[g]) * Q8_ROWS;
+    int rows;
+    const bf16* xin;
+    if (g < a.E) {
+      rows = a.counts[g];
+      const size_t base = (size_t)a.pad_off[g];
+      xin = a.x_rows + (base + m0) * K;
+      out = a.out_rows + (base + m0) * a.ldo;
+    } else {
+      rows = a.tokens;
+      xin = a.x_shared + (size_t)m0 * K;
+      out = a.out_shared + (size_t)m0 * a.ldo;
+    }
+    mrows = min(Q8_ROWS, rows - m0);
+    sc = a.scale + (size_t)g * a.s_group_stride;
+    __syncthreads();                                  // everyone is done with the previous tile
+    // four independent 16-byte loads in flight per thread (both weight register sets are live here),
+    // converted bf16 -> f16 on the way in
+    constexpr int SU = 4;
     const int cpr = K / 8, total = Q8_ROWS * cpr;
     int r = tid / cpr, c = tid - r * cpr;             // (row, 16-byte column) of this thread's first element
     const int dr = (Q8_WARPS * 32) / cpr, dc = (Q8_WARPS * 32) - dr * cpr;
@@ -128,7 +173,7 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
       for (int u = 0; u < SU; ++u) {
         rr[u] = r; cc[u] = c;
         v[u] = make_uint4(0, 0, 0, 0);
-        if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(m0 + r) * K + c * 8);
+        if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)r * K + c * 8);
         r += dr; c += dc;
         if (c >= cpr) { c -= cpr; ++r; }
       }
@@ -147,19 +192,13 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
         }
       }
     }
-  }
-  __syncthreads();
-
-  const float* sc = a.scale + (size_t)g * a.s_group_stride;
-  // this lane's fragments: unit (k / 4) of row pair gq; for quarter-chunks 2 and 3 the halves are swapped
-  const unsigned char* xa0 = q8_smem + gq * pitch + (4 * q) * 16;
-  const int sw = (q & 2) ? 32 : 0;
-  const unsigned char* xa = xa0;              // compute cursor into the token tile
-  int m_nb = blockIdx.x, m_c = 0;
-  float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    __syncthreads();
+    staged_tile = mc.tile;
+  };
 
   auto multiply = [&](const Chunk& ch) {
-    const int n0 = (m_nb * Q8_WARPS + warp) * COLS;
+    if (mc.c == 0 && mc.tile != staged_tile) stage_tile();   // uniform over the CTA
+    const int n0 = mc.nb * Q8_WARPS * COLS + n0_warp;
     const bool live = n0 < a.N;              // warp-uniform
     if (live) {
 #pragma unroll
@@ -168,7 +207,6 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
         const uint32_t uu[4] = {ch.u[u].x ^ 0x80808080u, ch.u[u].y ^ 0x80808080u, ch.u[u].z ^ 0x80808080u, ch.u[u].w ^ 0x80808080u};
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
-          // reduction slots of this MMA: (2q, 2q+1) <- k+4s+{0,1}, (2q+8, 2q+9) <- k+4s+{2,3}
           // the A registers of reduction values k + 4s .. k + 4s + 3, rows gq and gq + 8, in one load
           const uint4 f = *reinterpret_cast<const uint4*>((s < 2 ? xa + sw : xa + (32 - sw)) + u * (Q8_CHUNK * 4) + (s & 1) * 16);
           mma_f16_16816(acc0, f.x, f.y, f.z, f.w, s8x2_to_f16x2(ww[s], 0), s8x2_to_f16x2(ww[s], 2));
@@ -177,8 +215,8 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
       }
     }
     xa += STEP * 4;   // 16 bytes per four reduction values
-    if (++m_c < chunks) return;
-    // last chunk of a column block: scale, activate, store.
+    if (++mc.c < chunks) return;
+    // last chunk of an item: scale, activate, store.
     // accumulator layout: c[0], c[1] -> row gq, columns 2q, 2q+1; c[2], c[3] -> row gq+8
     if (live) {
 #pragma unroll
@@ -190,7 +228,7 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
         for (int half = 0; half < 2; ++half) {
           const int r = gq + 8 * half;
           if (r >= mrows) continue;
-          bf16* o = out + (size_t)(m0 + r) * a.ldo + col;
+          bf16* o = out + (size_t)r * a.ldo + col;
           const float v0 = acc0[2 * half + j] * s0, v1 = acc1[2 * half + j] * s1;
           if (SWIGLU) { o[0] = __float2bfloat16_rn(siluf_(v0) * v1); }
           else { o[0] = __float2bfloat16_rn(v0); o[8] = __float2bfloat16_rn(v1); }
@@ -199,11 +237,11 @@ __global__ void __launch_bounds__(Q8_WARPS * 32) q8_rows_kernel(Q8Args a) {
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) { acc0[i] = 0.f; acc1[i] = 0.f; }
-    m_c = 0; m_nb += gridDim.x; xa = xa0;
+    seek(mc, mc.item + 1);
+    xa = xa0;
   };
 
-  const int my_blocks = blockIdx.x < n_blocks ? (n_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int iters = my_blocks * chunks;
+  const int iters = (i1 - i0) * chunks;
   for (int it = 0; it < iters; it += 2) {
     fetch(cb);
     multiply(ca);
@@ -223,11 +261,9 @@ static cudaError_t launch_q8_variant(const Q8Args& a, dim3 grid, size_t smem, cu
 
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
-  const int groups = a.E + (a.x_shared ? 1 : 0);
-  // gate|up: two column blocks (of 64 hidden columns) per CTA, so the token tile is staged once for
-  // twice the weight stream; the down projection has 128 output columns per block and few blocks
-  const int nblocks = ceil_div(a.N, (swiglu ? 8 : 16) * Q8_WARPS);
-  const dim3 grid(swiglu ? ceil_div(nblocks, 2) : nblocks, ceil_div(a.tokens, Q8_ROWS), groups);
+  // two CTAs per SM (registers and, for the down projection, shared memory allow no more); the work
+  // list is cut on the device, where the routing counts are
+  const dim3 grid(2 * a.sm_count);
   const size_t smem = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
   const bool deep = a.K % (Q8_CHUNK * 4) == 0;   // K is always a multiple of 64
   if (swiglu) return deep ? launch_q8_variant<true, 4>(a, grid, smem, stream) : launch_q8_variant<true, 1>(a, grid, smem, stream);

@@ -187,6 +187,7 @@ struct Q8Args {
   const int* pad_off;      // [E+1]
   long long w_group_stride, s_group_stride;
   int E, tokens, K, N, ldo;
+  int sm_count;            // grid = two CTAs per SM
 };
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream);
 

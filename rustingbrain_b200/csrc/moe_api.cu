@@ -248,7 +248,10 @@ __global__ void pack_q8_kernel(const int8_t* __restrict__ src, const float* __re
   if (i >= (long long)rows * cols) return;
   const int r = (int)(i / cols), c = (int)(i - (long long)r * cols);
   const int pr = kind == 0 ? r : gu_row(kind - 1, r);
-  dst[(long long)pr * ld + c] = src[i];
+  // fragment-major: blocks of 8 rows x 64 reduction values are contiguous (512 bytes, row-major inside),
+  // blocks of one 8-row stripe follow each other along the reduction: a warp of the decode kernel reads
+  // one block per load and streams a stripe front to back
+  dst[(long long)(pr / 8) * 8 * ld + (long long)(c / 64) * 512 + (pr % 8) * 64 + (c % 64)] = src[i];
   if (c == 0) scale_dst[pr] = scale_src[r];
 }
 // Group table of the dense (shared expert, router) GEMMs for every possible token count: entry t is
@@ -477,14 +480,14 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     qa.out_rows = (bf16*)L->h; qa.out_shared = (bf16*)L->h_s;
     qa.w = L->q_gu; qa.scale = L->s_gu; qa.counts = L->meta.counts; qa.pad_off = L->meta.pad_off;
     qa.w_group_stride = 2ll * Fp * d; qa.s_group_stride = 2ll * Fp;
-    qa.E = L->E; qa.tokens = tokens; qa.K = d; qa.N = Fp; qa.ldo = Fp;
+    qa.sm_count = L->sm_count; qa.E = L->E; qa.tokens = tokens; qa.K = d; qa.N = Fp; qa.ldo = Fp;
     CK(launch_q8_rows(qa, true, st));
     Q8Args qb{};
     qb.x_rows = (const bf16*)L->h; qb.x_shared = L->shared ? (const bf16*)L->h_s : nullptr;
     qb.out_rows = (bf16*)L->y_perm; qb.out_shared = (bf16*)L->y_s;
     qb.w = L->q_d; qb.scale = L->s_d; qb.counts = L->meta.counts; qb.pad_off = L->meta.pad_off;
     qb.w_group_stride = (long long)d * Fp; qb.s_group_stride = d;
-    qb.E = L->E; qb.tokens = tokens; qb.K = Fp; qb.N = d; qb.ldo = d;
+    qb.sm_count = L->sm_count; qb.E = L->E; qb.tokens = tokens; qb.K = Fp; qb.N = d; qb.ldo = d;
     CK(launch_q8_rows(qb, false, st));
     rc = MOE_OK;
   } else if (ep) {
