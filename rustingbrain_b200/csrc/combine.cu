@@ -64,58 +64,105 @@ __device__ inline void unpack16(const uint4& q, float* v) {
   Vec16<T>::load(reinterpret_cast<const T*>(&q), v);
 }
 
-// The token's routed slots in ascending expert order (the order in which the
-// reference accumulates a token's contributions).  Returns the count.
-__device__ inline int ordered_slots(const int* expert_of, const int* slot_pos, const float* gates, int t, int k,
-                                    int* pos, float* gate) {
-  int ex[MAX_TOPK];
-  int n = 0;
-  for (int j = 0; j < k; ++j) {
-    const int e = expert_of[(size_t)t * k + j];
-    if (e < 0) continue;
-    const int p = slot_pos[(size_t)t * k + j];
-    if (p < 0) continue;
-    const float g = gates ? gates[(size_t)t * k + j] : 1.f;
-    int i = n++;
-    while (i > 0 && ex[i - 1] > e) {
-      ex[i] = ex[i - 1]; pos[i] = pos[i - 1]; gate[i] = gate[i - 1];
-      --i;
-    }
-    ex[i] = e; pos[i] = p; gate[i] = g;
+// The slots of one token, held in registers.  KMAX (a power of two >= k) is a template parameter and
+// every loop over the slots is fully unrolled, so the arrays are never indexed with a run-time value
+// (which would move them to local memory and put a load or store behind every row access).
+// Lane j < k reads slot j; the values reach all lanes by shuffles.
+constexpr unsigned FULL = 0xffffffffu;
+
+// Slot order (the order of the top-k selection).  pos < 0: the slot moves no row.
+template <int KMAX>
+__device__ __forceinline__ void slots_in_order(const int* slot_pos, const float* gates, int t, int k, int lane,
+                                               int (&pos)[KMAX], float (&gate)[KMAX]) {
+  int p = -1;
+  float g = 0.f;
+  if (lane < k) {
+    p = slot_pos[(size_t)t * k + lane];
+    g = gates ? gates[(size_t)t * k + lane] : 1.f;
   }
-  return n;
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    pos[j] = __shfl_sync(FULL, p, j);
+    gate[j] = __shfl_sync(FULL, g, j);
+  }
 }
 
-template <typename T>
+// Ascending expert order (the order in which the reference accumulates a token's contributions,
+// moe.rs:290-319): the first n entries are the token's routed rows, the rest have pos = -1.
+template <int KMAX>
+__device__ __forceinline__ int slots_by_expert(const int* expert_of, const int* slot_pos, const float* gates, int t, int k,
+                                               int lane, int (&pos)[KMAX], float (&gate)[KMAX]) {
+  int e = -1, p = -1;
+  float g = 0.f;
+  if (lane < k) {
+    e = expert_of[(size_t)t * k + lane];
+    p = slot_pos[(size_t)t * k + lane];
+    g = gates ? gates[(size_t)t * k + lane] : 1.f;
+  }
+  const bool valid = e >= 0 && p >= 0;
+  int rank = 0;   // routed slots of this token that come before this one
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    const int ej = __shfl_sync(FULL, e, j);
+    const int vj = __shfl_sync(FULL, (int)valid, j);
+    rank += (vj && (ej < e || (ej == e && j < lane))) ? 1 : 0;
+  }
+#pragma unroll
+  for (int s = 0; s < KMAX; ++s) {
+    const unsigned m = __ballot_sync(FULL, valid && rank == s);
+    const int src = m ? __ffs(m) - 1 : 0;
+    const int ps = __shfl_sync(FULL, p, src);
+    gate[s] = __shfl_sync(FULL, g, src);
+    pos[s] = m ? ps : -1;
+  }
+  return __popc(__ballot_sync(FULL, valid));
+}
+
+// Launches kernel<T, KMAX> for the smallest KMAX in {1, 2, 4, 8, 16} that holds k.
+#define DISPATCH_KMAX(KERNEL, T, k, grid, stream, args)                                         \
+  do {                                                                                           \
+    if ((k) <= 1) KERNEL<T, 1><<<grid, CB_WARPS * 32, 0, stream>>>(args);                        \
+    else if ((k) <= 2) KERNEL<T, 2><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
+    else if ((k) <= 4) KERNEL<T, 4><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
+    else if ((k) <= 8) KERNEL<T, 8><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
+    else KERNEL<T, 16><<<grid, CB_WARPS * 32, 0, stream>>>(args);                                \
+    count_launch();                                                                              \
+  } while (0)
+
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;
-  int pos[MAX_TOPK];
-  float gate[MAX_TOPK];
-  const int n = ordered_slots(a.expert_of, a.slot_pos, a.gates, t, a.k, pos, gate);
+  int pos[KMAX];
+  float gate[KMAX];
+  const int n = slots_by_expert<KMAX>(a.expert_of, a.slot_pos, a.gates, t, a.k, lane, pos, gate);
   const size_t rb = (size_t)a.d * sizeof(T);
   const T* sh = (const T*)a.shared;
   T* y = (T*)a.y + (size_t)t * a.d;
   constexpr int V = Vec16<T>::N;
+  constexpr int RB = KMAX < ROW_BATCH ? KMAX : ROW_BATCH;
   const int d = a.d;
   if (d % V == 0) {
     for (int c = lane * V; c < d; c += 32 * V) {
       float acc[V];
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = 0.f;
-      for (int j0 = 0; j0 < n; j0 += ROW_BATCH) {
-        uint4 raw[ROW_BATCH];
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b)
+      for (int j0 = 0; j0 < KMAX; j0 += RB) {
+        if (j0 >= n) break;
+        uint4 raw[RB];
+#pragma unroll
+        for (int b = 0; b < RB; ++b)
           if (j0 + b < n) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b) {
-          if (j0 + b >= n) break;
-          float v[V];
-          unpack16<T>(raw[b], v);
+        for (int b = 0; b < RB; ++b) {
+          if (j0 + b < n) {
+            float v[V];
+            unpack16<T>(raw[b], v);
 #pragma unroll
-          for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j0 + b], v[i]));
+            for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], __fmul_rn(gate[j0 + b], v[i]));
+          }
         }
       }
       if (sh) {
@@ -135,7 +182,9 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   } else {
     for (int c = lane; c < d; c += 32) {
       float acc = 0.f;
-      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, __fmul_rn(gate[j], to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c])));
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j)
+        if (j < n) acc = __fadd_rn(acc, __fmul_rn(gate[j], to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c])));
       if (sh) acc = __fadd_rn(acc, to_f32<T>(sh[(size_t)t * d + c]));
       if (a.accumulate) acc = __fadd_rn(to_f32<T>(y[c]), acc);
       y[c] = from_f32<T>(acc);
@@ -146,74 +195,75 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
 cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
   const int grid = ceil_div(a.tokens, CB_WARPS);
-  if (precision == PREC_BF16) { combine_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
-  else { combine_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  if (precision == PREC_BF16) DISPATCH_KMAX(combine_kernel, bf16, a.k, grid, stream, a);
+  else DISPATCH_KMAX(combine_kernel, float, a.k, grid, stream, a);
   return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradArgs a) {
   const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;
   const int k = a.k, d = a.d;
-  int pos[MAX_TOPK];
-  float gate[MAX_TOPK], dot[MAX_TOPK];
-  for (int j = 0; j < k; ++j) {
-    pos[j] = a.slot_pos[(size_t)t * k + j];
-    gate[j] = a.gates[(size_t)t * k + j];
-    dot[j] = 0.f;
-  }
+  int pos[KMAX];
+  float gate[KMAX], dot[KMAX];
+  slots_in_order<KMAX>(a.slot_pos, a.gates, t, k, lane, pos, gate);
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) dot[j] = 0.f;
   const T* gy = (const T*)a.grad_y + (size_t)t * d;
   const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
+  constexpr int RB = KMAX < ROW_BATCH ? KMAX : ROW_BATCH;
   if (d % V == 0) {
     for (int c = lane * V; c < d; c += 32 * V) {
       float g[V];
       Vec16<T>::load(gy + c, g);
-      for (int j0 = 0; j0 < k; j0 += ROW_BATCH) {
-        uint4 raw[ROW_BATCH];
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b)
-          if (j0 + b < k && pos[j0 + b] >= 0)
-            raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
+      for (int j0 = 0; j0 < KMAX; j0 += RB) {
+        uint4 raw[RB];
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b) {
-          const int j = j0 + b;
-          if (j >= k) break;
-          if (pos[j] < 0) continue;
-          float o[V], s[V];
-          unpack16<T>(raw[b], o);
+        for (int b = 0; b < RB; ++b)
+          if (pos[j0 + b] >= 0) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
 #pragma unroll
-          for (int i = 0; i < V; ++i) {
-            dot[j] = fmaf(g[i], o[i], dot[j]);
-            s[i] = gate[j] * g[i];
+        for (int b = 0; b < RB; ++b) {
+          if (pos[j0 + b] >= 0) {
+            float o[V], s[V];
+            unpack16<T>(raw[b], o);
+#pragma unroll
+            for (int i = 0; i < V; ++i) {
+              dot[j0 + b] = fmaf(g[i], o[i], dot[j0 + b]);
+              s[i] = gate[j0 + b] * g[i];
+            }
+            Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j0 + b], rb) + c, s);
           }
-          Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j], rb) + c, s);
         }
       }
     }
   } else {
     for (int c = lane; c < d; c += 32) {
       const float g = to_f32<T>(gy[c]);
-      for (int j = 0; j < k; ++j) {
-        if (pos[j] < 0) continue;
-        dot[j] = fmaf(g, to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c]), dot[j]);
-        ((T*)row_ptr(a.grad_y_perm, pos[j], rb))[c] = from_f32<T>(gate[j] * g);
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) {
+        if (pos[j] >= 0) {
+          dot[j] = fmaf(g, to_f32<T>(((const T*)row_ptr(a.y_perm, pos[j], rb))[c]), dot[j]);
+          ((T*)row_ptr(a.grad_y_perm, pos[j], rb))[c] = from_f32<T>(gate[j] * g);
+        }
       }
     }
   }
-  for (int j = 0; j < k; ++j) {
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
     const float s = warp_sum(dot[j]);
-    if (lane == 0) a.grad_gates[(size_t)t * k + j] = pos[j] < 0 ? 0.f : s;
+    if (lane == 0 && j < k) a.grad_gates[(size_t)t * k + j] = pos[j] < 0 ? 0.f : s;
   }
 }
 
 cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
   const int grid = ceil_div(a.tokens, CB_WARPS);
-  if (precision == PREC_BF16) { gather_grad_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
-  else { gather_grad_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  if (precision == PREC_BF16) DISPATCH_KMAX(gather_grad_kernel, bf16, a.k, grid, stream, a);
+  else DISPATCH_KMAX(gather_grad_kernel, float, a.k, grid, stream, a);
   return cudaGetLastError();
 }
 
@@ -232,28 +282,33 @@ __device__ inline float* aux_ptr(const RowSpace& s, int id, size_t aux_off, int 
   return reinterpret_cast<float*>((char*)s.base[r] + aux_off) + (size_t)which * s.cap + row;
 }
 
-template <typename T>
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a) {
   const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;
   const int k = a.k, d = a.d;
-  int pos[MAX_TOPK];
-  for (int j = 0; j < k; ++j) pos[j] = a.slot_pos[(size_t)t * k + j];
-  if (lane < k && pos[lane] >= 0) *aux_ptr(a.rows, pos[lane], a.aux_off, 0) = a.gates[(size_t)t * k + lane];
+  int pos[KMAX];
+  float gate[KMAX];
+  slots_in_order<KMAX>(a.slot_pos, a.gates, t, k, lane, pos, gate);
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j)
+    if (lane == j && pos[j] >= 0) *aux_ptr(a.rows, pos[j], a.aux_off, 0) = gate[j];
   const T* gy = (const T*)a.grad_y + (size_t)t * d;
   const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
   if (d % V == 0) {
     for (int c = lane * V; c < d; c += 32 * V) {
       const uint4 q = *reinterpret_cast<const uint4*>(gy + c);
-      for (int j = 0; j < k; ++j)
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j)
         if (pos[j] >= 0) *reinterpret_cast<uint4*>((T*)row_ptr(a.rows, pos[j], rb) + c) = q;
     }
   } else {
     for (int c = lane; c < d; c += 32) {
       const T g = gy[c];
-      for (int j = 0; j < k; ++j)
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j)
         if (pos[j] >= 0) ((T*)row_ptr(a.rows, pos[j], rb))[c] = g;
     }
   }
@@ -262,8 +317,8 @@ __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a
 cudaError_t launch_push_grad(const PushGradArgs& a, int precision, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
   const int grid = ceil_div(a.tokens, CB_WARPS);
-  if (precision == PREC_BF16) { push_grad_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
-  else { push_grad_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  if (precision == PREC_BF16) DISPATCH_KMAX(push_grad_kernel, bf16, a.k, grid, stream, a);
+  else DISPATCH_KMAX(push_grad_kernel, float, a.k, grid, stream, a);
   return cudaGetLastError();
 }
 
@@ -385,74 +440,80 @@ cudaError_t launch_router_bwd(const RouterBwdArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-template <typename T>
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) unpermute_kernel(UnpermuteArgs a) {
   const int lane = threadIdx.x & 31;
   // grid-stride over tokens: the launcher may cap the grid so that the kernel fits beside a
   // persistent GEMM on every SM
   for (int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5); t < a.tokens; t += gridDim.x * CB_WARPS) {
-  int pos[MAX_TOPK];
-  float unused[MAX_TOPK];
-  const int n = ordered_slots(a.expert_of, a.slot_pos, nullptr, t, a.k, pos, unused);
-  const int d = a.d, E = a.E;
-  const size_t rb = (size_t)a.d * sizeof(T);
-  const T* sh = (const T*)a.shared;
-  const T* ex = (const T*)a.extra;
-  const float* gl = a.grad_logits ? a.grad_logits + (size_t)t * E : nullptr;
-  T* gx = (T*)a.grad_x + (size_t)t * d;
-  constexpr int V = Vec16<T>::N;
-  if (d % V == 0 && d % 4 == 0) {
-    for (int c = lane * V; c < d; c += 32 * V) {
-      float acc[V], r[V];
+    int pos[KMAX];
+    float unused[KMAX];
+    const int n = slots_by_expert<KMAX>(a.expert_of, a.slot_pos, nullptr, t, a.k, lane, pos, unused);
+    const int d = a.d, E = a.E;
+    const size_t rb = (size_t)a.d * sizeof(T);
+    const T* sh = (const T*)a.shared;
+    const T* ex = (const T*)a.extra;
+    const float* gl = a.grad_logits ? a.grad_logits + (size_t)t * E : nullptr;
+    T* gx = (T*)a.grad_x + (size_t)t * d;
+    constexpr int V = Vec16<T>::N;
+    constexpr int RB = KMAX < ROW_BATCH ? KMAX : ROW_BATCH;
+    if (d % V == 0 && d % 4 == 0) {
+      for (int c = lane * V; c < d; c += 32 * V) {
+        float acc[V], r[V];
 #pragma unroll
-      for (int i = 0; i < V; ++i) { acc[i] = 0.f; r[i] = 0.f; }
-      if (sh) Vec16<T>::load(sh + (size_t)t * d + c, acc);
-      for (int j0 = 0; j0 < n; j0 += ROW_BATCH) {
-        uint4 raw[ROW_BATCH];
+        for (int i = 0; i < V; ++i) { acc[i] = 0.f; r[i] = 0.f; }
+        if (sh) Vec16<T>::load(sh + (size_t)t * d + c, acc);
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b)
-          if (j0 + b < n) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.grad_x_perm, pos[j0 + b], rb) + c);
+        for (int j0 = 0; j0 < KMAX; j0 += RB) {
+          if (j0 >= n) break;
+          uint4 raw[RB];
 #pragma unroll
-        for (int b = 0; b < ROW_BATCH; ++b) {
-          if (j0 + b >= n) break;
+          for (int b = 0; b < RB; ++b)
+            if (j0 + b < n) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.grad_x_perm, pos[j0 + b], rb) + c);
+#pragma unroll
+          for (int b = 0; b < RB; ++b) {
+            if (j0 + b < n) {
+              float v[V];
+              unpack16<T>(raw[b], v);
+#pragma unroll
+              for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+            }
+          }
+        }
+        if (ex) Vec16<T>::load(ex + (size_t)t * d + c, r);
+        for (int e = 0; gl && e < E; ++e) {
+          const float g = gl[e];
+          const float* w = a.w_router + (size_t)e * d + c;
+#pragma unroll
+          for (int i = 0; i < V; i += 4) {
+            const float4 q = *reinterpret_cast<const float4*>(w + i);
+            r[i] = fmaf(g, q.x, r[i]); r[i + 1] = fmaf(g, q.y, r[i + 1]);
+            r[i + 2] = fmaf(g, q.z, r[i + 2]); r[i + 3] = fmaf(g, q.w, r[i + 3]);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
+        if (a.accumulate) {
           float v[V];
-          unpack16<T>(raw[b], v);
+          Vec16<T>::load(gx + c, v);
 #pragma unroll
-          for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
+          for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(v[i], acc[i]);
         }
+        Vec16<T>::store(gx + c, acc);
       }
-      if (ex) Vec16<T>::load(ex + (size_t)t * d + c, r);
-      for (int e = 0; gl && e < E; ++e) {
-        const float g = gl[e];
-        const float* w = a.w_router + (size_t)e * d + c;
+    } else {
+      for (int c = lane; c < d; c += 32) {
+        float acc = sh ? to_f32<T>(sh[(size_t)t * d + c]) : 0.f;
 #pragma unroll
-        for (int i = 0; i < V; i += 4) {
-          const float4 q = *reinterpret_cast<const float4*>(w + i);
-          r[i] = fmaf(g, q.x, r[i]); r[i + 1] = fmaf(g, q.y, r[i + 1]);
-          r[i + 2] = fmaf(g, q.z, r[i + 2]); r[i + 3] = fmaf(g, q.w, r[i + 3]);
-        }
+        for (int j = 0; j < KMAX; ++j)
+          if (j < n) acc = __fadd_rn(acc, to_f32<T>(((const T*)row_ptr(a.grad_x_perm, pos[j], rb))[c]));
+        float r = ex ? to_f32<T>(ex[(size_t)t * d + c]) : 0.f;
+        for (int e = 0; gl && e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
+        acc = __fadd_rn(acc, r);
+        if (a.accumulate) acc = __fadd_rn(to_f32<T>(gx[c]), acc);
+        gx[c] = from_f32<T>(acc);
       }
-#pragma unroll
-      for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], r[i]);
-      if (a.accumulate) {
-        float v[V];
-        Vec16<T>::load(gx + c, v);
-#pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(v[i], acc[i]);
-      }
-      Vec16<T>::store(gx + c, acc);
     }
-  } else {
-    for (int c = lane; c < d; c += 32) {
-      float acc = sh ? to_f32<T>(sh[(size_t)t * d + c]) : 0.f;
-      for (int j = 0; j < n; ++j) acc = __fadd_rn(acc, to_f32<T>(((const T*)row_ptr(a.grad_x_perm, pos[j], rb))[c]));
-      float r = ex ? to_f32<T>(ex[(size_t)t * d + c]) : 0.f;
-      for (int e = 0; gl && e < E; ++e) r = fmaf(gl[e], a.w_router[(size_t)e * d + c], r);
-      acc = __fadd_rn(acc, r);
-      if (a.accumulate) acc = __fadd_rn(to_f32<T>(gx[c]), acc);
-      gx[c] = from_f32<T>(acc);
-    }
-  }
   }   // tokens
 }
 
@@ -460,8 +521,8 @@ cudaError_t launch_unpermute(const UnpermuteArgs& a, int precision, cudaStream_t
   if (a.tokens <= 0) return cudaSuccess;
   int grid = ceil_div(a.tokens, CB_WARPS);
   if (max_blocks > 0) grid = min(grid, max_blocks);
-  if (precision == PREC_BF16) { unpermute_kernel<bf16><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
-  else { unpermute_kernel<float><<<grid, CB_WARPS * 32, 0, stream>>>(a); count_launch(); }
+  if (precision == PREC_BF16) DISPATCH_KMAX(unpermute_kernel, bf16, a.k, grid, stream, a);
+  else DISPATCH_KMAX(unpermute_kernel, float, a.k, grid, stream, a);
   return cudaGetLastError();
 }
 
