@@ -416,7 +416,7 @@ __global__ void cursor_base_kernel(int* __restrict__ hist, int nb, int E, const 
   if (i < nb * E) hist[i] += pad_off[i % E];
 }
 
-template <typename T>
+template <typename T, int KMAX>
 __global__ void __launch_bounds__(256)
 permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const float* __restrict__ gates,
                const int* __restrict__ cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
@@ -476,34 +476,38 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
   const bool vec_ok = (d % VEC) == 0;
   const size_t row_bytes = (size_t)d * sizeof(T);
   if (vec_ok) {
-    // flat over (row, 16-byte chunk): neighbouring threads take neighbouring chunks of one row,
-    // and each thread keeps four independent loads in flight
+    // One warp per token row; the row's destination pointers sit in registers (KMAX is a template
+    // parameter, the loops over the slots are unrolled), each lane keeps four independent 16-byte loads
+    // in flight and stores every chunk to all of the token's rows.
     const int cpr = d / VEC;                 // chunks per row
     // small batches: gridDim.y blocks share one 64-token group; each repeats the (cheap) ranking
     // and copies its own slice of the rows, so the copy is not one block's latency chain
     const int slice = ceil_div(rows, (int)gridDim.y);
     const int r_begin = min(rows, (int)blockIdx.y * slice), r_end = min(rows, r_begin + slice);
-    const int total = r_end * cpr;
     constexpr int U = 4;
-    for (int base = r_begin * cpr + tid; base < total; base += blockDim.x * U) {
-      uint4 v[U];
-      int rr[U], cc[U];
+    for (int r = r_begin + warp; r < r_end; r += blockDim.x / 32) {
+      const int* p = spos + r * k;
+      if (p[0] < 0) continue;                // padding row: routed nowhere
+      uint4* dst[KMAX];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int idx = base + u * blockDim.x;
-        rr[u] = -1;
-        if (idx < total) {
-          rr[u] = idx / cpr; cc[u] = idx - rr[u] * cpr;
-          if (spos[rr[u] * k] < 0) rr[u] = -1;   // padding row: routed nowhere
-          else v[u] = reinterpret_cast<const uint4*>(x + (size_t)(t0 + rr[u]) * d)[cc[u]];
-        }
+      for (int j = 0; j < KMAX; ++j) {
+        const int pj = j < k ? p[j] : -1;
+        dst[j] = pj >= 0 ? reinterpret_cast<uint4*>(row_ptr(x_perm, pj, row_bytes)) : nullptr;
       }
+      const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(t0 + r) * d);
+      for (int c0 = lane; c0 < cpr; c0 += 32 * U) {
+        uint4 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (rr[u] < 0) continue;
-        const int* p = spos + rr[u] * k;
-        for (int j = 0; j < k; ++j)
-          if (p[j] >= 0) reinterpret_cast<uint4*>(row_ptr(x_perm, p[j], row_bytes))[cc[u]] = v[u];
+        for (int u = 0; u < U; ++u)
+          if (c0 + 32 * u < cpr) v[u] = src[c0 + 32 * u];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c0 + 32 * u < cpr) {
+#pragma unroll
+            for (int j = 0; j < KMAX; ++j)
+              if (dst[j]) dst[j][c0 + 32 * u] = v[u];
+          }
+        }
       }
     }
   } else {
@@ -614,15 +618,22 @@ cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t str
   const size_t smem = sizeof(int) * ((size_t)a.E + (size_t)ROUTER_ROWS * a.k);
   const dim3 pgrid(nb, nb <= 16 ? 8 : 1);
   if (nb > 0) {
-    if (precision == PREC_BF16) {
-      permute_kernel<bf16><<<pgrid, 256, smem, stream>>>((const bf16*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens,
-                                                      a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token,
-                                                      a.row_gate, a.token_of, a.slot_of);
-    } else {
-      permute_kernel<float><<<pgrid, 256, smem, stream>>>((const float*)a.x, a.expert_of, a.gates, a.cursor, a.meta,
-                                                       a.tokens, a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos,
-                                                       a.row_token, a.row_gate, a.token_of, a.slot_of);
-    }
+#define PERMUTE_LAUNCH(T, KMAX)                                                                                   \
+  permute_kernel<T, KMAX><<<pgrid, 256, smem, stream>>>((const T*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens, \
+                                                        a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token,     \
+                                                        a.row_gate, a.token_of, a.slot_of)
+#define PERMUTE_BY_K(T)                                                                          \
+  do {                                                                                           \
+    if (a.k <= 1) PERMUTE_LAUNCH(T, 1);                                                          \
+    else if (a.k <= 2) PERMUTE_LAUNCH(T, 2);                                                     \
+    else if (a.k <= 4) PERMUTE_LAUNCH(T, 4);                                                     \
+    else if (a.k <= 8) PERMUTE_LAUNCH(T, 8);                                                     \
+    else PERMUTE_LAUNCH(T, 16);                                                                  \
+  } while (0)
+    if (precision == PREC_BF16) PERMUTE_BY_K(bf16);
+    else PERMUTE_BY_K(float);
+#undef PERMUTE_BY_K
+#undef PERMUTE_LAUNCH
     count_launch();
   }
   if (a.dest_base || a.skip_pad) return cudaGetLastError();   // remote rows: the owners zero their own padding
