@@ -201,7 +201,7 @@ cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t str
 }
 
 template <typename T, int KMAX>
-__global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradArgs a) {
+__global__ void __launch_bounds__(CB_WARPS * 32, 2) gather_grad_kernel(GatherGradArgs a) {
   const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;
@@ -214,28 +214,44 @@ __global__ void __launch_bounds__(CB_WARPS * 32) gather_grad_kernel(GatherGradAr
   const T* gy = (const T*)a.grad_y + (size_t)t * d;
   const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
-  constexpr int RB = KMAX < ROW_BATCH ? KMAX : ROW_BATCH;
+  constexpr int RB = ROW_BATCH;
   if (d % V == 0) {
-    for (int c = lane * V; c < d; c += 32 * V) {
-      float g[V];
-      Vec16<T>::load(gy + c, g);
+    // The lane keeps up to U chunks of grad_y[token] (a 4 KB piece of the row per warp) and walks the
+    // token's rows one after the other, so every row is read and written in contiguous pieces instead
+    // of 512 bytes at a time interleaved with seven other rows (DRAM pages stay open).
+    constexpr int U = 8;
+    const int cpr = d / V;
+    const uint4* gsrc = reinterpret_cast<const uint4*>(gy);
+    for (int c0 = lane; c0 < cpr; c0 += 32 * U) {
+      uint4 gq[U];
 #pragma unroll
-      for (int j0 = 0; j0 < KMAX; j0 += RB) {
-        uint4 raw[RB];
+      for (int u = 0; u < U; ++u)
+        if (c0 + 32 * u < cpr) gq[u] = gsrc[c0 + 32 * u];
 #pragma unroll
-        for (int b = 0; b < RB; ++b)
-          if (pos[j0 + b] >= 0) raw[b] = *reinterpret_cast<const uint4*>((const T*)row_ptr(a.y_perm, pos[j0 + b], rb) + c);
+      for (int j = 0; j < KMAX; ++j) {
+        if (pos[j] >= 0) {
+          const uint4* yrow = reinterpret_cast<const uint4*>(row_ptr(a.y_perm, pos[j], rb));
+          uint4* drow = reinterpret_cast<uint4*>(row_ptr(a.grad_y_perm, pos[j], rb));
 #pragma unroll
-        for (int b = 0; b < RB; ++b) {
-          if (pos[j0 + b] >= 0) {
-            float o[V], s[V];
-            unpack16<T>(raw[b], o);
+          for (int u0 = 0; u0 < U; u0 += RB) {
+            uint4 raw[RB];
 #pragma unroll
-            for (int i = 0; i < V; ++i) {
-              dot[j0 + b] = fmaf(g[i], o[i], dot[j0 + b]);
-              s[i] = gate[j0 + b] * g[i];
+            for (int b = 0; b < RB; ++b)
+              if (c0 + 32 * (u0 + b) < cpr) raw[b] = yrow[c0 + 32 * (u0 + b)];
+#pragma unroll
+            for (int b = 0; b < RB; ++b) {
+              if (c0 + 32 * (u0 + b) < cpr) {
+                float g[V], o[V], sv[V];
+                unpack16<T>(gq[u0 + b], g);
+                unpack16<T>(raw[b], o);
+#pragma unroll
+                for (int i = 0; i < V; ++i) {
+                  dot[j] = fmaf(g[i], o[i], dot[j]);
+                  sv[i] = gate[j] * g[i];
+                }
+                Vec16<T>::store(reinterpret_cast<T*>(drow + c0 + 32 * (u0 + b)), sv);
+              }
             }
-            Vec16<T>::store((T*)row_ptr(a.grad_y_perm, pos[j0 + b], rb) + c, s);
           }
         }
       }
@@ -298,11 +314,24 @@ __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a
   const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
   if (d % V == 0) {
-    for (int c = lane * V; c < d; c += 32 * V) {
-      const uint4 q = *reinterpret_cast<const uint4*>(gy + c);
+    // row by row, 8 KB pieces: the writes of one DRAM page (or one NVLink destination) stay together
+    constexpr int U = 16;
+    const int cpr = d / V;
+    const uint4* gsrc = reinterpret_cast<const uint4*>(gy);
+    for (int c0 = lane; c0 < cpr; c0 += 32 * U) {
+      uint4 gq[U];
 #pragma unroll
-      for (int j = 0; j < KMAX; ++j)
-        if (pos[j] >= 0) *reinterpret_cast<uint4*>((T*)row_ptr(a.rows, pos[j], rb) + c) = q;
+      for (int u = 0; u < U; ++u)
+        if (c0 + 32 * u < cpr) gq[u] = gsrc[c0 + 32 * u];
+#pragma unroll
+      for (int j = 0; j < KMAX; ++j) {
+        if (pos[j] >= 0) {
+          uint4* drow = reinterpret_cast<uint4*>(row_ptr(a.rows, pos[j], rb));
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            if (c0 + 32 * u < cpr) drow[c0 + 32 * u] = gq[u];
+        }
+      }
     }
   } else {
     for (int c = lane; c < d; c += 32) {

@@ -477,14 +477,14 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
   const size_t row_bytes = (size_t)d * sizeof(T);
   if (vec_ok) {
     // One warp per token row; the row's destination pointers sit in registers (KMAX is a template
-    // parameter, the loops over the slots are unrolled), each lane keeps four independent 16-byte loads
-    // in flight and stores every chunk to all of the token's rows.
+    // parameter, the loops over the slots are unrolled), each lane loads up to sixteen 16-byte chunks of
+    // the row and stores them to the token's rows.
     const int cpr = d / VEC;                 // chunks per row
     // small batches: gridDim.y blocks share one 64-token group; each repeats the (cheap) ranking
     // and copies its own slice of the rows, so the copy is not one block's latency chain
     const int slice = ceil_div(rows, (int)gridDim.y);
     const int r_begin = min(rows, (int)blockIdx.y * slice), r_end = min(rows, r_begin + slice);
-    constexpr int U = 4;
+    constexpr int U = 16;   // 16-byte chunks per lane held at once: 8 KB of the row per pass
     for (int r = r_begin + warp; r < r_end; r += blockDim.x / 32) {
       const int* p = spos + r * k;
       if (p[0] < 0) continue;                // padding row: routed nowhere
@@ -500,12 +500,14 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
 #pragma unroll
         for (int u = 0; u < U; ++u)
           if (c0 + 32 * u < cpr) v[u] = src[c0 + 32 * u];
+        // destination row by destination row: each row receives its 8 KB back to back, which keeps
+        // the writes of one DRAM page together
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (c0 + 32 * u < cpr) {
+        for (int j = 0; j < KMAX; ++j) {
+          if (dst[j]) {
 #pragma unroll
-            for (int j = 0; j < KMAX; ++j)
-              if (dst[j]) dst[j][c0 + 32 * u] = v[u];
+            for (int u = 0; u < U; ++u)
+              if (c0 + 32 * u < cpr) dst[j][c0 + 32 * u] = v[u];
           }
         }
       }
