@@ -27,6 +27,11 @@
 namespace moe {
 namespace tc {
 
+// Build-time knobs for timing experiments (never defined in the shipped library):
+//   TC_STAGES / TC_PAIR_STAGES  depth of the operand ring;
+//   TC_EXP_NOEPI   skip the epilogue, TC_EXP_NOLOAD skip the TMA loads (the MMAs run on whatever is
+//   in shared memory), TC_EXP_NOMMA skip the MMAs (the ring is filled and released).  The last three
+//   isolate one part of the mainloop; their results are meaningless, only their duration is.
 #ifndef TC_STAGES
 #define TC_STAGES 4
 #endif
