@@ -519,7 +519,10 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   return MOE_OK;
 }
 
-int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaStream_t st) {
+// force_mode 3 (host entry point, one GPU): like overlap mode 2 but the fork comes as late as possible
+// (every tensor-core launch that feeds grad_x goes first, so nothing on the caller's stream queues behind
+// the weight-gradient GEMMs) and the caller joins the side stream before it returns.
+int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaStream_t st, int force_mode = -1) {
   if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
   if (!L->have_cache) { L->err = "InvalidInput: moe_backward needs a preceding moe_forward with save_for_backward"; return MOE_INVALID_INPUT; }
   if (!gy || !gx) { L->err = "InvalidInput: null gradient pointer"; return MOE_INVALID_INPUT; }
@@ -546,16 +549,53 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     if (!ep) CK(launch_pad_rows(L->dy_perm, L->d, L->meta, L->E, L->act, st));
   }
 
+  tc::Operand RA{L->gl_bf16, tokens, L->E, 1};
+  auto router_backward = [&]() -> int {
+    RouterBwdArgs rb{};
+    rb.probs = L->probs; rb.lse = L->lse; rb.expert_of = L->expert_of; rb.grad_gates = L->grad_gates;
+    rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
+    rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
+    rb.grad_logits_bf16 = L->tc_router ? L->gl_bf16 : nullptr;
+    if (ep) { rb.ext_stats = L->ext_stats; rb.ext_counts = L->ext_counts; }
+    { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
+    if (L->tc_router && tokens > 0) {
+      // router input gradient grad_logits W_r: one more launch of the grouped tensor-core GEMM
+      Span sp(L, 12, st);
+      tc::GemmArgs g{};
+      g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;
+      g.N = L->d; g.K = L->E; g.out0 = L->dx_r; g.ld0 = L->d;
+      tc::Operand B{L->wb + L->off_router, L->E, L->d, 1};
+      CK(tc::gemm_rows_nn(RA, B, g, tc::EPI_STORE, L->sm_count, st));
+    }
+    return MOE_OK;
+  };
+  auto router_weight_gradient = [&](cudaStream_t s) -> int {
+    if (L->tc_router && tokens > 0) {
+      Span sp(L, 12, s);
+      tc::GemmArgs wg{};
+      wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
+      wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
+      tc::Operand Ax{L->last_x, tokens, L->d, 1};
+      CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
+    } else {
+      RouterWgradArgs rw{};
+      rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
+      rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
+      Span sp(L, 12, s); CK(launch_router_wgrad(rw, L->act, s));
+    }
+    return MOE_OK;
+  };
   // mode 2: only the input-gradient chain stays on the caller's stream; both routed weight gradients
   // go to the side stream and are joined by whichever later call needs their inputs or outputs
-  const int mode = L->prof_on ? 0 : overlap_mode();
-  const int first_parts = mode == 2 ? 1 : 3;
+  const int mode = L->prof_on ? 0 : (force_mode == 3 && !ep ? 3 : overlap_mode());
+  const int first_parts = mode >= 2 ? 1 : 3;
   Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
   ExpertIO io{};
   io.x = L->x_perm; io.gu = L->gu; io.h = L->h; io.y = L->y_perm; io.dy = L->dy_perm; io.dgu = L->dgu;
   io.dx = L->dx_perm; io.dh = L->dh; io.w_gu = L->off_gu; io.w_d = L->off_d;
   int rc = join_side(L, st);
   if (rc != MOE_OK) return rc;
+  if (mode == 3 && (rc = router_backward()) != MOE_OK) return rc;   // needs the gate gradients only
   rc = ep ? ep_backward_experts(L, st, first_parts) : experts_backward(L, G, io, st, true, first_parts);
   if (rc != MOE_OK) return rc;
   if (mode == 2) {
@@ -583,23 +623,14 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     if (rc != MOE_OK) return rc;
   }
 
-  RouterBwdArgs rb{};
-  rb.probs = L->probs; rb.lse = L->lse; rb.expert_of = L->expert_of; rb.grad_gates = L->grad_gates;
-  rb.counts = L->meta.counts; rb.total = L->meta.total; rb.tokens = tokens; rb.E = L->E; rb.k = L->k;
-  rb.aux_w = L->aux_w; rb.z_w = L->z_w; rb.grad_logits = L->grad_logits;
-  rb.grad_logits_bf16 = L->tc_router ? L->gl_bf16 : nullptr;
-  if (ep) { rb.ext_stats = L->ext_stats; rb.ext_counts = L->ext_counts; }
-  { Span sp(L, 10, st); CK(launch_router_bwd(rb, st)); }
-
-  tc::Operand RA{L->gl_bf16, tokens, L->E, 1};
-  if (L->tc_router && tokens > 0) {
-    // router input gradient grad_logits W_r: one more launch of the grouped tensor-core GEMM
-    Span sp(L, 12, st);
-    tc::GemmArgs g{};
-    g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;
-    g.N = L->d; g.K = L->E; g.out0 = L->dx_r; g.ld0 = L->d;
-    tc::Operand B{L->wb + L->off_router, L->E, L->d, 1};
-    CK(tc::gemm_rows_nn(RA, B, g, tc::EPI_STORE, L->sm_count, st));
+  if (mode != 3 && (rc = router_backward()) != MOE_OK) return rc;
+  if (mode == 3) {
+    CK(cudaEventRecord(L->ev_fork, st));
+    CK(cudaStreamWaitEvent(L->side_stream, L->ev_fork, 0));
+    if ((rc = experts_backward(L, G, io, L->side_stream, true, 6)) != MOE_OK) return rc;
+    if ((rc = router_weight_gradient(L->side_stream)) != MOE_OK) return rc;
+    CK(cudaEventRecord(L->ev_join, L->side_stream));
+    L->side_pending = true;
   }
 
   // Everything the input gradient needs exists now.
@@ -621,24 +652,13 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     CK(cudaEventRecord(L->ev_join, L->side_stream));
   } else {
     { Span sp(L, 11, st); CK(launch_unpermute(ua, L->act, st)); }
-    if (mode != 2) {
+    if (mode < 2) {
       rc = ep ? ep_backward_experts(L, st, 4) : experts_backward(L, G, io, st, true, 4);
       if (rc != MOE_OK) return rc;
     }
   }
 
-  if (L->tc_router && tokens > 0) {
-    Span sp(L, 12, st);
-    tc::GemmArgs wg{};
-    wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
-    wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
-    tc::Operand Ax{L->last_x, tokens, L->d, 1};
-    CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, st));
-  }
-  RouterWgradArgs rw{};
-  rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
-  rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
-  if (!L->tc_router || tokens == 0) { Span sp(L, 12, st); CK(launch_router_wgrad(rw, L->act, st)); }
+  if (mode != 3 && (rc = router_weight_gradient(st)) != MOE_OK) return rc;
   if (ep) {
     Span sp(L, 12, st);
     rc = ep_allreduce_replicated(L, st);
@@ -1025,7 +1045,10 @@ int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
       CK(launch_cast_f32_to_bf16(L->host_stage_f32, (bf16*)L->host_y, n, st));
     }
   }
-  int rc = backward_impl(L, L->host_y, L->host_gx, 0, st);
+  // The weight-gradient GEMMs feed nothing that leaves the device: they run on the side stream while
+  // grad_x crosses PCIe, and both are waited for before the call returns.
+  static const bool defer = [] { const char* e = getenv("MOE_B200_HOST_DEFER"); return !(e && *e == '0'); }();
+  int rc = backward_impl(L, L->host_y, L->host_gx, 0, st, defer ? 3 : -1);
   if (rc != MOE_OK) return rc;
   if (n > 0) {
     if (L->act == PREC_F32) {
@@ -1036,6 +1059,7 @@ int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
     }
   }
   CK(cudaStreamSynchronize(st));
+  if (L->side_pending) { CK(cudaStreamSynchronize(L->side_stream)); L->side_pending = false; }
   return check_flag(L);
 }
 
