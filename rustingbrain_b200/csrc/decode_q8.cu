@@ -59,8 +59,12 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 // A warp owns two 8-column MMA tiles that share the token fragments: for the fused pass the gate
 // rows of 8 hidden columns and the matching up rows, otherwise 16 adjacent output columns.
 // U = 16-byte loads per lane and tile in one chunk of 64 U reduction values; K is a multiple of 64 U.
-template <bool SWIGLU, int U>
-__global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
+// NSLOT = 0: the weight stream lands in registers (two alternating sets, one chunk ahead).  NSLOT > 0:
+// it lands in a per-warp ring of NSLOT chunk slots in shared memory, filled by cp.async NSLOT - 1
+// chunks ahead, so that more bytes are in flight per SM than registers could hold; every lane copies
+// and later reads only its own 16 bytes of a slot, so the ring needs no barrier.
+template <bool SWIGLU, int U, int NSLOT>
+__global__ void __launch_bounds__(Q8_WARPS * 32, NSLOT > 0 ? 1 : 2) q8_rows_kernel(Q8Args a) {
   extern __shared__ __align__(16) unsigned char q8_smem[];
   __shared__ int tile_start[MAX_EXPERTS + 2];   // first token tile of every group
   // Token tile in MMA-fragment order: rows r and r + 8 are interleaved so that one 16-byte unit holds
@@ -128,8 +132,28 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
     }
     if (++fc.c == chunks) { seek(fc, fc.item + 1); fp = stripe(fc); }
   };
+  constexpr int SLOT_BYTES = 2 * U * 512;
+  unsigned char* ring = q8_smem + 8 * pitch + (size_t)warp * (NSLOT > 0 ? NSLOT : 1) * SLOT_BYTES + 16 * lane;
+  auto fetch_slot = [&](int slot) {
+    if (fp) {
+      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + slot * SLOT_BYTES);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 * u), "l"(fp + 512 * u) : "memory");
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 * (U + u)), "l"(fp + tile1 + 512 * u) : "memory");
+      }
+      fp += 512 * U;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");   // also when empty: the group count stays in step
+    if (++fc.c == chunks) { seek(fc, fc.item + 1); fp = stripe(fc); }
+  };
   Chunk ca, cb;
-  fetch(ca);
+  if (NSLOT > 0) {
+#pragma unroll
+    for (int i = 0; i < NSLOT - 1; ++i) fetch_slot(i);
+  } else {
+    fetch(ca);
+  }
 
   Cursor mc{0, 0, 0, 0, 0};
   seek(mc, i0);
@@ -242,32 +266,56 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
   };
 
   const int iters = (i1 - i0) * chunks;
-  for (int it = 0; it < iters; it += 2) {
-    fetch(cb);
-    multiply(ca);
-    if (it + 1 >= iters) break;
-    fetch(ca);
-    multiply(cb);
+  if (NSLOT > 0) {
+    int slot = 0;
+    for (int it = 0; it < iters; ++it) {
+      fetch_slot(slot == 0 ? NSLOT - 1 : slot - 1);   // the slot consumed one iteration ago
+      asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT > 0 ? NSLOT - 1 : 0) : "memory");
+      const uint4* src = reinterpret_cast<const uint4*>(ring + slot * SLOT_BYTES);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        ca.w[u] = src[32 * u];          // 512 bytes per u, 16 per lane
+        ca.u[u] = src[32 * (U + u)];
+      }
+      multiply(ca);
+      slot = slot + 1 == NSLOT ? 0 : slot + 1;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+  } else {
+    for (int it = 0; it < iters; it += 2) {
+      fetch(cb);
+      multiply(ca);
+      if (it + 1 >= iters) break;
+      fetch(ca);
+      multiply(cb);
+    }
   }
 }
 
-template <bool SWIGLU, int U>
-static cudaError_t launch_q8_variant(const Q8Args& a, dim3 grid, size_t smem, cudaStream_t stream) {
-  if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  q8_rows_kernel<SWIGLU, U><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
+template <bool SWIGLU, int U, int NSLOT>
+static cudaError_t launch_q8_variant(const Q8Args& a, size_t tile_bytes, cudaStream_t stream) {
+  const size_t smem = tile_bytes + (size_t)Q8_WARPS * NSLOT * 2 * U * 512;
+  const dim3 grid((NSLOT > 0 ? 1 : 2) * a.sm_count);   // resident CTAs per SM times SMs
+  if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U, NSLOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  q8_rows_kernel<SWIGLU, U, NSLOT><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
   count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
-  // two CTAs per SM (registers and, for the down projection, shared memory allow no more); the work
-  // list is cut on the device, where the routing counts are
-  const dim3 grid(2 * a.sm_count);
-  const size_t smem = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
+  // The work list is cut on the device, where the routing counts are.  Gate|up (small token tile): one
+  // CTA per SM with a five-slot shared-memory ring per warp (four 4 KB chunks in flight per warp).  Down
+  // (a 90 KB token tile leaves no room for such a ring): two CTAs per SM, weights through registers.
+  const size_t tile_bytes = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
   const bool deep = a.K % (Q8_CHUNK * 4) == 0;   // K is always a multiple of 64
-  if (swiglu) return deep ? launch_q8_variant<true, 4>(a, grid, smem, stream) : launch_q8_variant<true, 1>(a, grid, smem, stream);
-  return deep ? launch_q8_variant<false, 4>(a, grid, smem, stream) : launch_q8_variant<false, 1>(a, grid, smem, stream);
+  const bool ring = deep && tile_bytes + (size_t)Q8_WARPS * 5 * 2 * 4 * 512 <= 200 * 1024;
+  if (swiglu) {
+    if (ring) return launch_q8_variant<true, 4, 5>(a, tile_bytes, stream);
+    return deep ? launch_q8_variant<true, 4, 0>(a, tile_bytes, stream) : launch_q8_variant<true, 1, 0>(a, tile_bytes, stream);
+  }
+  if (ring) return launch_q8_variant<false, 4, 5>(a, tile_bytes, stream);
+  return deep ? launch_q8_variant<false, 4, 0>(a, tile_bytes, stream) : launch_q8_variant<false, 1, 0>(a, tile_bytes, stream);
 }
 
 }  // namespace moe
