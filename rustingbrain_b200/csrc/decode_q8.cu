@@ -27,7 +27,8 @@ constexpr int Q8_WARPS = 8;
 constexpr int Q8_CHUNK = 64;    // reduction values per warp-wide 16-byte load round
 
 // Two int8 weights -> two f16 values in two instructions.  `wx` is the weight word with every
-// byte's sign bit flipped (v + 128 as an unsigned byte); a byte permute drops two of those bytes
+// byte's sign bit flipped (v + 128 as an unsigned byte; the library stores the int8 matrices that
+// way, see pack_q8_kernel); a byte permute drops two of those bytes
 // under the f16 exponent 0x64 (= 1024 + byte, exact), and one packed subtract of 1152 restores v.
 // Going through f16 rather than bf16 is what makes this cheap; the products are exact either way
 // and the token rows are converted bf16 -> f16 once per CTA when they are staged.
@@ -59,12 +60,8 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 // A warp owns two 8-column MMA tiles that share the token fragments: for the fused pass the gate
 // rows of 8 hidden columns and the matching up rows, otherwise 16 adjacent output columns.
 // U = 16-byte loads per lane and tile in one chunk of 64 U reduction values; K is a multiple of 64 U.
-// NSLOT = 0: the weight stream lands in registers (two alternating sets, one chunk ahead).  NSLOT > 0:
-// it lands in a per-warp ring of NSLOT chunk slots in shared memory, filled by cp.async NSLOT - 1
-// chunks ahead, so that more bytes are in flight per SM than registers could hold; every lane copies
-// and later reads only its own 16 bytes of a slot, so the ring needs no barrier.
-template <bool SWIGLU, int U, int NSLOT>
-__global__ void __launch_bounds__(Q8_WARPS * 32, NSLOT > 0 ? 1 : 2) q8_rows_kernel(Q8Args a) {
+template <bool SWIGLU, int U>
+__global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
   extern __shared__ __align__(16) unsigned char q8_smem[];
   __shared__ int tile_start[MAX_EXPERTS + 2];   // first token tile of every group
   // Token tile in MMA-fragment order: rows r and r + 8 are interleaved so that one 16-byte unit holds
@@ -132,28 +129,8 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, NSLOT > 0 ? 1 : 2) q8_rows_kern
     }
     if (++fc.c == chunks) { seek(fc, fc.item + 1); fp = stripe(fc); }
   };
-  constexpr int SLOT_BYTES = 2 * U * 512;
-  unsigned char* ring = q8_smem + 8 * pitch + (size_t)warp * (NSLOT > 0 ? NSLOT : 1) * SLOT_BYTES + 16 * lane;
-  auto fetch_slot = [&](int slot) {
-    if (fp) {
-      const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + slot * SLOT_BYTES);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 * u), "l"(fp + 512 * u) : "memory");
-        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512 * (U + u)), "l"(fp + tile1 + 512 * u) : "memory");
-      }
-      fp += 512 * U;
-    }
-    asm volatile("cp.async.commit_group;" ::: "memory");   // also when empty: the group count stays in step
-    if (++fc.c == chunks) { seek(fc, fc.item + 1); fp = stripe(fc); }
-  };
   Chunk ca, cb;
-  if (NSLOT > 0) {
-#pragma unroll
-    for (int i = 0; i < NSLOT - 1; ++i) fetch_slot(i);
-  } else {
-    fetch(ca);
-  }
+  fetch(ca);
 
   Cursor mc{0, 0, 0, 0, 0};
   seek(mc, i0);
@@ -227,8 +204,9 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, NSLOT > 0 ? 1 : 2) q8_rows_kern
     if (live) {
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const uint32_t ww[4] = {ch.w[u].x ^ 0x80808080u, ch.w[u].y ^ 0x80808080u, ch.w[u].z ^ 0x80808080u, ch.w[u].w ^ 0x80808080u};
-        const uint32_t uu[4] = {ch.u[u].x ^ 0x80808080u, ch.u[u].y ^ 0x80808080u, ch.u[u].z ^ 0x80808080u, ch.u[u].w ^ 0x80808080u};
+        // stored with the sign bit already flipped (see s8x2_to_f16x2)
+        const uint32_t ww[4] = {ch.w[u].x, ch.w[u].y, ch.w[u].z, ch.w[u].w};
+        const uint32_t uu[4] = {ch.u[u].x, ch.u[u].y, ch.u[u].z, ch.u[u].w};
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
           // the A registers of reduction values k + 4s .. k + 4s + 3, rows gq and gq + 8, in one load
@@ -266,56 +244,32 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, NSLOT > 0 ? 1 : 2) q8_rows_kern
   };
 
   const int iters = (i1 - i0) * chunks;
-  if (NSLOT > 0) {
-    int slot = 0;
-    for (int it = 0; it < iters; ++it) {
-      fetch_slot(slot == 0 ? NSLOT - 1 : slot - 1);   // the slot consumed one iteration ago
-      asm volatile("cp.async.wait_group %0;" ::"n"(NSLOT > 0 ? NSLOT - 1 : 0) : "memory");
-      const uint4* src = reinterpret_cast<const uint4*>(ring + slot * SLOT_BYTES);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        ca.w[u] = src[32 * u];          // 512 bytes per u, 16 per lane
-        ca.u[u] = src[32 * (U + u)];
-      }
-      multiply(ca);
-      slot = slot + 1 == NSLOT ? 0 : slot + 1;
-    }
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-  } else {
-    for (int it = 0; it < iters; it += 2) {
-      fetch(cb);
-      multiply(ca);
-      if (it + 1 >= iters) break;
-      fetch(ca);
-      multiply(cb);
-    }
+  for (int it = 0; it < iters; it += 2) {
+    fetch(cb);
+    multiply(ca);
+    if (it + 1 >= iters) break;
+    fetch(ca);
+    multiply(cb);
   }
 }
 
-template <bool SWIGLU, int U, int NSLOT>
-static cudaError_t launch_q8_variant(const Q8Args& a, size_t tile_bytes, cudaStream_t stream) {
-  const size_t smem = tile_bytes + (size_t)Q8_WARPS * NSLOT * 2 * U * 512;
-  const dim3 grid((NSLOT > 0 ? 1 : 2) * a.sm_count);   // resident CTAs per SM times SMs
-  if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U, NSLOT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  q8_rows_kernel<SWIGLU, U, NSLOT><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
+template <bool SWIGLU, int U>
+static cudaError_t launch_q8_variant(const Q8Args& a, dim3 grid, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  q8_rows_kernel<SWIGLU, U><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
   count_launch();
   return cudaGetLastError();
 }
 
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream) {
   if (a.tokens <= 0) return cudaSuccess;
-  // The work list is cut on the device, where the routing counts are.  Gate|up (small token tile): one
-  // CTA per SM with a five-slot shared-memory ring per warp (four 4 KB chunks in flight per warp).  Down
-  // (a 90 KB token tile leaves no room for such a ring): two CTAs per SM, weights through registers.
-  const size_t tile_bytes = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
+  // two CTAs per SM (registers and, for the down projection, shared memory allow no more); the work
+  // list is cut on the device, where the routing counts are
+  const dim3 grid(2 * a.sm_count);
+  const size_t smem = (size_t)(Q8_ROWS / 2) * (a.K / 4 + 1) * 16;
   const bool deep = a.K % (Q8_CHUNK * 4) == 0;   // K is always a multiple of 64
-  const bool ring = deep && tile_bytes + (size_t)Q8_WARPS * 5 * 2 * 4 * 512 <= 200 * 1024;
-  if (swiglu) {
-    if (ring) return launch_q8_variant<true, 4, 5>(a, tile_bytes, stream);
-    return deep ? launch_q8_variant<true, 4, 0>(a, tile_bytes, stream) : launch_q8_variant<true, 1, 0>(a, tile_bytes, stream);
-  }
-  if (ring) return launch_q8_variant<false, 4, 5>(a, tile_bytes, stream);
-  return deep ? launch_q8_variant<false, 4, 0>(a, tile_bytes, stream) : launch_q8_variant<false, 1, 0>(a, tile_bytes, stream);
+  if (swiglu) return deep ? launch_q8_variant<true, 4>(a, grid, smem, stream) : launch_q8_variant<true, 1>(a, grid, smem, stream);
+  return deep ? launch_q8_variant<false, 4>(a, grid, smem, stream) : launch_q8_variant<false, 1>(a, grid, smem, stream);
 }
 
 }  // namespace moe

@@ -251,7 +251,9 @@ __global__ void pack_q8_kernel(const int8_t* __restrict__ src, const float* __re
   // fragment-major: blocks of 8 rows x 64 reduction values are contiguous (512 bytes, row-major inside),
   // blocks of one 8-row stripe follow each other along the reduction: a warp of the decode kernel reads
   // one block per load and streams a stripe front to back
-  dst[(long long)(pr / 8) * 8 * ld + (long long)(c / 64) * 512 + (pr % 8) * 64 + (c % 64)] = src[i];
+  // and every byte has its sign bit flipped (value + 128 as an unsigned byte), which is the form the
+  // kernel's int8 -> f16 widening wants; padding bytes of the arena are written as 0x80 at allocation
+  dst[(long long)(pr / 8) * 8 * ld + (long long)(c / 64) * 512 + (pr % 8) * 64 + (c % 64)] = (int8_t)(src[i] ^ (int8_t)0x80);
   if (c == 0) scale_dst[pr] = scale_src[r];
 }
 // Group table of the dense (shared expert, router) GEMMs for every possible token count: entry t is
@@ -735,6 +737,9 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     const long long G = E + 1;   // the shared expert is stored as group E
     DA(L->q_gu, G * 2 * Fp * d, true); DA(L->s_gu, G * 2 * Fp * 4, true);
     DA(L->q_d, G * d * Fp, true); DA(L->s_d, G * d * 4, true);
+    // int8 zero in the stored form (sign bit flipped): padding rows and columns stay zero weights
+    CK(cudaMemset(L->q_gu, 0x80, (size_t)(G * 2 * Fp * d)));
+    CK(cudaMemset(L->q_d, 0x80, (size_t)(G * d * Fp)));
   } else {
     DA(L->w, L->n_params * 4, true);
     if (L->training) {
