@@ -97,3 +97,62 @@ def test_expert_parallel_matches_single_device(precision, transport, overlap, mo
         ret = mgr.dict()
         mp.spawn(_worker, args=(world, port, precision, transport, ret), nprocs=world, join=True)
         assert dict(ret) == {r: True for r in range(world)}
+
+
+def _overflow_worker(rank, world, port, transport, ret):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from helpers import seeded_weights
+        from oracle import ROUTER, GATE, UP, DOWN
+        from rustingbrain_b200 import MoeConfig, InvalidInput
+        from rustingbrain_b200.ep import ExpertParallelMoe
+        d, E, k, F, T = 128, 8, 2, 64, 1024
+        w = seeded_weights(d, E, F, False, 3, std=0.05, router_std=0.05)
+        # room for 1.1 x the balanced share (plus group padding): enough for a balanced batch, not for
+        # one whose every token goes to the same rank
+        layer = ExpertParallelMoe(d, MoeConfig(E, k, F, False), precision="bf16", max_tokens=T, device=rank,
+                                  capacity_factor=1.1, transport=transport)
+        router = w["router"].copy()
+        router[:, d - 1] = 0.0
+        router[:E // world, d - 1] = 8.0          # a constant input column sends every token to rank 0's experts
+        layer.set_weight(ROUTER, 0, router)
+        for e in layer.owned_experts():
+            layer.set_weight(GATE, e, w["gate"][e]); layer.set_weight(UP, e, w["up"][e]); layer.set_weight(DOWN, e, w["down"][e])
+        g = np.random.Generator(np.random.Philox(70 + rank))
+        x = g.standard_normal((T, d)).astype(np.float32)
+        x[:, d - 1] = 1.0
+        refused = False
+        try:
+            layer.forward_train(torch.from_numpy(x).cuda().bfloat16())
+            layer.synchronize()                    # the peer transport reports through a device flag
+        except InvalidInput as e:
+            refused = "ep_capacity_factor" in str(e)
+        # nothing was written past a buffer and the handle is not poisoned: a balanced batch still runs
+        x[:, d - 1] = 0.0
+        y, cache = layer.forward_train(torch.from_numpy(x).cuda().bfloat16())
+        layer.synchronize()
+        counts = cache.routing()[2]
+        ok = refused and bool(torch.isfinite(y.float()).all()) and int(counts.sum()) == T * k
+        if not ok:
+            print("rank", rank, "refused", refused, "counts", counts.tolist(), flush=True)
+        ret[rank] = bool(ok)
+        layer.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("transport", ["peer", "nccl"])
+def test_rows_beyond_a_ranks_capacity_are_refused_on_every_rank(transport):
+    """Dropless routing: when one rank's experts receive more rows than its buffers hold, every rank
+    gets InvalidInput (nobody sends), no memory is touched out of bounds and the handles stay usable."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    port = 29900 + (os.getpid() % 2000)
+    with mp.Manager() as mgr:
+        ret = mgr.dict()
+        mp.spawn(_overflow_worker, args=(2, port, transport, ret), nprocs=2, join=True)
+        assert dict(ret) == {0: True, 1: True}

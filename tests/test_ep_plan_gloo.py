@@ -109,3 +109,23 @@ def test_plan_shapes_and_offsets():
     assert p0["recv_row"].tolist() == [[0, 128], [3, 128]] and p0["local_tiles"].tolist() == [0, 1, 3]
     assert p1["local_counts"].tolist() == [200, 1] and p1["rows"] == 256 + 128
     assert p1["recv_row"].tolist() == [[0, 256], [200, 257]]
+
+
+def test_wrapper_needs_a_process_group():
+    """The expert-parallel wrapper refuses to build before torch.distributed is initialised
+    (a rank that never joined must not get as far as creating a communicator)."""
+    import torch.distributed as dist
+    from rustingbrain_b200 import MoeConfig
+    from rustingbrain_b200.ep import ExpertParallelMoe
+    assert not dist.is_initialized()
+    with pytest.raises(RuntimeError, match="torch.distributed"):
+        ExpertParallelMoe(64, MoeConfig(4, 2, 32))
+
+
+def test_plan_rejects_inconsistent_arguments():
+    from rustingbrain_b200.ep import exchange_plan
+    counts = np.zeros((2, 6), np.int32)
+    with pytest.raises(ValueError):
+        exchange_plan(counts, rank=2)            # no such rank
+    with pytest.raises(ValueError):
+        exchange_plan(np.zeros((4, 6), np.int32), rank=0)   # 6 experts do not split over 4 ranks
