@@ -200,6 +200,28 @@ int32_t moe_route_noalloc(const float* logits_dev, const uint8_t* valid_dev, int
                           float* probabilities_dev, float* log_sum_exp_dev, int32_t* expert_of_dev, float* gates_dev,
                           int32_t* counts_dev, float* losses_dev, void* stream, char* message, int32_t message_len);
 
+/* ---- low-rank adapters (LoRA) on the expert projections ------------------------------------------
+ * TransformerLm::add_lora / merge_lora over this layer (transformer.rs, `Lora` in param.rs:635-714,
+ * MoeLayer::lora_linears_mut in moe.rs:502-514): every gate, up and down projection of the routed
+ * experts this handle owns and of the shared expert gets an adapter
+ *     W_eff = W + (alpha / rank) * up * down,   down [rank, in],  up [out, rank]   (f32, host pointers)
+ * the router gets none, and while adapters are attached the base weights are frozen: moe_step_adam
+ * moves the adapters only.  The adapter is folded into the compute copy of the weights when it or a
+ * base weight changed (once per optimizer step), as the reference's device path does
+ * (gpu_model.rs:1390-1428); forward and backward run the same kernels as without adapters.
+ * moe_get_grad_f32 keeps returning dL/dW_eff; moe_lora_get_grad returns
+ *     d down = scale * up^T * dL/dW_eff        d up = scale * dL/dW_eff * down^T
+ * (what Lora::backward accumulates, param.rs:690-709).  Adapters start as zeros: set `down` (the
+ * reference initialises it He-uniform from its own RNG) and leave `up` zero to start from the base
+ * model.  moe_lora_merge adds the adapters into the master weights and removes them.
+ * Errors: MOE_INVALID_CONFIG for an int8 or inference-only handle, rank outside 1..64, a second attach
+ * or a call without adapters; MOE_INVALID_INPUT for the router or an expert this handle does not own. */
+int32_t moe_lora_attach(moe_layer_t* layer, int32_t rank, float alpha);
+int32_t moe_lora_set(moe_layer_t* layer, int32_t which, int32_t expert, const float* down, const float* up);
+int32_t moe_lora_get(moe_layer_t* layer, int32_t which, int32_t expert, float* down, float* up);
+int32_t moe_lora_get_grad(moe_layer_t* layer, int32_t which, int32_t expert, float* grad_down, float* grad_up);
+int32_t moe_lora_merge(moe_layer_t* layer);
+
 /* Device synchronisation for timing (TransformerLm::synchronize, transformer.rs:1323-1334). */
 int32_t moe_synchronize(moe_layer_t* layer);
 

@@ -79,6 +79,11 @@ def lib() -> C.CDLL:
         "moe_snapshot_info": (i32, [C.c_char_p, C.POINTER(SnapshotInfoC), C.c_char_p, i32]),
         "moe_load_snapshot_layer": (i32, [vp, C.c_char_p, i32]),
         "moe_load_optimizer_layer": (i32, [vp, C.c_char_p, C.POINTER(SnapshotInfoC), i32, C.POINTER(C.c_int64)]),
+        "moe_lora_attach": (i32, [vp, i32, f32]),
+        "moe_lora_set": (i32, [vp, i32, i32, vp, vp]),
+        "moe_lora_get": (i32, [vp, i32, i32, vp, vp]),
+        "moe_lora_get_grad": (i32, [vp, i32, i32, vp, vp]),
+        "moe_lora_merge": (i32, [vp]),
         "moe_route_noalloc": (i32, [vp, vp, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, C.c_char_p, i32]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),

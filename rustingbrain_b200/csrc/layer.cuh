@@ -35,6 +35,16 @@ struct moe_layer {
   float* stage = nullptr;  // staging for weight upload / download (one matrix)
   long long stage_elems = 0;
 
+  // low-rank adapters on the expert projections (moe_lora_attach); base weights are frozen meanwhile
+  int lora_rank = 0, lora_slots = 0;
+  float lora_scale = 0.f;            // alpha / rank
+  long long lora_n = 0;              // floats in the adapter arenas
+  float *la = nullptr, *lg = nullptr, *lm = nullptr, *lv = nullptr;   // adapters, their gradients, Adam moments
+  void* lora_table = nullptr;        // device array of LoraSlot
+  float* w_eff = nullptr;            // f32 handles: W + scale * up * down for the expert GEMMs
+  float* wc = nullptr;               // f32 weights the expert GEMMs read: w, or w_eff with adapters
+  bool lora_dirty = false;           // adapters or base weights changed since the last fold
+
   // int8 inference weights (Q8 precision)
   int8_t* q_gu = nullptr; float* s_gu = nullptr;   // [E][2F_pad][d], [E][2F_pad]
   int8_t* q_d = nullptr;  float* s_d = nullptr;    // [E][d][F_pad],  [E][d]

@@ -326,13 +326,13 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
     { Span sp(L, routed ? 3 : -1, st); CK(tc::gemm_rows_nt(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
   } else {
     SimtGemmArgs a{};
-    a.A = (const float*)io.x; a.B = L->w + io.w_gu; a.C = (float*)io.gu;
+    a.A = (const float*)io.x; a.B = L->wc + io.w_gu; a.C = (float*)io.gu;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows; a.b_rows = 0;
     a.N = 2 * Fp; a.K = d; a.b_group_stride = 2ll * Fp * d;
     { Span sp(L, routed ? 2 : -1, st); CK(simt_gemm_nt(a, st));
     CK(launch_swiglu_fwd_f32((const float*)io.gu, (float*)io.h, G.cap_rows, Fp, st)); }
     SimtGemmArgs b{};
-    b.A = (const float*)io.h; b.B = L->w + io.w_d; b.C = (float*)io.y;
+    b.A = (const float*)io.h; b.B = L->wc + io.w_d; b.C = (float*)io.y;
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = Fp; b.b_group_stride = (long long)d * Fp;
     { Span sp(L, routed ? 3 : -1, st); CK(simt_gemm_nt(b, st)); }
@@ -384,7 +384,7 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
   } else {
     if (parts & 1) {
     SimtGemmArgs a{};
-    a.A = (const float*)io.dy; a.B = L->w + io.w_d; a.C = (float*)io.dh;
+    a.A = (const float*)io.dy; a.B = L->wc + io.w_d; a.C = (float*)io.dh;
     a.group_row0 = G.row0; a.n_groups = G.n_groups; a.max_rows = G.cap_rows; a.a_rows = G.in_rows;
     a.N = Fp; a.K = d; a.b_group_stride = (long long)d * Fp;
     { Span sp(L, routed ? 6 : -1, st); CK(simt_gemm_nn(a, st));
@@ -399,7 +399,7 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     }
     if (parts & 1) {
     SimtGemmArgs b{};
-    b.A = (const float*)io.dgu; b.B = L->w + io.w_gu; b.C = (float*)io.dx;
+    b.A = (const float*)io.dgu; b.B = L->wc + io.w_gu; b.C = (float*)io.dx;
     b.group_row0 = G.row0; b.n_groups = G.n_groups; b.max_rows = G.cap_rows; b.a_rows = G.cap_rows;
     b.N = d; b.K = 2 * Fp; b.b_group_stride = 2ll * Fp * d;
     { Span sp(L, routed ? 8 : -1, st); CK(simt_gemm_nn(b, st)); }
@@ -416,6 +416,7 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
 }
 
 #include "ep_impl.inc"
+#include "lora_impl.inc"
 
 int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens, int cols, const uint8_t* valid,
                  void* y, int accumulate, int save, cudaStream_t st) {
@@ -435,6 +436,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   L->last_tokens = tokens;
   L->last_stream = st;
   if (tokens == 0 && !ep) return MOE_OK;   // an expert-parallel rank with no tokens still serves its experts
+  { const int fr = lora_fold(L, st); if (fr != MOE_OK) return fr; }   // adapters into the compute weights, if they changed
   if (L->training && overlap_mode() == 2) select_parity(L, L->parity ^ 1);   // deferred weight gradients may still read the other half
 
   RouterArgs ra{};
@@ -742,6 +744,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     CK(cudaMemset(L->q_d, 0x80, (size_t)(G * d * Fp)));
   } else {
     DA(L->w, L->n_params * 4, true);
+    L->wc = L->w;
     if (L->training) {
       DA(L->g, L->n_params * 4, true);
       DA(L->m, L->n_params * 4, true);
@@ -871,6 +874,7 @@ int32_t moe_set_weight_f32(moe_layer_t* L, int32_t which, int32_t expert, const 
     dev_src = L->stage;
   }
   pack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(dev_src, L->w + s.offset, L->wb ? L->wb + s.offset : nullptr, rows, cols, s.ld, s.kind); count_launch();
+  if (L->lora_rank > 0) L->lora_dirty = true;
   CK(cudaGetLastError());
   CK(cudaDeviceSynchronize());
   return MOE_OK;
@@ -990,9 +994,18 @@ int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, f
   if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
   cudaStream_t st = (cudaStream_t)stream;
   { const int jr = join_side(L, st); if (jr != MOE_OK) return jr; }
-  if (!L->grad_valid) CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
   AdamArgs a{};
-  a.w = L->w; a.g = L->g; a.m = L->m; a.v = L->v; a.w_bf16 = L->wb; a.n = L->n_params;
+  if (L->lora_rank > 0) {
+    // base weights are frozen (the reference's add_lora): only the adapters move
+    const int pr = lora_project_grads(L, st);
+    if (pr != MOE_OK) return pr;
+    CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
+    a.w = L->la; a.g = L->lg; a.m = L->lm; a.v = L->lv; a.w_bf16 = nullptr; a.n = L->lora_n;
+    L->lora_dirty = true;
+  } else {
+    if (!L->grad_valid) CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
+    a.w = L->w; a.g = L->g; a.m = L->m; a.v = L->v; a.w_bf16 = L->wb; a.n = L->n_params;
+  }
   a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
   a.c1 = 1.0f - powf(b1, (float)step);
   a.c2 = 1.0f - powf(b2, (float)step);
@@ -1186,6 +1199,71 @@ int32_t moe_ep_plan(const int32_t* counts_all, int32_t ranks, int32_t num_expert
                     int32_t* recv_row, int32_t* local_row0, int32_t* local_tiles, int32_t* local_counts) {
   if (!counts_all || ranks <= 0 || num_experts <= 0 || num_experts % ranks != 0 || rank < 0 || rank >= ranks) return -1;
   return ep_plan(counts_all, ranks, num_experts, rank, send_off, recv_row, local_row0, local_tiles, local_counts);
+}
+
+static int lora_slot_checked(moe_layer* L, int which, int expert, LoraSlot* out) {
+  if (L->lora_rank == 0) { L->err = "InvalidConfig: the layer has no adapters (moe_lora_attach)"; return MOE_INVALID_CONFIG; }
+  const int idx = lora_slot_index(L, which, expert);
+  if (idx < 0) { L->err = "InvalidInput: no adapter on that matrix (router, foreign or missing expert)"; return MOE_INVALID_INPUT; }
+  CK(cudaMemcpy(out, (const LoraSlot*)L->lora_table + idx, sizeof(LoraSlot), cudaMemcpyDeviceToHost));
+  return MOE_OK;
+}
+
+int32_t moe_lora_attach(moe_layer_t* L, int32_t rank, float alpha) {
+  ENTER(L);
+  return lora_attach(L, rank, alpha);
+}
+
+int32_t moe_lora_set(moe_layer_t* L, int32_t which, int32_t expert, const float* down, const float* up) {
+  ENTER(L);
+  LoraSlot s;
+  int rc = lora_slot_checked(L, which, expert, &s);
+  if (rc != MOE_OK) return rc;
+  if (!down || !up) { L->err = "InvalidInput: null adapter pointer"; return MOE_INVALID_INPUT; }
+  CK(cudaDeviceSynchronize());
+  CK(cudaMemcpy(L->la + s.a_off, down, (size_t)L->lora_rank * s.cols * 4, cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(L->la + s.a_off + (long long)L->lora_rank * s.cols, up, (size_t)s.rows * L->lora_rank * 4, cudaMemcpyHostToDevice));
+  L->lora_dirty = true;
+  return MOE_OK;
+}
+
+int32_t moe_lora_get(moe_layer_t* L, int32_t which, int32_t expert, float* down, float* up) {
+  ENTER(L);
+  LoraSlot s;
+  int rc = lora_slot_checked(L, which, expert, &s);
+  if (rc != MOE_OK) return rc;
+  CK(cudaDeviceSynchronize());
+  if (down) CK(cudaMemcpy(down, L->la + s.a_off, (size_t)L->lora_rank * s.cols * 4, cudaMemcpyDeviceToHost));
+  if (up) CK(cudaMemcpy(up, L->la + s.a_off + (long long)L->lora_rank * s.cols, (size_t)s.rows * L->lora_rank * 4, cudaMemcpyDeviceToHost));
+  return MOE_OK;
+}
+
+int32_t moe_lora_get_grad(moe_layer_t* L, int32_t which, int32_t expert, float* grad_down, float* grad_up) {
+  ENTER(L);
+  LoraSlot s;
+  int rc = lora_slot_checked(L, which, expert, &s);
+  if (rc != MOE_OK) return rc;
+  CK(cudaDeviceSynchronize());
+  if ((rc = lora_project_grads(L, nullptr)) != MOE_OK) return rc;
+  CK(cudaDeviceSynchronize());
+  if (grad_down) CK(cudaMemcpy(grad_down, L->lg + s.a_off, (size_t)L->lora_rank * s.cols * 4, cudaMemcpyDeviceToHost));
+  if (grad_up) CK(cudaMemcpy(grad_up, L->lg + s.a_off + (long long)L->lora_rank * s.cols, (size_t)s.rows * L->lora_rank * 4, cudaMemcpyDeviceToHost));
+  return MOE_OK;
+}
+
+int32_t moe_lora_merge(moe_layer_t* L) {
+  ENTER(L);
+  if (L->lora_rank == 0) { L->err = "InvalidConfig: the layer has no adapters (moe_lora_attach)"; return MOE_INVALID_CONFIG; }
+  CK(cudaDeviceSynchronize());
+  // W <- W + scale * up * down in the master weights and the bf16 compute copy, then drop the adapters
+  lora_fold_kernel<<<dim3(64, L->lora_slots), 256>>>((const LoraSlot*)L->lora_table, L->w, L->la, L->lora_rank, L->lora_scale, L->w, L->wb);
+  count_launch();
+  CK(cudaGetLastError());
+  CK(cudaDeviceSynchronize());
+  L->lora_rank = 0;          // the arenas stay allocated until the handle is destroyed
+  L->lora_dirty = false;
+  L->wc = L->w;
+  return MOE_OK;
 }
 
 int32_t moe_synchronize(moe_layer_t* L) {

@@ -246,6 +246,45 @@ class MoeLayer:
                                                      C.byref(step)))
         return int(step.value)
 
+    # ---- low-rank adapters on the expert projections (TransformerLm::add_lora / merge_lora) ----
+    def lora_attach(self, rank: int, alpha: float = None):
+        """Attaches `W + (alpha / rank) * up * down` adapters to every expert projection (not the router)
+        and freezes the base weights (param.rs:635-714, moe.rs:502-514).  ``alpha`` defaults to ``rank``."""
+        self._ck(_lib.lib().moe_lora_attach(self._h, int(rank), float(rank if alpha is None else alpha)))
+        self._lora_rank = int(rank)
+
+    def _lora_shapes(self, which):
+        rows, cols = self._shape(which)
+        r = getattr(self, "_lora_rank", 0)
+        return (r, cols), (rows, r)
+
+    def lora_set(self, which: int, expert: int, down, up):
+        ds, us = self._lora_shapes(which)
+        down = np.ascontiguousarray(down, dtype=np.float32)
+        up = np.ascontiguousarray(up, dtype=np.float32)
+        if down.shape != ds or up.shape != us:
+            raise InvalidInput("adapter shapes %s / %s, expected %s / %s" % (down.shape, up.shape, ds, us))
+        self._ck(_lib.lib().moe_lora_set(self._h, which, expert, down.ctypes.data, up.ctypes.data))
+
+    def _lora_read(self, fn, which, expert):
+        ds, us = self._lora_shapes(which)
+        down, up = np.empty(ds, np.float32), np.empty(us, np.float32)
+        self._ck(fn(self._h, which, expert, down.ctypes.data, up.ctypes.data))
+        return down, up
+
+    def lora_get(self, which: int, expert: int = 0):
+        """(down [rank, in], up [out, rank])."""
+        return self._lora_read(_lib.lib().moe_lora_get, which, expert)
+
+    def lora_get_grad(self, which: int, expert: int = 0):
+        """Gradients of (down, up) from the accumulated weight gradient (Lora::backward, param.rs:690-709)."""
+        return self._lora_read(_lib.lib().moe_lora_get_grad, which, expert)
+
+    def lora_merge(self):
+        """Adds the adapters into the weights and removes them (merge_lora)."""
+        self._ck(_lib.lib().moe_lora_merge(self._h))
+        self._lora_rank = 0
+
     def set_weights(self, router, gate, up, down, shared=None):
         """router [E,d]; gate/up [E,F,d]; down [E,d,F]; shared = (gate, up, down) of one expert."""
         self.set_weight(W_ROUTER, 0, router)
