@@ -628,4 +628,11 @@ cudaError_t launch_router_wgrad(const RouterWgradArgs& a, int precision, cudaStr
   return cudaGetLastError();
 }
 
+// Second stage alone: adds `splits` partial E x d results in order (the tensor-core path writes them).
+cudaError_t launch_router_wgrad_sum(const RouterWgradArgs& a, cudaStream_t stream) {
+  const long long n = (long long)a.E * a.d;
+  router_wgrad_stage2<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(a); count_launch();
+  return cudaGetLastError();
+}
+
 }  // namespace moe

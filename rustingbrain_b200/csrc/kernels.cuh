@@ -171,6 +171,7 @@ struct RouterWgradArgs {
   int tokens, d, E, splits, accumulate;
 };
 cudaError_t launch_router_wgrad(const RouterWgradArgs& a, int precision, cudaStream_t stream);
+cudaError_t launch_router_wgrad_sum(const RouterWgradArgs& a, cudaStream_t stream);
 
 // ----- int8 expert weights for decode-sized batches (decode_q8.cu) -----
 // out[row, n] = (sum_k x[row,k] * q_g[n,k]) * scale_g[n], rows of group g < E taken from the

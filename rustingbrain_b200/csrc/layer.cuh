@@ -74,6 +74,7 @@ struct moe_layer {
   void* dx_r = nullptr;           // [shared_rows_cap, d] router input gradient
   bool tc_router = false;         // router products on the tensor cores (bf16, E % 8 == 0)
   int rw_splits = 1;
+  int* rw_meta = nullptr;         // [splits + 1] token-chunk boundaries of the split router weight gradient
 
   // expert parallelism (ep_size > 1): the send side keeps the compact expert-major
   // layout in x_perm / y_perm / dy_perm / dx_perm; rows received for the local experts

@@ -256,6 +256,12 @@ __global__ void pack_q8_kernel(const int8_t* __restrict__ src, const float* __re
   dst[(long long)(pr / 8) * 8 * ld + (long long)(c / 64) * 512 + (pr % 8) * 64 + (c % 64)] = (int8_t)(src[i] ^ (int8_t)0x80);
   if (c == 0) scale_dst[pr] = scale_src[r];
 }
+// Row ranges of the token chunks the router weight gradient is split into (rows are the reduction of
+// that GEMM): meta[g] = min(g * chunk, padded), g = 0..splits.
+__global__ void split_meta_kernel(int* meta, int splits, int chunk, int padded) {
+  const int g = threadIdx.x;
+  if (g <= splits) meta[g] = min(g * chunk, padded);
+}
 // Group table of the dense (shared expert, router) GEMMs for every possible token count: entry t is
 // {row0[0], row0[1], tile_start[0], tile_start[1]} of one group of t rows.  Filled once, so a pass only
 // picks a pointer instead of launching a kernel.
@@ -575,12 +581,32 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   };
   auto router_weight_gradient = [&](cudaStream_t s) -> int {
     if (L->tc_router && tokens > 0) {
+      // E x d output = a handful of tiles, tokens = the reduction: split the tokens into chunks (one
+      // group each, partial results in scratch) so that every SM has a tile, then add the chunks in order
       Span sp(L, 12, s);
+      const int tiles = ceil_div(L->E, 128) * ceil_div(L->d, 256);
+      const int padded = round_up(tokens, GROUP_ALIGN);
+      int splits = std::max(1, std::min(std::min(L->rw_splits, 64), L->sm_count / std::max(1, tiles)));
+      const int chunk = round_up(ceil_div(padded, splits), GROUP_ALIGN);
+      splits = ceil_div(padded, chunk);
       tc::GemmArgs wg{};
-      wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.error_flag = L->error_flag;
-      wg.M = L->E; wg.N = L->d; wg.out0 = L->g + L->off_router; wg.ld0 = L->d; wg.accumulate = L->grad_valid ? 1 : 0;
+      wg.error_flag = L->error_flag;
+      wg.M = L->E; wg.N = L->d; wg.ld0 = L->d;
       tc::Operand Ax{L->last_x, tokens, L->d, 1};
-      CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
+      if (splits > 1) {
+        split_meta_kernel<<<1, 128, 0, s>>>(L->rw_meta, splits, chunk, padded); count_launch();
+        wg.group_row0 = L->rw_meta; wg.n_groups = splits; wg.out0 = L->rw_scratch;
+        wg.group_stride0 = (long long)L->E * L->d; wg.accumulate = 0;
+        CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
+        RouterWgradArgs rw{};
+        rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch; rw.d = L->d; rw.E = L->E; rw.splits = splits;
+        rw.accumulate = L->grad_valid ? 1 : 0;
+        CK(launch_router_wgrad_sum(rw, s));
+      } else {
+        wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.out0 = L->g + L->off_router;
+        wg.accumulate = L->grad_valid ? 1 : 0;
+        CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
+      }
     } else {
       RouterWgradArgs rw{};
       rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
@@ -818,6 +844,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     if (L->tc_router) { DA(L->gl_bf16, T * E * 2, true); DA(L->dx_r, sc * d * es, true); }
     L->rw_splits = (int)std::min<long long>(64, std::max<long long>(1, T / 256));
     DA(L->rw_scratch, (long long)L->rw_splits * E * d * 4, false);
+    DA(L->rw_meta, 130 * 4, true);
   }
   CK(cudaStreamCreateWithFlags(&L->side_stream, cudaStreamNonBlocking));
   CK(cudaEventCreateWithFlags(&L->ev_fork, cudaEventDisableTiming));
