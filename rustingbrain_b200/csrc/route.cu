@@ -251,39 +251,83 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
 }
 
 // One block.  hist[b][e] becomes the padded-row write cursor of block b for expert e.
-__global__ void __launch_bounds__(256)
+constexpr int FIN_THREADS = 1024;
+__global__ void __launch_bounds__(FIN_THREADS)
 finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int nb, int E, int k, float aux_w,
                 float z_w, RouteMeta meta, float* __restrict__ stats /*[E+2]: sums, lse2, V*/,
                 float* __restrict__ losses /*[2]*/, int align, int add_base) {
   __shared__ int s_counts[MAX_EXPERTS];
   __shared__ float s_sums[MAX_EXPERTS + 2];
+  __shared__ double seg_d[FIN_THREADS + 64];   // [parts][E + 2] partial statistics
+  __shared__ int seg_i[FIN_THREADS];           // [parts][E] rows per expert in a run of router blocks
   const int tid = threadIdx.x;
-  for (int e = tid; e < E + 2; e += blockDim.x) {
-    double s = 0.0;
-    for (int b0 = 0; b0 < nb; b0 += 8) {            // eight independent loads, then the ordered sum
-      float v[8];
+  // The router blocks are cut into `parts` consecutive runs, one thread per (run, column): the
+  // statistics are summed per run and then over the runs in order (in double, so the association does
+  // not show in the f32 result); the per-expert cursors take one pass for the run totals and a second
+  // one that writes the exclusive prefix.
+  {
+    const int cols = E + 2, parts = max(1, (int)blockDim.x / cols), seg = ceil_div(nb, parts);
+    const int part = tid / cols, e = tid - part * cols;
+    if (cols > (int)blockDim.x) {                    // more columns than threads: one run, strided columns
+      for (int c = tid; c < cols; c += blockDim.x) {
+        double sum = 0.0;
+        for (int b = 0; b < nb; ++b) sum += (double)partial[(size_t)b * cols + c];
+        seg_d[c] = sum;
+      }
+    } else if (part < parts) {
+      double sum = 0.0;
+      const int lo = part * seg, hi = min(nb, lo + seg);
+      for (int b0 = lo; b0 < hi; b0 += 8) {          // eight independent loads, then the ordered sum
+        float v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = b0 + i < nb ? partial[(size_t)(b0 + i) * (E + 2) + e] : 0.f;
+        for (int i = 0; i < 8; ++i) v[i] = b0 + i < hi ? partial[(size_t)(b0 + i) * cols + e] : 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) if (b0 + i < nb) s += (double)v[i];
+        for (int i = 0; i < 8; ++i) if (b0 + i < hi) sum += (double)v[i];
+      }
+      seg_d[part * cols + e] = sum;
     }
-    s_sums[e] = (float)s;
-    stats[e] = (float)s;
+    __syncthreads();
+    for (int c = tid; c < cols; c += blockDim.x) {
+      double t = 0.0;
+      for (int p = 0; p < (cols > (int)blockDim.x ? 1 : parts); ++p) t += seg_d[p * cols + c];
+      s_sums[c] = (float)t;
+      stats[c] = (float)t;
+    }
   }
-  for (int e = tid; e < E; e += blockDim.x) {
-    int run = 0;
-    for (int b0 = 0; b0 < nb; b0 += 8) {
-      int h[8];
+  {
+    const int parts = max(1, (int)blockDim.x / E), seg = ceil_div(nb, parts);
+    const int part = tid / E, e = tid - part * E;
+    const int lo = part * seg, hi = min(nb, lo + seg);
+    if (part < parts) {
+      int run = 0;
+      for (int b0 = lo; b0 < hi; b0 += 8) {
+        int h[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) h[i] = b0 + i < nb ? hist[(size_t)(b0 + i) * E + e] : 0;
+        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (b0 + i < nb) hist[(size_t)(b0 + i) * E + e] = run;
-        run += h[i];
+        for (int i = 0; i < 8; ++i) run += h[i];
+      }
+      seg_i[part * E + e] = run;
+    }
+    __syncthreads();
+    if (part < parts) {
+      int run = 0;
+      for (int p = 0; p < part; ++p) run += seg_i[p * E + e];
+      for (int b0 = lo; b0 < hi; b0 += 8) {
+        int h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (b0 + i < hi) hist[(size_t)(b0 + i) * E + e] = run;
+          run += h[i];
+        }
+      }
+      if (part == parts - 1) {        // the last run ends at the expert's total
+        s_counts[e] = run;
+        meta.counts[e] = run;
       }
     }
-    s_counts[e] = run;
-    meta.counts[e] = run;
   }
   __syncthreads();
   if (tid == 0) {
@@ -610,7 +654,7 @@ cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, fl
                             int align, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
   const int fold = nb <= 16 ? 1 : 0;
-  finalize_kernel<<<1, 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align, fold); count_launch();
+  finalize_kernel<<<1, nb > 32 ? FIN_THREADS : 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align, fold); count_launch();
   if (nb > 0 && !fold) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
   return cudaGetLastError();
 }

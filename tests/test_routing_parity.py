@@ -81,3 +81,12 @@ def test_ragged_token_counts_and_all_padding():
     logits = np.random.Generator(np.random.Philox(3)).standard_normal((5, 6)).astype(np.float32)
     cache = _run(5, 6, 2, logits, valid=np.zeros(5, np.uint8))
     assert cache.routing()[2].sum() == 0 and cache.auxiliary_loss() == 0.0
+
+
+def test_the_largest_expert_count():
+    """256 experts (the library's limit): 64 per lane in the four-lane top-k scan, more statistics
+    columns than threads in the small-batch finalize."""
+    for T, k in ((300, 4), (5000, 16)):
+        logits = np.random.Generator(np.random.Philox(256 + T)).standard_normal((T, 256)).astype(np.float32)
+        logits[::7] = np.round(logits[::7] * 4) / 4       # ties across lane ranges
+        _run(T, 256, k, logits)
