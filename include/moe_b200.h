@@ -273,6 +273,16 @@ int32_t moe_load_snapshot_layer(moe_layer_t* layer, const char* weights_path, in
 int32_t moe_load_optimizer_layer(moe_layer_t* layer, const char* moments_path, const moe_snapshot_info_t* info,
                                  int32_t block_index, int64_t* step);
 
+/* Fills the adapters of block `block_index` from an adapter file ("RBLOR001", TransformerLm::save_lora /
+ * load_lora, transformer.rs:1109-1202): magic, u64 header length, JSON LoraConfig {rank, alpha, seed}, u64
+ * parameter count, then per adapter matrix u64 rows, u64 cols and f32 data; the adapters of a model are
+ * written block by block, four attention projections then the feed-forward ones (for a MoE block every
+ * expert's gate, up, down and the shared expert's; never the router), `down` before `up`.  As load_lora
+ * does, the layer must already carry adapters of the file's rank and alpha (moe_lora_attach), and any
+ * mismatch fails without loading part of an adapter file's block.  `info` as for the moments file. */
+int32_t moe_load_lora_layer(moe_layer_t* layer, const char* lora_path, const moe_snapshot_info_t* info,
+                            int32_t block_index);
+
 #ifdef __cplusplus
 }
 #endif

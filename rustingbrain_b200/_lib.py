@@ -84,6 +84,7 @@ def lib() -> C.CDLL:
         "moe_lora_get": (i32, [vp, i32, i32, vp, vp]),
         "moe_lora_get_grad": (i32, [vp, i32, i32, vp, vp]),
         "moe_lora_merge": (i32, [vp]),
+        "moe_load_lora_layer": (i32, [vp, C.c_char_p, C.POINTER(SnapshotInfoC), i32]),
         "moe_route_noalloc": (i32, [vp, vp, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, C.c_char_p, i32]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),

@@ -38,6 +38,7 @@ struct moe_layer {
   // low-rank adapters on the expert projections (moe_lora_attach); base weights are frozen meanwhile
   int lora_rank = 0, lora_slots = 0;
   float lora_scale = 0.f;            // alpha / rank
+  float lora_alpha = 0.f;
   long long lora_n = 0;              // floats in the adapter arenas
   float *la = nullptr, *lg = nullptr, *lm = nullptr, *lv = nullptr;   // adapters, their gradients, Adam moments
   void* lora_table = nullptr;        // device array of LoraSlot

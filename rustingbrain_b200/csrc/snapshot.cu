@@ -472,4 +472,87 @@ int32_t moe_load_optimizer_layer(moe_layer_t* L, const char* moments_path, const
   return MOE_OK;
 }
 
+int32_t moe_load_lora_layer(moe_layer_t* L, const char* lora_path, const moe_snapshot_info_t* info, int32_t block_index) {
+  if (!L) return MOE_INVALID_INPUT;
+  if (L->status != MOE_OK) return MOE_POISONED;
+  if (!lora_path || !info) { L->err = "InvalidInput: null argument"; return MOE_INVALID_INPUT; }
+  int rc = check_block(L, *info, block_index);
+  if (rc != MOE_OK) return rc;
+  if (L->lora_rank == 0) {   // transformer.rs:1168-1172
+    L->err = "InvalidSnapshot: this layer has no LoRA adapter to load into; call moe_lora_attach first";
+    return MOE_INVALID_INPUT;
+  }
+  File in(lora_path);
+  char magic[8];
+  uint64_t hlen = 0, count = 0;
+  if (!in.f || !in.read(magic, 8) || memcmp(magic, "RBLOR001", 8) != 0) {
+    L->err = "InvalidSnapshot: not a RustingBrain LoRA file";   // transformer.rs:1150-1154
+    return MOE_INVALID_INPUT;
+  }
+  if (!in.u64(&hlen) || hlen == 0 || hlen > (1u << 20)) { L->err = "InvalidSnapshot: bad header length"; return MOE_INVALID_INPUT; }
+  std::string text(hlen, '\0');
+  if (!in.read(&text[0], hlen)) { L->err = "InvalidSnapshot: truncated header"; return MOE_INVALID_INPUT; }
+  JsonParser jp{text.data(), text.data() + text.size()};
+  const Json root = jp.value();
+  const Json* jr = jp.ok ? root.get("rank") : nullptr;
+  const Json* ja = jp.ok ? root.get("alpha") : nullptr;
+  if (!jr || jr->kind != Json::Number || !ja || ja->kind != Json::Number) {
+    L->err = "InvalidSnapshot: the header is not the LoraConfig save_lora writes";
+    return MOE_INVALID_INPUT;
+  }
+  if ((int)jr->num != L->lora_rank || (float)ja->num != L->lora_alpha) {   // transformer.rs:1161-1167
+    L->err = "InvalidSnapshot: adapter file holds rank " + std::to_string((int)jr->num) + " alpha " + std::to_string(ja->num) +
+             ", this layer has rank " + std::to_string(L->lora_rank) + " alpha " + std::to_string(L->lora_alpha);
+    return MOE_INVALID_INPUT;
+  }
+  // adapters sit on the four attention projections and on the feed-forward projections of every block
+  // (transformer_block.rs:274-278; a MoE block: experts and shared expert, not the router), two
+  // parameters each (down, up; param.rs:711-713), in block order
+  auto linears_of = [&](int64_t b) {
+    bool moe = false;
+    for (int i = 0; i < info->n_moe_layers; ++i) moe = moe || info->moe_layers[i] == b;
+    return (int64_t)4 + (moe ? 3 * info->num_experts + (info->shared_expert ? 3 : 0) : info->dense_ffn_params);
+  };
+  int64_t total = 0, before = 0;
+  for (int64_t b = 0; b < info->n_layers; ++b) {
+    if (b < block_index) before += linears_of(b);
+    total += linears_of(b);
+  }
+  if (!in.u64(&count) || (int64_t)count != 2 * total) {   // transformer.rs:1178-1183
+    L->err = "InvalidSnapshot: adapter file holds " + std::to_string(count) + " parameters, this model has " + std::to_string(2 * total);
+    return MOE_INVALID_INPUT;
+  }
+  auto skip = [&](int64_t n) {
+    for (int64_t i = 0; i < n; ++i) {
+      uint64_t rows, cols;
+      if (!in.u64(&rows) || !in.u64(&cols) || !in.skip(rows * cols * 4)) return false;
+    }
+    return true;
+  };
+  auto read = [&](uint64_t want_rows, uint64_t want_cols, std::vector<float>* out) {
+    uint64_t rows, cols;
+    if (!in.u64(&rows) || !in.u64(&cols)) { L->err = "InvalidSnapshot: truncated adapter file"; return false; }
+    if (rows != want_rows || cols != want_cols) {   // transformer.rs:1189-1194
+      L->err = "InvalidSnapshot: adapter file has a " + std::to_string(rows) + "x" + std::to_string(cols) +
+               " parameter where the layer has " + std::to_string(want_rows) + "x" + std::to_string(want_cols);
+      return false;
+    }
+    out->resize((size_t)(rows * cols));
+    if (!in.read(out->data(), out->size() * 4)) { L->err = "InvalidSnapshot: truncated adapter file"; return false; }
+    return true;
+  };
+  if (!skip(2 * (before + 4))) { L->err = "InvalidSnapshot: truncated adapter file"; return MOE_INVALID_INPUT; }
+  std::vector<float> down, up;
+  for (const Entry& en : moe_entries(L)) {
+    if (en.which == MOE_W_ROUTER) continue;
+    if (!en.mine) {
+      if (!skip(2)) { L->err = "InvalidSnapshot: truncated adapter file"; return MOE_INVALID_INPUT; }
+      continue;
+    }
+    if (!read((uint64_t)L->lora_rank, en.cols, &down) || !read(en.rows, (uint64_t)L->lora_rank, &up)) return MOE_INVALID_INPUT;
+    if ((rc = moe_lora_set(L, en.which, en.expert, down.data(), up.data())) != MOE_OK) return rc;
+  }
+  return MOE_OK;
+}
+
 }  // extern "C"

@@ -280,6 +280,11 @@ class MoeLayer:
         """Gradients of (down, up) from the accumulated weight gradient (Lora::backward, param.rs:690-709)."""
         return self._lora_read(_lib.lib().moe_lora_get_grad, which, expert)
 
+    def load_lora(self, path, info, block: int):
+        """Fills the attached adapters from block ``block`` of a ``save_lora`` file
+        (transformer.rs:1109-1202); ``info`` is `snapshot.snapshot_info` of the matching weight file."""
+        self._ck(_lib.lib().moe_load_lora_layer(self._h, str(path).encode(), C.byref(info._c), int(block)))
+
     def lora_merge(self):
         """Adds the adapters into the weights and removes them (merge_lora)."""
         self._ck(_lib.lib().moe_lora_merge(self._h))

@@ -23,6 +23,7 @@ from . import _lib
 
 WEIGHTS_MAGIC = b"RBWTS001"
 OPTIMIZER_MAGIC = b"RBOPT001"
+LORA_MAGIC = b"RBLOR001"
 
 
 class InvalidSnapshot(ValueError):
@@ -154,3 +155,32 @@ def write_optimizer_state(path: str, moments: Sequence[Optional[Tuple[np.ndarray
             f.write(struct.pack("<QQ", m.shape[0], m.shape[1]))
             f.write(m.astype("<f4").tobytes())
             f.write(v.astype("<f4").tobytes())
+
+
+def adapter_names(config: Dict[str, object], rank: int, dense_ffn_params: int = 3) -> List[Tuple[str, Tuple[int, int]]]:
+    """(name, (rows, cols)) of every adapter matrix in `save_lora` order: per block the four attention
+    projections, then the feed-forward projections (MoE: every expert's and the shared expert's, never
+    the router; transformer_block.rs:274-278, moe.rs:502-514), `down` [rank, in] before `up` [out, rank]
+    (param.rs:711-713)."""
+    out: List[Tuple[str, Tuple[int, int]]] = []
+    for name, (rows, cols) in parameter_names(config, dense_ffn_params):
+        part = name.split(".")
+        adapted = len(part) > 2 and (part[2] == "attention" or part[2] == "ffn" or
+                                     (part[2] == "moe" and part[3] != "router"))
+        if adapted:
+            out += [(name + ".lora.down", (rank, cols)), (name + ".lora.up", (rows, rank))]
+    return out
+
+
+def write_lora(path: str, rank: int, alpha: float, tensors: Iterable[np.ndarray], seed: int = 0) -> None:
+    """save_lora: the adapter matrices in `adapter_names` order."""
+    header = json.dumps({"rank": int(rank), "alpha": float(alpha), "seed": int(seed)}, separators=(",", ":")).encode()
+    tensors = [np.ascontiguousarray(t, dtype=np.float32) for t in tensors]
+    with open(path, "wb") as f:
+        f.write(LORA_MAGIC)
+        f.write(struct.pack("<Q", len(header)))
+        f.write(header)
+        f.write(struct.pack("<Q", len(tensors)))
+        for t in tensors:
+            f.write(struct.pack("<QQ", t.shape[0], t.shape[1]))
+            f.write(t.astype("<f4").tobytes())

@@ -226,3 +226,41 @@ def test_adam_moments_are_restored(tmp_path):
     from rustingbrain_b200 import InvalidInput
     with pytest.raises(InvalidInput, match="optimizer state"):
         layer.load_optimizer_state(tmp_path / "bad.opt", info, 1)
+
+
+@pytest.mark.gpu
+def test_adapter_file_fills_the_attached_adapters(tmp_path):
+    torch, MoeConfig, MoeLayer = _gpu_imports()
+    from rustingbrain_b200 import InvalidInput
+    from rustingbrain_b200.snapshot import adapter_names, write_lora
+    cfg = tiny_config()
+    _, ts = tensors_for(cfg)
+    write_snapshot(tmp_path / "m.rbw", cfg, ts)
+    info = snapshot_info(tmp_path / "m.rbw")
+    rank, alpha = 4, 8.0
+    names = adapter_names(cfg, rank)
+    g = np.random.Generator(np.random.Philox(17))
+    ad = [(g.standard_normal(s) * 0.1).astype(np.float32) for _, s in names]
+    write_lora(tmp_path / "m.lora", rank, alpha, ad)
+    layer = MoeLayer(64, MoeConfig(4, 2, 64, True), precision="f32", max_tokens=8)
+    with pytest.raises(InvalidInput, match="moe_lora_attach"):
+        layer.load_lora(tmp_path / "m.lora", info, 2)           # load_lora wants the adapters to exist already
+    layer.lora_attach(rank, alpha)
+    layer.load_lora(tmp_path / "m.lora", info, 2)
+    by_name = {n: t for (n, _), t in zip(names, ad)}
+    for e in range(4):
+        for part, which in WHICH.items():
+            down, up = layer.lora_get(which, e)
+            key = "blocks.2.moe.experts.%d.%s.lora." % (e, part)
+            assert np.array_equal(down, by_name[key + "down"]) and np.array_equal(up, by_name[key + "up"]), key
+    for part, which in WHICH.items():
+        down, up = layer.lora_get(which + 3, 0)
+        key = "blocks.2.moe.shared.%s.lora." % part
+        assert np.array_equal(down, by_name[key + "down"]) and np.array_equal(up, by_name[key + "up"])
+    other = MoeLayer(64, MoeConfig(4, 2, 64, True), precision="f32", max_tokens=8)
+    other.lora_attach(rank, 4.0)
+    with pytest.raises(InvalidInput, match="alpha"):
+        other.load_lora(tmp_path / "m.lora", info, 2)           # rank and alpha must be the file's
+    write_lora(tmp_path / "short.lora", rank, alpha, ad[:-2])
+    with pytest.raises(InvalidInput, match="parameters"):
+        layer.load_lora(tmp_path / "short.lora", info, 2)
