@@ -239,8 +239,9 @@ int32_t moe_synchronize(moe_layer_t* layer);
  * (transformer.rs:1620-1630): embedding; per block attention norm, query, key, value, output,
  * feed-forward norm, then the feed-forward (dense: gate, up, down — or up, down for the GELU
  * variant; MoE: router, every expert's gate, up, down, then the shared expert's); final norm;
- * the LM head unless the embeddings are tied.  Files of a model with LoRA adapters attached
- * (config.lora set: two more parameters per projection) are refused with MOE_UNSUPPORTED. */
+ * the LM head unless the embeddings are tied.  In the file of a model with LoRA adapters attached
+ * (config.lora set) every adapted projection (attention and feed-forward, not the router, embedding or
+ * LM head) is followed by its `down` [rank, in] and `up` [out, rank]. */
 typedef struct moe_snapshot_info {
   int64_t vocab_size, d_model, n_layers, n_heads, n_kv_heads, head_dim, d_ff, moe_d_ff;
   int64_t num_experts, experts_per_token, max_seq_len;
@@ -251,7 +252,9 @@ typedef struct moe_snapshot_info {
   int32_t moe_layers[256];      /* block indices with a MoE feed-forward, ascending */
   int64_t optimizer_step;
   int64_t parameter_count;      /* as written in the file */
-  int32_t dense_ffn_params;     /* 3 (SwiGLU) or 2 (GELU) parameters per dense feed-forward, 0 if none */
+  int32_t dense_ffn_params;     /* 3 (SwiGLU) or 2 (GELU) projections per dense feed-forward, 0 if none */
+  int32_t lora_rank;            /* 0, or config.lora.rank: every adapted projection is followed by its down and up */
+  float lora_alpha;
 } moe_snapshot_info_t;
 
 /* Parses the header of a weight file.  Host only (no GPU needed).  `message` (optional) receives
@@ -264,7 +267,9 @@ int32_t moe_snapshot_info(const char* weights_path, moe_snapshot_info_t* out, ch
  * the router, which stays f32 in an int8 handle, is dequantized), an int8 file is dequantized for an
  * f32 / bf16 handle exactly as load_bin does (value = int8 * scale), an f32 file is quantized for an
  * int8 handle on the reference's grid (scale = max|row| / 127, round half away from zero, clamp to
- * +-127; transformer.rs:514-519, quantized.rs:8-12).  An expert-parallel handle takes its own experts only. */
+ * +-127; transformer.rs:514-519, quantized.rs:8-12).  An expert-parallel handle takes its own experts only.
+ * Adapters in the file are loaded into the layer's adapters when it has some of the same rank and alpha
+ * (moe_lora_attach first), otherwise only the base weights are taken. */
 int32_t moe_load_snapshot_layer(moe_layer_t* layer, const char* weights_path, int32_t block_index);
 
 /* Restores the Adam moments of block `block_index` from a moments file; `info` is the configuration

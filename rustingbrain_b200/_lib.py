@@ -34,7 +34,7 @@ class SnapshotInfoC(C.Structure):
         ("aux_loss_weight", C.c_float), ("router_z_loss_weight", C.c_float), ("rope_base", C.c_float),
         ("rmsnorm_eps", C.c_float), ("precision", C.c_int32), ("n_moe_layers", C.c_int32),
         ("moe_layers", C.c_int32 * 256), ("optimizer_step", C.c_int64), ("parameter_count", C.c_int64),
-        ("dense_ffn_params", C.c_int32),
+        ("dense_ffn_params", C.c_int32), ("lora_rank", C.c_int32), ("lora_alpha", C.c_float),
     ]
 
 

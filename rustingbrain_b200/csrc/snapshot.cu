@@ -160,24 +160,24 @@ bool integer_field(const Json& cfg, const char* key, int64_t* out, char* msg, in
 
 // Where the parameters of one block start and how many each block has.
 struct Layout {
-  std::vector<int64_t> block_first;   // index of the block's first parameter (its attention norm)
-  std::vector<int> block_is_moe;
+  std::vector<int64_t> ffn_first;   // index of the first feed-forward parameter of every block
   int64_t total = 0;
 };
 
 Layout layout_of(const moe_snapshot_info_t& s) {
   Layout l;
+  const int64_t per_linear = s.lora_rank > 0 ? 3 : 1;   // weight (+ down, up)
   int64_t idx = 1;   // embedding
   for (int64_t b = 0; b < s.n_layers; ++b) {
     bool moe = false;
     for (int i = 0; i < s.n_moe_layers; ++i) moe = moe || s.moe_layers[i] == b;
-    l.block_first.push_back(idx);
-    l.block_is_moe.push_back(moe ? 1 : 0);
-    idx += 6;   // attention norm, query, key, value, output, feed-forward norm
-    idx += moe ? 1 + 3 * s.num_experts + (s.shared_expert ? 3 : 0) : s.dense_ffn_params;
+    idx += 1 + 4 * per_linear + 1;   // attention norm, query, key, value, output, feed-forward norm
+    l.ffn_first.push_back(idx);
+    // the router carries no adapter (moe.rs:502-504)
+    idx += moe ? 1 + (3 * s.num_experts + (s.shared_expert ? 3 : 0)) * per_linear : s.dense_ffn_params * per_linear;
   }
   idx += 1;   // final norm
-  if (!s.tie_embeddings) idx += 1;
+  if (!s.tie_embeddings) idx += 1;   // the LM head is not adapted either
   l.total = idx;
   return l;
 }
@@ -230,9 +230,17 @@ int open_weights(File& in, moe_snapshot_info_t* s, char* msg, int len) {
   s->rope_base = real("rope_base");
   s->rmsnorm_eps = real("rmsnorm_eps");
   const Json* lora = cfg->get("lora");
-  if (lora && lora->kind != Json::Null) {
-    say(msg, len, "Unsupported: the file holds LoRA adapters; merge them (merge_lora) before saving");
-    return MOE_UNSUPPORTED;
+  if (lora && lora->kind == Json::Object) {
+    // the file of an adapted model holds, after every adapted projection, its `down` and `up`
+    // (Linear::params_mut, param.rs:859-865)
+    const Json* jr = lora->get("rank");
+    const Json* ja = lora->get("alpha");
+    if (!jr || jr->kind != Json::Number || jr->num < 1 || !ja || ja->kind != Json::Number) {
+      say(msg, len, "InvalidSnapshot: config.lora is not a LoraConfig");
+      return MOE_INVALID_INPUT;
+    }
+    s->lora_rank = (int32_t)jr->num;
+    s->lora_alpha = (float)ja->num;
   }
   const Json* ml = cfg->get("moe_layers");
   if (!ml || ml->kind != Json::Array || ml->items.size() > 256) {
@@ -404,18 +412,39 @@ int32_t moe_load_snapshot_layer(moe_layer_t* L, const char* weights_path, int32_
   if (rc != MOE_OK) { L->err = msg; return rc; }
   if ((rc = check_block(L, s, block_index)) != MOE_OK) return rc;
   const Layout lay = layout_of(s);
-  if (!skip_params(in, s.precision, lay.block_first[(size_t)block_index] + 6)) {
+  if (!skip_params(in, s.precision, lay.ffn_first[(size_t)block_index])) {
     L->err = "InvalidSnapshot: truncated weight file";
     return MOE_INVALID_INPUT;
   }
+  // adapters in the file go into the layer's adapters when it has some of the same rank and alpha;
+  // a layer without adapters takes the base weights only
+  const bool file_lora = s.lora_rank > 0;
+  const bool take_lora = file_lora && L->lora_rank == s.lora_rank && L->lora_alpha == s.lora_alpha;
   for (const Entry& en : moe_entries(L)) {
+    const int extra = file_lora && en.which != MOE_W_ROUTER ? 2 : 0;
     if (!en.mine) {   // an expert another rank owns
-      if (!skip_params(in, s.precision, 1)) { L->err = "InvalidSnapshot: truncated weight file"; return MOE_INVALID_INPUT; }
+      if (!skip_params(in, s.precision, 1 + extra)) { L->err = "InvalidSnapshot: truncated weight file"; return MOE_INVALID_INPUT; }
       continue;
     }
     Tensor t;
     if ((rc = read_param(in, s.precision, en.rows, en.cols, &t, &L->err)) != MOE_OK) return rc;
     if ((rc = put_weight(L, en.which, en.expert, s.precision, t)) != MOE_OK) return rc;
+    if (extra == 0) continue;
+    if (!take_lora) {
+      if (!skip_params(in, s.precision, 2)) { L->err = "InvalidSnapshot: truncated weight file"; return MOE_INVALID_INPUT; }
+      continue;
+    }
+    Tensor down, up;
+    if ((rc = read_param(in, s.precision, (uint64_t)s.lora_rank, en.cols, &down, &L->err)) != MOE_OK) return rc;
+    if ((rc = read_param(in, s.precision, en.rows, (uint64_t)s.lora_rank, &up, &L->err)) != MOE_OK) return rc;
+    for (Tensor* a : {&down, &up}) {
+      if (s.precision != MOE_PRECISION_Q8) continue;
+      a->f32.resize((size_t)(a->rows * a->cols));
+      for (uint64_t r = 0; r < a->rows; ++r)
+        for (uint64_t c = 0; c < a->cols; ++c)
+          a->f32[(size_t)(r * a->cols + c)] = (float)a->q[(size_t)(r * a->cols + c)] * a->scale[(size_t)r];
+    }
+    if ((rc = moe_lora_set(L, en.which, en.expert, down.f32.data(), up.f32.data())) != MOE_OK) return rc;
   }
   return MOE_OK;
 }
@@ -427,6 +456,10 @@ int32_t moe_load_optimizer_layer(moe_layer_t* L, const char* moments_path, const
   if (!moments_path || !info) { L->err = "InvalidInput: null argument"; return MOE_INVALID_INPUT; }
   int rc = check_block(L, *info, block_index);
   if (rc != MOE_OK) return rc;
+  if (info->lora_rank > 0) {
+    L->err = "Unsupported: optimizer state of a model with LoRA adapters (the base weights are frozen, the adapter moments have no entry point yet)";
+    return MOE_UNSUPPORTED;
+  }
   File in(moments_path);
   char magic[8];
   uint64_t count = 0, file_step = 0;
@@ -448,7 +481,7 @@ int32_t moe_load_optimizer_layer(moe_layer_t* L, const char* moments_path, const
     return true;
   };
   const Layout lay = layout_of(*info);
-  if (!skip_moments(lay.block_first[(size_t)block_index] + 6)) { L->err = "InvalidSnapshot: truncated optimizer state file"; return MOE_INVALID_INPUT; }
+  if (!skip_moments(lay.ffn_first[(size_t)block_index])) { L->err = "InvalidSnapshot: truncated optimizer state file"; return MOE_INVALID_INPUT; }
   std::vector<float> m, v;
   for (const Entry& en : moe_entries(L)) {
     if (!en.mine) {

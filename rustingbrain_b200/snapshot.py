@@ -39,6 +39,8 @@ class SnapshotInfo:
     parameter_count: int
     dense_ffn_params: int          # 3 SwiGLU, 2 GELU, 0 when every block is MoE
     moe_layers: List[int] = field(default_factory=list)
+    lora_rank: int = 0             # config.lora.rank when the file holds adapters
+    lora_alpha: float = 0.0
     _c: Optional[_lib.SnapshotInfoC] = None
 
 
@@ -48,10 +50,7 @@ def snapshot_info(path: str) -> SnapshotInfo:
     msg = C.create_string_buffer(512)
     rc = _lib.lib().moe_snapshot_info(str(path).encode(), C.byref(c), msg, len(msg))
     if rc != _lib.OK:
-        text = msg.value.decode(errors="replace")
-        if rc == _lib.UNSUPPORTED:
-            raise NotImplementedError(text)
-        raise InvalidSnapshot(text)
+        raise InvalidSnapshot(msg.value.decode(errors="replace"))
     names = ("vocab_size", "d_model", "n_layers", "n_heads", "n_kv_heads", "head_dim", "d_ff", "moe_d_ff",
              "num_experts", "experts_per_token", "max_seq_len")
     config: Dict[str, object] = {n: int(getattr(c, n)) for n in names}
@@ -62,12 +61,34 @@ def snapshot_info(path: str) -> SnapshotInfo:
     config["moe_layers"] = layers
     return SnapshotInfo(config=config, precision="Q8" if c.precision == _lib.PRECISION_Q8 else "F32",
                         optimizer_step=int(c.optimizer_step), parameter_count=int(c.parameter_count),
-                        dense_ffn_params=int(c.dense_ffn_params), moe_layers=layers, _c=c)
+                        dense_ffn_params=int(c.dense_ffn_params), moe_layers=layers, lora_rank=int(c.lora_rank),
+                        lora_alpha=float(c.lora_alpha), _c=c)
 
 
 def parameter_names(config: Dict[str, object], dense_ffn_params: int = 3) -> List[Tuple[str, Tuple[int, int]]]:
     """(name, (rows, cols)) of every parameter in file order (params_mut, transformer.rs:1620-1630;
-    block order transformer_block.rs:286-292; MoE order moe.rs:516-525; SwiGLU order ffn.rs:126-131)."""
+    block order transformer_block.rs:286-292; MoE order moe.rs:516-525; SwiGLU order ffn.rs:126-131).
+    With ``config["lora"]`` set every adapted projection is followed by its adapter's down and up
+    (Linear::params_mut, param.rs:859-865)."""
+    base = _base_parameter_names(config, dense_ffn_params)
+    lora = config.get("lora")
+    if not lora:
+        return base
+    rank = int(lora["rank"])
+    out: List[Tuple[str, Tuple[int, int]]] = []
+    for name, (rows, cols) in base:
+        out.append((name, (rows, cols)))
+        if _adapted(name):
+            out += [(name + ".lora.down", (rank, cols)), (name + ".lora.up", (rows, rank))]
+    return out
+
+
+def _adapted(name: str) -> bool:
+    part = name.split(".")
+    return len(part) > 2 and (part[2] in ("attention", "ffn") or (part[2] == "moe" and part[3] != "router"))
+
+
+def _base_parameter_names(config: Dict[str, object], dense_ffn_params: int = 3) -> List[Tuple[str, Tuple[int, int]]]:
     d = int(config["d_model"]); V = int(config["vocab_size"]); F = int(config["d_ff"]); Fm = int(config["moe_d_ff"])
     H = int(config["n_heads"]); Hkv = int(config["n_kv_heads"]); hd = int(config["head_dim"]); E = int(config["num_experts"])
     moe = set(int(i) for i in config["moe_layers"])
@@ -163,11 +184,8 @@ def adapter_names(config: Dict[str, object], rank: int, dense_ffn_params: int = 
     the router; transformer_block.rs:274-278, moe.rs:502-514), `down` [rank, in] before `up` [out, rank]
     (param.rs:711-713)."""
     out: List[Tuple[str, Tuple[int, int]]] = []
-    for name, (rows, cols) in parameter_names(config, dense_ffn_params):
-        part = name.split(".")
-        adapted = len(part) > 2 and (part[2] == "attention" or part[2] == "ffn" or
-                                     (part[2] == "moe" and part[3] != "router"))
-        if adapted:
+    for name, (rows, cols) in _base_parameter_names(config, dense_ffn_params):
+        if _adapted(name):
             out += [(name + ".lora.down", (rank, cols)), (name + ".lora.up", (rows, rank))]
     return out
 

@@ -82,7 +82,7 @@ def test_bad_files_are_refused(tmp_path):
     with pytest.raises(InvalidSnapshot, match="truncated"):
         snapshot_info(tmp_path / "cut.rbw")
     write_snapshot(tmp_path / "lora.rbw", {**cfg, "lora": {"rank": 4, "alpha": 4.0, "seed": 0}}, ts)
-    with pytest.raises(NotImplementedError, match="LoRA"):
+    with pytest.raises(InvalidSnapshot, match="parameters"):      # an adapted model writes three matrices per projection
         snapshot_info(tmp_path / "lora.rbw")
     write_snapshot(tmp_path / "layers.rbw", {**cfg, "moe_layers": [1, 7]}, ts)
     with pytest.raises(InvalidSnapshot, match="moe_layers"):
@@ -264,3 +264,45 @@ def test_adapter_file_fills_the_attached_adapters(tmp_path):
     write_lora(tmp_path / "short.lora", rank, alpha, ad[:-2])
     with pytest.raises(InvalidInput, match="parameters"):
         layer.load_lora(tmp_path / "short.lora", info, 2)
+
+
+def test_adapted_model_files_are_understood(tmp_path):
+    cfg = tiny_config(lora={"rank": 4, "alpha": 8.0, "seed": 0})
+    names, ts = tensors_for(cfg)
+    assert sum(1 for n, _ in names if n.endswith(".lora.down")) == 4 * 3 + 3 + 2 * (4 * 3 + 3)   # attention + ffn linears
+    write_snapshot(tmp_path / "adapted.rbw", cfg, ts)
+    info = snapshot_info(tmp_path / "adapted.rbw")
+    assert info.lora_rank == 4 and info.lora_alpha == 8.0 and info.parameter_count == len(names)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("file_precision", ["F32", "Q8"])
+def test_adapted_model_file_fills_weights_and_adapters(tmp_path, file_precision):
+    torch, MoeConfig, MoeLayer = _gpu_imports()
+    cfg = tiny_config(lora={"rank": 4, "alpha": 8.0, "seed": 0})
+    names, ts = tensors_for(cfg)
+    write_snapshot(tmp_path / "adapted.rbw", cfg, ts, file_precision)
+    by_name = {n: t for (n, _), t in zip(names, ts)}
+
+    def expect(t):
+        if file_precision == "F32":
+            return t
+        q, s = quantize_rows(t)
+        return q.astype(np.float32) * s[:, None]
+
+    plain = MoeLayer(64, MoeConfig(4, 2, 64, True), precision="f32", max_tokens=8)
+    plain.load_snapshot(tmp_path / "adapted.rbw", 1)                 # no adapters attached: base weights only
+    assert np.array_equal(plain.get_weight(3, 2), expect(by_name["blocks.1.moe.experts.2.down"]))
+    adapted = MoeLayer(64, MoeConfig(4, 2, 64, True), precision="f32", max_tokens=8)
+    adapted.lora_attach(4, 8.0)
+    adapted.load_snapshot(tmp_path / "adapted.rbw", 2)
+    assert np.array_equal(adapted.get_weight(0, 0), expect(by_name["blocks.2.moe.router"]))
+    for e in range(4):
+        for part, which in WHICH.items():
+            key = "blocks.2.moe.experts.%d.%s" % (e, part)
+            assert np.array_equal(adapted.get_weight(which, e), expect(by_name[key])), key
+            down, up = adapted.lora_get(which, e)
+            assert np.array_equal(down, expect(by_name[key + ".lora.down"])) and np.array_equal(up, expect(by_name[key + ".lora.up"]))
+    down, up = adapted.lora_get(6, 0)
+    assert np.array_equal(down, expect(by_name["blocks.2.moe.shared.down.lora.down"]))
+    assert np.array_equal(up, expect(by_name["blocks.2.moe.shared.down.lora.up"]))
