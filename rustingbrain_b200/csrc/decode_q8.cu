@@ -74,11 +74,15 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, q = lane & 3;
   const int G = a.E + (a.x_shared ? 1 : 0);
+  // the counts are read by one thread each (one load latency, not one per group), then scanned in place
+  for (int g = tid; g < G; g += Q8_WARPS * 32) tile_start[g + 1] = ceil_div(g < a.E ? a.counts[g] : a.tokens, Q8_ROWS);
+  __syncthreads();
   if (tid == 0) {
     int run = 0;
     for (int g = 0; g < G; ++g) {
+      const int n = tile_start[g + 1];
       tile_start[g] = run;
-      run += ceil_div(g < a.E ? a.counts[g] : a.tokens, Q8_ROWS);
+      run += n;
     }
     tile_start[G] = run;
   }

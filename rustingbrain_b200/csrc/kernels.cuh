@@ -189,8 +189,15 @@ struct Q8Args {
   long long w_group_stride, s_group_stride;
   int E, tokens, K, N, ldo;
   int sm_count;            // grid = two CTAs per SM
+  // tensor-core variant only (decode_q8_tc.cu)
+  long long x_rows_cap;    // readable rows of x_rows
+  long long x_shared_rows; // readable rows of x_shared
+  int* error_flag;         // bounded waits report here
 };
 cudaError_t launch_q8_rows(const Q8Args& a, bool swiglu, cudaStream_t stream);
+// tcgen05 variant: the weights are the 128-row MMA operand, widened to f16 in shared memory
+bool q8_tc_supported(const Q8Args& a, bool swiglu);
+cudaError_t launch_q8_rows_tc(const Q8Args& a, bool swiglu, cudaStream_t stream);
 
 // ----- optimizer and casts -----
 struct AdamArgs {

@@ -281,6 +281,12 @@ bool is_device_pointer(const void* p) {
   return a.type == cudaMemoryTypeDevice || a.type == cudaMemoryTypeManaged;
 }
 
+// MOE_B200_Q8_TC=1 selects the tcgen05 variant of the int8 decode projections (decode_q8_tc.cu).
+bool q8_tc_mode() {
+  static const bool on = [] { const char* v = getenv("MOE_B200_Q8_TC"); return v && atoi(v) != 0; }();
+  return on;
+}
+
 int check_flag(moe_layer* L) {
   int flag = 0;
   CK(cudaMemcpy(&flag, L->error_flag, sizeof(int), cudaMemcpyDeviceToHost));
@@ -491,14 +497,17 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     qa.w = L->q_gu; qa.scale = L->s_gu; qa.counts = L->meta.counts; qa.pad_off = L->meta.pad_off;
     qa.w_group_stride = 2ll * Fp * d; qa.s_group_stride = 2ll * Fp;
     qa.sm_count = L->sm_count; qa.E = L->E; qa.tokens = tokens; qa.K = d; qa.N = Fp; qa.ldo = Fp;
-    CK(launch_q8_rows(qa, true, st));
+    qa.x_rows_cap = L->rows_cap; qa.x_shared_rows = tokens; qa.error_flag = L->error_flag;
+    const bool tc = q8_tc_mode();
+    if (tc && q8_tc_supported(qa, true)) CK(launch_q8_rows_tc(qa, true, st)); else CK(launch_q8_rows(qa, true, st));
     Q8Args qb{};
     qb.x_rows = (const bf16*)L->h; qb.x_shared = L->shared ? (const bf16*)L->h_s : nullptr;
     qb.out_rows = (bf16*)L->y_perm; qb.out_shared = (bf16*)L->y_s;
     qb.w = L->q_d; qb.scale = L->s_d; qb.counts = L->meta.counts; qb.pad_off = L->meta.pad_off;
     qb.w_group_stride = (long long)d * Fp; qb.s_group_stride = d;
     qb.sm_count = L->sm_count; qb.E = L->E; qb.tokens = tokens; qb.K = Fp; qb.N = d; qb.ldo = d;
-    CK(launch_q8_rows(qb, false, st));
+    qb.x_rows_cap = L->rows_cap; qb.x_shared_rows = L->shared_rows_cap; qb.error_flag = L->error_flag;
+    if (tc && q8_tc_supported(qb, false)) CK(launch_q8_rows_tc(qb, false, st)); else CK(launch_q8_rows(qb, false, st));
     rc = MOE_OK;
   } else if (ep) {
     rc = ep_forward_experts(L, save != 0, st);

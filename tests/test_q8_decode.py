@@ -51,3 +51,16 @@ def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
 def test_a_quantized_layer_refuses_to_train():  # transformer.rs:2202-2280: quantizing is one-way
     with pytest.raises(InvalidConfig):
         MoeLayer(64, MoeConfig(4, 2, 64), precision="q8", max_tokens=8, training=True)
+
+
+def test_the_tensor_core_variant_passes_the_same_parity_cases():
+    """MOE_B200_Q8_TC=1 routes both projections through the tcgen05 kernel (decode_q8_tc.cu); the switch is read
+    once per process, so the parity cases above run again in a child process with it set."""
+    import os, subprocess, sys
+    env = dict(os.environ, MOE_B200_Q8_TC="1")
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = subprocess.run([sys.executable, "-m", "pytest", os.path.join(here, "test_q8_decode.py"), "-q", "-x",
+                          "-k", "matches_the_quantized_checker", "-p", "no:cacheprovider"],
+                         env=env, cwd=os.path.dirname(here), capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    assert "3 passed" in out.stdout
