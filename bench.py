@@ -38,6 +38,10 @@ WORKLOADS = {
                 name="HBM-kernel profiling case: 16384 tokens, d_model 2048, 8 experts top-8, d_ff 256"),
     "cfg5": dict(T=64, d=1024, E=16, k=2, F=2816, shared=True, seed=9, precision="q8", zipf=False,
                  name="KV-cached decode step through a quantized MoE layer: 64 sequences x 1 token, d_model 1024, 16 experts top-2 + shared, d_ff 2816, int8 weights"),
+    # the attention half of the same decode step: 64 caches of 4096 positions, d_model 1024 = 16 query heads x 64,
+    # 4 key/value heads (the head split of the reference's README model scaled to d_model 1024), bf16 cache
+    "cfg5_attn": dict(S=64, H=16, Hkv=4, hd=64, history=4096, precision="attn", seed=9,
+                      name="KV-cached decode attention: 64 sequences x 1 token over 4096 cached positions, 16 query heads, 4 kv heads, head_dim 64, bf16 cache"),
     # BASELINE config 2 is a whole-model train_step; only its MoE layers are on this path.  One of its
     # six MoE blocks (layers 2..7: 8 experts top-2, expert d_ff 352 + shared, 8 x 1024 tokens), forward +
     # backward + Adam, bf16 GEMMs over f32 master weights.
@@ -194,6 +198,28 @@ def run_reference(args, w):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    if w["precision"] == "attn":
+        # the checker's single-sequence decode step (numpy, one thread), scaled to the workload's sequences
+        from oracle import attention as ora
+        H, Hkv, hd, L, S = w["H"], w["Hkv"], w["hd"], w["history"], w["S"]
+        g = np.random.Generator(np.random.Philox(w["seed"]))
+        o = ora.KvCacheOracle(H, Hkv, hd, L + 8)
+        o.keys = g.standard_normal((L - 1, Hkv * hd)).astype(np.float32)
+        o.values = g.standard_normal((L - 1, Hkv * hd)).astype(np.float32)
+        q, k, v = (g.standard_normal((1, n * hd)).astype(np.float32) for n in (H, Hkv, Hkv))
+        ts = []
+        for it in range(min(args.warmup, 1) + max(args.steps, 1)):
+            o.keys, o.values = o.keys[:L - 1], o.values[:L - 1]
+            t0 = time.perf_counter(); o.forward_cached(q, k, v); ts.append(time.perf_counter() - t0)
+        us = float(np.median(ts[min(args.warmup, 1):])) * 1e6 * S
+        print(json.dumps({"impl": "reference", "metric": "p50 microseconds per KV-cached attention decode step (64 sequences)",
+                          "value": us, "unit": "us", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+                          "ms_per_step": us / 1e3, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                          "dtype": "f32", "data": "synthetic", "config": {"workload": w["name"]},
+                          "cpu_baseline": {"value": us, "unit": "us", "cores": 1, "kind": "port",
+                                           "sample": "one sequence's decode step at the workload's history, times %d sequences" % S},
+                          "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
+        return
     value, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else w["T"], max(args.steps, 1), min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "MoE-layer tokens/s (forward + backward)", "value": value, "unit": "tokens/s",
@@ -269,6 +295,61 @@ def run_decode(args, w):
     print(json.dumps(line))
 
 
+def run_decode_attention(args, w):
+    """One decode step of the batched KV-cache attention at a fixed history (p50 over replays).  Every step
+    rotates and appends one row per sequence and streams every cached key and value once."""
+    import torch
+    from rustingbrain_b200 import _lib
+    from rustingbrain_b200.kv_attention import KvCache
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    S, H, Hkv, hd, L = w["S"], w["H"], w["Hkv"], w["hd"], w["history"]
+    cache = KvCache(S, H, Hkv, hd, capacity=L + 8, precision="bf16")
+    gen = torch.Generator(device=dev).manual_seed(w["seed"])
+    rnd = lambda *shape: torch.randn(*shape, device=dev, generator=gen).bfloat16()
+    chunk = 512                                  # prefill in pieces: the history only has to be there
+    for p0 in range(0, L - 1, chunk):
+        n = min(chunk, L - 1 - p0)
+        cache.forward_cached(rnd(S * n, H * hd), rnd(S * n, Hkv * hd), rnd(S * n, Hkv * hd), rows_per_sequence=n)
+    q, k, v = rnd(S, H * hd), rnd(S, Hkv * hd), rnd(S, Hkv * hd)
+    out = torch.empty_like(q)
+    q0 = q.clone()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    reps = max(args.steps, 1) * 50
+    l0 = _lib.lib().moe_debug_launch_count()
+    times = []
+    sampler = None
+    for it in range(max(args.warmup, 3) * 10 + reps):
+        if it == max(args.warmup, 3) * 10:
+            torch.cuda.synchronize()
+            l0 = _lib.lib().moe_debug_launch_count()
+            sampler = ClockSampler(0)
+        cache.truncate(L - 1)                    # the same step every time: history L - 1, one new row
+        q.copy_(q0)
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); cache.forward_cached(q, k, v, out=out); e1.record()
+        e1.synchronize()
+        if sampler is not None:
+            times.append(e0.elapsed_time(e1) * 1e3)
+    clocks = sampler.stop()
+    launches = _lib.lib().moe_debug_launch_count() - l0
+    times = np.array(times)
+    p50 = float(np.percentile(times, 50))
+    kv_bytes = 2 * S * L * Hkv * hd * 2          # every cached key and value once, bf16
+    pk = peaks()
+    line = {"metric": "p50 microseconds per KV-cached attention decode step (64 sequences)", "value": p50, "unit": "us",
+            "n_gpus": 1, "steps": reps, "warmup": max(args.warmup, 3) * 10, "ms_per_step": p50 / 1e3,
+            "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 cache, f32 softmax",
+            "data": "synthetic", "config": {"workload": w["name"], "l2": "256 MB buffer written between steps",
+                                            "launches": "3 per step (rotate+append, partial attention, merge) + 1 to reset the length"},
+            "clocks": clocks, "gpu_launches": int(launches), "p90_us": float(np.percentile(times, 90)),
+            "roofline": {"bound": "hbm", "achieved": kv_bytes / (p50 * 1e-6) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
+                         "frac": kv_bytes / (p50 * 1e-6) / 1e9 / pk["hbm"], "traffic": None,
+                         "note": "cached keys + values (%.0f MB) / whole-step p50" % (kv_bytes / 1e6)}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -285,6 +366,9 @@ def main():
         return
     if w["precision"] == "q8":
         run_decode(args, w)
+        return
+    if w["precision"] == "attn":
+        run_decode_attention(args, w)
         return
 
     import torch

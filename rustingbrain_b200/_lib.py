@@ -38,6 +38,13 @@ class SnapshotInfoC(C.Structure):
     ]
 
 
+class KvCacheConfigC(C.Structure):
+    """kv_cache_config_t of include/kv_attention_b200.h."""
+    _fields_ = [("sequences", C.c_int32), ("num_heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("capacity", C.c_int32), ("max_seq_len", C.c_int32), ("rope_base", C.c_float), ("rope", C.c_int32),
+                ("precision", C.c_int32), ("device", C.c_int32)]
+
+
 _lib = None
 
 
@@ -91,6 +98,14 @@ def lib() -> C.CDLL:
         "moe_ep_export_buffers": (i32, [vp, vp, i32]),
         "moe_ep_import_buffers": (i32, [vp, i32, vp, i32]),
         "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
+        "kv_cache_create": (i32, [C.POINTER(KvCacheConfigC), C.POINTER(vp)]),
+        "kv_cache_destroy": (None, [vp]),
+        "kv_cache_last_error": (C.c_char_p, [vp]),
+        "kv_cache_clear": (i32, [vp, i32, vp]),
+        "kv_cache_truncate": (i32, [vp, i32, i32, vp]),
+        "kv_cache_lengths": (i32, [vp, ip, vp]),
+        "kv_attention_forward_cached": (i32, [vp, i32, i32, vp, vp, vp, i32, vp, vp]),
+        "kv_cache_read": (i32, [vp, i32, fp, fp, vp]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
         "moe_debug_set_tc_pair": (i32, [i32]),
@@ -113,5 +128,5 @@ def exported_symbols():
     for h in sorted(os.listdir(inc)):
         if h.endswith(".h"):
             text = open(os.path.join(inc, h)).read()
-            names += re.findall(r"\b(moe_[a-z0-9_]+)\s*\(", text)
+            names += re.findall(r"\b((?:moe|kv)_[a-z0-9_]+)\s*\(", text)
     return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight")))
