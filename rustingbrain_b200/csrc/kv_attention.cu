@@ -15,6 +15,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <new>
 #include <string>
 #include <vector>
@@ -38,10 +39,19 @@ template <> struct Slice8<float> {
     const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
     o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
   }
+  static __device__ __forceinline__ void from_shared(const unsigned char* p, float* o) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *(reinterpret_cast<const float4*>(p) + 1);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  }
 };
 template <> struct Slice8<bf16> {
   static __device__ __forceinline__ void load(const bf16* p, float* o) {
-    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+    widen(__ldg(reinterpret_cast<const uint4*>(p)), o);
+  }
+  static __device__ __forceinline__ void from_shared(const unsigned char* p, float* o) {
+    widen(*reinterpret_cast<const uint4*>(p), o);
+  }
+  static __device__ __forceinline__ void widen(const uint4 a, float* o) {
     const uint32_t w[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {   // a bf16 is the upper half of its f32
@@ -50,6 +60,13 @@ template <> struct Slice8<bf16> {
     }
   }
 };
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+// slots of the per-thread copy ring (48 KiB of shared memory per CTA either way)
+template <typename T> struct KvRing;
+template <> struct KvRing<bf16> { static constexpr int DEPTH = 6; };
+template <> struct KvRing<float> { static constexpr int DEPTH = 3; };
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
@@ -111,7 +128,8 @@ __global__ void __launch_bounds__(KV_THREADS)
 kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* __restrict__ values,
                   const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
   constexpr int LPK = HD / 8, KPW = 32 / LPK, NG = KV_WARPS * KPW, PW = HD + 2;
-  extern __shared__ float kv_sm[];   // [KV_QT][NG][PW]
+  constexpr int SLOT = 8 * (int)sizeof(T), DEPTH = KvRing<T>::DEPTH;
+  extern __shared__ __align__(16) float kv_sm[];   // the copy ring, then [KV_QT][NG][PW] for the merge
   const int split = blockIdx.x, kvh = blockIdx.y, sj = blockIdx.z, seq = s.first + sj;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane / LPK, ls = lane % LPK;
   const int len0 = lengths[seq], total = len0 + s.rows;
@@ -144,22 +162,44 @@ kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* 
     }
     // a slice ends where the last query of this pass stops seeing
     const int kend = min(k1, vis[KV_QT - 1] > 0 ? vis[KV_QT - 1] : len0 + (nq - 1) / group + 1);
+    // Each thread streams its own 8-channel slices of the keys and values through a ring of DEPTH
+    // slots in shared memory (cp.async, 16 bytes each): DEPTH - 1 positions per thread are in flight
+    // while one is used, which is what covers DRAM latency at two or three CTAs per SM.  A thread reads
+    // back only what it copied itself, so waiting on its own copy groups is all the ordering needed.
     // The loop is uniform across the warp (the shuffles below need every lane); a lane group whose
-    // position lies past the end loads nothing and updates nothing.
-    float kf[8], vf[8], kn[8], vn[8];
+    // position lies past the end copies nothing and updates nothing.
+    const int base0 = k0 + warp * KPW + sub;
+    const int iters = kend > k0 + warp * KPW ? ceil_div(kend - (k0 + warp * KPW), NG) : 0;
+    unsigned char* slot0 = reinterpret_cast<unsigned char*>(kv_sm) + (size_t)threadIdx.x * SLOT;
+    auto issue = [&](int it) {
+      const int key = base0 + it * NG;
+      if (it < iters && key < kend) {
+        unsigned char* dk = slot0 + (size_t)(it % DEPTH) * (2 * KV_THREADS * SLOT);
+        unsigned char* dv = dk + KV_THREADS * SLOT;
+        const unsigned char* gk = reinterpret_cast<const unsigned char*>(kbase + (size_t)key * W);
+        const unsigned char* gv = reinterpret_cast<const unsigned char*>(vbase + (size_t)key * W);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) kf[c] = vf[c] = kn[c] = vn[c] = 0.f;
-    const int base0 = k0 + warp * KPW;
-    if (base0 + sub < kend) {
-      Slice8<T>::load(kbase + (size_t)(base0 + sub) * W, kf);
-      Slice8<T>::load(vbase + (size_t)(base0 + sub) * W, vf);
-    }
-    for (int base = base0; base < kend; base += NG) {
-      const int key = base + sub, nxt = key + NG;
+        for (int b = 0; b < SLOT; b += 16) {
+          cp_async16(dk + b, gk + b);
+          cp_async16(dv + b, gv + b);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");   // one group per step, empty or not
+    };
+    for (int it = 0; it < DEPTH - 1; ++it) issue(it);
+    for (int it = 0; it < iters; ++it) {
+      issue(it + DEPTH - 1);
+      asm volatile("cp.async.wait_group %0;" ::"n"(DEPTH - 1) : "memory");   // step `it` has landed
+      const int key = base0 + it * NG;
       const bool live = key < kend;
-      if (nxt < kend) {     // next position's loads are in flight while this one is used
-        Slice8<T>::load(kbase + (size_t)nxt * W, kn);
-        Slice8<T>::load(vbase + (size_t)nxt * W, vn);
+      float kf[8], vf[8];
+      if (live) {
+        const unsigned char* dk = slot0 + (size_t)(it % DEPTH) * (2 * KV_THREADS * SLOT);
+        Slice8<T>::from_shared(dk, kf);
+        Slice8<T>::from_shared(dk + KV_THREADS * SLOT, vf);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 8; ++c) kf[c] = vf[c] = 0.f;
       }
 #pragma unroll
       for (int j = 0; j < KV_QT; ++j) {
@@ -177,12 +217,11 @@ kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* 
           m[j] = mn;
         }
       }
-#pragma unroll
-      for (int c = 0; c < 8; ++c) { kf[c] = kn[c]; vf[c] = vn[c]; }
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // merge the lane groups of the CTA
-    __syncthreads();   // the previous pass has finished reading the buffer
+    __syncthreads();   // every thread is done with its ring slots, and the previous pass with the merge buffer
 #pragma unroll
     for (int j = 0; j < KV_QT; ++j) {
       float* dst = kv_sm + ((size_t)j * NG + grp) * PW;
@@ -210,6 +249,200 @@ kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* 
       out[c] = num;
       if (c == 0) { out[HD] = mx; out[HD + 1] = den; }
     }
+    __syncthreads();   // the next pass copies into the memory the merge has just read
+  }
+}
+
+// ---- the same slice on the tensor cores (bf16 cache, head_dim 64 or 128) ----
+// The scalar kernel above spends most of its issue slots on the dot products and on softmax arithmetic
+// that every lane of a position repeats.  Here a warp takes blocks of 16 positions: S = Q K^T and
+// O += P V are mma.sync m16n8k16 products whose 16 rows are the queries of the group (rows past the
+// group are zero), the key and value blocks come through a warp-private cp.async ring in shared memory
+// (16-byte chunks XOR-swizzled by row so that ldmatrix is conflict-free), and the softmax touches each
+// score once.  Same slice bounds, same result format as the scalar kernel.
+constexpr int TC_WARPS = 4, TC_KB = 16, TC_DEPTH = 3;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t* r) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16_zfill(uint32_t smem_dst, const void* gmem_src, int src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_dst), "l"(gmem_src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(TC_WARPS * 32)
+kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, const bf16* __restrict__ values,
+                     const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
+  constexpr int RB = HD * 2, TILE = TC_KB * RB, CPR = HD / 8, PW = HD + 2, KT = HD / 16, NT = HD / 8;
+  constexpr int COPIES = TC_KB * CPR / 32;    // 16-byte chunks per lane and tile
+  extern __shared__ __align__(128) unsigned char tc_sm[];
+  const int split = blockIdx.x, kvh = blockIdx.y, sj = blockIdx.z, seq = s.first + sj;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int len0 = lengths[seq], total = len0 + s.rows;
+  const int chunk = round_up(ceil_div(total, splits), TC_WARPS * TC_KB);
+  const int k0 = split * chunk, k1 = min(total, k0 + chunk);
+  const int group = s.H / s.Hkv, nq = s.rows * group, W = s.Hkv * s.HD;
+  const bf16* kg = keys + (size_t)seq * s.cap * W + kvh * HD;
+  const bf16* vg = values + (size_t)seq * s.cap * W + kvh * HD;
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(tc_sm) + warp * (TC_DEPTH * 2 * TILE);
+  float* mb = reinterpret_cast<float*>(tc_sm);   // [16][TC_WARPS][PW], after the rings are drained
+
+  for (int q0 = 0; q0 < nq; q0 += 16) {
+    // query fragments: rows gid and gid + 8 of the pass
+    uint32_t qa[KT][4];
+    int lim[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int qi = q0 + gid + 8 * h, ok = qi < nq;
+      const int i = ok ? qi / group : 0, g = ok ? qi - i * group : 0;
+      lim[h] = ok ? min(len0 + i + 1, k1) : 0;     // positions 0 ..= len + i, inside this slice
+      const bf16* qr = q + ((size_t)(sj * s.rows + i) * s.H + kvh * group + g) * HD + 2 * tig;
+#pragma unroll
+      for (int kk = 0; kk < KT; ++kk) {
+        qa[kk][h] = ok ? *reinterpret_cast<const uint32_t*>(qr + 16 * kk) : 0u;
+        qa[kk][2 + h] = ok ? *reinterpret_cast<const uint32_t*>(qr + 16 * kk + 8) : 0u;
+      }
+    }
+    const int last = min(q0 + 15, nq - 1);
+    const int kend = min(k1, len0 + last / group + 1);
+    const int first_blk = k0 + warp * TC_KB;
+    const int nblk = kend > first_blk ? ceil_div(kend - first_blk, TC_WARPS * TC_KB) : 0;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f}, o[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+
+    auto issue = [&](int b) {
+      if (b < nblk) {
+        const int kb = first_blk + b * (TC_WARPS * TC_KB);
+        const uint32_t dk = ring + (b % TC_DEPTH) * (2 * TILE), dv = dk + TILE;
+#pragma unroll
+        for (int i = 0; i < COPIES; ++i) {
+          const int idx = lane + 32 * i, row = idx / CPR, ch = idx - row * CPR;
+          const int key = kb + row, live = key < kend ? 16 : 0;      // rows past the end are zero-filled
+          const size_t src = (size_t)min(key, total - 1) * W + ch * 8;
+          const uint32_t off = row * RB + (((ch & ~7) | ((ch ^ row) & 7)) << 4);
+          cp_async16_zfill(dk + off, kg + src, live);
+          cp_async16_zfill(dv + off, vg + src, live);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    for (int b = 0; b < TC_DEPTH - 1; ++b) issue(b);
+    for (int b = 0; b < nblk; ++b) {
+      issue(b + TC_DEPTH - 1);
+      asm volatile("cp.async.wait_group %0;" ::"n"(TC_DEPTH - 1) : "memory");
+      __syncwarp();                                  // every lane's copies of block b have landed
+      const int kb = first_blk + b * (TC_WARPS * TC_KB);
+      const uint32_t tk = ring + (b % TC_DEPTH) * (2 * TILE), tv = tk + TILE;
+      // S = Q K^T: two tiles of 8 positions
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const int mi = lane >> 3, r = lane & 7, key = (mi >> 1) * 8 + r;
+#pragma unroll
+        for (int kk = 0; kk < KT; ++kk) {
+          const int ch = 2 * kk + (mi & 1);
+          uint32_t bfr[4];
+          ldsm_x4(tk + key * RB + (((ch & ~7) | ((ch ^ key) & 7)) << 4), bfr);
+          mma_bf16_16816(sc[0], qa[kk], bfr[0], bfr[1]);
+          mma_bf16_16816(sc[1], qa[kk], bfr[2], bfr[3]);
+        }
+      }
+      // softmax of the block, base-2 domain; thread holds (row gid | gid + 8) x (positions 8 j + 2 tig, + 1)
+      uint32_t pa[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float v[4];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int key = kb + 8 * j + 2 * tig + e;
+            v[2 * j + e] = key < lim[h] ? sc[j][2 * h + e] * scale_log2 : -INFINITY;
+          }
+        float bm = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+        bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 2));
+        const float mn = fmaxf(m[h], bm);
+        const float ref = mn > -INFINITY ? mn : 0.f;          // nothing visible yet: every weight is 0
+        const float corr = exp2f(m[h] - ref);
+        float p[4], ps = 0.f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { p[e] = exp2f(v[e] - ref); ps += p[e]; }
+        l[h] = fmaf(l[h], corr, ps);                          // this thread's share; summed over the quad at the end
+        m[h] = mn;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { o[nt][2 * h] *= corr; o[nt][2 * h + 1] *= corr; }
+        pa[h] = pack_bf16x2(p[0], p[1]);                      // positions 2 tig, + 1
+        pa[2 + h] = pack_bf16x2(p[2], p[3]);                  // positions 8 + 2 tig, + 1
+      }
+      // O += P V: 16 positions x HD channels, two 8-channel tiles per ldmatrix
+      {
+        const int mi = lane >> 3, r = lane & 7, key = (mi & 1) * 8 + r;
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+          const int ch = 2 * np + (mi >> 1);
+          uint32_t bfr[4];
+          ldsm_x4_t(tv + key * RB + (((ch & ~7) | ((ch ^ key) & 7)) << 4), bfr);
+          mma_bf16_16816(o[2 * np], pa, bfr[0], bfr[1]);
+          mma_bf16_16816(o[2 * np + 1], pa, bfr[2], bfr[3]);
+        }
+      }
+      __syncwarp();                                  // the slot may be refilled by the next issue
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+      l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    __syncthreads();   // every warp has drained its ring; the merge buffer takes its place
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float* dst = mb + ((size_t)(gid + 8 * h) * TC_WARPS + warp) * PW;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        dst[8 * nt + 2 * tig] = o[nt][2 * h];
+        dst[8 * nt + 2 * tig + 1] = o[nt][2 * h + 1];
+      }
+      if (tig == 0) { dst[HD] = m[h]; dst[HD + 1] = l[h]; }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < 16 * HD; idx += TC_WARPS * 32) {
+      const int r = idx / HD, c = idx - r * HD, qi = q0 + r;
+      if (qi >= nq) continue;
+      const float* src = mb + (size_t)r * TC_WARPS * PW;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < TC_WARPS; ++w) mx = fmaxf(mx, src[w * PW + HD]);
+      float num = 0.f, den = 0.f;
+      if (mx > -INFINITY) {
+#pragma unroll
+        for (int w = 0; w < TC_WARPS; ++w) {
+          const float wt = exp2f(src[w * PW + HD] - mx);
+          num = fmaf(wt, src[w * PW + c], num);
+          den = fmaf(wt, src[w * PW + HD + 1], den);
+        }
+      }
+      const int i = qi / group, g = qi - i * group;
+      float* out = part + (((size_t)(sj * s.rows + i) * s.H + kvh * group + g) * splits + split) * PW;
+      out[c] = num;
+      if (c == 0) { out[HD] = mx; out[HD + 1] = den; }
+    }
+    __syncthreads();   // the next pass copies into the memory the merge has just read
   }
 }
 
@@ -290,13 +523,40 @@ size_t elem_size(const kv_cache* c) { return c->cfg.precision == MOE_PRECISION_B
 
 bool head_dim_ok(int hd) { return hd == 8 || hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256; }
 
+// KV_B200_SCALAR=1 keeps the bf16 cache on the scalar kernel (for comparison).
+bool kv_scalar_only() {
+  static const bool on = [] { const char* v = getenv("KV_B200_SCALAR"); return v && atoi(v) != 0; }();
+  return on;
+}
+
+template <int HD>
+cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, KvShape s, int n_seq, int splits, float scale_log2,
+                              cudaStream_t st) {
+  const size_t smem = std::max((size_t)TC_WARPS * TC_DEPTH * 2 * TC_KB * HD * 2, sizeof(float) * 16 * TC_WARPS * (HD + 2));
+  static bool configured = false;
+  if (!configured && smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kv_partial_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  kv_partial_tc_kernel<HD><<<dim3(splits, s.Hkv, n_seq), TC_WARPS * 32, smem, st>>>(
+      q, (const bf16*)c->keys, (const bf16*)c->values, c->lengths, c->part, s, splits, scale_log2);
+  count_launch();
+  return cudaGetLastError();
+}
+
 template <typename T>
 cudaError_t launch_partial(const kv_cache* c, const T* q, KvShape s, int n_seq, int splits, cudaStream_t st) {
   const float scale_log2 = LOG2E / sqrtf((float)s.HD);   // attention.rs:294-296
+  if (sizeof(T) == 2 && !kv_scalar_only()) {
+    if (s.HD == 64) return launch_partial_tc<64>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
+    if (s.HD == 128) return launch_partial_tc<128>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
+  }
   const dim3 grid(splits, s.Hkv, n_seq);
 #define KV_CASE(HDV)                                                                                         \
   case HDV: {                                                                                                \
-    const size_t smem = sizeof(float) * KV_QT * (KV_WARPS * (32 / (HDV / 8))) * (HDV + 2);                   \
+    const size_t smem = std::max(sizeof(float) * KV_QT * (KV_WARPS * (32 / (HDV / 8))) * (HDV + 2),          \
+                                 (size_t)KvRing<T>::DEPTH * 2 * KV_THREADS * 8 * sizeof(T));                 \
     kv_partial_kernel<T, HDV><<<grid, KV_THREADS, smem, st>>>(q, (const T*)c->keys, (const T*)c->values,     \
                                                                c->lengths, c->part, s, splits, scale_log2);  \
     break;                                                                                                   \
@@ -317,10 +577,10 @@ int forward_t(kv_cache* c, int first, int n_seq, void* q, const void* k, const v
   KvShape s{g.num_heads, g.kv_heads, g.head_dim, g.capacity, rows, first};
   int longest = 0;
   for (int i = 0; i < n_seq; ++i) longest = std::max(longest, c->host_len[first + i] + rows);
-  // enough CTAs for two per SM, slices of at least 256 positions
+  // about eight CTAs per SM (two or three are resident: several waves even out the tail), slices of at least 128 positions
   long long ctas = (long long)n_seq * g.kv_heads;
-  int splits = (int)std::min<long long>(KV_MAX_SPLITS, std::max<long long>(1, (2ll * c->sm_count + ctas - 1) / ctas));
-  splits = std::max(1, std::min(splits, (longest + 255) / 256));
+  int splits = (int)std::min<long long>(KV_MAX_SPLITS, std::max<long long>(1, (8ll * c->sm_count + ctas - 1) / ctas));
+  splits = std::max(1, std::min(splits, (longest + 127) / 128));
   const size_t need = (size_t)n_seq * rows * g.num_heads * splits * (g.head_dim + 2);
   if (need > c->part_floats) {
     if (c->part) { KCK(cudaStreamSynchronize(st)); cudaFree(c->part); c->part = nullptr; c->part_floats = 0; }
