@@ -46,7 +46,10 @@ const char* kv_cache_last_error(const kv_cache_t* cache);
 /* KvCache::clear (attention.rs:58-62) for every sequence, or for one when sequence >= 0. */
 int32_t kv_cache_clear(kv_cache_t* cache, int32_t sequence, void* stream);
 
-/* KvCache::len of every sequence into host memory (read from the device; synchronises the stream). */
+/* KvCache::len of every sequence into host memory (read from the device; synchronises the stream).
+ * The capacity checks of the calls below use a host copy of the lengths that every call keeps up to
+ * date; a step replayed from a captured CUDA graph advances the device lengths only, and this call
+ * brings the host copy back in line (the caller of a graph keeps within capacity itself). */
 int32_t kv_cache_lengths(kv_cache_t* cache, int32_t* lengths_host, void* stream);
 
 /* forward_cached without the projections, for sequences first_sequence .. first_sequence + n_sequences - 1

@@ -55,6 +55,13 @@ def lib() -> C.CDLL:
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
             "libmoe_b200.so is not built (run `python -m rustingbrain_b200.build`); there is no host fallback")
+    # The library needs libnccl.so.2.  When PyTorch is going to be used in the same process its bundled
+    # (newer) NCCL has to be the copy that gets loaded: loading this library first would bind the
+    # system's older libnccl, and `import torch` would then fail on symbols that copy lacks.
+    try:
+        import torch  # noqa: F401
+    except ImportError:
+        pass
     L = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
     vp, i32, f32 = C.c_void_p, C.c_int32, C.c_float
     fp, ip, bp = C.POINTER(C.c_float), C.POINTER(C.c_int32), C.POINTER(C.c_uint8)

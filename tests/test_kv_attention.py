@@ -75,6 +75,27 @@ def test_sequences_of_different_lengths_advance_together(precision, tol):
     assert rel_l2(values, oracles[2].values) <= (1e-6 if precision == "f32" else 1e-2)
 
 
+@pytest.mark.parametrize("H,Hkv,hd,rows", [(8, 1, 128, 1), (16, 2, 128, 3), (4, 4, 64, 5), (32, 2, 64, 1)])
+def test_bf16_cache_on_the_tensor_core_kernel(H, Hkv, hd, rows):
+    """bf16 caches with head_dim 64 / 128 take the mma.sync kernel: groups of 1 to 16 query heads, several new
+    rows per step (more than 16 queries per kv head means more than one pass), histories that end inside a block."""
+    S = 3
+    cache = KvCache(S, H, Hkv, hd, capacity=600, precision="bf16")
+    oracles = [ora.KvCacheOracle(H, Hkv, hd, 600) for _ in range(S)]
+    rnd = lambda a: _dev(a, "bf16").float().cpu().numpy()
+    for s, n in enumerate((1, 77, 530)):
+        q, k, v = _qkv(n, H, Hkv, hd, seed=300 + s)
+        cache.forward_cached(_dev(q, "bf16"), _dev(k, "bf16"), _dev(v, "bf16"), rows_per_sequence=n, first_sequence=s, n_sequences=1)
+        oracles[s].forward_cached(rnd(q), rnd(k), rnd(v))
+    for step in range(2):
+        q, k, v = _qkv(S * rows, H, Hkv, hd, seed=400 + step)
+        got = cache.forward_cached(_dev(q, "bf16"), _dev(k, "bf16"), _dev(v, "bf16"), rows_per_sequence=rows).float().cpu().numpy()
+        for s in range(S):
+            sl = slice(s * rows, (s + 1) * rows)
+            want = oracles[s].forward_cached(rnd(q[sl]), rnd(k[sl]), rnd(v[sl]))
+            assert rel_l2(got[sl], want) <= 2e-2, (step, s)
+
+
 def test_clear_and_truncate_and_a_restarted_sequence():
     S, H, Hkv, hd = 3, 4, 2, 32
     cache = KvCache(S, H, Hkv, hd, capacity=64, precision="f32")
