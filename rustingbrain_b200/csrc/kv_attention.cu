@@ -6,11 +6,12 @@
 // positions (attention.rs:1100-1160).  A decode step streams every cached key and value once, so the
 // kernel is bound by HBM: the cache is [sequence][position][kv_head * head_dim], one CTA takes one
 // (sequence, kv head, slice of the positions) and serves every query head of that kv head's group from
-// the same loads (grouped-query attention reads the cache once, not once per query head); the slices of
-// a kv head are merged by whichever of its CTAs finishes last (split softmax: running maximum,
-// denominator and weighted sum), which also advances the lengths.
+// the same loads (grouped-query attention reads the cache once, not once per query head); slices are
+// merged by a second small kernel (split softmax: running maximum, denominator and weighted sum).
 //
-// Two launches per step: rotate + append, attention.
+// Three launches per step: rotate + append, partial attention, merge (which also advances the lengths).
+// Merging inside the attention kernel (the last CTA of a kv head to finish merges its slices) was tried:
+// it saves a launch and measured 4 us slower per step than the separate merge kernel.
 
 #include <algorithm>
 #include <cmath>
@@ -117,48 +118,6 @@ __global__ void kv_append_kernel(T* __restrict__ q, const T* __restrict__ k, con
   }
 }
 
-// ---- merging the slices: done by whichever CTA of a (sequence, kv head) finishes last ----
-// Every CTA publishes its slice results (fence, then a counter per (sequence, kv head)); the CTA that
-// sees the full count merges all slices of that kv head's query heads (split softmax: common maximum,
-// weighted sums and denominators), writes the merged heads and resets the counter for the next step.
-// The last kv head of a sequence to finish moves that sequence's length on: by then every CTA that
-// reads the length has read it.  Nothing waits on anything, so no CTA depends on another being resident.
-template <typename T>
-__device__ void kv_finish(const float* __restrict__ part, T* __restrict__ merged, int* __restrict__ lengths,
-                          int* __restrict__ done_kv, int* __restrict__ done_seq, const KvShape& s, int splits,
-                          int sj, int seq, int kvh) {
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) s_last = atomicAdd(&done_kv[seq * s.Hkv + kvh], 1) == splits - 1;
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  const int HD = s.HD, PW = HD + 2, group = s.H / s.Hkv, nq = s.rows * group;
-  for (int idx = threadIdx.x; idx < nq * HD; idx += blockDim.x) {
-    const int qi = idx / HD, c = idx - qi * HD, i = qi / group, g = qi - i * group;
-    const size_t rh = (size_t)(sj * s.rows + i) * s.H + kvh * group + g;
-    const float* src = part + rh * splits * PW;
-    float mx = -INFINITY;
-    for (int p = 0; p < splits; ++p) mx = fmaxf(mx, __ldcg(src + p * PW + HD));
-    float num = 0.f, den = 0.f;
-    for (int p = 0; p < splits; ++p) {
-      const float mp = __ldcg(src + p * PW + HD);
-      const float w = mp > -INFINITY ? exp2f(mp - mx) : 0.f;
-      num = fmaf(w, __ldcg(src + p * PW + c), num);
-      den = fmaf(w, __ldcg(src + p * PW + HD + 1), den);
-    }
-    merged[rh * HD + c] = from_f32<T>(den > 0.f ? num / den : 0.f);   // activations.rs:65-69
-  }
-  if (threadIdx.x == 0) {
-    done_kv[seq * s.Hkv + kvh] = 0;
-    if (atomicAdd(&done_seq[seq], 1) == s.Hkv - 1) {
-      done_seq[seq] = 0;
-      lengths[seq] += s.rows;
-    }
-  }
-}
-
 // ---- partial attention over one slice of one sequence's positions, for one kv head ----
 // HD / 8 lanes share a position (each holds 8 channels of its key and of its value), so a warp takes
 // 256 / HD positions per step and every load is 16 bytes (bf16) or 32 bytes (f32) per lane, adjacent
@@ -169,8 +128,7 @@ __device__ void kv_finish(const float* __restrict__ part, T* __restrict__ merged
 template <typename T, int HD>
 __global__ void __launch_bounds__(KV_THREADS)
 kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* __restrict__ values,
-                  int* __restrict__ lengths, float* __restrict__ part, T* __restrict__ merged, int* __restrict__ done_kv,
-                  int* __restrict__ done_seq, KvShape s, int splits, float scale_log2) {
+                  const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
   constexpr int LPK = HD / 8, KPW = 32 / LPK, NG = KV_WARPS * KPW, PW = HD + 2;
   constexpr int SLOT = 8 * (int)sizeof(T), DEPTH = KvRing<T>::DEPTH;
   extern __shared__ __align__(16) float kv_sm[];   // the copy ring, then [KV_QT][NG][PW] for the merge
@@ -295,7 +253,6 @@ kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* 
     }
     __syncthreads();   // the next pass copies into the memory the merge has just read
   }
-  kv_finish<T>(part, merged, lengths, done_kv, done_seq, s, splits, sj, seq, kvh);
 }
 
 // ---- the same slice on the tensor cores (bf16 cache, head_dim 64 or 128) ----
@@ -331,8 +288,7 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 template <int HD>
 __global__ void __launch_bounds__(TC_WARPS * 32)
 kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, const bf16* __restrict__ values,
-                     int* __restrict__ lengths, float* __restrict__ part, bf16* __restrict__ merged,
-                     int* __restrict__ done_kv, int* __restrict__ done_seq, KvShape s, int splits, float scale_log2) {
+                     const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
   constexpr int RB = HD * 2, TILE = TC_KB * RB, CPR = HD / 8, PW = HD + 2, KT = HD / 16, NT = HD / 8;
   constexpr int COPIES = TC_KB * CPR / 32;    // 16-byte chunks per lane and tile
   extern __shared__ __align__(128) unsigned char tc_sm[];
@@ -490,7 +446,29 @@ kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, 
     }
     __syncthreads();   // the next pass copies into the memory the merge has just read
   }
-  kv_finish<bf16>(part, merged, lengths, done_kv, done_seq, s, splits, sj, seq, kvh);
+}
+
+// ---- merge the slices, write the merged heads, advance the cache lengths ----
+template <typename T>
+__global__ void kv_merge_kernel(const float* __restrict__ part, T* __restrict__ merged, int* __restrict__ lengths,
+                                KvShape s, int splits) {
+  const int PW = s.HD + 2;
+  const int rh = blockIdx.x;                      // row * H + head
+  const float* src = part + (size_t)rh * splits * PW;
+  float mx = -INFINITY;
+  for (int p = 0; p < splits; ++p) mx = fmaxf(mx, src[p * PW + s.HD]);
+  for (int c = threadIdx.x; c < s.HD; c += blockDim.x) {
+    float num = 0.f, den = 0.f;
+    for (int p = 0; p < splits; ++p) {
+      const float w = src[p * PW + s.HD] > -INFINITY ? exp2f(src[p * PW + s.HD] - mx) : 0.f;
+      num = fmaf(w, src[p * PW + c], num);
+      den = fmaf(w, src[p * PW + s.HD + 1], den);
+    }
+    merged[(size_t)rh * s.HD + c] = from_f32<T>(den > 0.f ? num / den : 0.f);   // activations.rs:65-69
+  }
+  // one thread per sequence moves its length on (every earlier launch of this step has read it)
+  const int row = rh / s.H, head = rh - row * s.H;
+  if (head == 0 && row % s.rows == 0 && threadIdx.x == 0) lengths[s.first + row / s.rows] += s.rows;
 }
 
 __global__ void kv_set_lengths_kernel(int* lengths, int first, int count, int value) {
@@ -514,8 +492,6 @@ struct kv_cache {
   void* keys = nullptr;
   void* values = nullptr;
   int* lengths = nullptr;           // device, one per sequence
-  int* done_kv = nullptr;           // finished slices per (sequence, kv head); zero between steps
-  int* done_seq = nullptr;          // finished kv heads per sequence; zero between steps
   std::vector<int> host_len;        // mirror: every change goes through this object
   float* cos_t = nullptr;
   float* sin_t = nullptr;
@@ -556,8 +532,8 @@ bool kv_scalar_only() {
 }
 
 template <int HD>
-cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, bf16* merged, KvShape s, int n_seq, int splits,
-                              float scale_log2, cudaStream_t st) {
+cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, KvShape s, int n_seq, int splits, float scale_log2,
+                              cudaStream_t st) {
   const size_t smem = std::max((size_t)TC_WARPS * TC_DEPTH * 2 * TC_KB * HD * 2, sizeof(float) * 16 * TC_WARPS * (HD + 2));
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
@@ -566,18 +542,17 @@ cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, bf16* merged, Kv
     configured = true;
   }
   kv_partial_tc_kernel<HD><<<dim3(splits, s.Hkv, n_seq), TC_WARPS * 32, smem, st>>>(
-      q, (const bf16*)c->keys, (const bf16*)c->values, c->lengths, c->part, merged, c->done_kv, c->done_seq, s, splits,
-      scale_log2);
+      q, (const bf16*)c->keys, (const bf16*)c->values, c->lengths, c->part, s, splits, scale_log2);
   count_launch();
   return cudaGetLastError();
 }
 
 template <typename T>
-cudaError_t launch_partial(const kv_cache* c, const T* q, T* merged, KvShape s, int n_seq, int splits, cudaStream_t st) {
+cudaError_t launch_partial(const kv_cache* c, const T* q, KvShape s, int n_seq, int splits, cudaStream_t st) {
   const float scale_log2 = LOG2E / sqrtf((float)s.HD);   // attention.rs:294-296
   if (sizeof(T) == 2 && !kv_scalar_only()) {
-    if (s.HD == 64) return launch_partial_tc<64>(c, (const bf16*)q, (bf16*)merged, s, n_seq, splits, scale_log2, st);
-    if (s.HD == 128) return launch_partial_tc<128>(c, (const bf16*)q, (bf16*)merged, s, n_seq, splits, scale_log2, st);
+    if (s.HD == 64) return launch_partial_tc<64>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
+    if (s.HD == 128) return launch_partial_tc<128>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
   }
   const dim3 grid(splits, s.Hkv, n_seq);
 #define KV_CASE(HDV)                                                                                         \
@@ -585,8 +560,7 @@ cudaError_t launch_partial(const kv_cache* c, const T* q, T* merged, KvShape s, 
     const size_t smem = std::max(sizeof(float) * KV_QT * (KV_WARPS * (32 / (HDV / 8))) * (HDV + 2),          \
                                  (size_t)KvRing<T>::DEPTH * 2 * KV_THREADS * 8 * sizeof(T));                 \
     kv_partial_kernel<T, HDV><<<grid, KV_THREADS, smem, st>>>(q, (const T*)c->keys, (const T*)c->values,     \
-                                                               c->lengths, c->part, merged, c->done_kv,      \
-                                                               c->done_seq, s, splits, scale_log2);          \
+                                                               c->lengths, c->part, s, splits, scale_log2);  \
     break;                                                                                                   \
   }
   switch (s.HD) {
@@ -623,7 +597,11 @@ int forward_t(kv_cache* c, int first, int n_seq, void* q, const void* k, const v
                                                     c->lengths, c->cos_t, c->sin_t, s, g.rope);
   count_launch();
   KCK(cudaGetLastError());
-  KCK(launch_partial<T>(c, (const T*)q, (T*)merged, s, n_seq, splits, st));
+  KCK(launch_partial<T>(c, (const T*)q, s, n_seq, splits, st));
+  kv_merge_kernel<T><<<n_seq * rows * g.num_heads, std::min(256, std::max(32, g.head_dim)), 0, st>>>(
+      c->part, (T*)merged, c->lengths, s, splits);
+  count_launch();
+  KCK(cudaGetLastError());
   for (int i = 0; i < n_seq; ++i) c->host_len[first + i] += rows;
   return MOE_OK;
 }
@@ -661,10 +639,6 @@ int32_t kv_cache_create(const kv_cache_config_t* config, kv_cache_t** out) {
   }
   KCK(cudaMalloc(&c->lengths, sizeof(int) * g.sequences));
   KCK(cudaMemset(c->lengths, 0, sizeof(int) * g.sequences));
-  KCK(cudaMalloc(&c->done_kv, sizeof(int) * g.sequences * g.kv_heads));
-  KCK(cudaMemset(c->done_kv, 0, sizeof(int) * g.sequences * g.kv_heads));
-  KCK(cudaMalloc(&c->done_seq, sizeof(int) * g.sequences));
-  KCK(cudaMemset(c->done_seq, 0, sizeof(int) * g.sequences));
   c->host_len.assign(g.sequences, 0);
   // the tables of Rope::new (rope.rs:77-90), in f32 arithmetic like the reference
   const int half = g.head_dim / 2;
@@ -686,7 +660,7 @@ int32_t kv_cache_create(const kv_cache_config_t* config, kv_cache_t** out) {
 
 void kv_cache_destroy(kv_cache_t* c) {
   if (!c) return;
-  cudaFree(c->keys); cudaFree(c->values); cudaFree(c->lengths); cudaFree(c->done_kv); cudaFree(c->done_seq); cudaFree(c->cos_t); cudaFree(c->sin_t);
+  cudaFree(c->keys); cudaFree(c->values); cudaFree(c->lengths); cudaFree(c->cos_t); cudaFree(c->sin_t);
   cudaFree(c->part); cudaFree(c->read_buf);
   delete c;
 }
