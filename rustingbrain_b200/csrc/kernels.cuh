@@ -38,6 +38,9 @@ struct PermuteArgs {
 };
 
 cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t stream);
+// bf16 logits product for decode-sized batches (d a multiple of 8): one CTA per token row
+cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
+                                      cudaStream_t stream);
 // `align`: every expert's row group starts at a multiple of this many rows (128 for the
 // local expert GEMMs, 1 for the compact send layout of an expert-parallel rank).
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,

@@ -458,7 +458,12 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.partial = L->partial; ra.hist = L->hist;
   L->shared_meta = L->shared_meta_table + 4 * tokens;
   { Span sp(L, 0, st);
-  if (L->tc_router && !logits_in) {
+  if (L->tc_router && !logits_in && tokens <= 256 && L->d % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+    // decode-sized batch: a CTA per token row beats one tensor-core tile on one SM
+    CK(launch_router_logits_rows(x, L->wb + L->off_router, L->logits, tokens, L->d, L->E, st));
+    ra.logits_in = L->logits;
+    ra.logits_out = nullptr;
+  } else if (L->tc_router && !logits_in) {
     // logits = x W_r^T on the tensor cores, f32 out; softmax/top-k then read them back
     tc::GemmArgs g{};
     g.group_row0 = L->shared_meta; g.tile_start = L->shared_meta + 2; g.n_groups = 1; g.error_flag = L->error_flag;

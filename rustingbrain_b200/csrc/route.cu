@@ -650,6 +650,38 @@ cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float
   return cudaGetLastError();
 }
 
+// Router logits for decode-sized batches: logits[t, e] = sum_c x[t, c] * w[e, c], bf16 operands, f32
+// sums.  One CTA per token row, a warp per expert (round robin), 16-byte loads; a single 128-row
+// tensor-core tile would leave this to one SM and a 16-step dependent pipeline.
+__global__ void __launch_bounds__(128)
+router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits, int d, int E) {
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * d);
+  for (int e = warp; e < E; e += 4) {
+    const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)e * d);
+    float acc = 0.f;
+    for (int c = lane; c < d / 8; c += 32) {
+      const uint4 a = __ldg(xr + c), b = __ldg(wr + c);
+      const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc = fmaf(__uint_as_float(av[i] << 16), __uint_as_float(bv[i] << 16), acc);
+        acc = fmaf(__uint_as_float(av[i] & 0xffff0000u), __uint_as_float(bv[i] & 0xffff0000u), acc);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) logits[(size_t)t * E + e] = acc;
+  }
+}
+cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
+                                      cudaStream_t stream) {
+  if (tokens <= 0) return cudaSuccess;
+  router_logits_rows_kernel<<<tokens, 128, 0, stream>>>((const bf16*)x, (const bf16*)w_bf16, logits, d, E);
+  count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
                             int align, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
