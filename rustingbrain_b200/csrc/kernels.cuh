@@ -5,6 +5,16 @@
 
 namespace moe {
 
+// When the whole batch fits one router block the routing tables are finalized by that block (no second launch).
+struct RouterFinalize {
+  int enabled;              // set by the caller; honoured when tokens <= rows of one router block
+  float aux_w, z_w;
+  RouteMeta meta;
+  float* stats;
+  float* losses;
+  int align;
+};
+
 struct RouterArgs {
   const void* x;            // [tokens, d] activations (f32 or bf16); unused when logits_in is set
   const float* w_router;    // [E, d]
@@ -18,6 +28,7 @@ struct RouterArgs {
   float* gates;             // [tokens*k]
   float* partial;           // [blocks, E+2]
   int* hist;                // [blocks, E]; after finalize: padded-row write cursors
+  RouterFinalize fin;       // optional, see above
 };
 
 struct PermuteArgs {

@@ -456,6 +456,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.tokens = tokens; ra.d = L->d; ra.E = L->E; ra.k = L->k;
   ra.logits_out = L->logits; ra.probs = L->probs; ra.lse = L->lse; ra.expert_of = L->expert_of; ra.gates = L->gates;
   ra.partial = L->partial; ra.hist = L->hist;
+  ra.fin = RouterFinalize{1, L->aux_w, L->z_w, L->meta, L->stats, L->losses, ep ? 1 : GROUP_ALIGN};
   L->shared_meta = L->shared_meta_table + 4 * tokens;
   { Span sp(L, 0, st);
   if (L->tc_router && !logits_in && tokens <= 256 && L->d % 8 == 0 && ((uintptr_t)x & 15) == 0) {

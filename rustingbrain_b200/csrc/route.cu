@@ -75,12 +75,140 @@ __device__ __forceinline__ float expf_libm(float x) {
 constexpr int RT_THREADS = 256;
 constexpr int RT_KC = 32;
 
+// One block.  hist[b][e] becomes the padded-row write cursor of block b for expert e.
+constexpr int FIN_THREADS = 1024;
+// Plain pointers: the single-block router calls this on what it has just written itself.
+__device__ __forceinline__ void finalize_body(const float* partial, int* hist, int nb, int E, int k, float aux_w,
+                                              float z_w, RouteMeta meta, float* stats /*[E+2]: sums, lse2, V*/,
+                                              float* losses /*[2]*/, int align, int add_base) {
+  __shared__ int s_counts[MAX_EXPERTS];
+  __shared__ float s_sums[MAX_EXPERTS + 2];
+  __shared__ double seg_d[FIN_THREADS + 64];   // [parts][E + 2] partial statistics
+  __shared__ int seg_i[FIN_THREADS];           // [parts][E] rows per expert in a run of router blocks
+  const int tid = threadIdx.x;
+  // The router blocks are cut into `parts` consecutive runs, one thread per (run, column): the
+  // statistics are summed per run and then over the runs in order (in double, so the association does
+  // not show in the f32 result); the per-expert cursors take one pass for the run totals and a second
+  // one that writes the exclusive prefix.
+  {
+    const int cols = E + 2, parts = max(1, (int)blockDim.x / cols), seg = ceil_div(nb, parts);
+    const int part = tid / cols, e = tid - part * cols;
+    if (cols > (int)blockDim.x) {                    // more columns than threads: one run, strided columns
+      for (int c = tid; c < cols; c += blockDim.x) {
+        double sum = 0.0;
+        for (int b = 0; b < nb; ++b) sum += (double)partial[(size_t)b * cols + c];
+        seg_d[c] = sum;
+      }
+    } else if (part < parts) {
+      double sum = 0.0;
+      const int lo = part * seg, hi = min(nb, lo + seg);
+      for (int b0 = lo; b0 < hi; b0 += 8) {          // eight independent loads, then the ordered sum
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = b0 + i < hi ? partial[(size_t)(b0 + i) * cols + e] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) if (b0 + i < hi) sum += (double)v[i];
+      }
+      seg_d[part * cols + e] = sum;
+    }
+    __syncthreads();
+    for (int c = tid; c < cols; c += blockDim.x) {
+      double t = 0.0;
+      for (int p = 0; p < (cols > (int)blockDim.x ? 1 : parts); ++p) t += seg_d[p * cols + c];
+      s_sums[c] = (float)t;
+      stats[c] = (float)t;
+    }
+  }
+  {
+    const int parts = max(1, (int)blockDim.x / E), seg = ceil_div(nb, parts);
+    const int part = tid / E, e = tid - part * E;
+    const int lo = part * seg, hi = min(nb, lo + seg);
+    if (part < parts) {
+      int run = 0;
+      for (int b0 = lo; b0 < hi; b0 += 8) {
+        int h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) run += h[i];
+      }
+      seg_i[part * E + e] = run;
+    }
+    __syncthreads();
+    if (part < parts) {
+      int run = 0;
+      for (int p = 0; p < part; ++p) run += seg_i[p * E + e];
+      for (int b0 = lo; b0 < hi; b0 += 8) {
+        int h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (b0 + i < hi) hist[(size_t)(b0 + i) * E + e] = run;
+          run += h[i];
+        }
+      }
+      if (part == parts - 1) {        // the last run ends at the expert's total
+        s_counts[e] = run;
+        meta.counts[e] = run;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int off = 0, pad = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      meta.offsets[e] = off;
+      meta.pad_off[e] = pad;
+      meta.tile_start[e] = tiles;
+      off += s_counts[e];
+      const int padded = round_up(s_counts[e], align);
+      pad += padded;
+      tiles += ceil_div(padded, GROUP_ALIGN);
+    }
+    meta.offsets[E] = off;
+    meta.pad_off[E] = pad;
+    meta.tile_start[E] = tiles;
+    const int V = (int)s_sums[E + 1];
+    meta.total[0] = off;
+    meta.total[1] = pad;
+    meta.total[2] = tiles;
+    meta.total[3] = V;
+    // auxiliary_losses (moe.rs:602-639) over the rows this device saw.
+    const float* sums = s_sums;
+    const float Vf = (float)V;
+    float aux = 0.f, z = 0.f;
+    if (Vf > 0.f) {
+      const float slots = Vf * (float)k;
+      for (int e = 0; e < E; ++e) {
+        const float load = (float)s_counts[e] / slots;
+        const float mass = sums[e] / Vf;
+        aux += load * mass;
+      }
+      aux *= (float)E * aux_w;
+      z = z_w * sums[E] / Vf;
+    }
+    losses[0] = aux;
+    losses[1] = z;
+  }
+  if (add_base) {   // few blocks: the cursors get their group base here instead of in a second launch
+    __syncthreads();
+    for (int i = tid; i < nb * E; i += blockDim.x) hist[i] += meta.pad_off[i % E];
+  }
+}
+
+__global__ void __launch_bounds__(FIN_THREADS)
+finalize_kernel(const float* partial, int* hist, int nb, int E, int k, float aux_w, float z_w, RouteMeta meta,
+                float* stats, float* losses, int align, int add_base) {
+  finalize_body(partial, hist, nb, E, k, aux_w, z_w, meta, stats, losses, align, add_base);
+}
+
 template <typename T, int EPT, bool FROM_LOGITS>
 __global__ void __launch_bounds__(RT_THREADS)
 router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const float* __restrict__ logits_in,
               const uint8_t* __restrict__ valid, int tokens, int d, int E, int k, float* __restrict__ logits_out,
               float* __restrict__ probs, float* __restrict__ lse, int* __restrict__ expert_of,
-              float* __restrict__ gates, float* __restrict__ partial /*[nb, E+2]*/, int* __restrict__ hist /*[nb,E]*/) {
+              float* __restrict__ gates, float* partial /*[nb, E+2]*/, int* hist /*[nb,E]*/, RouterFinalize fin) {
   extern __shared__ float rt_smem[];
   const int ldl = E + 1;
   float* lg = rt_smem;                          // [64][E+1] logits, then probabilities
@@ -248,127 +376,9 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
     part[E] = s;
     part[E + 1] = (float)v;
   }
-}
-
-// One block.  hist[b][e] becomes the padded-row write cursor of block b for expert e.
-constexpr int FIN_THREADS = 1024;
-__global__ void __launch_bounds__(FIN_THREADS)
-finalize_kernel(const float* __restrict__ partial, int* __restrict__ hist, int nb, int E, int k, float aux_w,
-                float z_w, RouteMeta meta, float* __restrict__ stats /*[E+2]: sums, lse2, V*/,
-                float* __restrict__ losses /*[2]*/, int align, int add_base) {
-  __shared__ int s_counts[MAX_EXPERTS];
-  __shared__ float s_sums[MAX_EXPERTS + 2];
-  __shared__ double seg_d[FIN_THREADS + 64];   // [parts][E + 2] partial statistics
-  __shared__ int seg_i[FIN_THREADS];           // [parts][E] rows per expert in a run of router blocks
-  const int tid = threadIdx.x;
-  // The router blocks are cut into `parts` consecutive runs, one thread per (run, column): the
-  // statistics are summed per run and then over the runs in order (in double, so the association does
-  // not show in the f32 result); the per-expert cursors take one pass for the run totals and a second
-  // one that writes the exclusive prefix.
-  {
-    const int cols = E + 2, parts = max(1, (int)blockDim.x / cols), seg = ceil_div(nb, parts);
-    const int part = tid / cols, e = tid - part * cols;
-    if (cols > (int)blockDim.x) {                    // more columns than threads: one run, strided columns
-      for (int c = tid; c < cols; c += blockDim.x) {
-        double sum = 0.0;
-        for (int b = 0; b < nb; ++b) sum += (double)partial[(size_t)b * cols + c];
-        seg_d[c] = sum;
-      }
-    } else if (part < parts) {
-      double sum = 0.0;
-      const int lo = part * seg, hi = min(nb, lo + seg);
-      for (int b0 = lo; b0 < hi; b0 += 8) {          // eight independent loads, then the ordered sum
-        float v[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = b0 + i < hi ? partial[(size_t)(b0 + i) * cols + e] : 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) if (b0 + i < hi) sum += (double)v[i];
-      }
-      seg_d[part * cols + e] = sum;
-    }
+  if (fin.enabled) {   // the only router block of the pass: finalize what it has just written
     __syncthreads();
-    for (int c = tid; c < cols; c += blockDim.x) {
-      double t = 0.0;
-      for (int p = 0; p < (cols > (int)blockDim.x ? 1 : parts); ++p) t += seg_d[p * cols + c];
-      s_sums[c] = (float)t;
-      stats[c] = (float)t;
-    }
-  }
-  {
-    const int parts = max(1, (int)blockDim.x / E), seg = ceil_div(nb, parts);
-    const int part = tid / E, e = tid - part * E;
-    const int lo = part * seg, hi = min(nb, lo + seg);
-    if (part < parts) {
-      int run = 0;
-      for (int b0 = lo; b0 < hi; b0 += 8) {
-        int h[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) run += h[i];
-      }
-      seg_i[part * E + e] = run;
-    }
-    __syncthreads();
-    if (part < parts) {
-      int run = 0;
-      for (int p = 0; p < part; ++p) run += seg_i[p * E + e];
-      for (int b0 = lo; b0 < hi; b0 += 8) {
-        int h[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) h[i] = b0 + i < hi ? hist[(size_t)(b0 + i) * E + e] : 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (b0 + i < hi) hist[(size_t)(b0 + i) * E + e] = run;
-          run += h[i];
-        }
-      }
-      if (part == parts - 1) {        // the last run ends at the expert's total
-        s_counts[e] = run;
-        meta.counts[e] = run;
-      }
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int off = 0, pad = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      meta.offsets[e] = off;
-      meta.pad_off[e] = pad;
-      meta.tile_start[e] = tiles;
-      off += s_counts[e];
-      const int padded = round_up(s_counts[e], align);
-      pad += padded;
-      tiles += ceil_div(padded, GROUP_ALIGN);
-    }
-    meta.offsets[E] = off;
-    meta.pad_off[E] = pad;
-    meta.tile_start[E] = tiles;
-    const int V = (int)s_sums[E + 1];
-    meta.total[0] = off;
-    meta.total[1] = pad;
-    meta.total[2] = tiles;
-    meta.total[3] = V;
-    // auxiliary_losses (moe.rs:602-639) over the rows this device saw.
-    const float* sums = s_sums;
-    const float Vf = (float)V;
-    float aux = 0.f, z = 0.f;
-    if (Vf > 0.f) {
-      const float slots = Vf * (float)k;
-      for (int e = 0; e < E; ++e) {
-        const float load = (float)s_counts[e] / slots;
-        const float mass = sums[e] / Vf;
-        aux += load * mass;
-      }
-      aux *= (float)E * aux_w;
-      z = z_w * sums[E] / Vf;
-    }
-    losses[0] = aux;
-    losses[1] = z;
-  }
-  if (add_base) {   // few blocks: the cursors get their group base here instead of in a second launch
-    __syncthreads();
-    for (int i = tid; i < nb * E; i += blockDim.x) hist[i] += meta.pad_off[i % E];
+    finalize_body(partial, hist, 1, E, k, fin.aux_w, fin.z_w, fin.meta, fin.stats, fin.losses, fin.align, 1);
   }
 }
 
@@ -606,16 +616,20 @@ template <typename T, int EPT>
 static cudaError_t launch_router_ept(const RouterArgs& a, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
   const size_t smem = router_smem(a.E, a.k);
+  // the kernel also holds the 15 KB of static tables of the finalize step: opt in to more than the default
+  // 48 KB as soon as the sum passes it
+  RouterFinalize fin = a.fin;
+  fin.enabled = (a.fin.enabled && nb == 1) ? 1 : 0;
   if (a.logits_in) {
     auto kern = router_kernel<T, EPT, true>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem + 16 * 1024 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
-                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist); count_launch();
+                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
   } else {
     auto kern = router_kernel<T, EPT, false>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem + 16 * 1024 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
-                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist); count_launch();
+                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
   }
   return cudaGetLastError();
 }
@@ -685,6 +699,7 @@ cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* 
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
                             int align, cudaStream_t stream) {
   const int nb = ceil_div(a.tokens, ROUTER_ROWS);
+  if (a.fin.enabled && nb == 1) return cudaSuccess;   // done by the router block itself
   const int fold = nb <= 16 ? 1 : 0;
   finalize_kernel<<<1, nb > 32 ? FIN_THREADS : 256, 0, stream>>>(a.partial, a.hist, nb, a.E, a.k, aux_w, z_w, meta, stats, losses, align, fold); count_launch();
   if (nb > 0 && !fold) { cursor_base_kernel<<<ceil_div(nb * a.E, 256), 256, 0, stream>>>(a.hist, nb, a.E, meta.pad_off); count_launch(); }
