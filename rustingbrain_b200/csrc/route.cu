@@ -671,21 +671,37 @@ __global__ void __launch_bounds__(128)
 router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits, int d, int E) {
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * d);
-  for (int e = warp; e < E; e += 4) {
-    const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)e * d);
-    float acc = 0.f;
-    for (int c = lane; c < d / 8; c += 32) {
-      const uint4 a = __ldg(xr + c), b = __ldg(wr + c);
-      const uint32_t av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+  constexpr int EG = 8;   // experts a warp works on at once: their loads are all in flight together
+  for (int e0 = warp; e0 < E; e0 += 4 * EG) {
+    float acc[EG];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        acc = fmaf(__uint_as_float(av[i] << 16), __uint_as_float(bv[i] << 16), acc);
-        acc = fmaf(__uint_as_float(av[i] & 0xffff0000u), __uint_as_float(bv[i] & 0xffff0000u), acc);
+    for (int j = 0; j < EG; ++j) acc[j] = 0.f;
+    for (int c = lane; c < d / 8; c += 32) {
+      const uint4 a = __ldg(xr + c);
+      uint4 b[EG];
+#pragma unroll
+      for (int j = 0; j < EG; ++j) {
+        const int e = e0 + 4 * j;
+        b[j] = e < E ? __ldg(reinterpret_cast<const uint4*>(w + (size_t)e * d) + c) : make_uint4(0, 0, 0, 0);
+      }
+      const uint32_t av[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int j = 0; j < EG; ++j) {
+        const uint32_t bv[4] = {b[j].x, b[j].y, b[j].z, b[j].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[j] = fmaf(__uint_as_float(av[i] << 16), __uint_as_float(bv[i] << 16), acc[j]);
+          acc[j] = fmaf(__uint_as_float(av[i] & 0xffff0000u), __uint_as_float(bv[i] & 0xffff0000u), acc[j]);
+        }
       }
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) logits[(size_t)t * E + e] = acc;
+    for (int j = 0; j < EG; ++j) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
+      const int e = e0 + 4 * j;
+      if (lane == 0 && e < E) logits[(size_t)t * E + e] = acc[j];
+    }
   }
 }
 cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
