@@ -56,8 +56,10 @@ int32_t kv_cache_lengths(kv_cache_t* cache, int32_t* lengths_host, void* stream)
  * (all of them for a decode step, one of them for the prefill of a new request).
  * q [n_sequences * rows_per_sequence, num_heads * head_dim], k and v [same rows, kv_heads * head_dim],
  * rows of one sequence adjacent (row = j * rows_per_sequence + i for the j-th sequence of the range);
- * row i of a sequence sits at position len + i and sees positions 0 ..= len + i.  q is rotated in
- * place (as `project` returns rotated queries, attention.rs:920-944); k and v are read only.
+ * row i of a sequence sits at position len + i and sees positions 0 ..= len + i.  q, k and v are the
+ * projections BEFORE rotation (`project`, attention.rs:920-944, rotates queries and keys; here the call
+ * does).  q is scratch: one kernel path rotates it in place, the other rotates in registers and leaves it
+ * alone, so its contents after the call are unspecified; k and v are read only.
  * merged [rows, num_heads * head_dim] is the input of the output projection.
  * SequenceTooLong -> MOE_INVALID_INPUT when a cache would pass its capacity (rope.rs:194-200); nothing
  * is appended in that case. */

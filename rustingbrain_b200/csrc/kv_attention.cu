@@ -9,7 +9,8 @@
 // the same loads (grouped-query attention reads the cache once, not once per query head); slices are
 // merged by a second small kernel (split softmax: running maximum, denominator and weighted sum).
 //
-// Three launches per step: rotate + append, partial attention, merge (which also advances the lengths).
+// Launches per step: [rotate + append: scalar path only; the tensor-core kernel does both itself,] partial
+// attention, merge (which also advances the lengths).
 // Merging inside the attention kernel (the last CTA of a kv head to finish merges its slices) was tried:
 // it saves a launch and measured 4 us slower per step than the separate merge kernel.
 
@@ -287,8 +288,10 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
 
 template <int HD>
 __global__ void __launch_bounds__(TC_WARPS * 32)
-kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, const bf16* __restrict__ values,
-                     const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
+kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ knew, const bf16* __restrict__ vnew,
+                     bf16* keys, bf16* values, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                     const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2,
+                     int rope) {
   constexpr int RB = HD * 2, TILE = TC_KB * RB, CPR = HD / 8, PW = HD + 2, KT = HD / 16, NT = HD / 8;
   constexpr int COPIES = TC_KB * CPR / 32;    // 16-byte chunks per lane and tile
   extern __shared__ __align__(128) unsigned char tc_sm[];
@@ -298,10 +301,35 @@ kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, 
   const int chunk = round_up(ceil_div(total, splits), TC_WARPS * TC_KB);
   const int k0 = split * chunk, k1 = min(total, k0 + chunk);
   const int group = s.H / s.Hkv, nq = s.rows * group, W = s.Hkv * s.HD;
-  const bf16* kg = keys + (size_t)seq * s.cap * W + kvh * HD;
-  const bf16* vg = values + (size_t)seq * s.cap * W + kvh * HD;
+  bf16* kg = keys + (size_t)seq * s.cap * W + kvh * HD;
+  bf16* vg = values + (size_t)seq * s.cap * W + kvh * HD;
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(tc_sm) + warp * (TC_DEPTH * 2 * TILE);
   float* mb = reinterpret_cast<float*>(tc_sm);   // [16][TC_WARPS][PW], after the rings are drained
+  constexpr int HALF = HD / 2;
+
+  // Append: the new positions that fall into this slice are rotated (keys) and stored by this CTA, for
+  // its kv head, before it reads the slice; every new position lies in exactly one slice, and no CTA reads
+  // positions outside its own slice, so no CTA depends on another one's stores.
+  {
+    const int a0 = max(k0, len0), a1 = min(k0 + chunk, total);
+    for (int idx = threadIdx.x; idx < (a1 - a0) * HALF; idx += TC_WARPS * 32) {
+      const int r = idx / HALF, c = idx - r * HALF, pos = a0 + r;
+      const size_t src = (size_t)(sj * s.rows + pos - len0) * W + kvh * HD;
+      const float lo = __bfloat162float(knew[src + c]), hi = __bfloat162float(knew[src + HALF + c]);
+      float a = lo, b = hi;
+      if (rope) {
+        const float co = cos_t[(size_t)pos * HALF + c], si = sin_t[(size_t)pos * HALF + c];
+        a = lo * co - hi * si;                                  // rope.rs:213-218
+        b = hi * co + lo * si;
+      }
+      kg[(size_t)pos * W + c] = __float2bfloat16_rn(a);
+      kg[(size_t)pos * W + HALF + c] = __float2bfloat16_rn(b);
+      vg[(size_t)pos * W + c] = vnew[src + c];
+      vg[(size_t)pos * W + HALF + c] = vnew[src + HALF + c];
+    }
+    __threadfence();
+    __syncthreads();
+  }
 
   for (int q0 = 0; q0 < nq; q0 += 16) {
     // query fragments: rows gid and gid + 8 of the pass
@@ -317,6 +345,23 @@ kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ keys, 
       for (int kk = 0; kk < KT; ++kk) {
         qa[kk][h] = ok ? *reinterpret_cast<const uint32_t*>(qr + 16 * kk) : 0u;
         qa[kk][2 + h] = ok ? *reinterpret_cast<const uint32_t*>(qr + 16 * kk + 8) : 0u;
+      }
+      if (ok && rope) {
+        // rotate-half inside the fragments: channel c (k-step kk) pairs with c + HD / 2 (k-step kk + KT / 2),
+        // same register slot; rounded to bf16 as a rotated query stored in memory would be
+        const float* ct = cos_t + (size_t)(len0 + i) * HALF + 2 * tig;
+        const float* st = sin_t + (size_t)(len0 + i) * HALF + 2 * tig;
+#pragma unroll
+        for (int kk = 0; kk < KT / 2; ++kk)
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {           // channels 16 kk + 2 tig (+1), then + 8
+            const int c = 16 * kk + 8 * u;
+            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk][2 * u + h]));
+            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&qa[kk + KT / 2][2 * u + h]));
+            const float c0 = ct[c], c1 = ct[c + 1], s0 = st[c], s1 = st[c + 1];
+            qa[kk][2 * u + h] = pack_bf16x2(lo.x * c0 - hi.x * s0, lo.y * c1 - hi.y * s1);
+            qa[kk + KT / 2][2 * u + h] = pack_bf16x2(hi.x * c0 + lo.x * s0, hi.y * c1 + lo.y * s1);
+          }
       }
     }
     const int last = min(q0 + 15, nq - 1);
@@ -532,8 +577,8 @@ bool kv_scalar_only() {
 }
 
 template <int HD>
-cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, KvShape s, int n_seq, int splits, float scale_log2,
-                              cudaStream_t st) {
+cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, const bf16* k, const bf16* v, KvShape s, int n_seq,
+                              int splits, float scale_log2, cudaStream_t st) {
   const size_t smem = std::max((size_t)TC_WARPS * TC_DEPTH * 2 * TC_KB * HD * 2, sizeof(float) * 16 * TC_WARPS * (HD + 2));
   static bool configured = false;
   if (!configured && smem > 48 * 1024) {
@@ -542,17 +587,22 @@ cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, KvShape s, int n
     configured = true;
   }
   kv_partial_tc_kernel<HD><<<dim3(splits, s.Hkv, n_seq), TC_WARPS * 32, smem, st>>>(
-      q, (const bf16*)c->keys, (const bf16*)c->values, c->lengths, c->part, s, splits, scale_log2);
+      q, k, v, (bf16*)c->keys, (bf16*)c->values, c->cos_t, c->sin_t, c->lengths, c->part, s, splits, scale_log2, c->cfg.rope);
   count_launch();
   return cudaGetLastError();
 }
 
+// The tensor-core kernel rotates and appends by itself; the scalar one needs kv_append_kernel first.
 template <typename T>
-cudaError_t launch_partial(const kv_cache* c, const T* q, KvShape s, int n_seq, int splits, cudaStream_t st) {
+bool takes_tc_path(int head_dim) { return sizeof(T) == 2 && !kv_scalar_only() && (head_dim == 64 || head_dim == 128); }
+
+template <typename T>
+cudaError_t launch_partial(const kv_cache* c, const T* q, const T* k, const T* v, KvShape s, int n_seq, int splits,
+                           cudaStream_t st) {
   const float scale_log2 = LOG2E / sqrtf((float)s.HD);   // attention.rs:294-296
-  if (sizeof(T) == 2 && !kv_scalar_only()) {
-    if (s.HD == 64) return launch_partial_tc<64>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
-    if (s.HD == 128) return launch_partial_tc<128>(c, (const bf16*)q, s, n_seq, splits, scale_log2, st);
+  if (takes_tc_path<T>(s.HD)) {
+    if (s.HD == 64) return launch_partial_tc<64>(c, (const bf16*)q, (const bf16*)k, (const bf16*)v, s, n_seq, splits, scale_log2, st);
+    return launch_partial_tc<128>(c, (const bf16*)q, (const bf16*)k, (const bf16*)v, s, n_seq, splits, scale_log2, st);
   }
   const dim3 grid(splits, s.Hkv, n_seq);
 #define KV_CASE(HDV)                                                                                         \
@@ -593,11 +643,13 @@ int forward_t(kv_cache* c, int first, int n_seq, void* q, const void* k, const v
     }
     c->part_floats = need;
   }
-  kv_append_kernel<T><<<n_seq * rows, 128, 0, st>>>((T*)q, (const T*)k, (const T*)v, (T*)c->keys, (T*)c->values,
-                                                    c->lengths, c->cos_t, c->sin_t, s, g.rope);
-  count_launch();
-  KCK(cudaGetLastError());
-  KCK(launch_partial<T>(c, (const T*)q, s, n_seq, splits, st));
+  if (!takes_tc_path<T>(g.head_dim)) {
+    kv_append_kernel<T><<<n_seq * rows, 128, 0, st>>>((T*)q, (const T*)k, (const T*)v, (T*)c->keys, (T*)c->values,
+                                                      c->lengths, c->cos_t, c->sin_t, s, g.rope);
+    count_launch();
+    KCK(cudaGetLastError());
+  }
+  KCK(launch_partial<T>(c, (const T*)q, (const T*)k, (const T*)v, s, n_seq, splits, st));
   kv_merge_kernel<T><<<n_seq * rows * g.num_heads, std::min(256, std::max(32, g.head_dim)), 0, st>>>(
       c->part, (T*)merged, c->lengths, s, splits);
   count_launch();

@@ -80,7 +80,7 @@ class KvCache:
     # -- forward_cached -----------------------------------------------------------------------------
     def forward_cached(self, q, k, v, rows_per_sequence: int = 1, first_sequence: int = 0,
                        n_sequences: Optional[int] = None, out=None, stream=None):
-        """Device tensors q [rows, num_heads * head_dim] (rotated in place), k and v
+        """Device tensors q [rows, num_heads * head_dim] (scratch: may be rotated in place), k and v
         [rows, kv_heads * head_dim], rows = n_sequences * rows_per_sequence; returns the merged heads."""
         import torch
         n_seq = self.sequences - first_sequence if n_sequences is None else n_sequences
