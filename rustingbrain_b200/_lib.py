@@ -113,6 +113,9 @@ def lib() -> C.CDLL:
         "kv_cache_lengths": (i32, [vp, ip, vp]),
         "kv_attention_forward_cached": (i32, [vp, i32, i32, vp, vp, vp, i32, vp, vp]),
         "kv_cache_read": (i32, [vp, i32, fp, fp, vp]),
+        "rmsnorm_forward": (i32, [vp, vp, vp, i32, i32, f32, i32, vp, C.c_char_p, i32]),
+        "rmsnorm_scratch_bytes": (C.c_int64, [i32, i32]),
+        "rmsnorm_backward": (i32, [vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp, C.c_char_p, i32]),
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
         "moe_debug_set_tc_pair": (i32, [i32]),
@@ -135,5 +138,5 @@ def exported_symbols():
     for h in sorted(os.listdir(inc)):
         if h.endswith(".h"):
             text = open(os.path.join(inc, h)).read()
-            names += re.findall(r"\b((?:moe|kv)_[a-z0-9_]+)\s*\(", text)
+            names += re.findall(r"\b((?:moe|kv|rmsnorm)_[a-z0-9_]+)\s*\(", text)
     return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight")))

@@ -584,7 +584,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // K-stage that is 32 KiB of shared memory instead of 48, so the ring holds 6 stages
 // instead of 4 (longer latency cover for the same 192 KiB) and the L2 -> SM traffic per
 // FLOP drops by a third.  CTA 0 of the pair issues the MMAs; both run their epilogue on
-// their own 128 TMEM lanes.  No load is multicast: every CTA fetches what it stores.
+// their own 128 TMEM lanes.  Every CTA fetches what it stores; no load is shared across the cluster.
 //
 //   full[s]      (leader's)  one arrive.expect_tx by the leader for BOTH CTAs' bytes; the
 //                            peer's TMA completes its bytes on the leader's barrier
