@@ -42,6 +42,9 @@ WORKLOADS = {
     # 4 key/value heads (the head split of the reference's README model scaled to d_model 1024), bf16 cache
     "cfg5_attn": dict(S=64, H=16, Hkv=4, hd=64, history=4096, precision="attn", seed=9,
                       name="KV-cached decode attention: 64 sequences x 1 token over 4096 cached positions, 16 query heads, 4 kv heads, head_dim 64, bf16 cache"),
+    # the normalisation in front of the layer, on cfg 4's activations (268 MB per tensor in bf16: larger than L2)
+    "rmsnorm": dict(T=32768, d=4096, precision="rmsnorm", seed=2024,
+                    name="RMSNorm forward + backward bf16: 32768 tokens, d_model 4096"),
     # BASELINE config 2 is a whole-model train_step; only its MoE layers are on this path.  One of its
     # six MoE blocks (layers 2..7: 8 experts top-2, expert d_ff 352 + shared, 8 x 1024 tokens), forward +
     # backward + Adam, bf16 GEMMs over f32 master weights.
@@ -377,6 +380,47 @@ def run_decode_attention(args, w):
     print(json.dumps(line))
 
 
+def run_rmsnorm(args, w):
+    """RMSNorm forward + backward over activations larger than L2; each direction timed with CUDA events."""
+    import torch
+    from rustingbrain_b200 import _lib
+    from rustingbrain_b200.norm import RmsNorm
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    T, d = w["T"], w["d"]
+    gen = torch.Generator(device=dev).manual_seed(w["seed"])
+    x = torch.randn(T, d, device=dev, generator=gen).bfloat16()
+    gy = torch.randn(T, d, device=dev, generator=gen).bfloat16()
+    norm = RmsNorm(d, 1e-6)
+    y = torch.empty_like(x)
+    steps, warm = max(args.steps, 1), max(args.warmup, 3)
+    for _ in range(warm):
+        norm.forward(x, out=y); norm.backward(x, gy)
+    torch.cuda.synchronize()
+    l0 = _lib.lib().moe_debug_launch_count()
+    sampler = ClockSampler(0)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3 * steps)]
+    for i in range(steps):
+        ev[3 * i].record(); norm.forward(x, out=y); ev[3 * i + 1].record(); norm.backward(x, gy); ev[3 * i + 2].record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    launches = _lib.lib().moe_debug_launch_count() - l0
+    fwd = float(np.mean([ev[3 * i].elapsed_time(ev[3 * i + 1]) for i in range(steps)]))
+    bwd = float(np.mean([ev[3 * i + 1].elapsed_time(ev[3 * i + 2]) for i in range(steps)]))
+    tensor = T * d * 2
+    pk = peaks()
+    fb, bb = 2 * tensor / (fwd * 1e-3) / 1e9, 3 * tensor / (bwd * 1e-3) / 1e9
+    line = {"metric": "RMSNorm tokens/s (forward + backward)", "value": T / ((fwd + bwd) * 1e-3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": fwd + bwd, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations, f32 arithmetic", "data": "synthetic",
+            "config": {"workload": w["name"], "l2": "inputs larger than L2 (%.0f MB per tensor)" % (tensor / 1e6)},
+            "clocks": clocks, "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": bb, "peak": pk["hbm"], "unit": "GB/s", "frac": bb / pk["hbm"], "traffic": None,
+                         "note": "backward: x and grad_y read, grad_x written (%.0f MB) / %.3f ms; forward: %.0f MB / %.3f ms = %.0f GB/s = %.2f"
+                                 % (3 * tensor / 1e6, bwd, 2 * tensor / 1e6, fwd, fb, fb / pk["hbm"])}}
+    print(json.dumps(line))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,6 +440,9 @@ def main():
         return
     if w["precision"] == "attn":
         run_decode_attention(args, w)
+        return
+    if w["precision"] == "rmsnorm":
+        run_rmsnorm(args, w)
         return
 
     import torch

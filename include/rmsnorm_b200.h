@@ -3,8 +3,9 @@
  *
  *   y[r, c]  = x[r, c] * inverse_rms(r) * weight[c],   inverse_rms = 1 / sqrt(mean_c(x^2) + eps)
  *   dx[r, c] = dy[r, c] * weight[c] * inverse_rms - x[r, c] * (sum_c dy * weight * x) * inverse_rms^3 / d
- *   dweight[c] += sum_r dy[r, c] * x[r, c] * inverse_rms(r)     (rows summed in tiles of 32, tiles in order:
- *                                                                the reference's fixed order, norm.rs:8-14)
+ *   dweight[c] += sum_r dy[r, c] * x[r, c] * inverse_rms(r)     (rows summed in tiles of 32 in row order, the
+ *                                                                reference's tiles, norm.rs:8-14; tile totals in a
+ *                                                                fixed order: independent of scheduling)
  *
  * Stateless: all pointers are device pointers owned by the caller; activations are f32
  * (MOE_PRECISION_F32) or bf16 (MOE_PRECISION_BF16), weight and its gradient f32.  Status codes are the

@@ -126,36 +126,60 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ weight, co
     load8<float>(weight + c, w);
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int r = 0; r < nrows; ++r) {
-      float v[8], g[8], o[8];
-      load8<T>(x + (size_t)(row0 + r) * d + c, v);
-      load8<T>(gy + (size_t)(row0 + r) * d + c, g);
-      const float inv = s_inv[r], sh = s_shared[r];
+    for (int r0 = 0; r0 < nrows; r0 += 4) {     // four rows' loads in flight, then the rows in order
+      float v[4][8], g[4][8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        o[i] = __fsub_rn(__fmul_rn(__fmul_rn(g[i], w[i]), inv), __fmul_rn(v[i], sh));   // norm.rs:97-98
-        acc[i] = __fadd_rn(acc[i], __fmul_rn(__fmul_rn(g[i], v[i]), inv));               // norm.rs:103
+      for (int u = 0; u < 4; ++u) {
+        const int r = min(r0 + u, nrows - 1);
+        load8<T>(x + (size_t)(row0 + r) * d + c, v[u]);
+        load8<T>(gy + (size_t)(row0 + r) * d + c, g[u]);
       }
-      store8<T>(gx + (size_t)(row0 + r) * d + c, o);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int r = r0 + u;
+        if (r < nrows) {
+          const float inv = s_inv[r], sh = s_shared[r];
+          float o[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            o[i] = __fsub_rn(__fmul_rn(__fmul_rn(g[u][i], w[i]), inv), __fmul_rn(v[u][i], sh));   // norm.rs:97-98
+            acc[i] = __fadd_rn(acc[i], __fmul_rn(__fmul_rn(g[u][i], v[u][i]), inv));               // norm.rs:103
+          }
+          store8<T>(gx + (size_t)(row0 + r) * d + c, o);
+        }
+      }
     }
     if (partial) store8<float>(partial + (size_t)blockIdx.x * d + c, acc);
   }
 }
 
-// grad_weight[c] += partial[0][c]; += partial[1][c]; ...  (norm.rs:113-117: tile by tile, in order)
-__global__ void rmsnorm_wgrad_kernel(const float* __restrict__ partial, float* __restrict__ grad_weight, int tiles, int d) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= d) return;
-  float g = grad_weight[c];
-  for (int t0 = 0; t0 < tiles; t0 += 8) {     // eight independent loads, then the ordered sum
-    float v[8];
+// grad_weight[c] += sum over the tiles of partial[t][c] (norm.rs:113-117).  The tiles are cut into eight
+// consecutive runs, one warp per run and 32 columns per CTA; a run is summed in tile order and the eight
+// run totals are added in run order, so the result does not depend on how the work was scheduled.
+__global__ void __launch_bounds__(256)
+rmsnorm_wgrad_kernel(const float* __restrict__ partial, float* __restrict__ grad_weight, int tiles, int d) {
+  __shared__ float s_run[8][32];
+  const int lane = threadIdx.x & 31, run = threadIdx.x >> 5, c = blockIdx.x * 32 + lane;
+  const int per = ceil_div(tiles, 8), t_lo = run * per, t_hi = min(tiles, t_lo + per);
+  float g = 0.f;
+  if (c < d) {
+    for (int t0 = t_lo; t0 < t_hi; t0 += 8) {     // eight independent loads, then the ordered sum
+      float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = t0 + i < tiles ? partial[(size_t)(t0 + i) * d + c] : 0.f;
+      for (int i = 0; i < 8; ++i) v[i] = t0 + i < t_hi ? partial[(size_t)(t0 + i) * d + c] : 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (t0 + i < tiles) g = __fadd_rn(g, v[i]);
+      for (int i = 0; i < 8; ++i)
+        if (t0 + i < t_hi) g = __fadd_rn(g, v[i]);
+    }
   }
-  grad_weight[c] = g;
+  s_run[run][lane] = g;
+  __syncthreads();
+  if (run == 0 && c < d) {
+    float total = grad_weight[c];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) total = __fadd_rn(total, s_run[r][lane]);
+    grad_weight[c] = total;
+  }
 }
 
 int rn_fail(char* message, int len, int code, const char* text) {
@@ -216,7 +240,7 @@ int32_t rmsnorm_backward(const void* x, const float* weight, const void* grad_y,
     rmsnorm_bwd_kernel<float><<<tiles, RN_THREADS, 0, st>>>((const float*)x, weight, (const float*)grad_y, (float*)grad_x, partial, rows, d, eps);
   count_launch();
   if (grad_weight) {
-    rmsnorm_wgrad_kernel<<<ceil_div(d, 256), 256, 0, st>>>(partial, grad_weight, tiles, d);
+    rmsnorm_wgrad_kernel<<<ceil_div(d, 32), 256, 0, st>>>(partial, grad_weight, tiles, d);
     count_launch();
   }
   const cudaError_t e = cudaGetLastError();
