@@ -153,14 +153,110 @@ rmsnorm_bwd_kernel(const T* __restrict__ x, const float* __restrict__ weight, co
   }
 }
 
-// grad_weight[c] += sum over the tiles of partial[t][c] (norm.rs:113-117).  The tiles are cut into eight
-// consecutive runs, one warp per run and 32 columns per CTA; a run is summed in tile order and the eight
-// run totals are added in run order, so the result does not depend on how the work was scheduled.
-__global__ void __launch_bounds__(256)
+// The same tile in sub-tiles of 8 rows (d <= 2048 NG): phase A and phase B alternate per sub-tile, so what
+// phase B reads again (8 rows of x and grad_y, 128 KB at d 4096 in bf16) is still in L1 / L2 — with whole
+// 32-row tiles the CTAs in flight hold more than L2 and the second read came from HBM (1.02 GB read per
+// launch against 0.54 GB algorithmic).  The partial weight gradient stays in registers across the
+// sub-tiles, rows in order.
+template <typename T, int NG>
+__global__ void __launch_bounds__(RN_THREADS)
+rmsnorm_bwd_sub_kernel(const T* __restrict__ x, const float* __restrict__ weight, const T* __restrict__ gy,
+                       T* __restrict__ gx, float* __restrict__ partial /*[tiles, d] or null*/, int rows, int d, float eps) {
+  constexpr int SUB = RN_THREADS / 32;   // one row per warp in phase A
+  __shared__ float s_inv[SUB], s_shared[SUB];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * RN_TILE, nrows = min(RN_TILE, rows - row0);
+  float w[NG][8], acc[NG][8];
+#pragma unroll
+  for (int n = 0; n < NG; ++n) {
+    const int c = threadIdx.x * 8 + n * RN_THREADS * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { acc[n][i] = 0.f; w[n][i] = 0.f; }
+    if (c < d) load8<float>(weight + c, w[n]);
+  }
+  for (int sub = 0; sub < nrows; sub += SUB) {
+    const int nsub = min(SUB, nrows - sub);
+    if (warp < nsub) {
+      const T* xr = x + (size_t)(row0 + sub + warp) * d;
+      const T* gr = gy + (size_t)(row0 + sub + warp) * d;
+      float ss = 0.f, proj = 0.f;
+      for (int c = lane * 8; c < d; c += 256) {
+        float v[8], g[8], ww[8];
+        load8<T>(xr + c, v);
+        load8<T>(gr + c, g);
+        load8<float>(weight + c, ww);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          ss = fmaf(v[i], v[i], ss);
+          proj = fmaf(g[i] * ww[i], v[i], proj);
+        }
+      }
+      ss = warp_sum(ss);
+      proj = warp_sum(proj);
+      if (lane == 0) {
+        const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+        s_inv[warp] = inv;
+        s_shared[warp] = proj * (inv * inv * inv) / (float)d;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int n = 0; n < NG; ++n) {
+      const int c = threadIdx.x * 8 + n * RN_THREADS * 8;
+      if (c >= d) continue;
+      for (int r0 = 0; r0 < nsub; r0 += 4) {     // four rows' loads in flight, then the rows in order
+        float v[4][8], g[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int r = min(r0 + u, nsub - 1);
+          load8<T>(x + (size_t)(row0 + sub + r) * d + c, v[u]);
+          load8<T>(gy + (size_t)(row0 + sub + r) * d + c, g[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int r = r0 + u;
+          if (r < nsub) {
+            const float inv = s_inv[r], sh = s_shared[r];
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              o[i] = __fsub_rn(__fmul_rn(__fmul_rn(g[u][i], w[n][i]), inv), __fmul_rn(v[u][i], sh));   // norm.rs:97-98
+              acc[n][i] = __fadd_rn(acc[n][i], __fmul_rn(__fmul_rn(g[u][i], v[u][i]), inv));           // norm.rs:103
+            }
+            store8<T>(gx + (size_t)(row0 + sub + r) * d + c, o);
+          }
+        }
+      }
+    }
+    __syncthreads();   // the next sub-tile overwrites s_inv / s_shared
+  }
+  if (partial) {
+#pragma unroll
+    for (int n = 0; n < NG; ++n) {
+      const int c = threadIdx.x * 8 + n * RN_THREADS * 8;
+      if (c < d) store8<float>(partial + (size_t)blockIdx.x * d + c, acc[n]);
+    }
+  }
+}
+
+template <typename T>
+void launch_bwd(const T* x, const float* weight, const T* gy, T* gx, float* partial, int rows, int d, float eps, int tiles,
+                cudaStream_t st) {
+  if (d <= 2048) rmsnorm_bwd_sub_kernel<T, 1><<<tiles, RN_THREADS, 0, st>>>(x, weight, gy, gx, partial, rows, d, eps);
+  else if (d <= 4096) rmsnorm_bwd_sub_kernel<T, 2><<<tiles, RN_THREADS, 0, st>>>(x, weight, gy, gx, partial, rows, d, eps);
+  else if (d <= 8192) rmsnorm_bwd_sub_kernel<T, 4><<<tiles, RN_THREADS, 0, st>>>(x, weight, gy, gx, partial, rows, d, eps);
+  else rmsnorm_bwd_kernel<T><<<tiles, RN_THREADS, 0, st>>>(x, weight, gy, gx, partial, rows, d, eps);
+}
+
+// grad_weight[c] += sum over the tiles of partial[t][c] (norm.rs:113-117).  The tiles are cut into 32
+// consecutive runs, one warp per run and 32 columns per CTA; a run is summed in tile order and the run
+// totals are added in run order, so the result does not depend on how the work was scheduled.
+constexpr int RN_RUNS = 32;
+__global__ void __launch_bounds__(32 * RN_RUNS)
 rmsnorm_wgrad_kernel(const float* __restrict__ partial, float* __restrict__ grad_weight, int tiles, int d) {
-  __shared__ float s_run[8][32];
+  __shared__ float s_run[RN_RUNS][32];
   const int lane = threadIdx.x & 31, run = threadIdx.x >> 5, c = blockIdx.x * 32 + lane;
-  const int per = ceil_div(tiles, 8), t_lo = run * per, t_hi = min(tiles, t_lo + per);
+  const int per = ceil_div(tiles, RN_RUNS), t_lo = run * per, t_hi = min(tiles, t_lo + per);
   float g = 0.f;
   if (c < d) {
     for (int t0 = t_lo; t0 < t_hi; t0 += 8) {     // eight independent loads, then the ordered sum
@@ -177,7 +273,7 @@ rmsnorm_wgrad_kernel(const float* __restrict__ partial, float* __restrict__ grad
   if (run == 0 && c < d) {
     float total = grad_weight[c];
 #pragma unroll
-    for (int r = 0; r < 8; ++r) total = __fadd_rn(total, s_run[r][lane]);
+    for (int r = 0; r < RN_RUNS; ++r) total = __fadd_rn(total, s_run[r][lane]);
     grad_weight[c] = total;
   }
 }
@@ -234,13 +330,11 @@ int32_t rmsnorm_backward(const void* x, const float* weight, const void* grad_y,
   const int tiles = ceil_div(rows, RN_TILE);
   cudaStream_t st = (cudaStream_t)stream;
   float* partial = grad_weight ? (float*)scratch : nullptr;
-  if (precision == MOE_PRECISION_BF16)
-    rmsnorm_bwd_kernel<bf16><<<tiles, RN_THREADS, 0, st>>>((const bf16*)x, weight, (const bf16*)grad_y, (bf16*)grad_x, partial, rows, d, eps);
-  else
-    rmsnorm_bwd_kernel<float><<<tiles, RN_THREADS, 0, st>>>((const float*)x, weight, (const float*)grad_y, (float*)grad_x, partial, rows, d, eps);
+  if (precision == MOE_PRECISION_BF16) launch_bwd<bf16>((const bf16*)x, weight, (const bf16*)grad_y, (bf16*)grad_x, partial, rows, d, eps, tiles, st);
+  else launch_bwd<float>((const float*)x, weight, (const float*)grad_y, (float*)grad_x, partial, rows, d, eps, tiles, st);
   count_launch();
   if (grad_weight) {
-    rmsnorm_wgrad_kernel<<<ceil_div(d, 32), 256, 0, st>>>(partial, grad_weight, tiles, d);
+    rmsnorm_wgrad_kernel<<<ceil_div(d, 32), 32 * RN_RUNS, 0, st>>>(partial, grad_weight, tiles, d);
     count_launch();
   }
   const cudaError_t e = cudaGetLastError();
