@@ -87,6 +87,47 @@ rmsnorm_fwd_kernel(const T* __restrict__ x, const float* __restrict__ weight, T*
   }
 }
 
+// The same with the row held in registers between the two passes (d = 256 NC exactly, bf16): every load
+// of the row is issued before the first use, and x is read once.
+template <int NC>
+__global__ void __launch_bounds__(RN_THREADS, 2)
+rmsnorm_fwd_regs_kernel(const bf16* __restrict__ x, const float* __restrict__ weight, bf16* __restrict__ y, int rows, float eps) {
+  constexpr int d = 256 * NC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (RN_THREADS / 32) + warp;
+  if (row >= rows) return;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * d) + lane;
+  uint4 raw[NC];
+#pragma unroll
+  for (int n = 0; n < NC; ++n) raw[n] = xr[32 * n];
+  float ss = 0.f;
+#pragma unroll
+  for (int n = 0; n < NC; ++n) {
+    const uint32_t w[4] = {raw[n].x, raw[n].y, raw[n].z, raw[n].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float a = __uint_as_float(w[i] << 16), b = __uint_as_float(w[i] & 0xffff0000u);
+      ss = fmaf(a, a, ss);
+      ss = fmaf(b, b, ss);
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)d + eps);       // norm.rs:124-127
+  bf16* yr = y + (size_t)row * d + lane * 8;
+#pragma unroll
+  for (int n = 0; n < NC; ++n) {
+    const uint32_t w[4] = {raw[n].x, raw[n].y, raw[n].z, raw[n].w};
+    float v[8], ww[8];
+    load8<float>(weight + lane * 8 + 256 * n, ww);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16) * inv * ww[2 * i];             // norm.rs:56
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u) * inv * ww[2 * i + 1];
+    }
+    store8<bf16>(yr + 256 * n, v);
+  }
+}
+
 // One CTA per tile of 32 rows.  Phase A (a warp per row): inverse RMS and the shared term
 // projection * inverse_rms^3 / d (norm.rs:88-94).  Phase B (a thread per 8 columns, rows in order):
 // grad_x and the tile's partial weight gradient, summed over the rows in row order (norm.rs:96-104).
@@ -307,7 +348,15 @@ int32_t rmsnorm_forward(const void* x, const float* weight, void* y, int32_t row
   if (rows == 0) return MOE_OK;
   const int grid = ceil_div(rows, RN_THREADS / 32);
   cudaStream_t st = (cudaStream_t)stream;
-  if (precision == MOE_PRECISION_BF16) rmsnorm_fwd_kernel<bf16><<<grid, RN_THREADS, 0, st>>>((const bf16*)x, weight, (bf16*)y, rows, d, eps);
+  const int nc = d % 256 == 0 ? d / 256 : 0;
+  if (precision == MOE_PRECISION_BF16 && (nc == 2 || nc == 4 || nc == 8 || nc == 16)) {
+    const bf16* xb = (const bf16*)x;
+    bf16* yb = (bf16*)y;
+    if (nc == 2) rmsnorm_fwd_regs_kernel<2><<<grid, RN_THREADS, 0, st>>>(xb, weight, yb, rows, eps);
+    else if (nc == 4) rmsnorm_fwd_regs_kernel<4><<<grid, RN_THREADS, 0, st>>>(xb, weight, yb, rows, eps);
+    else if (nc == 8) rmsnorm_fwd_regs_kernel<8><<<grid, RN_THREADS, 0, st>>>(xb, weight, yb, rows, eps);
+    else rmsnorm_fwd_regs_kernel<16><<<grid, RN_THREADS, 0, st>>>(xb, weight, yb, rows, eps);
+  } else if (precision == MOE_PRECISION_BF16) rmsnorm_fwd_kernel<bf16><<<grid, RN_THREADS, 0, st>>>((const bf16*)x, weight, (bf16*)y, rows, d, eps);
   else rmsnorm_fwd_kernel<float><<<grid, RN_THREADS, 0, st>>>((const float*)x, weight, (float*)y, rows, d, eps);
   count_launch();
   const cudaError_t e = cudaGetLastError();
