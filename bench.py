@@ -45,7 +45,7 @@ WORKLOADS = {
     # the normalisation in front of the layer, on cfg 4's activations (268 MB per tensor in bf16: larger than L2)
     "rmsnorm": dict(T=32768, d=4096, precision="rmsnorm", seed=2024,
                     name="RMSNorm forward + backward bf16: 32768 tokens, d_model 4096"),
-    # BASELINE config 2 is a whole-model train_step; only its MoE layers are on this path.  One of its
+    # The 55M language model workload is a whole-model train_step; only its MoE layers are on this path.  One of its
     # six MoE blocks (layers 2..7: 8 experts top-2, expert d_ff 352 + shared, 8 x 1024 tokens), forward +
     # backward + Adam, bf16 GEMMs over f32 master weights.
     "cfg2": dict(T=8192, d=512, E=8, k=2, F=352, shared=True, seed=42, precision="bf16", zipf=False, adam=True,
@@ -238,7 +238,7 @@ def run_reference(args, w):
 
 
 def run_decode(args, w):
-    """BASELINE config 5: latency of one quantized MoE layer on a decode-sized batch (p50 over graph replays)."""
+    """Latency of one quantized MoE layer on a decode-sized batch (p50 over graph replays)."""
     import torch
     from rustingbrain_b200 import MoeConfig, MoeLayer, _lib
     dev = torch.device("cuda", 0)

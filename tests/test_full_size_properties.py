@@ -1,4 +1,4 @@
-"""BASELINE configurations 3 (16384 tokens, d_model 2048, 64 experts top-8 + shared, d_ff 1408,
+"""Benchmark configurations 3 (16384 tokens, d_model 2048, 64 experts top-8 + shared, d_ff 1408,
 Zipf-like router bias) and 4 (one rank's 32768 tokens, d_model 4096, 64 experts top-8, d_ff 1536,
 uniform expected load) at their full sizes in bf16, checked through properties that do not need the
 CPU checker to run the whole batch:

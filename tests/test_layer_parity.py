@@ -93,7 +93,7 @@ def test_unrouted_experts_get_exactly_zero_gradient():  # moe.rs:861-893
 
 
 def test_f32_config1_forward():
-    """BASELINE config 1: 2048 tokens, d 512, 8 experts top-2, F 1408, no shared expert, N(0,0.02) seed 42 / N(0,1) seed 7."""
+    """Benchmark configuration 1: 2048 tokens, d 512, 8 experts top-2, F 1408, no shared expert, N(0,0.02) seed 42 / N(0,1) seed 7."""
     T, d, E, k, F = 2048, 512, 8, 2, 1408
     dev, ora, _ = make_pair(d, E, k, F, False, seed=42, precision="f32", max_tokens=T, training=False)
     x = np.random.Generator(np.random.Philox(7)).standard_normal((T, d)).astype(np.float32)

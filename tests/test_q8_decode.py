@@ -19,7 +19,7 @@ def _pair(T, d, E, k, F, shared, seed):
     ora.set_weight(ROUTER, 0, router)
 
     def put(which, expert, rows, cols):
-        q = g.integers(-127, 128, (rows, cols)).astype(np.int8)      # BASELINE config 5: uniform in [-127, 127]
+        q = g.integers(-127, 128, (rows, cols)).astype(np.int8)      # benchmark configuration 5: uniform in [-127, 127]
         s = g.uniform(1e-3, 4e-3, rows).astype(np.float32)           # scales uniform in [1e-3, 4e-3]
         dev.set_weight_q8(which, expert, q, s)
         ora.set_weight_q8(which, expert, q, s)
@@ -32,7 +32,7 @@ def _pair(T, d, E, k, F, shared, seed):
     return dev, ora, x
 
 
-@pytest.mark.parametrize("T,d,E,k,F,shared", [(64, 1024, 16, 2, 2816, True),   # BASELINE config 5
+@pytest.mark.parametrize("T,d,E,k,F,shared", [(64, 1024, 16, 2, 2816, True),   # benchmark configuration 5
                                               (200, 128, 4, 2, 96, True),      # many rows per expert, padded d_ff
                                               (5, 64, 8, 1, 64, False)])       # most experts empty
 def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
