@@ -50,3 +50,30 @@ def test_create_fails_closed_without_a_device():  # lib.rs:72-76: never a silent
     h = C.c_void_p()
     rc = _lib.lib().moe_create(C.byref(_cfg()), C.byref(h))
     assert rc != _lib.OK
+
+
+def test_rmsnorm_and_kv_cache_arguments_are_checked_before_any_device_work():
+    L = _lib.lib()
+    msg = C.create_string_buffer(128)
+    assert L.rmsnorm_scratch_bytes(70, 64) == 3 * 64 * 4          # three tiles of 32 rows (norm.rs:14)
+    assert L.rmsnorm_scratch_bytes(0, 64) == 0
+    assert L.rmsnorm_forward(None, None, None, 4, 64, 1e-6, _lib.PRECISION_F32, None, msg, 128) == _lib.INVALID_INPUT
+    assert b"null" in msg.value
+    buf = (C.c_float * 64)()
+    p = C.cast(buf, C.c_void_p)
+    assert L.rmsnorm_forward(p, p, p, 1, 12, 1e-6, _lib.PRECISION_F32, None, msg, 128) == _lib.UNSUPPORTED
+    assert L.rmsnorm_forward(p, p, p, 1, 16, 1e-6, 7, None, msg, 128) == _lib.INVALID_CONFIG
+    for bad in (dict(num_heads=3, kv_heads=2), dict(kv_heads=8), dict(head_dim=7), dict(sequences=0),
+                dict(capacity=64, max_seq_len=32), dict(precision=_lib.PRECISION_Q8)):      # attention.rs:173-186, rope.rs:72-76
+        kw = dict(sequences=2, num_heads=4, kv_heads=2, head_dim=8, capacity=16, max_seq_len=16, rope_base=10000.0, rope=1,
+                  precision=_lib.PRECISION_F32, device=0)
+        kw.update(bad)
+        h = C.c_void_p()
+        assert L.kv_cache_create(C.byref(_lib.KvCacheConfigC(**kw)), C.byref(h)) == _lib.INVALID_CONFIG, bad
+        assert L.kv_cache_last_error(h)
+        L.kv_cache_destroy(h)
+    h = C.c_void_p()
+    kw = dict(sequences=2, num_heads=4, kv_heads=2, head_dim=6, capacity=16, max_seq_len=16, rope_base=10000.0, rope=1,
+              precision=_lib.PRECISION_F32, device=0)
+    assert L.kv_cache_create(C.byref(_lib.KvCacheConfigC(**kw)), C.byref(h)) == _lib.UNSUPPORTED   # even, but no kernel
+    L.kv_cache_destroy(h)
