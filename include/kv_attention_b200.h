@@ -49,7 +49,11 @@ int32_t kv_cache_clear(kv_cache_t* cache, int32_t sequence, void* stream);
 /* KvCache::len of every sequence into host memory (read from the device; synchronises the stream).
  * The capacity checks of the calls below use a host copy of the lengths that every call keeps up to
  * date; a step replayed from a captured CUDA graph advances the device lengths only, and this call
- * brings the host copy back in line (the caller of a graph keeps within capacity itself). */
+ * brings the host copy back in line.  A replayed step that no longer fits is caught on the device: for a
+ * sequence whose cache cannot take the step's rows the kernels store nothing, leave its length alone, write
+ * zeros as its merged heads and mark it; the other sequences of the call proceed.  This call reports such a
+ * mark as MOE_INVALID_INPUT ("SequenceTooLong", attention.rs:364-371) once and clears it; kv_cache_clear /
+ * kv_cache_truncate of the sequence clear it too. */
 int32_t kv_cache_lengths(kv_cache_t* cache, int32_t* lengths_host, void* stream);
 
 /* forward_cached without the projections, for sequences first_sequence .. first_sequence + n_sequences - 1

@@ -192,7 +192,10 @@ int32_t moe_ep_plan(const int32_t* counts_all, int32_t ranks, int32_t num_expert
  * device looks up the array's device address (cudaGetSymbolAddress); make that call before any
  * stream capture begins.  All calls on one device share the array: two calls that overlap on the GPU
  * (different streams, no dependency) race on it.  Nothing in it has to be cleared between calls,
- * because each call writes every word it later reads.  `message` (optional) receives the error text. */
+ * because each call writes every word it later reads.  Host side: the entry is not thread safe in the
+ * sense above (callers serialise their launches); the one piece of host state, the per-device table of the
+ * array's address, is written without a lock, which is harmless because every thread that fills an entry
+ * stores the same value.  `message` (optional) receives the error text. */
 #define MOE_ROUTE_NOALLOC_MAX_TOKENS 16384
 #define MOE_ROUTE_NOALLOC_MAX_EXPERTS 64
 int32_t moe_route_noalloc(const float* logits_dev, const uint8_t* valid_dev, int32_t tokens, int32_t num_experts,

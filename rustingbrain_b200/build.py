@@ -21,7 +21,8 @@ def sources():
 
 def _newest_header():
     hdrs = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inc"))]
-    hdrs.append(os.path.join(HERE, "..", "include", "moe_b200.h"))
+    inc = os.path.join(HERE, "..", "include")
+    hdrs += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]   # every public header is part of the ABI
     return max(os.path.getmtime(h) for h in hdrs if os.path.exists(h))
 
 

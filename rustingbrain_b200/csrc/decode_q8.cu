@@ -46,9 +46,14 @@ __device__ __forceinline__ void mma_f16_16816(float* c, uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// bf16 reaches 3.4e38, f16 ends at 65504: an activation beyond that SATURATES to +-65504 here instead of
+// becoming an infinity (a NaN stays a NaN).  A normalised transformer's activations are orders of magnitude
+// below the limit, so the clamp changes no result that was finite before; it keeps one outlier from turning
+// a whole output row into inf / NaN.
+__device__ __forceinline__ float clamp_f16_range(float x) { return fabsf(x) > 65504.f ? copysignf(65504.f, x) : x; }
 __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
   const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&v);
-  const __half2 h = __floats2half2_rn(__low2float(b), __high2float(b));
+  const __half2 h = __floats2half2_rn(clamp_f16_range(__low2float(b)), clamp_f16_range(__high2float(b)));
   return *reinterpret_cast<const uint32_t*>(&h);
 }
 

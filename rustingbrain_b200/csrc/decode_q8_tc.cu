@@ -381,7 +381,11 @@ q8_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant
           uint32_t* w = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            const __half2 h = __float22half2_rn(__bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[c])));
+            float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[c]));
+            // saturate at the end of the f16 range instead of overflowing to infinity (as the mma.sync kernel does)
+            f.x = fabsf(f.x) > 65504.f ? copysignf(65504.f, f.x) : f.x;
+            f.y = fabsf(f.y) > 65504.f ? copysignf(65504.f, f.y) : f.y;
+            const __half2 h = __float22half2_rn(f);
             w[c] = *reinterpret_cast<const uint32_t*>(&h);
           }
           bt[i] = v;

@@ -27,18 +27,7 @@
 namespace moe {
 namespace tc {
 
-// Build-time knobs for timing experiments (never defined in the shipped library):
-//   TC_STAGES / TC_PAIR_STAGES  depth of the operand ring;
-//   TC_EXP_NOEPI   skip the epilogue, TC_EXP_NOLOAD skip the TMA loads (the MMAs run on whatever is
-//   in shared memory), TC_EXP_NOMMA skip the MMAs (the ring is filled and released).  The last three
-//   isolate one part of the mainloop; their results are meaningless, only their duration is.
-#ifndef TC_STAGES
-#define TC_STAGES 4
-#endif
-#ifndef TC_PAIR_STAGES
-#define TC_PAIR_STAGES 6
-#endif
-constexpr int STAGES = TC_STAGES;
+constexpr int STAGES = 4;          // depth of the operand ring (one-SM tiles)
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;           // 16 KiB
 constexpr int B_BYTES = BN * BK * 2;           // 32 KiB
@@ -313,9 +302,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
                                               bool have_acc, uint8_t* stg) {
   const int lane = row_in_tile & 31;
   const long long wrow = (long long)tl.row0 + (row_in_tile & ~31);   // first row of this warp
-#ifdef TC_EXP_NOEPI
-  return;
-#endif
   if (EPI == EPI_STORE) {
     bf16* out = (bf16*)p.out0 + wrow * p.ld0;
 #pragma unroll 1
@@ -458,9 +444,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-#ifdef TC_EXP_NOLOAD
-          break;
-#endif
           if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101)) { ok = false; break; }
           const uint32_t bar = smem_u32(&st->full[stage]);
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -508,13 +491,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
         const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-#ifndef TC_EXP_NOLOAD
           if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103)) { ok = false; break; }
-#endif
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
-#ifndef TC_EXP_NOMMA
 #pragma unroll
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = make_desc(sa + kk * a_adv, a_lbo, a_sbo);
@@ -522,18 +502,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             umma_bf16(d_tmem, da, db, idesc, (ki | kk) != 0 ? 1u : 0u);
           }
           umma_commit(smem_u32(&st->empty[stage]));   // frees the stage once these MMAs have read it
-#else
-          mbar_arrive(smem_u32(&st->empty[stage]));
-#endif
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-#ifdef TC_EXP_NOMMA
-        mbar_arrive(smem_u32(&st->tmem_full[acc]));
-#else
         if (tl.k_iters > 0) umma_commit(smem_u32(&st->tmem_full[acc]));
         else mbar_arrive(smem_u32(&st->tmem_full[acc]));   // empty group: nothing was accumulated
-#endif
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok) st->dead = 1;
@@ -592,7 +565,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 //   tmem_full[a] (each CTA)  one tcgen05.commit per CTA after the tile's last MMA
 //   tmem_empty[a](leader's)  one arrival per epilogue warp of both CTAs
 // ---------------------------------------------------------------------------
-constexpr int P_STAGES = TC_PAIR_STAGES;
+constexpr int P_STAGES = 6;
 constexpr int P_B_BYTES = (BN / 2) * BK * 2;            // 16 KiB: this CTA's half of B
 constexpr int P_STAGE_BYTES = A_BYTES + P_B_BYTES;      // 32 KiB
 
@@ -919,16 +892,26 @@ bool pair_mode() {
   return g_pair_mode == 1;
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel:
+// one flag per device, so a process that holds layers on several GPUs configures each of them.
+constexpr int MAX_DEVICES = 64;
+template <typename Kernel>
+static cudaError_t opt_in_smem(Kernel kern, bool* configured, int bytes) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev >= 0 && dev < MAX_DEVICES && configured[dev]) return cudaSuccess;
+  e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess && dev >= 0 && dev < MAX_DEVICES) configured[dev] = true;
+  return e;
+}
+
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
 static cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
                                cudaStream_t stream) {
   auto kern = grouped_gemm_pair_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, P_SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static bool configured[MAX_DEVICES] = {};
+  { const cudaError_t e = opt_in_smem(kern, configured, P_SMEM_BYTES); if (e != cudaSuccess) return e; }
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)(sm_count & ~1));
   cfg.blockDim = dim3(NUM_THREADS);
@@ -949,12 +932,8 @@ static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const Ge
                           cudaStream_t stream) {
   if (pair_mode()) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
   auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static bool configured[MAX_DEVICES] = {};
+  { const cudaError_t e = opt_in_smem(kern, configured, SMEM_BYTES); if (e != cudaSuccess) return e; }
   kern<<<sm_count, NUM_THREADS, SMEM_BYTES, stream>>>(ma, mb, args); count_launch();
   return cudaGetLastError();
 }

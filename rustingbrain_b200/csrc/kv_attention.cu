@@ -85,6 +85,7 @@ __global__ void kv_append_kernel(T* __restrict__ q, const T* __restrict__ k, con
                                  T* __restrict__ keys, T* __restrict__ values, const int* __restrict__ lengths,
                                  const float* __restrict__ cos_t, const float* __restrict__ sin_t, KvShape s, int rope) {
   const int row = blockIdx.x, seq = s.first + row / s.rows, i = row % s.rows;
+  if (lengths[seq] + s.rows > s.cap) return;   // no room (reported by the attention kernel): nothing is stored
   const int pos = lengths[seq] + i, half = s.HD / 2;
   const float* ct = cos_t + (size_t)pos * half;
   const float* st = sin_t + (size_t)pos * half;
@@ -129,13 +130,18 @@ __global__ void kv_append_kernel(T* __restrict__ q, const T* __restrict__ k, con
 template <typename T, int HD>
 __global__ void __launch_bounds__(KV_THREADS)
 kv_partial_kernel(const T* __restrict__ q, const T* __restrict__ keys, const T* __restrict__ values,
-                  const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2) {
+                  const int* __restrict__ lengths, int* __restrict__ full, float* __restrict__ part, KvShape s, int splits,
+                  float scale_log2) {
   constexpr int LPK = HD / 8, KPW = 32 / LPK, NG = KV_WARPS * KPW, PW = HD + 2;
   constexpr int SLOT = 8 * (int)sizeof(T), DEPTH = KvRing<T>::DEPTH;
   extern __shared__ __align__(16) float kv_sm[];   // the copy ring, then [KV_QT][NG][PW] for the merge
   const int split = blockIdx.x, kvh = blockIdx.y, sj = blockIdx.z, seq = s.first + sj;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane / LPK, ls = lane % LPK;
   const int len0 = lengths[seq], total = len0 + s.rows;
+  if (total > s.cap) {   // the cache of this sequence has no room for the step: mark it, touch nothing
+    if (threadIdx.x == 0) full[seq] = 1;
+    return;
+  }
   const int chunk = round_up(ceil_div(total, splits), NG);
   const int k0 = split * chunk, k1 = min(total, k0 + chunk);
   const int group = s.H / s.Hkv, nq = s.rows * group, W = s.Hkv * s.HD;
@@ -290,14 +296,18 @@ template <int HD>
 __global__ void __launch_bounds__(TC_WARPS * 32)
 kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ knew, const bf16* __restrict__ vnew,
                      bf16* keys, bf16* values, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
-                     const int* __restrict__ lengths, float* __restrict__ part, KvShape s, int splits, float scale_log2,
-                     int rope) {
+                     const int* __restrict__ lengths, int* __restrict__ full, float* __restrict__ part, KvShape s,
+                     int splits, float scale_log2, int rope) {
   constexpr int RB = HD * 2, TILE = TC_KB * RB, CPR = HD / 8, PW = HD + 2, KT = HD / 16, NT = HD / 8;
   constexpr int COPIES = TC_KB * CPR / 32;    // 16-byte chunks per lane and tile
   extern __shared__ __align__(128) unsigned char tc_sm[];
   const int split = blockIdx.x, kvh = blockIdx.y, sj = blockIdx.z, seq = s.first + sj;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
   const int len0 = lengths[seq], total = len0 + s.rows;
+  if (total > s.cap) {   // no room for the step: mark the sequence; nothing is appended, read or advanced
+    if (threadIdx.x == 0) full[seq] = 1;
+    return;
+  }
   const int chunk = round_up(ceil_div(total, splits), TC_WARPS * TC_KB);
   const int k0 = split * chunk, k1 = min(total, k0 + chunk);
   const int group = s.H / s.Hkv, nq = s.rows * group, W = s.Hkv * s.HD;
@@ -496,9 +506,15 @@ kv_partial_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ knew, 
 // ---- merge the slices, write the merged heads, advance the cache lengths ----
 template <typename T>
 __global__ void kv_merge_kernel(const float* __restrict__ part, T* __restrict__ merged, int* __restrict__ lengths,
-                                KvShape s, int splits) {
+                                const int* __restrict__ full, KvShape s, int splits) {
   const int PW = s.HD + 2;
   const int rh = blockIdx.x;                      // row * H + head
+  if (full[s.first + rh / s.H / s.rows]) {
+    // the attention kernel found this sequence's cache full: zeros out, length unchanged; the mark stays
+    // until the host reads it (kv_cache_lengths) or the sequence is truncated
+    for (int c = threadIdx.x; c < s.HD; c += blockDim.x) merged[(size_t)rh * s.HD + c] = from_f32<T>(0.f);
+    return;
+  }
   const float* src = part + (size_t)rh * splits * PW;
   float mx = -INFINITY;
   for (int p = 0; p < splits; ++p) mx = fmaxf(mx, src[p * PW + s.HD]);
@@ -516,9 +532,9 @@ __global__ void kv_merge_kernel(const float* __restrict__ part, T* __restrict__ 
   if (head == 0 && row % s.rows == 0 && threadIdx.x == 0) lengths[s.first + row / s.rows] += s.rows;
 }
 
-__global__ void kv_set_lengths_kernel(int* lengths, int first, int count, int value) {
+__global__ void kv_set_lengths_kernel(int* lengths, int* full, int first, int count, int value) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i < count) lengths[first + i] = value;
+  if (i < count) { lengths[first + i] = value; full[first + i] = 0; }
 }
 
 template <typename T>
@@ -537,6 +553,8 @@ struct kv_cache {
   void* keys = nullptr;
   void* values = nullptr;
   int* lengths = nullptr;           // device, one per sequence
+  int* full = nullptr;              // device, one per sequence: set by a step that found no room (a replayed graph can get there)
+  std::vector<int> host_full;
   std::vector<int> host_len;        // mirror: every change goes through this object
   float* cos_t = nullptr;
   float* sin_t = nullptr;
@@ -580,14 +598,16 @@ template <int HD>
 cudaError_t launch_partial_tc(const kv_cache* c, const bf16* q, const bf16* k, const bf16* v, KvShape s, int n_seq,
                               int splits, float scale_log2, cudaStream_t st) {
   const size_t smem = std::max((size_t)TC_WARPS * TC_DEPTH * 2 * TC_KB * HD * 2, sizeof(float) * 16 * TC_WARPS * (HD + 2));
-  static bool configured = false;
-  if (!configured && smem > 48 * 1024) {
+  // the opt-in is an attribute of the kernel on the CURRENT device: one flag per device
+  static bool configured[64] = {};
+  const int dev = c->cfg.device;
+  if (smem > 48 * 1024 && !(dev >= 0 && dev < 64 && configured[dev])) {
     cudaError_t e = cudaFuncSetAttribute(kv_partial_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   kv_partial_tc_kernel<HD><<<dim3(splits, s.Hkv, n_seq), TC_WARPS * 32, smem, st>>>(
-      q, k, v, (bf16*)c->keys, (bf16*)c->values, c->cos_t, c->sin_t, c->lengths, c->part, s, splits, scale_log2, c->cfg.rope);
+      q, k, v, (bf16*)c->keys, (bf16*)c->values, c->cos_t, c->sin_t, c->lengths, c->full, c->part, s, splits, scale_log2, c->cfg.rope);
   count_launch();
   return cudaGetLastError();
 }
@@ -610,7 +630,8 @@ cudaError_t launch_partial(const kv_cache* c, const T* q, const T* k, const T* v
     const size_t smem = std::max(sizeof(float) * KV_QT * (KV_WARPS * (32 / (HDV / 8))) * (HDV + 2),          \
                                  (size_t)KvRing<T>::DEPTH * 2 * KV_THREADS * 8 * sizeof(T));                 \
     kv_partial_kernel<T, HDV><<<grid, KV_THREADS, smem, st>>>(q, (const T*)c->keys, (const T*)c->values,     \
-                                                               c->lengths, c->part, s, splits, scale_log2);  \
+                                                               c->lengths, c->full, c->part, s, splits,      \
+                                                               scale_log2);                                  \
     break;                                                                                                   \
   }
   switch (s.HD) {
@@ -636,6 +657,11 @@ int forward_t(kv_cache* c, int first, int n_seq, void* q, const void* k, const v
   if (const char* v = getenv("KV_B200_SPLITS")) splits = std::max(1, std::min(KV_MAX_SPLITS, atoi(v)));   // experiments
   const size_t need = (size_t)n_seq * rows * g.num_heads * splits * (g.head_dim + 2);
   if (need > c->part_floats) {
+    // Only a prefill (several rows per sequence) gets here: the buffer made at creation holds a decode step
+    // of every sequence at the largest slice count.  Growing allocates, which a capturing stream may not do.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) == cudaSuccess && cap != cudaStreamCaptureStatusNone)
+      return kv_fail(c, MOE_UNSUPPORTED, "Unsupported: this step needs a larger slice buffer (%zu floats); run it once outside stream capture", need);
     if (c->part) { KCK(cudaStreamSynchronize(st)); cudaFree(c->part); c->part = nullptr; c->part_floats = 0; }
     if (cudaMalloc(&c->part, need * sizeof(float)) != cudaSuccess) {
       cudaGetLastError();
@@ -651,7 +677,7 @@ int forward_t(kv_cache* c, int first, int n_seq, void* q, const void* k, const v
   }
   KCK(launch_partial<T>(c, (const T*)q, (const T*)k, (const T*)v, s, n_seq, splits, st));
   kv_merge_kernel<T><<<n_seq * rows * g.num_heads, std::min(256, std::max(32, g.head_dim)), 0, st>>>(
-      c->part, (T*)merged, c->lengths, s, splits);
+      c->part, (T*)merged, c->lengths, c->full, s, splits);
   count_launch();
   KCK(cudaGetLastError());
   for (int i = 0; i < n_seq; ++i) c->host_len[first + i] += rows;
@@ -691,7 +717,18 @@ int32_t kv_cache_create(const kv_cache_config_t* config, kv_cache_t** out) {
   }
   KCK(cudaMalloc(&c->lengths, sizeof(int) * g.sequences));
   KCK(cudaMemset(c->lengths, 0, sizeof(int) * g.sequences));
+  KCK(cudaMalloc(&c->full, sizeof(int) * g.sequences));
+  KCK(cudaMemset(c->full, 0, sizeof(int) * g.sequences));
   c->host_len.assign(g.sequences, 0);
+  c->host_full.assign(g.sequences, 0);
+  // slice results of one decode step (one row per sequence) at the largest slice count, so that a serving
+  // loop never allocates; a prefill with more rows grows it once
+  c->part_floats = (size_t)g.sequences * g.num_heads * KV_MAX_SPLITS * (g.head_dim + 2);
+  if (cudaMalloc(&c->part, c->part_floats * sizeof(float)) != cudaSuccess) {
+    cudaGetLastError();
+    c->part = nullptr; c->part_floats = 0;
+    return kv_fail(c, MOE_OUT_OF_MEMORY, "OutOfMemory: slice results");
+  }
   // the tables of Rope::new (rope.rs:77-90), in f32 arithmetic like the reference
   const int half = g.head_dim / 2;
   std::vector<float> co((size_t)g.max_seq_len * half), si((size_t)g.max_seq_len * half);
@@ -712,7 +749,7 @@ int32_t kv_cache_create(const kv_cache_config_t* config, kv_cache_t** out) {
 
 void kv_cache_destroy(kv_cache_t* c) {
   if (!c) return;
-  cudaFree(c->keys); cudaFree(c->values); cudaFree(c->lengths); cudaFree(c->cos_t); cudaFree(c->sin_t);
+  cudaFree(c->keys); cudaFree(c->values); cudaFree(c->lengths); cudaFree(c->full); cudaFree(c->cos_t); cudaFree(c->sin_t);
   cudaFree(c->part); cudaFree(c->read_buf);
   delete c;
 }
@@ -727,7 +764,7 @@ int32_t kv_cache_truncate(kv_cache_t* c, int32_t sequence, int32_t length, void*
   for (int i = 0; i < count; ++i)
     if (c->host_len[first + i] < length)
       return kv_fail(c, MOE_INVALID_INPUT, "InvalidInput: sequence %d holds %d positions, cannot keep %d", first + i, c->host_len[first + i], length);
-  kv_set_lengths_kernel<<<ceil_div(count, 256), 256, 0, (cudaStream_t)stream>>>(c->lengths, first, count, length);
+  kv_set_lengths_kernel<<<ceil_div(count, 256), 256, 0, (cudaStream_t)stream>>>(c->lengths, c->full, first, count, length);
   count_launch();
   KCK(cudaGetLastError());
   for (int i = 0; i < count; ++i) c->host_len[first + i] = length;
@@ -739,9 +776,19 @@ int32_t kv_cache_clear(kv_cache_t* c, int32_t sequence, void* stream) { return k
 int32_t kv_cache_lengths(kv_cache_t* c, int32_t* lengths_host, void* stream) {
   if (!c || !lengths_host) return MOE_INVALID_INPUT;
   KCK(cudaMemcpyAsync(lengths_host, c->lengths, sizeof(int) * c->cfg.sequences, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  KCK(cudaMemcpyAsync(c->host_full.data(), c->full, sizeof(int) * c->cfg.sequences, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   KCK(cudaStreamSynchronize((cudaStream_t)stream));
   // the device is the truth: a step replayed from a CUDA graph advances it without passing through here
   for (int i = 0; i < c->cfg.sequences; ++i) c->host_len[i] = lengths_host[i];
+  // ... and such a step can run into the end of a cache, which only the device sees: the kernels then leave the
+  // cache, the lengths and the tables alone and mark the sequence; the mark is reported and cleared here
+  for (int i = 0; i < c->cfg.sequences; ++i)
+    if (c->host_full[i]) {
+      KCK(cudaMemsetAsync(c->full, 0, sizeof(int) * c->cfg.sequences, (cudaStream_t)stream));
+      KCK(cudaStreamSynchronize((cudaStream_t)stream));
+      return kv_fail(c, MOE_INVALID_INPUT, "SequenceTooLong: a step found the cache of sequence %d full at length %d of %d; the step was skipped for it (output zeros, nothing stored)",
+                     i, c->host_len[i], c->cfg.capacity);
+    }
   return MOE_OK;
 }
 

@@ -909,8 +909,12 @@ int32_t moe_set_weight_f32(moe_layer_t* L, int32_t which, int32_t expert, const 
   int rc = slot_of_weight(L, which, expert, &s);
   if (rc != MOE_OK) { L->status = MOE_OK; return rc; }
   if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  if (!src) { L->err = "InvalidInput: null weight pointer"; return MOE_INVALID_INPUT; }
   const long long n = (long long)rows * cols;
   const float* dev_src = src;
+  // the pack kernel runs on the default stream: wait for passes or optimizer steps still in flight on the
+  // caller's (possibly non-blocking) streams before the arenas are rewritten under them
+  CK(cudaDeviceSynchronize());
   if (!is_device_pointer(src)) {
     CK(cudaMemcpy(L->stage, src, (size_t)n * 4, cudaMemcpyHostToDevice));
     dev_src = L->stage;
@@ -929,9 +933,11 @@ static int read_arena(moe_layer* L, const float* arena, int which, int expert, f
   if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
   if (!arena) { L->err = "InvalidConfig: the handle holds no such buffer (training = 0 or quantized)"; return MOE_INVALID_CONFIG; }
   const long long n = (long long)rows * cols;
+  if (!dst) { L->err = "InvalidInput: null destination pointer"; return MOE_INVALID_INPUT; }
   const bool dev = is_device_pointer(dst);
   float* out = dev ? dst : L->stage;
   if (L->side_pending) { CK(cudaStreamSynchronize(L->side_stream)); L->side_pending = false; }   // deferred weight gradients
+  CK(cudaDeviceSynchronize());   // the unpack kernel runs on the default stream: see what every stream has written
   unpack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(arena + s.offset, out, rows, cols, s.ld, s.kind, zero ? 1 : 0); count_launch();
   CK(cudaGetLastError());
   if (!dev) CK(cudaMemcpy(dst, L->stage, (size_t)n * 4, cudaMemcpyDeviceToHost));
@@ -961,7 +967,9 @@ int32_t moe_set_moments_f32(moe_layer_t* L, int32_t which, int32_t expert, const
   int rc = slot_of_weight(L, which, expert, &s);
   if (rc != MOE_OK) { L->status = MOE_OK; return rc; }
   if (rows != s.rows || cols != s.cols) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+  if (!m || !v) { L->err = "InvalidInput: null moment pointer"; return MOE_INVALID_INPUT; }
   const long long n = (long long)rows * cols;
+  CK(cudaDeviceSynchronize());   // an optimizer step may still be running on a non-blocking stream
   const float* srcs[2] = {m, v};
   float* dsts[2] = {L->m, L->v};
   for (int i = 0; i < 2; ++i) {
@@ -997,6 +1005,7 @@ int32_t moe_set_weight_q8(moe_layer_t* L, int32_t which, int32_t expert, const i
   const long long n = (long long)rows * cols;
   int8_t* qs = reinterpret_cast<int8_t*>(L->stage);
   float* ss = L->stage + L->stage_elems;   // second half of the staging buffer
+  CK(cudaDeviceSynchronize());   // a decode step may still be reading the weights on a non-blocking stream
   CK(cudaMemcpy(qs, q, (size_t)n, is_device_pointer(q) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
   CK(cudaMemcpy(ss, scale, (size_t)rows * 4, is_device_pointer(scale) ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
   int8_t* dst = down ? L->q_d + (long long)group * d * Fp : L->q_gu + (long long)group * 2 * Fp * d;

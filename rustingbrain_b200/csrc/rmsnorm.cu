@@ -2,8 +2,12 @@
 //
 // Both directions are bound by HBM: forward reads x and writes y once; backward reads x and grad_y,
 // writes grad_x, and leaves one partial weight gradient per tile of 32 rows (the reference's
-// ROWS_PER_TILE, norm.rs:14), which a second small kernel adds to the gradient tile by tile so that the
-// sum has the reference's fixed order.  Arithmetic is f32 whatever the activation type.
+// ROWS_PER_TILE, norm.rs:14).  A second small kernel adds the tile partials to the gradient: the tiles are
+// cut into 32 consecutive runs, each run is summed in tile order, and the run totals are added in run order.
+// That order is fixed (scheduling cannot change it, two runs of the same input are bit-equal) but its
+// association differs from the reference's single tile-by-tile chain (norm.rs:113-117), so the weight
+// gradient matches the reference to f32 rounding, not bit for bit.  Arithmetic is f32 whatever the
+// activation type.
 
 #include <cstdio>
 #include <cstring>

@@ -131,3 +131,48 @@ def test_without_rotation_and_errors():
         kw.update(bad)
         with pytest.raises(InvalidConfig):                               # attention.rs:173-186, rope.rs:72-76
             KvCache(**kw)
+
+
+@pytest.mark.parametrize("precision,hd", [("bf16", 64), ("f32", 32)])
+def test_a_replayed_step_that_runs_into_the_end_of_a_cache_is_skipped_not_written(precision, hd):
+    """A step replayed from a CUDA graph advances the device lengths only, so only the device can see
+    a replay that no longer fits.  The kernels then store nothing, leave the length alone, return zeros
+    for that sequence and mark it; kv_cache_lengths reports the mark as SequenceTooLong and clears it.
+    The other sequence of the cache keeps stepping and its rows are untouched by the skipped one."""
+    from rustingbrain_b200 import InvalidInput
+    S, H, Hkv, cap = 2, 4, 2, 8
+    dt = torch.bfloat16 if precision == "bf16" else torch.float32
+    cache = KvCache(S, H, Hkv, hd, capacity=cap, precision=precision)
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    rnd = lambda *shape: torch.randn(*shape, device="cuda", generator=gen).to(dt)
+    # sequence 0 starts with 5 positions, sequence 1 with 2
+    cache.forward_cached(rnd(5, H * hd), rnd(5, Hkv * hd), rnd(5, Hkv * hd), rows_per_sequence=5, first_sequence=0, n_sequences=1)
+    cache.forward_cached(rnd(2, H * hd), rnd(2, Hkv * hd), rnd(2, Hkv * hd), rows_per_sequence=2, first_sequence=1, n_sequences=1)
+    q, k, v = rnd(S, H * hd), rnd(S, Hkv * hd), rnd(S, Hkv * hd)
+    q0, out = q.clone(), torch.empty_like(q)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        cache.forward_cached(q, k, v, out=out)             # lengths 6 and 3 (warm-up before the capture)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        cache.forward_cached(q, k, v, out=out)             # captured, not run
+    for _ in range(2):                                     # 7 / 4, then 8 / 5: sequence 0 is now full
+        q.copy_(q0); graph.replay()
+    torch.cuda.synchronize()
+    before = cache.keys_values(0)
+    assert cache.lengths() == [cap, 5]
+    q.copy_(q0); graph.replay()                            # sequence 0 has no room; sequence 1 goes to 6
+    torch.cuda.synchronize()
+    assert float(out[0].float().abs().max()) == 0.0 and float(out[1].float().abs().max()) > 0.0
+    with pytest.raises(InvalidInput, match="SequenceTooLong"):
+        cache.lengths()
+    assert cache.lengths() == [cap, 6]                     # reported once; the length never passed capacity
+    after = cache.keys_values(0)
+    assert np.array_equal(before[0], after[0]) and np.array_equal(before[1], after[1])
+    k1, _ = cache.keys_values(1)
+    assert k1.shape[0] == 6
+    cache.truncate(4, sequence=0)                          # room again: the same graph steps it normally
+    q.copy_(q0); graph.replay()
+    torch.cuda.synchronize()
+    assert cache.lengths() == [5, 7] and float(out[0].float().abs().max()) > 0.0

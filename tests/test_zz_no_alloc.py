@@ -60,6 +60,25 @@ def test_two_calls_in_a_row_match_the_handle_based_routing():
         np.testing.assert_allclose(got[5], want[5], rtol=1e-6)
 
 
+def test_it_matches_the_cpu_checker_directly():
+    """The same step against the CPU restatement of the reference's route / softmax_rows / auxiliary_losses
+    (moe.rs:553-656), not only against the library's other entry point."""
+    from oracle import OracleMoe
+    T, E, k, d = 1500, 32, 4, 8
+    g = np.random.Generator(np.random.Philox(11))
+    logits = (g.standard_normal((T, E)) * 2.0).astype(np.float32)
+    logits[5] = logits[5, 0]                                   # an all-equal row: ties go to the lowest index
+    valid = (np.arange(T) % 7 != 3).astype(np.uint8)
+    ora = OracleMoe(d, E, k, 8, False)
+    ora.forward(np.zeros((T, d), np.float32), valid=valid, logits=logits)
+    e_o, g_o, c_o, _, _ = ora.routing()
+    got = _no_alloc(T, E, k, logits, valid)
+    assert np.array_equal(got[0], np.asarray(e_o).reshape(T, k)) and np.array_equal(got[2], c_o)
+    assert np.max(np.abs(got[1] - np.asarray(g_o).reshape(T, k))) <= 1e-6
+    a, z = ora.losses()
+    np.testing.assert_allclose(got[5], [a, z], rtol=1e-5)
+
+
 def test_sizes_beyond_the_static_scratch_are_rejected():
     msg = C.create_string_buffer(256)
     one = torch.zeros(1, device="cuda")
