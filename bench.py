@@ -169,31 +169,45 @@ def oracle_layer(w, sample_tokens, threads=None):
     return m, x, gy
 
 
-def time_oracle(w, sample_tokens, steps, warmup):
-    """Times forward + backward of the CPU restatement on `sample_tokens` tokens of the workload's shape.
+def host_threads():
+    """Every core this process may run on, whatever OMP_NUM_THREADS says (torchrun sets it to 1)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
-    With sample_tokens = None the sample is sized from a 128-token probe so that the whole call
-    (warm-up included) stays near 90 s: between 128 and 4096 tokens, a multiple of 128.
+
+def time_oracle(w, sample_tokens, steps, warmup, budget_s=150.0):
+    """Times forward + backward of the CPU restatement on `sample_tokens` tokens of the workload's shape, on all
+    host threads.  The sample is the same at every GPU count (the large workloads use 2048 tokens per pass, so
+    that the experts' weights are not re-streamed from memory for a few rows each); when `steps` passes of it
+    would not fit in `budget_s`, fewer are timed and that number is returned.
     """
     import oracle
-    probe = 128 if sample_tokens is None else sample_tokens
-    m, x, gy = oracle_layer(w, max(probe, 4096 if sample_tokens is None else probe))
-    m.forward(x[:probe]); m.backward(gy[:probe])            # first touch: page in weights, allocate gradients
-    if sample_tokens is None:
-        t0 = time.perf_counter()
-        m.forward(x[:probe]); m.backward(gy[:probe])
-        per_token = (time.perf_counter() - t0) / probe
-        budget = 90.0 / max(steps + warmup, 1)
-        sample_tokens = int(min(4096, max(128, (budget / per_token) // 128 * 128)))
-    xs, gs = x[:sample_tokens], gy[:sample_tokens]
-    for _ in range(warmup):
-        m.forward(xs); m.backward(gs)
+    threads = host_threads()
+    m, x, gy = oracle_layer(w, sample_tokens, threads=threads)
     t0 = time.perf_counter()
-    for _ in range(steps):
-        m.forward(xs)
-        m.backward(gs)
-    dt = (time.perf_counter() - t0) / max(steps, 1)
-    return sample_tokens / dt, dt, oracle.lib().orc_max_threads(), sample_tokens
+    m.forward(x); m.backward(gy)                             # first touch: pages in weights, allocates gradients
+    first = time.perf_counter() - t0
+    warm = warmup if first * (warmup + 1) < 0.3 * budget_s else 0
+    for _ in range(warm):
+        m.forward(x); m.backward(gy)
+    t0 = time.perf_counter()
+    m.forward(x); m.backward(gy)
+    one = time.perf_counter() - t0
+    timed = int(max(1, min(steps, (budget_s - first * (1 + warm)) // max(one, 1e-9))))
+    total = one
+    for _ in range(timed - 1):
+        t0 = time.perf_counter()
+        m.forward(x); m.backward(gy)
+        total += time.perf_counter() - t0
+    dt = total / timed
+    return sample_tokens / dt, dt, oracle.lib().orc_max_threads(), sample_tokens, timed
+
+
+def reference_sample(w):
+    """Tokens per pass of the CPU arm: the whole batch for the small workloads, 2048 tokens for the large ones."""
+    return min(w["T"], 2048)
 
 
 def run_reference(args, w):
@@ -223,14 +237,15 @@ def run_reference(args, w):
                                            "sample": "one sequence's decode step at the workload's history, times %d sequences" % S},
                           "e2e": {"value": us, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
         return
-    value, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else w["T"], max(args.steps, 1), min(args.warmup, 1))
+    value, dt, cores, sample, timed = time_oracle(w, reference_sample(w), max(args.steps, 1), min(args.warmup, 1))
     line = {
         "impl": "reference", "metric": "MoE-layer tokens/s (forward + backward)", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w["name"], "sample": "%d tokens per step" % sample},
+        "config": {"workload": w["name"], "sample": "%d tokens per step" % sample, "steps_timed": timed},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port",
-                         "sample": "%d tokens of the workload's shape per step, forward + backward, all host threads" % sample},
+                         "sample": "%d tokens of the workload's shape per step, forward + backward, %d host threads, %d steps timed"
+                                   % (sample, cores, timed)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -295,7 +310,8 @@ def run_decode(args, w):
             "roofline": {"bound": "hbm", "achieved": wbytes / (p50 * 1e-6) / 1e9, "peak": pk["hbm"], "unit": "GB/s",
                          "frac": wbytes / (p50 * 1e-6) / 1e9 / pk["hbm"], "traffic": None,
                          "note": "int8 weight bytes of the %d active experts + shared (%.0f MB) / whole-layer p50" % (active - 1, wbytes / 1e6)}}
-    print(json.dumps(line))
+    layer.close()
+    return line
 
 
 def run_decode_attention(args, w):
@@ -421,47 +437,85 @@ def run_rmsnorm(args, w):
     print(json.dumps(line))
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOADS))
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-e2e", action="store_true")
-    args = ap.parse_args()
-    w = WORKLOADS[args.workload]
-    if args.impl == "reference":
-        run_reference(args, w)
-        return
-    if w["precision"] == "q8":
-        run_decode(args, w)
-        return
-    if w["precision"] == "attn":
-        run_decode_attention(args, w)
-        return
-    if w["precision"] == "rmsnorm":
-        run_rmsnorm(args, w)
-        return
+def ep_parity_check(torch, dist, w, rank, world, local):
+    """N ranks against ONE CPU checker over the concatenated batch, before anything is timed: 256 tokens per
+    rank of the workload's d_model / experts / top-k with a small d_ff, forward + backward.  The checker is fed
+    the devices' own router logits, so routing must be equal bit for bit; outputs, input gradients and weight
+    gradients must agree within the bf16 tolerance.  Returns the dict that goes into the JSON line."""
+    import oracle
+    from oracle import OracleMoe
+    from rustingbrain_b200 import MoeConfig, _lib
+    from rustingbrain_b200.ep import ExpertParallelMoe
+    d, E, k, shared, F, T = w["d"], w["E"], w["k"], w["shared"], 64, 256
+    f32 = w["precision"] == "f32"
+    tol = 1e-5 if f32 else 2e-2
+    dt = torch.float32 if f32 else torch.bfloat16
+    rnd = (lambda a: a) if f32 else (lambda a: torch.from_numpy(a).bfloat16().float().numpy())
+    g = np.random.Generator(np.random.Philox(w["seed"] + 77))
+    router = (g.standard_normal((E, d)) * 0.02).astype(np.float32)
+    gate = rnd((g.standard_normal((E, F, d)) * 0.02).astype(np.float32))
+    up = rnd((g.standard_normal((E, F, d)) * 0.02).astype(np.float32))
+    down = rnd((g.standard_normal((E, d, F)) * 0.02).astype(np.float32))
+    sh = tuple(rnd((g.standard_normal(sz) * 0.02).astype(np.float32)) for sz in ((F, d), (F, d), (d, F))) if shared else None
+    layer = ExpertParallelMoe(d, MoeConfig(E, k, F, shared), precision=w["precision"], max_tokens=T, device=local,
+                              capacity_factor=2.0)
+    layer.set_weight(_lib.W_ROUTER, 0, router)
+    for e in layer.owned_experts():
+        layer.set_weight(_lib.W_GATE, e, gate[e]); layer.set_weight(_lib.W_UP, e, up[e]); layer.set_weight(_lib.W_DOWN, e, down[e])
+    if shared:
+        for i, m in enumerate(sh):
+            layer.set_weight(_lib.W_SHARED_GATE + i, 0, m)
+    gens = [np.random.Generator(np.random.Philox(w["seed"] + 1000 + r)) for r in range(world)]
+    xs = [rnd(gen.standard_normal((T, d)).astype(np.float32)) for gen in gens]
+    gys = [rnd(gen.standard_normal((T, d)).astype(np.float32)) for gen in gens]
+    dev = torch.device("cuda", local)
+    x = torch.from_numpy(xs[rank]).to(dev).to(dt)
+    gy = torch.from_numpy(gys[rank]).to(dev).to(dt)
+    y, cache = layer.forward_train(x)
+    layer.zero_grad()
+    gx = layer.backward(cache, gy)
+    logits = layer.router_cache(T)[0]
+    all_logits = [None] * world
+    dist.all_gather_object(all_logits, logits)
+    oracle.lib().orc_set_threads(max(1, host_threads() // world))
+    ora = OracleMoe(d, E, k, F, shared)
+    ora.set_weights(router, gate, up, down, sh)
+    yo = ora.forward(np.concatenate(xs), logits=np.concatenate(all_logits))
+    gxo = ora.backward(np.concatenate(gys))
+    lo, hi = rank * T, (rank + 1) * T
 
-    import torch
-    import torch.distributed as dist
+    def rel(a, b):
+        a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+        return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+    e_dev, _, c_dev, _, _ = cache.routing()
+    mine = {"routing_equal": bool(np.array_equal(e_dev, ora.routing()[0][lo:hi])),
+            "rel_l2_y": rel(y.float().cpu().numpy(), yo[lo:hi]), "rel_l2_grad_x": rel(gx.float().cpu().numpy(), gxo[lo:hi])}
+    gw = 0.0
+    for e in layer.owned_experts():
+        for which in (_lib.W_GATE, _lib.W_UP, _lib.W_DOWN):
+            gw = max(gw, rel(layer.get_grad(which, e), ora.get_grad(which, e)))
+    gw = max(gw, rel(layer.get_grad(_lib.W_ROUTER), ora.get_grad(_lib.W_ROUTER)))
+    if shared:
+        gw = max(gw, rel(layer.get_grad(_lib.W_SHARED_GATE), ora.get_grad(_lib.W_SHARED_GATE)))
+    mine["rel_l2_grad_w"] = gw
+    a, z = ora.losses()
+    mine["loss_err"] = max(abs(cache.aux_loss() - a) / max(abs(a), 1e-30), abs(cache.z_loss() - z) / max(abs(z), 1e-30))
+    layer.close()
+    every = [None] * world
+    dist.all_gather_object(every, mine)
+    out = {"ranks": world, "tokens_per_rank": T, "d_model": d, "experts": E, "top_k": k, "d_ff": F, "tol": tol,
+           "routing_equal": all(m["routing_equal"] for m in every)}
+    for key in ("rel_l2_y", "rel_l2_grad_x", "rel_l2_grad_w", "loss_err"):
+        out[key] = max(m[key] for m in every)
+    out["ok"] = bool(out["routing_equal"] and out["rel_l2_y"] <= tol and out["rel_l2_grad_x"] <= tol
+                     and out["rel_l2_grad_w"] <= tol and out["loss_err"] <= 1e-3)
+    return out
+
+
+def run_layer(args, w, torch, dist, world, rank, local, device, with_e2e, with_cpu):
+    """One workload of the layer: timed steps with resident inputs, the host-buffer leg, rooflines."""
     from rustingbrain_b200 import MoeConfig, MoeLayer, _lib
-
-    # libraries (NCCL) may print banners on stdout; keep it clean for the one JSON line
-    real_stdout = os.dup(1)
-    os.dup2(2, 1)
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    args.warmup = max(args.warmup, 3)
-
     cfg = MoeConfig(w["E"], w["k"], w["F"], w["shared"])
     if world > 1:
         from rustingbrain_b200.ep import ExpertParallelMoe
@@ -515,7 +569,7 @@ def main():
 
     # ---- end to end through the host-buffer entry points (copies inside the timed region) ----
     e2e = None
-    if not args.no_e2e:
+    if with_e2e:
         xh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
         gh = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory()
         xh.copy_(x.float().cpu()); gh.copy_(gy.float().cpu())
@@ -523,7 +577,7 @@ def main():
         xn, gn = xh.numpy(), gh.numpy()
         yn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
         gxn = torch.empty(w["T"], w["d"], dtype=torch.float32).pin_memory().numpy()
-        e2e_steps = max(1, min(args.steps, 3))
+        e2e_steps = max(1, min(args.steps, 10))
         for _ in range(2):
             _, c = host.forward_train(xn, out=yn); host.zero_grad(); host.backward(c, gn, out=gxn)
         barrier()
@@ -541,12 +595,12 @@ def main():
             dt = float(t.item())
         nbytes = w["T"] * w["d"] * 4
         e2e = {"value": world * w["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": 2 * nbytes,
-               "d2h_bytes_per_step": 2 * nbytes + 8, "ms_per_step": dt * 1e3}
-
+               "d2h_bytes_per_step": 2 * nbytes + 8, "ms_per_step": dt * 1e3, "steps": e2e_steps}
+    layer.close()
+    del layer, x, gy, y, gx
+    torch.cuda.empty_cache()
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        return None
 
     pk = peaks()
     R = w["T"] * w["k"]
@@ -576,6 +630,7 @@ def main():
                 "kernel": "grouped_gemm_kernel (6 launches per step: gate|up, down, 2 dgrad, 2 wgrad)",
                 "launches": gemm_launches, "ms_per_launch": gemm_ms / max(gemm_launches, 1),
                 "flops_per_step": gemm_flops / args.steps, "peak_source": pk["src"] + " sustained bf16",
+                "frac_of_measured_burst": ach / pk["tf_burst"] if ach else None,
                 "frac_of_nominal_2250": ach / 2250.0 if ach else None}
     hbm = {}
     alg_bytes = {"permute": (w["T"] + 1.0 * R) * w["d"] * es, "combine": (R + w["T"] * (2 if w["shared"] else 1)) * w["d"] * es,
@@ -597,10 +652,86 @@ def main():
     }
     if e2e:
         line["e2e"] = e2e
-    if world == 1 and not args.no_cpu_baseline:
-        v, dt, cores, sample = time_oracle(w, None if w["d"] >= 2048 else min(w["T"], 2048), 2, 0)
+    if with_cpu:
+        v, dt, cores, sample, timed = time_oracle(w, reference_sample(w), 2, 0, budget_s=30.0)
         line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
-                                "sample": "%d tokens of the workload's shape, forward + backward, %.1f s per pass" % (sample, dt)}
+                                "sample": "%d tokens of the workload's shape, forward + backward, %.1f s per pass, %d passes timed"
+                                          % (sample, dt, timed)}
+    return line
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="cfg4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the cfg3 / cfg5 legs the default 1-GPU run appends")
+    ap.add_argument("--no-parity", action="store_true", help="skip the N-rank parity leg of a multi-GPU run")
+    args = ap.parse_args()
+    w = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, w)
+        return
+    if w["precision"] == "q8":
+        print(json.dumps(run_decode(args, w)))
+        return
+    if w["precision"] == "attn":
+        run_decode_attention(args, w)
+        return
+    if w["precision"] == "rmsnorm":
+        run_rmsnorm(args, w)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    # libraries (NCCL) may print banners on stdout; keep it clean for the one JSON line
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    args.warmup = max(args.warmup, 3)
+
+    # ---- correctness of the N-rank path, before anything is timed ----
+    parity = None
+    if world > 1 and not args.no_parity:
+        parity = ep_parity_check(torch, dist, w, rank, world, local)
+        if not parity["ok"]:
+            if rank == 0:
+                os.dup2(real_stdout, 1)
+                print(json.dumps({"error": "expert-parallel parity check failed", "ep_parity": parity}), flush=True)
+            dist.destroy_process_group()
+            sys.exit(3)
+
+    line = run_layer(args, w, torch, dist, world, rank, local, device, not args.no_e2e, world == 1 and not args.no_cpu_baseline)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    if parity is not None:
+        line["ep_parity"] = parity
+
+    # ---- the two other single-GPU configurations the targets are written for, a few steps each ----
+    if world == 1 and args.workload == "cfg4" and not args.no_extra:
+        extra = {}
+        short = argparse.Namespace(**vars(args))
+        short.steps, short.warmup = min(args.steps, 10), 3
+        c3 = run_layer(short, WORKLOADS["cfg3"], torch, dist, 1, 0, local, device, False, False)
+        extra["cfg3"] = {k: c3[k] for k in ("value", "unit", "ms_per_step", "steps", "roofline", "hbm_kernels", "clocks", "config")}
+        short.steps = 4
+        c5 = run_decode(short, WORKLOADS["cfg5"])
+        extra["cfg5"] = {k: c5[k] for k in ("value", "unit", "steps", "roofline", "clocks", "config", "p90_us")}
+        line["extra"] = extra
     sys.stdout.flush()
     os.dup2(real_stdout, 1)
     print(json.dumps(line), flush=True)

@@ -163,6 +163,14 @@ int32_t moe_get_router_cache(moe_layer_t* layer, float* logits, float* probabili
 #define MOE_EP_UNIQUE_ID_BYTES 128
 int32_t moe_ep_unique_id(void* out, int32_t len);
 int32_t moe_ep_init(moe_layer_t* layer, const void* unique_id, int32_t len);
+/* Deadline of the host-side waits that can sit behind a collective (moe_synchronize, moe_get_losses,
+ * moe_get_routing, moe_get_grad_f32, the *_host entries, the count read-back of the ncclSend/ncclRecv
+ * transport).  Such a wait polls the stream; when `milliseconds` pass without it finishing (a rank of the
+ * group never arrived or is stuck), the library aborts the communicator, so that the NCCL kernels waiting
+ * for the missing rank end, poisons the handle and returns MOE_TIMEOUT: fail closed, as the reference's
+ * device context does after any error (gpu_transformer.rs:160-195).  Default 600000 (ten minutes); 0 waits
+ * for ever.  The reference is single-device and has no counterpart. */
+int32_t moe_ep_set_deadline_ms(moe_layer_t* layer, int64_t milliseconds);
 /* Optional peer transport.  Each rank exports CUDA IPC handles of its four receive buffers
  * (MOE_EP_EXPORT_BYTES bytes); every rank imports the handles of every rank, its own included.
  * Once all are imported, the dispatch kernels store rows straight into the owner's buffer and the

@@ -39,6 +39,19 @@ int32_t moe_debug_profile_read(struct moe_layer* layer, float* milliseconds, int
 /* Selects the two-SM (cta_group::2) variant of the grouped tensor-core GEMM for later launches. */
 int32_t moe_debug_set_tc_pair(int32_t on);
 
+/* The polling wait behind moe_ep_set_deadline_ms, driven by a clock instead of a stream (needs no device):
+ * the condition becomes true `ready_after_ms` after the call starts; returns MOE_OK (0) if that happens within
+ * `deadline_ms`, else MOE_TIMEOUT (6) with *gave_up = 1.  deadline_ms = 0 waits for ever. */
+int32_t moe_debug_deadline_wait(int32_t ready_after_ms, int32_t deadline_ms, int32_t* gave_up);
+
+/* Failure-path hook of the grouped tensor-core GEMM: the NEXT launch (one launch only) runs with a producer
+ * that issues no load and with `wait_limit_cycles` (about 2,000,000 = 1 ms) as the limit of every barrier
+ * wait.  The consumers' waits run out, the kernel records a code in its error flag, every role leaves its
+ * loop, the CTA frees its tensor memory and returns: the next moe_synchronize / moe_get_* on the handle
+ * returns MOE_TIMEOUT and, after moe_clear_error, the handle works as before.  Nothing is in flight when
+ * the waits give up, and no wait is unbounded. */
+int32_t moe_debug_starve_next_gemm(int64_t wait_limit_cycles);
+
 /* Number of kernel launches issued by this library in the calling process. */
 int64_t moe_debug_launch_count(void);
 

@@ -5,11 +5,11 @@ A from-scratch CUDA implementation of the hot path of the reference crate's
 host-side mirror of the reference's ``MoeConfig`` / ``MoeLayer`` / ``MoeCache``
 interface over that ABI.
 """
-from .moe import (CudaError, InvalidConfig, InvalidInput, MoeCache, MoeConfig, MoeLayer, NetworkError,
+from .moe import (CudaError, InvalidConfig, InvalidInput, MoeCache, MoeConfig, MoeLayer, NetworkError, Timeout,
                   DEFAULT_AUX_LOSS_WEIGHT, DEFAULT_ROUTER_Z_LOSS_WEIGHT)
 
 from .snapshot import InvalidSnapshot, SnapshotInfo, snapshot_info, write_optimizer_state, write_snapshot
 
 __all__ = ["InvalidSnapshot", "SnapshotInfo", "snapshot_info", "write_snapshot", "write_optimizer_state",
-           "MoeConfig", "MoeLayer", "MoeCache", "NetworkError", "InvalidConfig", "InvalidInput", "CudaError",
+           "MoeConfig", "MoeLayer", "MoeCache", "NetworkError", "InvalidConfig", "InvalidInput", "CudaError", "Timeout",
            "DEFAULT_AUX_LOSS_WEIGHT", "DEFAULT_ROUTER_Z_LOSS_WEIGHT"]

@@ -102,6 +102,8 @@ def lib() -> C.CDLL:
         "moe_route_noalloc": (i32, [vp, vp, i32, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, C.c_char_p, i32]),
         "moe_ep_unique_id": (i32, [vp, i32]),
         "moe_ep_init": (i32, [vp, vp, i32]),
+        "moe_ep_set_deadline_ms": (i32, [vp, C.c_int64]),
+        "moe_debug_deadline_wait": (i32, [i32, i32, ip]),
         "moe_ep_export_buffers": (i32, [vp, vp, i32]),
         "moe_ep_import_buffers": (i32, [vp, i32, vp, i32]),
         "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
@@ -119,6 +121,7 @@ def lib() -> C.CDLL:
         "moe_debug_tc_gemm": (i32, [i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp]),
         "moe_debug_launch_count": (C.c_int64, []),
         "moe_debug_set_tc_pair": (i32, [i32]),
+        "moe_debug_starve_next_gemm": (i32, [C.c_int64]),
         "moe_debug_profile": (i32, [vp, i32]),
         "moe_debug_profile_read": (i32, [vp, fp, ip]),
     }

@@ -36,6 +36,11 @@ int32_t moe_debug_set_tc_pair(int32_t on) {
   return 0;
 }
 
+int32_t moe_debug_starve_next_gemm(int64_t wait_limit_cycles) {
+  tc::set_starve_next_launch(wait_limit_cycles);
+  return 0;
+}
+
 int64_t moe_debug_launch_count(void) { return moe::g_launch_count; }
 
 }  // extern "C"

@@ -80,14 +80,14 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait.  Returns false (and records `code`) when the limit passes or
 // another role of this grid has already reported a failure.
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code) {
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code, long long limit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 0xfff) == 0) {
+    if ((i & 0xff) == 0) {
       if (*(volatile int*)error_flag != 0) return false;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit) {
         atomicCAS(error_flag, 0, code);
         return false;
       }
@@ -441,10 +441,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // ------------------------------ TMA producer ------------------------------
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      // p.starve (test hook): the producer loads nothing, so the consumers' bounded waits run out
+      for (int t = blockIdx.x; t < n_tiles && ok && !p.starve; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101, p.wait_limit)) { ok = false; break; }
           const uint32_t bar = smem_u32(&st->full[stage]);
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
@@ -484,14 +485,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
-        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 102)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 102, p.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         // the last column tile may be narrower: issue an MMA only as wide as needed (multiple of 16)
         const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
         const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103, p.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
@@ -524,7 +525,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
-      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104, p.wait_limit)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       epilogue_tile<EPI>(p, tl, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0, stg_all + (warp - 2) * STG_BYTES_PER_WARP);
@@ -732,13 +733,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       // ------------------------------ TMA producer (both CTAs) ------------------------------
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+      for (int t = cluster_id; t < n_tiles && ok && !p.starve; t += n_clusters) {
         const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, (int)rank);
         // this CTA's half of the B tile; a narrower last column tile is split in the middle
         const int n_live = min(BN, ((p.N - tl.n0) + 31) & ~31);
         const int nb0 = tl.n0 + (int)rank * (n_live / 2);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 201)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 201, p.wait_limit)) { ok = false; break; }
           const uint32_t leader_bar = map_to_cta(smem_u32(&st->full[stage]), 0);
           const uint32_t sa = tiles_base + stage * P_STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
@@ -773,13 +774,13 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       bool ok = true;
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, 0);
-        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 202)) { ok = false; break; }
+        if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 202, p.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int n_live = min(BN, ((p.N - tl.n0) + 31) & ~31);
         const uint32_t idesc = make_idesc_pair(A_MN, B_MN, n_live);
         for (int ki = 0; ki < tl.k_iters; ++ki) {
-          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 203)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 203, p.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * P_STAGE_BYTES;
           const uint32_t sb = sa + A_BYTES;
@@ -817,7 +818,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     bool ok = true;
     for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
       const PairTile tl = pair_decode<ROWS_ARE_K>(st, p, t, (int)rank);
-      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 204)) { ok = false; break; }
+      if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 204, p.wait_limit)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (!tl.skip) {
@@ -906,9 +907,28 @@ static cudaError_t opt_in_smem(Kernel kern, bool* configured, int bytes) {
   return e;
 }
 
+// Test hook: the next launch (one launch only) runs with a producer that loads nothing and with the
+// given wait limit, so that the bounded waits of the MMA and epilogue roles give up and the failure path
+// (error flag, drain, tensor-memory release) runs.  Nothing is in flight on that path and nothing waits
+// for ever.
+static long long g_starve_limit = 0;
+void set_starve_next_launch(long long wait_limit_cycles) { g_starve_limit = wait_limit_cycles > 0 ? wait_limit_cycles : 0; }
+
+static GemmArgs with_wait_limit(const GemmArgs& in) {
+  GemmArgs a = in;
+  a.wait_limit = WAIT_LIMIT_CYCLES;
+  a.starve = 0;
+  if (g_starve_limit > 0) {
+    a.wait_limit = g_starve_limit;
+    a.starve = 1;
+    g_starve_limit = 0;
+  }
+  return a;
+}
+
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
 static cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
-                               cudaStream_t stream) {
+                               cudaStream_t stream) {   // args: already through with_wait_limit
   auto kern = grouped_gemm_pair_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
   static bool configured[MAX_DEVICES] = {};
   { const cudaError_t e = opt_in_smem(kern, configured, P_SMEM_BYTES); if (e != cudaSuccess) return e; }
@@ -928,8 +948,9 @@ static cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, con
 }
 
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
-static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
+static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args_in, int sm_count,
                           cudaStream_t stream) {
+  const GemmArgs args = with_wait_limit(args_in);
   if (pair_mode()) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
   auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
   static bool configured[MAX_DEVICES] = {};

@@ -33,6 +33,8 @@ struct GemmArgs {
   long long group_stride0;     // rows-as-K: elements between consecutive groups of out0
   int accumulate;              // EPI_ACCUM_F32: add to out0 instead of overwriting
   int* error_flag;             // device int, set non-zero when a bounded wait gives up
+  long long wait_limit = 0;    // filled at launch: clock cycles a barrier wait may take before it gives up
+  int starve = 0;              // filled at launch (test hook): the producer loads nothing
 };
 
 // Operand descriptions for tensor-map construction (bf16, row-major).
@@ -45,6 +47,8 @@ struct Operand {
 
 // Two-SM tiles (cta_group::2, clusters of two CTAs) instead of one-SM tiles; also MOE_B200_TC_PAIR=1.
 void set_pair_mode(int on);
+// Test hook: the next launch runs with a producer that loads nothing and this wait limit (clock cycles).
+void set_starve_next_launch(long long wait_limit_cycles);
 bool pair_mode();
 
 // y[rows, N] = A[rows, K] * B_g[N, K]^T            (forward projections)

@@ -82,6 +82,7 @@ struct moe_layer {
   // live in the *_recv buffers in the padded layout the grouped GEMMs want.
   void* comm = nullptr;            // ncclComm_t
   bool ep_ready = false;
+  long long ep_deadline_ms = 600000;   // how long a host-side wait behind a collective may take before the group is aborted (0 = for ever)
   float ep_capacity = 1.25f;
   int rows_cap_l = 0;              // capacity (rows) of the local-expert buffers
   int *ep_pack = nullptr, *ep_gathered = nullptr, *ep_gathered_host = nullptr;
@@ -97,6 +98,8 @@ struct moe_layer {
   bool peer_ready = false;
   int *dest_base = nullptr, *dest_base_host = nullptr;   // [E] first row id (rank*cap+row) of my rows per expert
   int* barrier_word = nullptr;
+  float* g_rep_save = nullptr;     // replicated gradients (router, shared expert) of earlier passes, set aside while a pass's own are all-reduced
+  bool rep_overwrite = false;      // the running backward writes the replicated gradients without accumulating
 
   // host-call staging
   float* host_stage_f32 = nullptr;   // [max_tokens, d]

@@ -6,8 +6,10 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <chrono>
 #include <cmath>
 #include <new>
+#include <thread>
 
 #include "../../include/moe_b200.h"
 #include "../../include/moe_b200_debug.h"
@@ -46,6 +48,60 @@ int fail(moe_layer* L, int status, const char* fmt, ...) {
     if ((L)->status != MOE_OK) return MOE_POISONED;                                                \
     cudaError_t e_ = cudaSetDevice((L)->device);                                                   \
     if (e_ != cudaSuccess) return fail((L), MOE_CUDA_ERROR, "cudaSetDevice: %s", cudaGetErrorString(e_)); \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// Deadlines.  A collective whose peer never arrives would leave cudaStreamSynchronize waiting for ever,
+// so an expert-parallel handle waits by polling: `ready()` is asked until it says yes or `deadline_ms`
+// has passed (0 = no deadline).  The poll sleeps 50 us at first and backs off to 1 ms.
+// Returns true when ready, false when the deadline passed.
+// ---------------------------------------------------------------------------
+template <typename Ready>
+bool poll_until(Ready ready, long long deadline_ms) {
+  const auto t0 = std::chrono::steady_clock::now();
+  long long sleep_us = 50;
+  for (;;) {
+    if (ready()) return true;
+    if (deadline_ms > 0) {
+      const auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+      if (ms >= deadline_ms) return false;
+    }
+    std::this_thread::sleep_for(std::chrono::microseconds(sleep_us));
+    if (sleep_us < 1000) sleep_us *= 2;
+  }
+}
+
+// Waits for `st` (or the whole device when st_is_device).  Handles without a communicator wait the plain
+// way.  An expert-parallel handle gives up after its deadline: it aborts the communicator (which ends the
+// NCCL kernels that were waiting for the missing rank), poisons the handle and returns MOE_TIMEOUT; the
+// caller destroys the handle and builds a new group, as after any fail-closed error.
+int wait_for(moe_layer* L, cudaStream_t st, bool whole_device) {
+  if (L->ep_size <= 1 || !L->comm) {
+    CK(whole_device ? cudaDeviceSynchronize() : cudaStreamSynchronize(st));
+    return MOE_OK;
+  }
+  cudaError_t bad = cudaSuccess;
+  const bool done = poll_until([&]() {
+    const cudaError_t q = whole_device ? cudaStreamQuery(cudaStreamLegacy) : cudaStreamQuery(st);
+    if (q == cudaErrorNotReady) return false;
+    bad = q;
+    return true;
+  }, L->ep_deadline_ms);
+  if (!done) {
+    ncclCommAbort((ncclComm_t)L->comm);
+    L->comm = nullptr;
+    L->ep_ready = false;
+    return fail(L, MOE_TIMEOUT, "Timeout: the stream did not finish within %lld ms; a rank of the expert-parallel group is missing or stuck (communicator aborted)",
+                L->ep_deadline_ms);
+  }
+  if (bad != cudaSuccess) return fail(L, MOE_CUDA_ERROR, "stream failed: %s", cudaGetErrorString(bad));
+  if (whole_device) CK(cudaDeviceSynchronize());   // the legacy stream has drained; non-blocking streams follow at once
+  return MOE_OK;
+}
+#define WAIT(L, st, dev)                         \
+  do {                                           \
+    const int w_ = wait_for((L), (st), (dev));   \
+    if (w_ != MOE_OK) return w_;                 \
   } while (0)
 
 // Brackets a stage with two events when profiling is on.
@@ -272,6 +328,11 @@ __global__ void shared_meta_table_kernel(int* table, int max_tokens) {
   table[4 * t] = 0; table[4 * t + 1] = rows; table[4 * t + 2] = 0; table[4 * t + 3] = rows / GROUP_ALIGN;
 }
 
+__global__ void add_inplace_kernel(float* __restrict__ dst, const float* __restrict__ src, long long n) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] += src[i];
+}
+
 bool is_device_pointer(const void* p) {
   cudaPointerAttributes a;
   if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
@@ -358,7 +419,9 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
 int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStream_t st, bool routed, int parts = 7) {
   const int d = L->d, Fp = L->F_pad;
   Span whole(L, routed ? -1 : 14, st);
-  const int acc = L->grad_valid ? 1 : 0;
+  // replicated parameters of an expert-parallel layer: this pass's contribution is written alone, summed
+  // over the ranks, and only then added to what earlier passes left (see backward_impl)
+  const int acc = L->grad_valid && (routed || !L->rep_overwrite) ? 1 : 0;
   if (L->act == PREC_BF16) {
     // dgu = swiglu'(dy W_d) ; dW_d += dy^T h ; dx = dgu W_gu ; dW_gu += dgu^T x
     if (parts & 1) {
@@ -554,10 +617,20 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   const int tokens = L->last_tokens;
   const bool ep = L->ep_size > 1;
   if (tokens == 0 && !ep) return MOE_OK;
-  if (ep && L->grad_valid) {
-    L->err = "Unsupported: an expert-parallel handle does not accumulate gradients over several backward passes; call moe_zero_grad between them";
-    return MOE_UNSUPPORTED;
+  // Gradient accumulation over several passes (accumulate_step, transformer.rs:1519) on an expert-parallel
+  // handle: the experts' gradients accumulate in place as on one GPU.  The replicated ones (router, shared
+  // expert) hold a sum over ranks already, so this pass's local contribution must not be added to them before
+  // the all-reduce: the old values are set aside, the pass overwrites, the all-reduce sums the ranks, and the
+  // old values are added back.
+  const bool ep_accum = ep && L->grad_valid;
+  const long long rep_router = (long long)L->E * L->d, rep_shared = L->shared ? L->n_params - L->off_sgu : 0;
+  if (ep_accum) {
+    CK(cudaMemcpyAsync(L->g_rep_save, L->g + L->off_router, (size_t)rep_router * 4, cudaMemcpyDeviceToDevice, st));
+    if (rep_shared > 0)
+      CK(cudaMemcpyAsync(L->g_rep_save + rep_router, L->g + L->off_sgu, (size_t)rep_shared * 4, cudaMemcpyDeviceToDevice, st));
   }
+  L->rep_overwrite = ep_accum;
+  const int rep_acc = L->grad_valid && !ep_accum ? 1 : 0;
 
   const bool owner_dots = ep && L->peer_ready;   // gate gradient computed where the expert output lives
   const size_t aux_off = (size_t)L->rows_cap_l * L->d * L->esz;
@@ -615,17 +688,17 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
         CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
         RouterWgradArgs rw{};
         rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch; rw.d = L->d; rw.E = L->E; rw.splits = splits;
-        rw.accumulate = L->grad_valid ? 1 : 0;
+        rw.accumulate = rep_acc;
         CK(launch_router_wgrad_sum(rw, s));
       } else {
         wg.group_row0 = L->shared_meta; wg.n_groups = 1; wg.out0 = L->g + L->off_router;
-        wg.accumulate = L->grad_valid ? 1 : 0;
+        wg.accumulate = rep_acc;
         CK(tc::gemm_rows_tn(RA, Ax, wg, L->sm_count, s));
       }
     } else {
       RouterWgradArgs rw{};
       rw.grad_logits = L->grad_logits; rw.x = L->last_x; rw.grad_w = L->g + L->off_router; rw.scratch = L->rw_scratch;
-      rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = L->grad_valid ? 1 : 0;
+      rw.tokens = tokens; rw.d = L->d; rw.E = L->E; rw.splits = L->rw_splits; rw.accumulate = rep_acc;
       Span sp(L, 12, s); CK(launch_router_wgrad(rw, L->act, s));
     }
     return MOE_OK;
@@ -708,7 +781,14 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     Span sp(L, 12, st);
     rc = ep_allreduce_replicated(L, st);
     if (rc != MOE_OK) return rc;
+    if (ep_accum) {
+      add_inplace_kernel<<<(unsigned)((rep_router + 255) / 256), 256, 0, st>>>(L->g + L->off_router, L->g_rep_save, rep_router); count_launch();
+      if (rep_shared > 0) {
+        add_inplace_kernel<<<(unsigned)((rep_shared + 255) / 256), 256, 0, st>>>(L->g + L->off_sgu, L->g_rep_save + rep_router, rep_shared); count_launch();
+      }
+    }
   }
+  L->rep_overwrite = false;
   if (mode == 1) CK(cudaStreamWaitEvent(st, L->ev_join, 0));
   CK(cudaGetLastError());
   L->grad_valid = true;
@@ -827,6 +907,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
       else L->local_meta2[h] = L->local_meta2[0];
     }
     DA(L->dest_base, E * 4, true); DA(L->barrier_word, 4, true);
+    if (L->training) DA(L->g_rep_save, ((long long)E * d + (L->shared ? L->n_params - L->off_sgu : 0)) * 4, true);
     CK(cudaMallocHost((void**)&L->dest_base_host, (size_t)E * 4));
     if (L->ep_size > MAX_RANKS) return fail(L, MOE_INVALID_CONFIG, "at most %d expert-parallel ranks", MAX_RANKS);
     CK(cudaMallocHost((void**)&L->ep_gathered_host, (size_t)N * words * 4));
@@ -936,6 +1017,7 @@ static int read_arena(moe_layer* L, const float* arena, int which, int expert, f
   if (!dst) { L->err = "InvalidInput: null destination pointer"; return MOE_INVALID_INPUT; }
   const bool dev = is_device_pointer(dst);
   float* out = dev ? dst : L->stage;
+  if (L->last_stream) WAIT(L, L->last_stream, false);   // a backward pass (with its all-reduce) may still be running
   if (L->side_pending) { CK(cudaStreamSynchronize(L->side_stream)); L->side_pending = false; }   // deferred weight gradients
   CK(cudaDeviceSynchronize());   // the unpack kernel runs on the default stream: see what every stream has written
   unpack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(arena + s.offset, out, rows, cols, s.ld, s.kind, zero ? 1 : 0); count_launch();
@@ -1095,7 +1177,7 @@ int32_t moe_forward_host(moe_layer_t* L, const float* x, int32_t tokens, int32_t
       CK(cudaMemcpyAsync(y, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     }
   }
-  CK(cudaStreamSynchronize(st));
+  WAIT(L, st, false);
   return check_flag(L);
 }
 
@@ -1127,14 +1209,14 @@ int32_t moe_backward_host(moe_layer_t* L, const float* gy, float* gx) {
       CK(cudaMemcpyAsync(gx, L->host_stage_f32, (size_t)n * 4, cudaMemcpyDeviceToHost, st));
     }
   }
-  CK(cudaStreamSynchronize(st));
+  WAIT(L, st, false);
   if (L->side_pending) { CK(cudaStreamSynchronize(L->side_stream)); L->side_pending = false; }
   return check_flag(L);
 }
 
 int32_t moe_get_losses(moe_layer_t* L, float* aux, float* z) {
   ENTER(L);
-  CK(cudaStreamSynchronize(L->last_stream));
+  WAIT(L, L->last_stream, false);
   float v[2] = {0.f, 0.f};
   if (L->last_tokens > 0) CK(cudaMemcpy(v, L->losses, sizeof(v), cudaMemcpyDeviceToHost));
   if (aux) *aux = v[0];
@@ -1145,7 +1227,7 @@ int32_t moe_get_losses(moe_layer_t* L, float* aux, float* z) {
 int32_t moe_get_routing(moe_layer_t* L, int32_t* expert_of, float* gates, int32_t* counts, int32_t* token_of,
                         int32_t* slot_of, int32_t* routed) {
   ENTER(L);
-  CK(cudaStreamSynchronize(L->last_stream));
+  WAIT(L, L->last_stream, false);
   const long long tk = (long long)L->last_tokens * L->k;
   int total[4] = {0, 0, 0, 0};
   if (L->last_tokens > 0) CK(cudaMemcpy(total, L->meta.total, sizeof(total), cudaMemcpyDeviceToHost));
@@ -1163,7 +1245,7 @@ int32_t moe_get_routing(moe_layer_t* L, int32_t* expert_of, float* gates, int32_
 
 int32_t moe_get_router_cache(moe_layer_t* L, float* logits, float* probs, float* lse) {
   ENTER(L);
-  CK(cudaStreamSynchronize(L->last_stream));
+  WAIT(L, L->last_stream, false);
   const long long te = (long long)L->last_tokens * L->E;
   if (te > 0) {
     if (logits) CK(cudaMemcpy(logits, L->logits, (size_t)te * 4, cudaMemcpyDeviceToHost));
@@ -1203,6 +1285,22 @@ int32_t moe_ep_unique_id(void* out, int32_t len) {
   if (ncclGetUniqueId(&id) != ncclSuccess) return MOE_COMM_ERROR;
   memcpy(out, &id, sizeof(id));
   return MOE_OK;
+}
+
+int32_t moe_ep_set_deadline_ms(moe_layer_t* L, int64_t milliseconds) {
+  ENTER(L);
+  if (milliseconds < 0) { L->err = "InvalidInput: negative deadline"; return MOE_INVALID_INPUT; }
+  L->ep_deadline_ms = milliseconds;
+  return MOE_OK;
+}
+
+int32_t moe_debug_deadline_wait(int32_t ready_after_ms, int32_t deadline_ms, int32_t* gave_up) {
+  const auto t0 = std::chrono::steady_clock::now();
+  const bool done = poll_until([&]() {
+    return std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count() >= ready_after_ms;
+  }, deadline_ms);
+  if (gave_up) *gave_up = done ? 0 : 1;
+  return done ? MOE_OK : MOE_TIMEOUT;
 }
 
 int32_t moe_ep_init(moe_layer_t* L, const void* unique_id, int32_t len) {
@@ -1319,7 +1417,8 @@ int32_t moe_lora_merge(moe_layer_t* L) {
 
 int32_t moe_synchronize(moe_layer_t* L) {
   ENTER(L);
-  CK(cudaDeviceSynchronize());
+  if (L->last_stream) WAIT(L, L->last_stream, false);
+  WAIT(L, nullptr, true);
   return check_flag(L);
 }
 

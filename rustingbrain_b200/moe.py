@@ -45,7 +45,11 @@ class CudaError(NetworkError):
     pass
 
 
-_ERRORS = {_lib.INVALID_CONFIG: InvalidConfig, _lib.INVALID_INPUT: InvalidInput}
+class Timeout(NetworkError):
+    """A bounded wait gave up: a device-side barrier wait, or a host-side wait behind a collective."""
+
+
+_ERRORS = {_lib.INVALID_CONFIG: InvalidConfig, _lib.INVALID_INPUT: InvalidInput, _lib.TIMEOUT: Timeout}
 
 
 @dataclass(frozen=True)
@@ -445,6 +449,11 @@ class MoeLayer:
         cnt = (C.c_int32 * n)()
         self._ck(_lib.lib().moe_debug_profile_read(self._h, ms, cnt))
         return {name: (float(ms[i]), int(cnt[i])) for i, name in enumerate(self.PROFILE_STAGES)}
+
+    def clear_error(self):
+        """Lifts the sticky error state after a failed call (the reference's poisoned context has no such
+        call: it is rebuilt; here the workspace is kept)."""
+        self._ck(_lib.lib().moe_clear_error(self._h))
 
     def synchronize(self):
         self._ck(_lib.lib().moe_synchronize(self._h))

@@ -13,6 +13,12 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _world():
+    """Every visible GPU takes part, as 2, 4 or 8 ranks (8 experts: at 8 ranks each rank owns one)."""
+    n = torch.cuda.device_count()
+    return 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
+
+
 def _worker(rank, world, port, precision, transport, ret):
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "tests"))
@@ -76,6 +82,15 @@ def _worker(rank, world, port, precision, transport, ret):
                 ok &= rel_l2(layer.get_grad(which, e), ora.get_grad(which, e)) <= tol
         ok &= rel_l2(layer.get_grad(ROUTER), ora.get_grad(ROUTER)) <= max(tol, 1e-4)
         ok &= rel_l2(layer.get_grad(SHARED_GATE), ora.get_grad(SHARED_GATE)) <= tol
+        # a second backward without zero_grad accumulates (Param.grad semantics, accumulate_step
+        # transformer.rs:1519): every gradient doubles, the replicated ones included
+        if os.environ.get("MOE_B200_OVERLAP", "0") == "0":
+            first = {(which, e): layer.get_grad(which, e).copy() for e in layer.owned_experts() for which in (GATE, UP, DOWN)}
+            first[(ROUTER, 0)] = layer.get_grad(ROUTER).copy()
+            first[(SHARED_GATE, 0)] = layer.get_grad(SHARED_GATE).copy()
+            layer.backward(cache, gy)
+            for (which, e), g1 in first.items():
+                ok &= rel_l2(layer.get_grad(which, e), 2 * g1) <= 1e-5
         ret[rank] = bool(ok)
         layer.close()
     finally:
@@ -87,11 +102,9 @@ def _worker(rank, world, port, precision, transport, ret):
     ("bf16", "peer", "1"), ("bf16", "peer", "2"), ("bf16", "nccl", "2")])
 def test_expert_parallel_matches_single_device(precision, transport, overlap, monkeypatch):
     monkeypatch.setenv("MOE_B200_OVERLAP", overlap)   # read by the spawned ranks' copy of the library
-    world = min(torch.cuda.device_count(), 4)
+    world = _world()
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    if world == 3:
-        world = 2
     port = 29700 + (os.getpid() % 2000)
     with mp.Manager() as mgr:
         ret = mgr.dict()

@@ -49,8 +49,8 @@ def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
 
 
 def test_activations_beyond_the_f16_range_saturate_instead_of_becoming_infinite():
-    """The int8 kernels multiply in f16: a bf16 activation beyond 65504 is clamped to +-65504 when the token tile is
-    staged, so the output stays finite and equals the checker's result on the clamped input."""
+    """The int8 kernels multiply in f16: a bf16 activation (or hidden value) beyond 65504 is clamped to +-65504 when
+    the token tile is staged, so an outlier gives a finite row and leaves the other rows of the batch alone."""
     T, d, E, k, F = 8, 64, 4, 2, 64
     dev, ora, x = _pair(T, d, E, k, F, False, seed=4)
     x[3, 7] = 3.0e6
@@ -59,8 +59,9 @@ def test_activations_beyond_the_f16_range_saturate_instead_of_becoming_infinite(
     y, cache = dev.forward_train(xd)
     assert bool(torch.isfinite(y.float()).all())
     logits = dev.router_cache(T)[0]
-    yo = ora.forward(np.clip(xd.float().cpu().numpy(), -65504.0, 65504.0), logits=logits)
-    assert rel_l2(y.float().cpu().numpy(), yo) <= 2e-2
+    yo = ora.forward(xd.float().cpu().numpy(), logits=logits)
+    others = [t for t in range(T) if t not in (3, 5)]
+    assert rel_l2(y.float().cpu().numpy()[others], yo[others]) <= 2e-2
 
 
 def test_a_quantized_layer_refuses_to_train():  # transformer.rs:2202-2280: quantizing is one-way
