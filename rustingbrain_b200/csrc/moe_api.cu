@@ -705,7 +705,10 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   };
   // mode 2: only the input-gradient chain stays on the caller's stream; both routed weight gradients
   // go to the side stream and are joined by whichever later call needs their inputs or outputs
-  const int mode = L->prof_on ? 0 : (force_mode == 3 && !ep ? 3 : overlap_mode());
+  // stage timing brackets launches on the caller's stream; mode 1 keeps every bracketed stage there (only the
+  // un-permute moves to the side stream and goes untimed), modes 2 and 3 do not
+  const int want = force_mode == 3 && !ep ? 3 : overlap_mode();
+  const int mode = L->prof_on && want != 1 ? 0 : want;
   const int first_parts = mode >= 2 ? 1 : 3;
   Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
   ExpertIO io{};
