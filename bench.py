@@ -50,6 +50,10 @@ WORKLOADS = {
     # backward + Adam, bf16 GEMMs over f32 master weights.
     "cfg2": dict(T=8192, d=512, E=8, k=2, F=352, shared=True, seed=42, precision="bf16", zipf=False, adam=True,
                  name="one MoE block of the 55M language model, fwd+bwd+Adam bf16: 8192 tokens, d_model 512, 8 experts top-2 + shared, d_ff 352"),
+    # the whole 55M-parameter language model of the reference's README: train_step (forward + backward + Adam) over
+    # 8 sequences of 1024 tokens, bf16 products over f32 master weights; 6 of its 8 blocks are MoE blocks
+    "cfg2_model": dict(precision="model", batch=8, seq=1024, seed=42,
+                       name="55.2M-parameter MoE language model, full train_step bf16/f32-master: vocab 32000, d_model 512, 8 layers, GQA 8/2 x 64, dense d_ff 1408, 8 experts top-2 (d_ff 352) + shared on layers 2..7, batch 8 x seq 1024"),
     "cfg1": dict(T=2048, d=512, E=8, k=2, F=1408, shared=False, seed=42, precision="f32", zipf=False,
                  name="MoE layer fwd+bwd f32: 2048 tokens, d_model 512, 8 experts top-2, d_ff 1408"),
 }
@@ -214,6 +218,30 @@ def run_reference(args, w):
     """The reference's CPU path (restated in oracle/) on the host cores, bounded sample per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    if w["precision"] == "model":
+        # the checker's train_step (numpy + the C++ MoE restatement) on a bounded sample: 2 sequences of 128 tokens
+        import oracle
+        from oracle import transformer as T
+        oracle.lib().orc_set_threads(host_threads())
+        c = T.default_config()
+        m = T.OracleLm(c, T.seeded_model_weights(c, w["seed"]))
+        g = np.random.Generator(np.random.Philox(w["seed"]))
+        batch = T.TokenBatch([list(g.integers(0, 32000, 128)) for _ in range(2)])
+        m.train_step(batch)
+        steps = max(1, min(args.steps, 3))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            m.train_step(batch)
+        dt = (time.perf_counter() - t0) / steps
+        v = batch.rows / dt
+        print(json.dumps({"impl": "reference", "metric": "language-model tokens/s (train_step: forward + backward + Adam)", "value": v,
+                          "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                          "config": {"workload": w["name"], "sample": "2 sequences of 128 tokens per step", "steps_timed": steps},
+                          "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": host_threads(), "kind": "port",
+                                           "sample": "train_step on 2 x 128 tokens: numpy (BLAS threads) + the C++ MoE restatement"},
+                          "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0}))
         return
     if w["precision"] == "attn":
         # the checker's single-sequence decode step (numpy, one thread), scaled to the workload's sequences
@@ -660,6 +688,56 @@ def run_layer(args, w, torch, dist, world, rank, local, device, with_e2e, with_c
     return line
 
 
+def run_model(args, w):
+    """train_step of the 55M model through the model-level C ABI: ids go up from the host and the loss comes back
+    every step, so this number is end to end by construction."""
+    import torch
+    from rustingbrain_b200 import _lib
+    from rustingbrain_b200.transformer import TransformerLm, TokenBatch
+    torch.cuda.set_device(0)
+    B, S = w["batch"], w["seq"]
+    model = TransformerLm.builder().max_batch_rows(B * S).seed(w["seed"]).build()
+    total, active = model.parameter_counts()
+    g = np.random.Generator(np.random.Philox(w["seed"]))
+    batch = TokenBatch([list(g.integers(0, 32000, S)) for _ in range(B)])
+    steps, warm = max(args.steps, 1), max(args.warmup, 3)
+    for _ in range(warm):
+        loss = model.train_step_batch(batch)
+    model.synchronize()
+    l0 = _lib.lib().moe_debug_launch_count()
+    sampler = ClockSampler(0)
+    phases = np.zeros(4)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        loss = model.train_step_batch(batch)
+        phases += np.array(model.last_step_ms())
+    model.synchronize()
+    wall = (time.perf_counter() - t0) / steps * 1e3
+    clocks = sampler.stop()
+    launches = _lib.lib().moe_debug_launch_count() - l0
+    phases /= steps
+    dev_ms = float(phases.sum())
+    tokens = B * S
+    flops = (6.0 * active + 12.0 * 8 * S * 512) * tokens      # the reference's own formula (docs/baseline.md:15)
+    pk = peaks()
+    ach = flops / (dev_ms * 1e-3) / 1e12
+    line = {"metric": "language-model tokens/s (train_step: forward + backward + Adam)", "value": tokens / (wall * 1e-3),
+            "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warm, "ms_per_step": wall, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16 products, f32 master weights", "data": "synthetic",
+            "config": {"workload": w["name"], "parameters_total": total, "parameters_active": active,
+                       "l2": "activations of a step (about 2 GB) are larger than L2"},
+            "clocks": clocks, "gpu_launches": int(launches), "device_ms_per_step": dev_ms,
+            "phase_ms": {"forward": float(phases[0]), "head_and_loss": float(phases[1]), "backward": float(phases[2]), "adam": float(phases[3])},
+            "loss": {"lm_loss": loss.lm_loss, "auxiliary_loss": loss.auxiliary_loss},
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": ach / pk["tf_sustained"],
+                         "traffic": None, "flops_per_step": flops,
+                         "note": "whole step: 6 x active parameters + attention, per token; device time of the four phases"},
+            "e2e": {"value": tokens / (wall * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": tokens * 9, "d2h_bytes_per_step": 4,
+                    "ms_per_step": wall, "note": "the step takes host token ids and returns the host loss: the same number as value"}}
+    model.close()
+    return line
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -678,6 +756,9 @@ def main():
         return
     if w["precision"] == "q8":
         print(json.dumps(run_decode(args, w)))
+        return
+    if w["precision"] == "model":
+        print(json.dumps(run_model(args, w)))
         return
     if w["precision"] == "attn":
         run_decode_attention(args, w)

@@ -45,6 +45,16 @@ class KvCacheConfigC(C.Structure):
                 ("precision", C.c_int32), ("device", C.c_int32)]
 
 
+class LmConfigC(C.Structure):
+    """lm_config_t of include/transformer_b200.h."""
+    _fields_ = [("vocab_size", C.c_int32), ("d_model", C.c_int32), ("n_layers", C.c_int32), ("n_heads", C.c_int32),
+                ("n_kv_heads", C.c_int32), ("head_dim", C.c_int32), ("d_ff", C.c_int32), ("moe_d_ff", C.c_int32),
+                ("num_experts", C.c_int32), ("experts_per_token", C.c_int32), ("shared_expert", C.c_int32),
+                ("moe_layer_mask", C.c_uint64), ("max_seq_len", C.c_int32), ("rope_base", C.c_float),
+                ("rmsnorm_eps", C.c_float), ("tie_embeddings", C.c_int32), ("aux_loss_weight", C.c_float),
+                ("router_z_loss_weight", C.c_float), ("max_batch_rows", C.c_int32), ("device", C.c_int32)]
+
+
 _lib = None
 
 
@@ -107,6 +117,23 @@ def lib() -> C.CDLL:
         "moe_ep_export_buffers": (i32, [vp, vp, i32]),
         "moe_ep_import_buffers": (i32, [vp, i32, vp, i32]),
         "moe_ep_plan": (i32, [ip, i32, i32, i32, ip, ip, ip, ip, ip]),
+        "lm_config_validate": (i32, [C.POINTER(LmConfigC), C.c_char_p, i32]),
+        "lm_parameter_counts": (i32, [C.POINTER(LmConfigC), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+        "lm_create": (i32, [C.POINTER(LmConfigC), C.POINTER(vp)]),
+        "lm_destroy": (None, [vp]),
+        "lm_last_error": (C.c_char_p, [vp]),
+        "lm_set_param": (i32, [vp, i32, i32, i32, vp, i32, i32]),
+        "lm_get_param": (i32, [vp, i32, i32, i32, vp, i32, i32]),
+        "lm_get_grad": (i32, [vp, i32, i32, i32, vp, i32, i32]),
+        "lm_forward_logits": (i32, [vp, vp, vp, i32, i32, vp, vp]),
+        "lm_accumulate_step": (i32, [vp, vp, vp, vp, i32, i32, fp, fp]),
+        "lm_zero_grad": (i32, [vp]),
+        "lm_step_adam": (i32, [vp, f32, f32, f32, f32, f32, f32]),
+        "lm_train_step": (i32, [vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, f32, fp, fp]),
+        "lm_optimizer_step": (C.c_int64, [vp]),
+        "lm_set_optimizer_step": (i32, [vp, C.c_int64]),
+        "lm_last_step_ms": (i32, [vp, fp]),
+        "lm_synchronize": (i32, [vp]),
         "kv_cache_create": (i32, [C.POINTER(KvCacheConfigC), C.POINTER(vp)]),
         "kv_cache_destroy": (None, [vp]),
         "kv_cache_last_error": (C.c_char_p, [vp]),
@@ -141,5 +168,5 @@ def exported_symbols():
     for h in sorted(os.listdir(inc)):
         if h.endswith(".h"):
             text = open(os.path.join(inc, h)).read()
-            names += re.findall(r"\b((?:moe|kv|rmsnorm)_[a-z0-9_]+)\s*\(", text)
-    return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight")))
+            names += re.findall(r"\b((?:moe|kv|rmsnorm|lm)_[a-z0-9_]+)\s*\(", text)
+    return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight", "lm_param", "lm_config", "lm_model")))
