@@ -110,6 +110,20 @@ int32_t lm_train_step(lm_model_t* model, const uint32_t* ids_host, const int32_t
 int64_t lm_optimizer_step(const lm_model_t* model);
 int32_t lm_set_optimizer_step(lm_model_t* model, int64_t step);
 
+/* KV-cached decode (TransformerLm::new_kv_caches + forward_cached, transformer.rs:649-660, 737-770), for
+ * `sequences` independent sequences that advance together: one batched cache per layer (kv_attention_b200.h,
+ * bf16), `capacity` positions each (at most max_seq_len).  lm_forward_cached feeds rows_per_sequence new token ids
+ * to each of the sequences first_sequence .. first_sequence + n_sequences - 1 (the whole prompt for a prefill, one
+ * id per sequence for a decode step; ids_host is sequence-major) and returns the logits of every new row,
+ * logits_host [n_sequences * rows_per_sequence, vocab] f32.  SequenceTooLong -> MOE_INVALID_INPUT, nothing appended. */
+typedef struct lm_decoder lm_decoder_t;
+int32_t lm_decoder_create(lm_model_t* model, int32_t sequences, int32_t capacity, lm_decoder_t** out);
+void lm_decoder_destroy(lm_decoder_t* decoder);
+/* KvCache::clear for every layer: one sequence, or all of them when sequence < 0. */
+int32_t lm_decoder_clear(lm_model_t* model, lm_decoder_t* decoder, int32_t sequence);
+int32_t lm_forward_cached(lm_model_t* model, lm_decoder_t* decoder, const uint32_t* ids_host, int32_t first_sequence,
+                          int32_t n_sequences, int32_t rows_per_sequence, float* logits_host);
+
 /* Kernel launches since creation and CUDA-event milliseconds of the last step's phases, for the benchmark:
  * ms[0] embedding + blocks forward, ms[1] head + loss (three products over the vocabulary), ms[2] blocks backward
  * + embedding scatter, ms[3] optimizer. */

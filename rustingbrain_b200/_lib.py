@@ -132,6 +132,10 @@ def lib() -> C.CDLL:
         "lm_train_step": (i32, [vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, f32, fp, fp]),
         "lm_optimizer_step": (C.c_int64, [vp]),
         "lm_set_optimizer_step": (i32, [vp, C.c_int64]),
+        "lm_decoder_create": (i32, [vp, i32, i32, C.POINTER(vp)]),
+        "lm_decoder_destroy": (None, [vp]),
+        "lm_decoder_clear": (i32, [vp, vp, i32]),
+        "lm_forward_cached": (i32, [vp, vp, vp, i32, i32, i32, vp]),
         "lm_last_step_ms": (i32, [vp, fp]),
         "lm_synchronize": (i32, [vp]),
         "kv_cache_create": (i32, [C.POINTER(KvCacheConfigC), C.POINTER(vp)]),
@@ -169,4 +173,4 @@ def exported_symbols():
         if h.endswith(".h"):
             text = open(os.path.join(inc, h)).read()
             names += re.findall(r"\b((?:moe|kv|rmsnorm|lm)_[a-z0-9_]+)\s*\(", text)
-    return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight", "lm_param", "lm_config", "lm_model")))
+    return sorted(set(n for n in names if n not in ("moe_status", "moe_precision", "moe_weight", "lm_param", "lm_config", "lm_model", "lm_decoder")))

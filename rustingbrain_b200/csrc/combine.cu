@@ -121,16 +121,17 @@ __device__ __forceinline__ int slots_by_expert(const int* expert_of, const int* 
 // Launches kernel<T, KMAX> for the smallest KMAX in {1, 2, 4, 8, 16} that holds k.
 #define DISPATCH_KMAX(KERNEL, T, k, grid, stream, args)                                         \
   do {                                                                                           \
-    if ((k) <= 1) KERNEL<T, 1><<<grid, CB_WARPS * 32, 0, stream>>>(args);                        \
-    else if ((k) <= 2) KERNEL<T, 2><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
-    else if ((k) <= 4) KERNEL<T, 4><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
-    else if ((k) <= 8) KERNEL<T, 8><<<grid, CB_WARPS * 32, 0, stream>>>(args);                   \
-    else KERNEL<T, 16><<<grid, CB_WARPS * 32, 0, stream>>>(args);                                \
+    if ((k) <= 1) launch_kernel(KERNEL<T, 1>, dim3(grid), dim3(CB_WARPS * 32), 0, stream, args);  \
+    else if ((k) <= 2) launch_kernel(KERNEL<T, 2>, dim3(grid), dim3(CB_WARPS * 32), 0, stream, args); \
+    else if ((k) <= 4) launch_kernel(KERNEL<T, 4>, dim3(grid), dim3(CB_WARPS * 32), 0, stream, args); \
+    else if ((k) <= 8) launch_kernel(KERNEL<T, 8>, dim3(grid), dim3(CB_WARPS * 32), 0, stream, args); \
+    else launch_kernel(KERNEL<T, 16>, dim3(grid), dim3(CB_WARPS * 32), 0, stream, args);          \
     count_launch();                                                                              \
   } while (0)
 
 template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
+  pdl_enter();
   const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;

@@ -35,6 +35,31 @@ enum Status {
 extern long long g_launch_count;
 inline void count_launch(int n = 1) { g_launch_count += n; }
 
+// Programmatic dependent launch.  While `g_pdl_scope` is set (the decode pass of a quantized layer sets it), the
+// kernels launched through launch_kernel() may start while their predecessor on the stream is still running: the
+// grid's blocks become resident early and wait in pdl_enter() until the predecessor has finished and its
+// writes are visible, so the launch latency and the prologue overlap the predecessor's tail.  Outside the scope
+// the launch is an ordinary one and pdl_enter() returns at once.
+extern thread_local bool g_pdl_scope;
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // this grid's successor may be scheduled
+  asm volatile("griddepcontrol.wait;" ::: "memory");                // everything before this grid is complete
+}
+template <typename Kernel, typename... Args>
+inline cudaError_t launch_kernel(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  if (!g_pdl_scope) {
+    kernel<<<grid, block, smem, stream>>>(args...);
+    return cudaGetLastError();
+  }
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 __host__ __device__ inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ inline int round_up(int a, int b) { return ceil_div(a, b) * b; }
 

@@ -6,6 +6,7 @@ using namespace moe;
 
 namespace moe {
 long long g_launch_count = 0;
+thread_local bool g_pdl_scope = false;
 }
 
 extern "C" {

@@ -67,6 +67,7 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
 // U = 16-byte loads per lane and tile in one chunk of 64 U reduction values; K is a multiple of 64 U.
 template <bool SWIGLU, int U>
 __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
+  pdl_enter();
   extern __shared__ __align__(16) unsigned char q8_smem[];
   __shared__ int tile_start[MAX_EXPERTS + 2];   // first token tile of every group
   // Token tile in MMA-fragment order: rows r and r + 8 are interleaved so that one 16-byte unit holds
@@ -265,7 +266,7 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
 template <bool SWIGLU, int U>
 static cudaError_t launch_q8_variant(const Q8Args& a, dim3 grid, size_t smem, cudaStream_t stream) {
   if (smem > 48 * 1024) cudaFuncSetAttribute(q8_rows_kernel<SWIGLU, U>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  q8_rows_kernel<SWIGLU, U><<<grid, Q8_WARPS * 32, smem, stream>>>(a);
+  launch_kernel(q8_rows_kernel<SWIGLU, U>, grid, dim3(Q8_WARPS * 32), smem, stream, a);
   count_launch();
   return cudaGetLastError();
 }

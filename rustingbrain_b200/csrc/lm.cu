@@ -64,6 +64,11 @@ struct lm_model {
   uint8_t* valid = nullptr;
   void* rms_scratch = nullptr;
   uint32_t* ids_pin = nullptr; int* targets_pin = nullptr; uint8_t* valid_pin = nullptr; float* loss_pin = nullptr;
+  int *first_pin = nullptr, *next_pin = nullptr;
+  std::vector<int> last_seen;       // per vocabulary id: last row that held it (host scratch of the scatter chains)
+  float* split_scratch = nullptr;   // partial weight gradients of the row-split products
+  long long split_elems = 0;
+  int* split_meta = nullptr;        // group tables of the row-split products
   cudaStream_t st = nullptr;
   cudaEvent_t ev[5] = {};
   float last_ms[4] = {0, 0, 0, 0};
@@ -186,6 +191,44 @@ int mm_tn(lm_model* M, const void* A, long long a_rows, int Mo, const void* B, l
   a.group_row0 = mt.row0; a.n_groups = mt.groups; a.error_flag = M->error_flag;
   a.M = Mo; a.N = N; a.out0 = out; a.ld0 = ld; a.group_stride0 = group_stride; a.accumulate = accumulate;
   LCK(tc::gemm_rows_tn(tc::Operand{A, a_rows, Mo, 1}, tc::Operand{B, b_rows, N, 1}, a, M->sm_count, M->st));
+  return MOE_OK;
+}
+#define RC_(call)                        \
+  do {                                   \
+    const int rc_ = (call);              \
+    if (rc_ != MOE_OK) return rc_;       \
+  } while (0)
+// Row ranges of a product whose rows are the reduction, cut into `splits` chunks: meta[g] = min(g * chunk, padded).
+__global__ void split_rows_kernel(int* meta, int splits, int chunk, int padded) {
+  const int g = threadIdx.x;
+  if (g <= splits) meta[g] = min(g * chunk, padded);
+}
+// dst[i] += sum over s (ascending) of part[s][i]
+__global__ void add_partials_kernel(float* __restrict__ dst, const float* __restrict__ part, long long n, int splits) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.f;
+  for (int s = 0; s < splits; ++s) acc += part[(long long)s * n + i];
+  dst[i] += acc;
+}
+
+// Weight gradient of a dense projection over the token rows: out[Mo, N] += A[rows, Mo]^T * B[rows, N].
+// The output is a handful of tiles and the token rows are the reduction, so with one group most SMs idle.  The
+// rows are cut into chunks (one group each, partial results in scratch) so that every SM has a tile; the chunks
+// are then added in order, which keeps the result independent of scheduling.
+int mm_tn_dense(lm_model* M, const void* A, int rows, int Mo, const void* B, int N, float* out, long long ld) {
+  const int tiles = ceil_div(Mo, tc::BM) * ceil_div(N, tc::BN);
+  const int padded = round_up(rows, GROUP_ALIGN);
+  int splits = std::min(16, std::max(1, M->sm_count / std::max(1, tiles)));
+  const int chunk = round_up(ceil_div(padded, splits), GROUP_ALIGN);
+  splits = ceil_div(padded, chunk);
+  if (splits <= 1 || ld != N || (long long)splits * Mo * N > M->split_elems)
+    return mm_tn(M, A, rows, Mo, B, rows, N, dense_meta(M, rows), out, ld, 0, 1);
+  split_rows_kernel<<<1, 32, 0, M->st>>>(M->split_meta, splits, chunk, padded); count_launch();
+  RC_(mm_tn(M, A, rows, Mo, B, rows, N, Meta{M->split_meta, nullptr, splits}, M->split_scratch, N, (long long)Mo * N, 0));
+  const long long n = (long long)Mo * N;
+  add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, M->st>>>(out, M->split_scratch, n, splits); count_launch();
+  LCK(cudaGetLastError());
   return MOE_OK;
 }
 #define RC(call)                         \
@@ -333,6 +376,10 @@ int32_t lm_create(const lm_config_t* config, lm_model_t** out) {
   LCK(cudaGetLastError());
   LCK(cudaMallocHost((void**)&M->ids_pin, (size_t)R * 4)); LCK(cudaMallocHost((void**)&M->targets_pin, (size_t)R * 4));
   LCK(cudaMallocHost((void**)&M->valid_pin, (size_t)R)); LCK(cudaMallocHost((void**)&M->loss_pin, 16));
+  LCK(cudaMallocHost((void**)&M->first_pin, (size_t)R * 4)); LCK(cudaMallocHost((void**)&M->next_pin, (size_t)R * 4));
+  M->last_seen.assign(M->V, -1);
+  M->split_elems = 16ll * std::max<long long>(std::max(QN, HD) * d, 2 * Fp * d);   // at most 16 partial results of the widest matrix
+  LA(M->split_scratch, M->split_elems * 4, false); LA(M->split_meta, 64 * 4, true);
 
   // the MoE blocks: handles of the layer library, bf16 products over f32 master weights
   for (int l = 0; l < M->L; ++l) {
@@ -360,6 +407,8 @@ void lm_destroy(lm_model_t* M) {
   if (M->targets_pin) cudaFreeHost(M->targets_pin);
   if (M->valid_pin) cudaFreeHost(M->valid_pin);
   if (M->loss_pin) cudaFreeHost(M->loss_pin);
+  if (M->first_pin) cudaFreeHost(M->first_pin);
+  if (M->next_pin) cudaFreeHost(M->next_pin);
   for (auto& e : M->ev) if (e) cudaEventDestroy(e);
   if (M->st) cudaStreamDestroy(M->st);
   delete M;
@@ -529,6 +578,20 @@ int prepare_batch(lm_model* M, const uint32_t* ids, const int32_t* lengths, cons
   a.B = B; a.S = S; a.H = M->H; a.Hkv = M->Hkv; a.hd = M->hd; a.g = M->H / M->Hkv;
   a.GR = round_up(a.g * S, GROUP_ALIGN); a.S_pad = round_up(S, 32); a.G = B * M->Hkv;
   b.TQ = (long long)a.G * a.GR; b.KV = (long long)a.G * a.S_pad;
+  if (need_targets) {
+    // chains of the rows that hold the same id, for the deterministic scatter of the embedding gradient
+    for (int r = 0; r < b.rows; ++r) {
+      const uint32_t id = M->ids_pin[r];
+      const int prev = M->last_seen[id];
+      M->first_pin[r] = prev < 0 ? 1 : 0;
+      M->next_pin[r] = -1;
+      if (prev >= 0) M->next_pin[prev] = r;
+      M->last_seen[id] = r;
+    }
+    for (int r = 0; r < b.rows; ++r) M->last_seen[M->ids_pin[r]] = -1;
+    LCK(cudaMemcpyAsync(M->first, M->first_pin, (size_t)b.rows * 4, cudaMemcpyHostToDevice, M->st));
+    LCK(cudaMemcpyAsync(M->next, M->next_pin, (size_t)b.rows * 4, cudaMemcpyHostToDevice, M->st));
+  }
   LCK(cudaMemcpyAsync(M->ids, M->ids_pin, (size_t)b.rows * 4, cudaMemcpyHostToDevice, M->st));
   LCK(cudaMemcpyAsync(M->targets, M->targets_pin, (size_t)b.rows * 4, cudaMemcpyHostToDevice, M->st));
   LCK(cudaMemcpyAsync(M->valid, M->valid_pin, (size_t)b.rows, cudaMemcpyHostToDevice, M->st));
@@ -626,15 +689,15 @@ int backward_blocks(lm_model* M, const Batch& bt) {
       RC(moe_rc(M, b, moe_backward(b.moe, cur, M->dxn, 0, M->st)));
     } else {
       RC(mm_nn(M, cur, rows, d, M->wb + b.wd, Fp, dm, M->dgu, 2 * Fp, tc::EPI_SWIGLU_BWD, b.gu, 2 * Fp));
-      RC(mm_tn(M, cur, rows, d, b.h, rows, Fp, dm, M->g + b.wd, Fp, 0, 1));
+      RC(mm_tn_dense(M, cur, rows, d, b.h, Fp, M->g + b.wd, Fp));
       RC(mm_nn(M, M->dgu, rows, 2 * Fp, M->wb + b.wgu, d, dm, M->dxn, d));
-      RC(mm_tn(M, M->dgu, rows, 2 * Fp, b.xn2, rows, d, dm, M->g + b.wgu, d, 0, 1));
+      RC(mm_tn_dense(M, M->dgu, rows, 2 * Fp, b.xn2, d, M->g + b.wgu, d));
     }
     RC(norm_bwd(M, b.res, b.ffn_norm, M->dxn, M->tmp, rows));
     LCK(lm::launch_add(M->tmp, cur, other, n, M->st));            // dL/dresidual
     // attention branch (attention.rs:404-556)
     RC(mm_nn(M, other, rows, d, M->wb + b.wo, HD, dm, M->d_merged, HD));
-    RC(mm_tn(M, other, rows, d, b.merged, rows, HD, dm, M->g + b.wo, HD, 0, 1));
+    RC(mm_tn_dense(M, other, rows, d, b.merged, HD, M->g + b.wo, HD));
     LCK(lm::launch_tokens_to_heads(M->d_merged, M->do_hm, a, M->st));
     RC(mm_nt(M, M->do_hm, bt.TQ, M->hd, b.v_hm, a.S_pad, am, M->scores, a.S_pad));                       // dL/dP
     RC(mm_tn(M, b.probs, bt.TQ, a.S_pad, M->do_hm, bt.TQ, M->hd, am, M->dv_hm, M->hd, kv_stride, 0));    // dL/dV, summed over the group
@@ -643,7 +706,7 @@ int backward_blocks(lm_model* M, const Batch& bt) {
     RC(mm_tn(M, M->scores, bt.TQ, a.S_pad, b.q_hm, bt.TQ, M->hd, am, M->dk_hm, M->hd, kv_stride, 0));    // dL/dK
     LCK(lm::launch_qkv_grad_unpack(M->dq_hm, M->dk_hm, M->dv_hm, M->cos_t, M->sin_t, M->dqkv, a, M->st));
     RC(mm_nn(M, M->dqkv, rows, M->QN, M->wb + b.wqkv, d, dm, M->dxn, d));
-    RC(mm_tn(M, M->dqkv, rows, M->QN, b.xn1, rows, d, dm, M->g + b.wqkv, d, 0, 1));
+    RC(mm_tn_dense(M, M->dqkv, rows, M->QN, b.xn1, d, M->g + b.wqkv, d));
     RC(norm_bwd(M, M->xs[l], b.attn_norm, M->dxn, M->tmp, rows));
     LCK(lm::launch_add(M->tmp, other, cur, n, M->st));            // dL/dinput of the block
   }
@@ -783,6 +846,114 @@ int32_t lm_last_step_ms(lm_model_t* M, float* ms4) {
 int32_t lm_synchronize(lm_model_t* M) {
   LENTER(M);
   LCK(cudaStreamSynchronize(M->st));
+  return check_device_flag(M);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// KV-cached decode
+// ---------------------------------------------------------------------------
+#include "../../include/kv_attention_b200.h"
+
+struct lm_decoder {
+  std::vector<kv_cache_t*> layers;
+  int sequences = 0, capacity = 0;
+};
+
+extern "C" {
+
+int32_t lm_decoder_create(lm_model_t* M, int32_t sequences, int32_t capacity, lm_decoder_t** out) {
+  LENTER(M);
+  if (!out) return MOE_INVALID_INPUT;
+  *out = nullptr;
+  if (sequences <= 0 || capacity <= 0 || capacity > M->cfg.max_seq_len)
+    return lfail(M, MOE_INVALID_CONFIG, "InvalidConfig: %d sequences of %d positions (max_seq_len %d)", sequences, capacity, M->cfg.max_seq_len);
+  lm_decoder* D = new (std::nothrow) lm_decoder;
+  if (!D) return MOE_OUT_OF_MEMORY;
+  D->sequences = sequences; D->capacity = capacity;
+  for (int l = 0; l < M->L; ++l) {
+    kv_cache_config_t kc{};
+    kc.sequences = sequences; kc.num_heads = M->H; kc.kv_heads = M->Hkv; kc.head_dim = M->hd; kc.capacity = capacity;
+    kc.max_seq_len = M->cfg.max_seq_len; kc.rope_base = M->cfg.rope_base; kc.rope = 1; kc.precision = MOE_PRECISION_BF16; kc.device = M->device;
+    kv_cache_t* c = nullptr;
+    const int rc = kv_cache_create(&kc, &c);
+    if (rc != MOE_OK) {
+      lfail(M, rc, "layer %d cache: %s", l, c ? kv_cache_last_error(c) : "kv_cache_create failed");
+      if (c) kv_cache_destroy(c);
+      for (auto* p : D->layers) kv_cache_destroy(p);
+      delete D;
+      return rc;
+    }
+    D->layers.push_back(c);
+  }
+  *out = D;
+  return MOE_OK;
+}
+
+void lm_decoder_destroy(lm_decoder_t* D) {
+  if (!D) return;
+  for (auto* p : D->layers) kv_cache_destroy(p);
+  delete D;
+}
+
+int32_t lm_decoder_clear(lm_model_t* M, lm_decoder_t* D, int32_t sequence) {
+  LENTER(M);
+  if (!D || sequence >= D->sequences) return lfail(M, MOE_INVALID_INPUT, "InvalidInput: no such sequence");
+  for (auto* c : D->layers) {
+    const int rc = kv_cache_clear(c, sequence, M->st);
+    if (rc != MOE_OK) return lfail(M, rc, "%s", kv_cache_last_error(c));
+  }
+  return MOE_OK;
+}
+
+int32_t lm_forward_cached(lm_model_t* M, lm_decoder_t* D, const uint32_t* ids, int32_t first, int32_t n_seq, int32_t per,
+                          float* logits_host) {
+  LENTER(M);
+  if (!D || (int)D->layers.size() != M->L)
+    return lfail(M, MOE_INVALID_CONFIG, "InvalidConfig: expected one kv cache per layer (%d)", M->L);   // transformer.rs:742-748
+  if (!ids || !logits_host || n_seq <= 0 || per <= 0 || first < 0 || first + n_seq > D->sequences)
+    return lfail(M, MOE_INVALID_INPUT, "InvalidInput: sequences %d .. %d of %d, %d rows each", first, first + n_seq - 1, D->sequences, per);
+  const int rows = n_seq * per, d = M->d, HD = M->H * M->hd, KD = M->Hkv * M->hd, Fp = M->Fd_pad;
+  if (rows > M->cfg.max_batch_rows) return lfail(M, MOE_INVALID_INPUT, "InvalidInput: %d rows exceed max_batch_rows %d", rows, M->cfg.max_batch_rows);
+  for (int r = 0; r < rows; ++r) {
+    if (ids[r] >= (uint32_t)M->V) return lfail(M, MOE_INVALID_INPUT, "TokenOutOfRange: id %u, vocab_size %d", ids[r], M->V);
+    M->ids_pin[r] = ids[r];
+  }
+  LCK(cudaMemcpyAsync(M->ids, M->ids_pin, (size_t)rows * 4, cudaMemcpyHostToDevice, M->st));
+  const Meta dm = dense_meta(M, rows);
+  // temporaries of the training pass double as the decode pass's scratch (the two never overlap in time)
+  bf16 *x = M->dxa, *y = M->dxb, *nrm = M->dxn, *q = M->dqkv, *k = q + (size_t)rows * HD, *v = k + (size_t)rows * KD;
+  LCK(lm::launch_embed_gather(M->ids, M->wb + M->off_emb, x, rows, d, M->st));
+  for (int l = 0; l < M->L; ++l) {
+    lm_block& b = M->blocks[l];
+    // transformer_block.rs:232-244
+    RC(norm_fwd(M, x, b.attn_norm, nrm, rows));
+    RC(mm_nt(M, nrm, rows, d, M->wb + b.wqkv, M->QN, dm, M->qkv, M->QN));
+    LCK(lm::launch_split_qkv(M->qkv, q, k, v, rows, HD, KD, M->st));
+    const int rc = kv_attention_forward_cached(D->layers[l], first, n_seq, q, k, v, per, M->d_merged, M->st);
+    if (rc != MOE_OK) return lfail(M, rc, "%s", kv_cache_last_error(D->layers[l]));
+    RC(mm_nt(M, M->d_merged, rows, HD, M->wb + b.wo, d, dm, M->tmp, d));
+    LCK(lm::launch_add(M->tmp, x, y, (long long)rows * d, M->st));                 // residual
+    RC(norm_fwd(M, y, b.ffn_norm, nrm, rows));
+    if (b.is_moe) {
+      RC(moe_rc(M, b, moe_forward(b.moe, nrm, rows, d, nullptr, y, 1, 0, M->st)));   // adds into the residual
+      std::swap(x, y);
+    } else {
+      RC(mm_nt(M, nrm, rows, d, M->wb + b.wgu, 2 * Fp, dm, M->dgu, Fp, tc::EPI_SWIGLU, nullptr, 0));
+      RC(mm_nt(M, M->dgu, rows, Fp, M->wb + b.wd, d, dm, M->tmp, d));
+      LCK(lm::launch_add(M->tmp, y, x, (long long)rows * d, M->st));
+    }
+  }
+  RC(norm_fwd(M, x, M->off_final_norm, M->xf, rows));
+  RC(mm_nt(M, M->xf, rows, d, M->wb + head_offset(M), M->V_pad, dm, M->logits, M->V_pad));
+  const int slab = (int)std::max<long long>(1, M->stage_elems / M->V);
+  for (int r0 = 0; r0 < rows; r0 += slab) {
+    const int n = std::min(slab, rows - r0);
+    LCK(lm::launch_cast_rows_to_f32(M->logits + (size_t)r0 * M->V_pad, M->V_pad, M->stage, n, M->V, M->st));
+    LCK(cudaMemcpyAsync(logits_host + (size_t)r0 * M->V, M->stage, (size_t)n * M->V * 4, cudaMemcpyDeviceToHost, M->st));
+    LCK(cudaStreamSynchronize(M->st));
+  }
   return check_device_flag(M);
 }
 

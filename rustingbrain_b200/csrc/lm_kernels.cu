@@ -22,20 +22,6 @@ __global__ void embed_gather_kernel(const uint32_t* __restrict__ ids, const bf16
   for (int c = threadIdx.x; c < d / 8; c += blockDim.x) dst[c] = src[c];
 }
 
-__global__ void embed_chain_kernel(const uint32_t* __restrict__ ids, int* __restrict__ first, int* __restrict__ next, int rows) {
-  const int r = blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= rows) return;
-  const uint32_t id = ids[r];
-  int f = 1;
-  for (int s = 0; s < r; ++s)
-    if (ids[s] == id) { f = 0; break; }
-  int n = -1;
-  for (int s = r + 1; s < rows; ++s)
-    if (ids[s] == id) { n = s; break; }
-  first[r] = f;
-  next[r] = n;
-}
-
 __global__ void embed_scatter_kernel(const uint32_t* __restrict__ ids, const bf16* __restrict__ grad_x,
                                      float* __restrict__ grad_table, const int* __restrict__ first,
                                      const int* __restrict__ next, int d) {
@@ -147,28 +133,67 @@ namespace {
 // (reference attention.rs:1024-1041 and :485-497; the scale 1/sqrt(head_dim) of :294-296 is applied here)
 // One warp per row; a row is at most a few KB, so the second and third pass hit L1.
 // ---------------------------------------------------------------------------
+// 16-byte (8 x bf16) accesses: S_pad is a multiple of 32, so a row is a whole number of them.
+__device__ __forceinline__ void unpack8(const uint4& q, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 t = __bfloat1622float2(h[i]); f[2 * i] = t.x; f[2 * i + 1] = t.y; }
+}
+__device__ __forceinline__ uint4 pack8(const float* f) {
+  uint4 q;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return q;
+}
+
 __global__ void __launch_bounds__(256)
 softmax_causal_kernel(const bf16* __restrict__ scores, bf16* __restrict__ probs, AttnShape a, float scale, int causal) {
   const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (long long)a.G * a.GR) return;
   const int within = (int)(row % a.GR);
-  const bf16* src = scores + row * a.S_pad;
-  bf16* dst = probs + row * a.S_pad;
+  const uint4* src = reinterpret_cast<const uint4*>(scores + row * a.S_pad);
+  uint4* dst = reinterpret_cast<uint4*>(probs + row * a.S_pad);
+  const int chunks = a.S_pad / 8;
   if (within >= a.g * a.S) {                      // padding row of the group
-    for (int j = lane; j < a.S_pad; j += 32) dst[j] = tb(0.f);
+    for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
     return;
   }
   const int visible = causal ? within % a.S + 1 : a.S;
+  const int vchunks = (visible + 7) / 8;
   float mx = -INFINITY;
-  for (int j = lane; j < visible; j += 32) mx = fmaxf(mx, bf(src[j]) * scale);
+  for (int c = lane; c < vchunks; c += 32) {
+    float f[8];
+    unpack8(src[c], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) mx = fmaxf(mx, f[i] * scale);
+  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float sum = 0.f;
-  for (int j = lane; j < visible; j += 32) sum += expf(bf(src[j]) * scale - mx);
+  for (int c = lane; c < vchunks; c += 32) {
+    float f[8];
+    unpack8(src[c], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) sum += expf(f[i] * scale - mx);
+  }
   sum = warp_sum(sum);
   const float inv = sum > 0.f ? 1.0f / sum : 1.0f;   // activations.rs:65-69
-  for (int j = lane; j < a.S_pad; j += 32) dst[j] = tb(j < visible ? expf(bf(src[j]) * scale - mx) * inv : 0.f);
+  for (int c = lane; c < chunks; c += 32) {
+    float f[8];
+    if (c < vchunks) {
+      unpack8(src[c], f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = c * 8 + i < visible ? expf(f[i] * scale - mx) * inv : 0.f;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = 0.f;
+    }
+    dst[c] = pack8(f);
+  }
 }
 
 // in place on grad: dL/dscore = p * (dL/dp - sum_j p_j dL/dp_j) * scale
@@ -177,14 +202,23 @@ softmax_backward_kernel(const bf16* __restrict__ probs, bf16* __restrict__ grad,
   const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (long long)a.G * a.GR) return;
-  const bf16* p = probs + row * a.S_pad;
-  bf16* g = grad + row * a.S_pad;
+  const uint4* p = reinterpret_cast<const uint4*>(probs + row * a.S_pad);
+  uint4* g = reinterpret_cast<uint4*>(grad + row * a.S_pad);
+  const int chunks = a.S_pad / 8;
   float dot = 0.f;
-  for (int j = lane; j < a.S_pad; j += 32) dot += bf(p[j]) * bf(g[j]);
+  for (int c = lane; c < chunks; c += 32) {
+    float fp[8], fg[8];
+    unpack8(p[c], fp); unpack8(g[c], fg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot += fp[i] * fg[i];
+  }
   dot = warp_sum(dot);
-  for (int j = lane; j < a.S_pad; j += 32) {
-    const float pj = bf(p[j]);
-    g[j] = tb(pj * (bf(g[j]) - dot) * scale);
+  for (int c = lane; c < chunks; c += 32) {
+    float fp[8], fg[8];
+    unpack8(p[c], fp); unpack8(g[c], fg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fg[i] = fp[i] * (fg[i] - dot) * scale;
+    g[c] = pack8(fg);
   }
 }
 
@@ -229,33 +263,53 @@ __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
   return r;
 }
 
+// ld is a multiple of 32, so a row is a whole number of 16-byte vectors; columns past `vocab` are padding.
 __global__ void __launch_bounds__(256)
 cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss, int vocab,
                      int ld, float inv_predicted) {
   __shared__ float sh[8];
   const int r = blockIdx.x, target = targets[r];
-  bf16* row = logits + (size_t)r * ld;
+  uint4* row = reinterpret_cast<uint4*>(logits + (size_t)r * ld);
+  const int chunks = ld / 8;
   if (target < 0) {                               // predicts nothing: zero gradient, no loss
-    for (int j = threadIdx.x; j < ld; j += blockDim.x) row[j] = tb(0.f);
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) row[c] = make_uint4(0, 0, 0, 0);
     if (threadIdx.x == 0) row_loss[r] = 0.f;
     return;
   }
-  float mx = -INFINITY;
-  for (int j = threadIdx.x; j < vocab; j += blockDim.x) mx = fmaxf(mx, bf(row[j]));
-  mx = block_reduce(mx, sh, true);
-  float sum = 0.f;
-  for (int j = threadIdx.x; j < vocab; j += blockDim.x) sum += expf(bf(row[j]) - mx);
-  sum = block_reduce(sum, sh, false);
+  // one pass: running maximum and the sum of exponentials relative to it
+  float mx = -INFINITY, sum = 0.f;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float f[8];
+    unpack8(row[c], f);
+    float cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < vocab) cm = fmaxf(cm, f[i]);
+    if (cm > mx) { sum *= expf(mx - cm); mx = cm; }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < vocab) sum += expf(f[i] - mx);
+  }
+  const float bm = block_reduce(mx, sh, true);
+  sum = block_reduce(mx > -INFINITY ? sum * expf(mx - bm) : 0.f, sh, false);
   const float inv = sum > 0.f ? 1.0f / sum : 1.0f;
-  if (threadIdx.x == 0) row_loss[r] = -logf(fmaxf(expf(bf(row[target]) - mx) * inv, FLT_MIN));
+  if (threadIdx.x == 0)
+    row_loss[r] = -logf(fmaxf(expf(bf(logits[(size_t)r * ld + target]) - bm) * inv, FLT_MIN));
   __syncthreads();                                // the target's logit has been read before it is overwritten
-  for (int j = threadIdx.x; j < ld; j += blockDim.x) {
-    float g = 0.f;
-    if (j < vocab) {
-      g = expf(bf(row[j]) - mx) * inv * inv_predicted;
-      if (j == target) g -= inv_predicted;
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+    float f[8];
+    unpack8(row[c], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int j = c * 8 + i;
+      float g = 0.f;
+      if (j < vocab) {
+        g = expf(f[i] - bm) * inv * inv_predicted;
+        if (j == target) g -= inv_predicted;
+      }
+      f[i] = g;
     }
-    row[j] = tb(g);
+    row[c] = pack8(f);
   }
 }
 
@@ -291,6 +345,19 @@ __global__ void unpack_kernel(const float* __restrict__ src, float* __restrict__
   dst[i] = src[(long long)(row0 + (kind == 0 ? r : gu_row(kind - 1, r))) * ld + c];
 }
 
+__global__ void split_qkv_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q, bf16* __restrict__ k, bf16* __restrict__ v,
+                                 int qn, int kn) {
+  const int r = blockIdx.x, w = (qn + 2 * kn) / 8;
+  const uint4* src = reinterpret_cast<const uint4*>(qkv + (size_t)r * (qn + 2 * kn));
+  for (int c = threadIdx.x; c < w; c += blockDim.x) {
+    const int col = c * 8;
+    uint4* dst = col < qn ? reinterpret_cast<uint4*>(q + (size_t)r * qn + col)
+                          : col < qn + kn ? reinterpret_cast<uint4*>(k + (size_t)r * kn + (col - qn))
+                                          : reinterpret_cast<uint4*>(v + (size_t)r * kn + (col - qn - kn));
+    *dst = src[c];
+  }
+}
+
 unsigned blocks_for(long long n, int threads) { return (unsigned)((n + threads - 1) / threads); }
 
 }  // namespace
@@ -303,10 +370,9 @@ cudaError_t launch_embed_gather(const uint32_t* ids, const bf16* table, bf16* x,
   embed_gather_kernel<<<rows, 64, 0, st>>>(ids, table, x, d); count_launch();
   return cudaGetLastError();
 }
-cudaError_t launch_embed_scatter(const uint32_t* ids, const bf16* grad_x, float* grad_table, int* first, int* next, int rows,
-                                 int d, cudaStream_t st) {
+cudaError_t launch_embed_scatter(const uint32_t* ids, const bf16* grad_x, float* grad_table, const int* first, const int* next,
+                                 int rows, int d, cudaStream_t st) {
   if (rows <= 0) return cudaSuccess;
-  embed_chain_kernel<<<blocks_for(rows, 128), 128, 0, st>>>(ids, first, next, rows); count_launch();
   embed_scatter_kernel<<<rows, 128, 0, st>>>(ids, grad_x, grad_table, first, next, d); count_launch();
   return cudaGetLastError();
 }
@@ -340,6 +406,11 @@ cudaError_t launch_qkv_grad_unpack(const bf16* dq_hm, const float* dk_hm, const 
 }
 cudaError_t launch_attn_meta(int* meta, int groups, int group_rows, cudaStream_t st) {
   attn_meta_kernel<<<1, 256, 0, st>>>(meta, groups, group_rows); count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_split_qkv(const bf16* qkv, bf16* q, bf16* k, bf16* v, int rows, int qn, int kn, cudaStream_t st) {
+  if (rows <= 0) return cudaSuccess;
+  split_qkv_kernel<<<rows, 64, 0, st>>>(qkv, q, k, v, qn, kn); count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_add(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t st) {

@@ -23,10 +23,11 @@ struct AttnShape {
 };
 
 cudaError_t launch_embed_gather(const uint32_t* ids, const bf16* table, bf16* x, int rows, int d, cudaStream_t st);
-// next[r]: the next row with the same id (-1: none); first[r]: no earlier row has it.  Then one block per first
-// occurrence walks its chain in row order and adds the sum to the gradient row: deterministic, no atomics.
-cudaError_t launch_embed_scatter(const uint32_t* ids, const bf16* grad_x, float* grad_table, int* first, int* next, int rows,
-                                 int d, cudaStream_t st);
+// next[r]: the next row with the same id (-1: none); first[r]: no earlier row has it (both made on the host, where
+// the ids come from).  One block per first occurrence walks its chain in row order and adds the sum to the
+// gradient row: deterministic, no atomics.
+cudaError_t launch_embed_scatter(const uint32_t* ids, const bf16* grad_x, float* grad_table, const int* first, const int* next,
+                                 int rows, int d, cudaStream_t st);
 
 cudaError_t launch_rope_pack(const bf16* qkv, const float* cos_t, const float* sin_t, bf16* q_hm, bf16* k_hm, bf16* v_hm,
                              AttnShape a, cudaStream_t st);
@@ -38,6 +39,8 @@ cudaError_t launch_qkv_grad_unpack(const bf16* dq_hm, const float* dk_hm, const 
                                    const float* sin_t, bf16* dqkv, AttnShape a, cudaStream_t st);
 cudaError_t launch_attn_meta(int* meta, int groups, int group_rows, cudaStream_t st);
 
+// packed [rows, qn + 2 kn] -> q [rows, qn], k [rows, kn], v [rows, kn] (the cached-decode attention takes them apart)
+cudaError_t launch_split_qkv(const bf16* qkv, bf16* q, bf16* k, bf16* v, int rows, int qn, int kn, cudaStream_t st);
 cudaError_t launch_add(const bf16* a, const bf16* b, bf16* out, long long n, cudaStream_t st);
 cudaError_t launch_cast_rows_to_f32(const bf16* src, long long ld, float* dst, int rows, int cols, cudaStream_t st);
 

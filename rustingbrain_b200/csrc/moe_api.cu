@@ -1104,6 +1104,10 @@ int32_t moe_set_weight_q8(moe_layer_t* L, int32_t which, int32_t expert, const i
 int32_t moe_forward(moe_layer_t* L, const void* x, int32_t tokens, int32_t cols, const uint8_t* valid, void* y,
                     int32_t accumulate, int32_t save, void* stream) {
   ENTER(L);
+  // the decode pass of a quantized layer is a chain of six short kernels: let each start under its predecessor's tail
+  static const bool pdl = [] { const char* e = getenv("MOE_B200_PDL"); return !(e && *e == '0'); }();
+  struct Scope { bool on; Scope(bool v) : on(v) { if (on) g_pdl_scope = true; } ~Scope() { if (on) g_pdl_scope = false; } }
+      scope(pdl && L->precision == MOE_PRECISION_Q8);
   return forward_impl(L, x, nullptr, tokens, cols, valid, y, accumulate, save, (cudaStream_t)stream);
 }
 

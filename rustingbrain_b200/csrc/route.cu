@@ -209,6 +209,7 @@ router_kernel(const T* __restrict__ x, const float* __restrict__ w_router, const
               const uint8_t* __restrict__ valid, int tokens, int d, int E, int k, float* __restrict__ logits_out,
               float* __restrict__ probs, float* __restrict__ lse, int* __restrict__ expert_of,
               float* __restrict__ gates, float* partial /*[nb, E+2]*/, int* hist /*[nb,E]*/, RouterFinalize fin) {
+  pdl_enter();
   extern __shared__ float rt_smem[];
   const int ldl = E + 1;
   float* lg = rt_smem;                          // [64][E+1] logits, then probabilities
@@ -476,6 +477,7 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
                const int* __restrict__ cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
                const RowSpace x_perm, const int* __restrict__ dest_base, int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/,
                float* __restrict__ row_gate /*[Rp]*/, int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of) {
+  pdl_enter();
   extern __shared__ int pm_smem[];
   int* cnt = pm_smem;        // [E] running cursors
   int* spos = cnt + E;       // [64*k] padded row of every slot of this block
@@ -623,13 +625,13 @@ static cudaError_t launch_router_ept(const RouterArgs& a, cudaStream_t stream) {
   if (a.logits_in) {
     auto kern = router_kernel<T, EPT, true>;
     if (smem + 16 * 1024 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
-                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
+    launch_kernel(kern, dim3(nb), dim3(RT_THREADS), smem, stream, (const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d,
+                  a.E, a.k, a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
   } else {
     auto kern = router_kernel<T, EPT, false>;
     if (smem + 16 * 1024 > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    kern<<<nb, RT_THREADS, smem, stream>>>((const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d, a.E, a.k,
-                                           a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
+    launch_kernel(kern, dim3(nb), dim3(RT_THREADS), smem, stream, (const T*)a.x, a.w_router, a.logits_in, a.valid, a.tokens, a.d,
+                  a.E, a.k, a.logits_out, a.probs, a.lse, a.expert_of, a.gates, a.partial, a.hist, fin); count_launch();
   }
   return cudaGetLastError();
 }
@@ -669,6 +671,7 @@ cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float
 // tensor-core tile would leave this to one SM and a 16-step dependent pipeline.
 __global__ void __launch_bounds__(128)
 router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits, int d, int E) {
+  pdl_enter();
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * d);
   constexpr int EG = 8;   // experts a warp works on at once: their loads are all in flight together
@@ -707,7 +710,7 @@ router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w
 cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
                                       cudaStream_t stream) {
   if (tokens <= 0) return cudaSuccess;
-  router_logits_rows_kernel<<<tokens, 128, 0, stream>>>((const bf16*)x, (const bf16*)w_bf16, logits, d, E);
+  launch_kernel(router_logits_rows_kernel, dim3(tokens), dim3(128), 0, stream, (const bf16*)x, (const bf16*)w_bf16, logits, d, E);
   count_launch();
   return cudaGetLastError();
 }
@@ -728,9 +731,8 @@ cudaError_t launch_permute(const PermuteArgs& a, int precision, cudaStream_t str
   const dim3 pgrid(nb, nb <= 16 ? 8 : 1);
   if (nb > 0) {
 #define PERMUTE_LAUNCH(T, KMAX)                                                                                   \
-  permute_kernel<T, KMAX><<<pgrid, 256, smem, stream>>>((const T*)a.x, a.expert_of, a.gates, a.cursor, a.meta, a.tokens, \
-                                                        a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token,     \
-                                                        a.row_gate, a.token_of, a.slot_of)
+  launch_kernel(permute_kernel<T, KMAX>, pgrid, dim3(256), smem, stream, (const T*)a.x, a.expert_of, a.gates, a.cursor, a.meta,  \
+                a.tokens, a.d, a.E, a.k, a.x_perm, a.dest_base, a.slot_pos, a.row_token, a.row_gate, a.token_of, a.slot_of)
 #define PERMUTE_BY_K(T)                                                                          \
   do {                                                                                           \
     if (a.k <= 1) PERMUTE_LAUNCH(T, 1);                                                          \

@@ -345,6 +345,25 @@ class TransformerLm:
 
     train_step = train_step_batch
 
+    # -- KV-cached decode ---------------------------------------------------------------------------
+    def new_kv_caches(self, sequences: int = 1, capacity: Optional[int] = None) -> "KvCaches":
+        """One cache per layer (transformer.rs:649-660), for ``sequences`` sequences that decode together."""
+        return KvCaches(self, sequences, capacity if capacity is not None else self.config.max_seq_len)
+
+    def forward_cached(self, ids, caches: "KvCaches", first_sequence: int = 0) -> np.ndarray:
+        """``ids``: one list of new token ids per sequence (equal lengths: the prompts for a prefill, one id each
+        for a decode step), or a flat list for a single sequence.  Returns logits [sequences * rows, vocab]."""
+        if len(ids) and not hasattr(ids[0], "__len__"):
+            ids = [ids]
+        per = len(ids[0])
+        if per == 0 or any(len(s) != per for s in ids):
+            raise InvalidInput("forward_cached takes the same number of new ids for every sequence")
+        flat = np.ascontiguousarray(np.asarray(ids, np.uint32).reshape(-1))
+        logits = np.empty((len(flat), self.config.vocab_size), np.float32)
+        self._ck(_lib.lib().lm_forward_cached(self._h, caches._h, flat.ctypes.data_as(C.c_void_p), first_sequence, len(ids), per,
+                                              logits.ctypes.data_as(C.c_void_p)))
+        return logits
+
     def optimizer_step(self) -> int:
         return int(_lib.lib().lm_optimizer_step(self._h))
 
@@ -363,4 +382,21 @@ class TransformerLm:
         self._ck(_lib.lib().lm_synchronize(self._h))
 
 
-__all__ = ["Adam", "TotalLoss", "TransformerConfig", "TransformerBuilder", "TransformerLm", "TokenBatch", "NetworkError"]
+class KvCaches:
+    """``Vec<KvCache>`` of the reference, batched over sequences; owned by the caller, tied to one model."""
+
+    def __init__(self, model: TransformerLm, sequences: int, capacity: int):
+        self._model, self.sequences, self.capacity = model, sequences, capacity
+        self._h = C.c_void_p()
+        model._ck(_lib.lib().lm_decoder_create(model._h, sequences, capacity, C.byref(self._h)))
+
+    def clear(self, sequence: int = -1) -> None:
+        self._model._ck(_lib.lib().lm_decoder_clear(self._model._h, self._h, sequence))
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            _lib.lib().lm_decoder_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+__all__ = ["KvCaches", "Adam", "TotalLoss", "TransformerConfig", "TransformerBuilder", "TransformerLm", "TokenBatch", "NetworkError"]

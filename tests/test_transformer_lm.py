@@ -199,3 +199,23 @@ def test_errors_follow_the_reference():
     with pytest.raises(InvalidConfig, match="multiple of n_kv_heads"):
         D.TransformerLm.builder().heads(6, 4, 64).build()
     assert D.TransformerLm.builder().parameter_counts() == (55_181_824, 35_717_632)
+
+
+def test_a_prefill_then_cached_decode_reproduces_the_full_forward():  # attention.rs:1318-1362 at model level
+    c = _config()
+    dev, _, _ = _pair(c)
+    seqs = _sequences(c, [24, 24, 24], seed=4)
+    full = dev.forward_batch(seqs).reshape(3, 24, -1)
+    caches = dev.new_kv_caches(sequences=3, capacity=32)
+    got = np.empty_like(full)
+    got[:, :16] = dev.forward_cached([s[:16] for s in seqs], caches).reshape(3, 16, -1)     # prefill
+    for t in range(16, 24):                                                                 # one token per sequence
+        got[:, t] = dev.forward_cached([[s[t]] for s in seqs], caches)
+    assert rel_l2(got, full) <= TOL
+    # a cleared slot restarts at position 0 while the others keep their state
+    caches.clear(1)
+    again = dev.forward_cached([seqs[1][:8]], caches, first_sequence=1).reshape(8, -1)
+    assert rel_l2(again, full[1, :8]) <= TOL
+    with pytest.raises(InvalidInput, match="SequenceTooLong"):
+        dev.forward_cached([list(seqs[0][:10])], caches, first_sequence=0)                  # 24 + 10 > 32
+    dev.close()
