@@ -146,6 +146,33 @@ __global__ void swiglu_bwd_f32_kernel(const float* __restrict__ dh, const float*
   o[gu_row(1, f)] = up * siluf_(g);
 }
 
+// f32 -> three bf16 pieces (value = hi + mid + lo to 24 bits: each piece is the bf16 rounding of what the earlier
+// ones left), laid out along the reduction as six segments of `cols` so that ONE bf16 tensor-core product of an
+// A-pattern matrix with a B-pattern matrix adds the six significant cross terms with f32 accumulation:
+//   A pattern  [hi | hi | mid | mid | hi | lo ]
+//   B pattern  [hi | mid| hi  | mid | lo | hi ]      ->  hi*hi + hi*mid + mid*hi + mid*mid + hi*lo + lo*hi
+// The dropped terms (mid*lo, lo*mid, lo*lo) are below 2^-24 of the product.
+__global__ void expand3_kernel(const float* __restrict__ src, bf16* __restrict__ dst, long long rows, int cols, int b_pattern) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * cols) return;
+  const long long r = i / cols;
+  const int c = (int)(i - r * cols);
+  const float a = src[i];
+  const bf16 hi = __float2bfloat16_rn(a);
+  const float r1 = a - __bfloat162float(hi);
+  const bf16 mid = __float2bfloat16_rn(r1);
+  const bf16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+  bf16* d = dst + r * 6 * cols + c;
+  if (b_pattern) { d[0] = hi; d[cols] = mid; d[2 * cols] = hi; d[3 * cols] = mid; d[4 * cols] = lo; d[5 * cols] = hi; }
+  else { d[0] = hi; d[cols] = hi; d[2 * cols] = mid; d[3 * cols] = mid; d[4 * cols] = hi; d[5 * cols] = lo; }
+}
+cudaError_t launch_expand3(const float* src, bf16* dst, long long rows, int cols, int b_pattern, cudaStream_t stream) {
+  const long long n = rows * cols;
+  if (n <= 0) return cudaSuccess;
+  expand3_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(src, dst, rows, cols, b_pattern); count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_swiglu_fwd_f32(const float* gu, float* h, long long rows, int f_pad, cudaStream_t stream) {
   const long long n = rows * f_pad;
   if (n <= 0) return cudaSuccess;

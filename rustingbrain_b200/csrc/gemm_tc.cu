@@ -352,7 +352,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
       store32_bf16_staged(out + col + GU_BLOCK, p.ld0, u, stg, lane);
     }
   } else if (EPI == EPI_STORE_F32) {
-    // f32 output with a row limit (p.M) and any column count: used for the router logits.
+    // f32 output with a row limit (p.M) and any column count: the router logits, and the products of the f32
+    // configuration (operands split into three bf16 pieces each, see moe_api.cu).
     const long long row = (long long)tl.row0 + row_in_tile;
     float* out = (float*)p.out0 + row * p.ld0;
 #pragma unroll 1
@@ -360,15 +361,41 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
       if (tl.n0 + c >= p.N) break;
       float v[32];
       tmem_ld32(taddr + c, v);
-      if (row < p.M) {
+      if (tl.n0 + c + 32 <= p.N && (p.ld0 & 3) == 0) {
+        // a whole block of 32 columns: through the staging tile, 8 rows x 64 contiguous bytes per store instruction
+        const long long row_warp = (long long)tl.row0 + (row_in_tile & ~31);
+        float* out_warp = (float*)p.out0 + row_warp * p.ld0 + tl.n0 + c;
+#pragma unroll
+        for (int hseg = 0; hseg < 2; ++hseg) {
+          uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            mine[i] = make_uint4(__float_as_uint(v[16 * hseg + 4 * i]), __float_as_uint(v[16 * hseg + 4 * i + 1]),
+                                 __float_as_uint(v[16 * hseg + 4 * i + 2]), __float_as_uint(v[16 * hseg + 4 * i + 3]));
+          __syncwarp();
+#pragma unroll
+          for (int it = 0; it < 4; ++it) {
+            const int r = it * 8 + (lane >> 2), ch = lane & 3;
+            if (row_warp + r < p.M) {
+              const uint4 q = *reinterpret_cast<const uint4*>(stg + r * STG_PITCH + ch * 16);
+              float4 o4 = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+              float4* dst = reinterpret_cast<float4*>(out_warp + (long long)r * p.ld0 + 16 * hseg + 4 * ch);
+              if (p.accumulate) {   // f32 addition on the CUDA cores, round to nearest
+                const float4 old = *dst;
+                o4.x += old.x; o4.y += old.y; o4.z += old.z; o4.w += old.w;
+              }
+              *dst = o4;
+            }
+          }
+          __syncwarp();
+        }
+      } else if (row < p.M) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (tl.n0 + c + i < p.N) out[tl.n0 + c + i] = v[i];
+          if (tl.n0 + c + i < p.N) out[tl.n0 + c + i] = p.accumulate ? out[tl.n0 + c + i] + v[i] : v[i];
       }
     }
   } else {  // EPI_ACCUM_F32
-    const int m = tl.m0 + row_in_tile;
-    float* out = (float*)p.out0 + (long long)tl.group * p.group_stride0 + (long long)m * p.ld0;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; c += 32) {
       if (tl.n0 + c >= p.N) break;
@@ -379,17 +406,34 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
-      if (m < p.M) {
-        float4* o4 = reinterpret_cast<float4*>(out + tl.n0 + c);
+      // Through the warp's staging tile, 16 columns (64 bytes per row) at a time: a lane holds one ROW, so direct
+      // stores would touch 32 rows per instruction, 16 bytes each; staged, an instruction covers 8 rows x 64
+      // contiguous bytes (and the read-modify-write of the accumulate mode loads the same way).
+      const int m_warp = tl.m0 + (row_in_tile & ~31);
+      float* out_warp = (float*)p.out0 + (long long)tl.group * p.group_stride0 + (long long)m_warp * p.ld0 + tl.n0 + c;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          float4 r = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-          if (p.accumulate) {
-            const float4 o = o4[i];
-            r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
+      for (int hseg = 0; hseg < 2; ++hseg) {
+        uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          mine[i] = make_uint4(__float_as_uint(v[16 * hseg + 4 * i]), __float_as_uint(v[16 * hseg + 4 * i + 1]),
+                               __float_as_uint(v[16 * hseg + 4 * i + 2]), __float_as_uint(v[16 * hseg + 4 * i + 3]));
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int row = it * 8 + (lane >> 2), ch = lane & 3;
+          if (m_warp + row < p.M) {
+            const uint4 q = *reinterpret_cast<const uint4*>(stg + row * STG_PITCH + ch * 16);
+            float4 r = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+            float4* o = reinterpret_cast<float4*>(out_warp + (long long)row * p.ld0 + 16 * hseg + 4 * ch);
+            if (p.accumulate) {
+              const float4 old = *o;
+              r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+            }
+            *o = r;
           }
-          o4[i] = r;
         }
+        __syncwarp();
       }
     }
   }
@@ -870,7 +914,8 @@ static bool make_map(CUtensorMap* map, const Operand& op, int box_cols, int box_
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t dims[3] = {(cuuint64_t)op.cols, (cuuint64_t)op.rows, (cuuint64_t)op.groups};
-  cuuint64_t strides[2] = {(cuuint64_t)op.cols * 2, (cuuint64_t)op.cols * (cuuint64_t)op.rows * 2};
+  const cuuint64_t ld = (cuuint64_t)(op.ld > 0 ? op.ld : op.cols);
+  cuuint64_t strides[2] = {ld * 2, ld * (cuuint64_t)op.rows * 2};
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, three_d ? 3 : 2, const_cast<void*>(op.ptr), dims,
@@ -880,7 +925,8 @@ static bool make_map(CUtensorMap* map, const Operand& op, int box_cols, int box_
 }
 
 static bool operand_ok(const Operand& op) {
-  return op.ptr && ((uintptr_t)op.ptr & 15) == 0 && op.cols > 0 && (op.cols % 8) == 0 && op.rows > 0 && op.groups > 0;
+  return op.ptr && ((uintptr_t)op.ptr & 15) == 0 && op.cols > 0 && (op.cols % 8) == 0 && op.rows > 0 && op.groups > 0 &&
+         (op.ld == 0 || (op.ld >= op.cols && op.ld % 8 == 0));
 }
 
 static int g_pair_mode = -1;   // -1: read MOE_B200_TC_PAIR from the environment on first use

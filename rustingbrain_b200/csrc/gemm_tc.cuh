@@ -43,6 +43,7 @@ struct Operand {
   long long rows;      // rows per group (or total rows for row-indexed operands)
   long long cols;      // contiguous dimension
   long long groups;    // 1 for row-indexed operands
+  long long ld = 0;    // elements between consecutive rows (0: cols); lets a product read a column range of a wider matrix
 };
 
 // Two-SM tiles (cta_group::2, clusters of two CTAs) instead of one-SM tiles; also MOE_B200_TC_PAIR=1.

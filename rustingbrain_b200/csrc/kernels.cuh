@@ -98,6 +98,8 @@ cudaError_t simt_gemm_tn(const SimtGemmArgs& a, cudaStream_t stream);
 
 // h[r, f] = silu(g) * u from the interleaved (g|u) rows; f32 path only (the bf16
 // path fuses this into the GEMM epilogue).
+// f32 [rows, cols] -> bf16 [rows, 6 * cols]: three bf16 pieces per value in the A or B segment pattern (gemm_simt.cu)
+cudaError_t launch_expand3(const float* src, bf16* dst, long long rows, int cols, int b_pattern, cudaStream_t stream);
 cudaError_t launch_swiglu_fwd_f32(const float* gu, float* h, long long rows, int f_pad, cudaStream_t stream);
 cudaError_t launch_swiglu_bwd_f32(const float* dh, const float* gu, float* dgu, long long rows, int f_pad,
                                   cudaStream_t stream);

@@ -45,6 +45,12 @@ struct moe_layer {
   float* w_eff = nullptr;            // f32 handles: W + scale * up * down for the expert GEMMs
   float* wc = nullptr;               // f32 weights the expert GEMMs read: w, or w_eff with adapters
   bool lora_dirty = false;           // adapters or base weights changed since the last fold
+  // f32 handles whose shapes fit the tensor-core tiles run their FORWARD expert products on tcgen05 with every
+  // operand split into three bf16 pieces (f32-level accuracy, six cross terms in one product): expanded weights
+  // [.., 6 * in] at 6 x the arena offsets, refreshed when `w3_dirty`; expanded activations per call
+  moe::bf16* w3 = nullptr;
+  moe::bf16 *xa3 = nullptr, *ha3 = nullptr;
+  bool w3_dirty = true;
 
   // int8 inference weights (Q8 precision)
   int8_t* q_gu = nullptr; float* s_gu = nullptr;   // [E][2F_pad][d], [E][2F_pad]
@@ -75,6 +81,9 @@ struct moe_layer {
   void* dx_r = nullptr;           // [shared_rows_cap, d] router input gradient
   bool tc_router = false;         // router products on the tensor cores (bf16, E % 8 == 0)
   int rw_splits = 1;
+  float* sh_scratch = nullptr;    // partial weight gradients of the row-split shared-expert products
+  long long sh_scratch_elems = 0;
+  int* sh_meta = nullptr;         // [splits + 1] token-chunk boundaries of those products
   int* rw_meta = nullptr;         // [splits + 1] token-chunk boundaries of the split router weight gradient
 
   // expert parallelism (ep_size > 1): the send side keeps the compact expert-major

@@ -397,6 +397,44 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
     tc::Operand A2{io.h, G.cap_rows, Fp, 1};
     tc::Operand B2{L->wb + io.w_d, d, Fp, G.n_groups};
     { Span sp(L, routed ? 3 : -1, st); CK(tc::gemm_rows_nt(A2, B2, b, tc::EPI_STORE, L->sm_count, st)); }
+  } else if (L->w3) {
+    // f32 on the tensor cores: three bf16 pieces per operand, six cross terms along a reduction six times as long
+    if (L->w3_dirty) {
+      const int El = L->E_local;
+      CK(launch_expand3(L->wc + L->off_gu, L->w3 + 6 * L->off_gu, (long long)El * 2 * Fp, d, 1, st));
+      CK(launch_expand3(L->wc + L->off_d, L->w3 + 6 * L->off_d, (long long)El * d, Fp, 1, st));
+      if (L->shared) {
+        CK(launch_expand3(L->wc + L->off_sgu, L->w3 + 6 * L->off_sgu, 2ll * Fp, d, 1, st));
+        CK(launch_expand3(L->wc + L->off_sd, L->w3 + 6 * L->off_sd, (long long)d, Fp, 1, st));
+      }
+      L->w3_dirty = false;
+    }
+    tc::GemmArgs a{};
+    a.group_row0 = G.row0; a.tile_start = G.tstart; a.n_groups = G.n_groups; a.error_flag = L->error_flag;
+    a.N = 2 * Fp; a.K = 6 * d; a.M = G.cap_rows; a.out0 = io.gu; a.ld0 = 2 * Fp;
+    { Span sp(L, routed ? 2 : -1, st);
+      CK(launch_expand3((const float*)io.x, L->xa3, G.in_rows, d, 0, st));
+      // The tensor core adds into its accumulator with truncation, a bias that grows with the number of additions:
+      // the leading term (hi x hi, first segment) therefore gets a product of its own over the short reduction, and
+      // the five small cross terms are accumulated apart and added to it in f32 by the epilogue.
+      a.K = d; a.accumulate = 0;
+      CK(tc::gemm_rows_nt(tc::Operand{L->xa3, G.in_rows, d, 1, 6 * d}, tc::Operand{L->w3 + 6 * io.w_gu, 2 * Fp, d, G.n_groups, 6 * d}, a,
+                          tc::EPI_STORE_F32, L->sm_count, st));
+      a.K = 5 * d; a.accumulate = 1;
+      CK(tc::gemm_rows_nt(tc::Operand{L->xa3 + d, G.in_rows, 5 * d, 1, 6 * d},
+                          tc::Operand{L->w3 + 6 * io.w_gu + d, 2 * Fp, 5 * d, G.n_groups, 6 * d}, a, tc::EPI_STORE_F32, L->sm_count, st));
+      CK(launch_swiglu_fwd_f32((const float*)io.gu, (float*)io.h, G.cap_rows, Fp, st)); }
+    tc::GemmArgs b{};
+    b.group_row0 = G.row0; b.tile_start = G.tstart; b.n_groups = G.n_groups; b.error_flag = L->error_flag;
+    b.N = d; b.K = 6 * Fp; b.M = G.cap_rows; b.out0 = io.y; b.ld0 = d;
+    { Span sp(L, routed ? 3 : -1, st);
+      CK(launch_expand3((const float*)io.h, L->ha3, G.cap_rows, Fp, 0, st));
+      b.K = Fp; b.accumulate = 0;
+      CK(tc::gemm_rows_nt(tc::Operand{L->ha3, G.cap_rows, Fp, 1, 6 * Fp}, tc::Operand{L->w3 + 6 * io.w_d, d, Fp, G.n_groups, 6 * Fp}, b,
+                          tc::EPI_STORE_F32, L->sm_count, st));
+      b.K = 5 * Fp; b.accumulate = 1;
+      CK(tc::gemm_rows_nt(tc::Operand{L->ha3 + Fp, G.cap_rows, 5 * Fp, 1, 6 * Fp},
+                          tc::Operand{L->w3 + 6 * io.w_d + Fp, d, 5 * Fp, G.n_groups, 6 * Fp}, b, tc::EPI_STORE_F32, L->sm_count, st)); }
   } else {
     SimtGemmArgs a{};
     a.A = (const float*)io.x; a.B = L->wc + io.w_gu; a.C = (float*)io.gu;
@@ -410,6 +448,42 @@ int experts_forward(moe_layer* L, const Groups& G, const ExpertIO& io, bool save
     b.N = d; b.K = Fp; b.b_group_stride = (long long)d * Fp;
     { Span sp(L, routed ? 3 : -1, st); CK(simt_gemm_nt(b, st)); }
   }
+  return MOE_OK;
+}
+
+// Weight gradient of the dense (shared expert) group: the output is a handful of tiles and the token rows are the
+// reduction, so as one group it would keep a dozen SMs busy.  When the tiles do not fill the GPU the rows are cut
+// into chunks (one group each, partial results in scratch) and the chunks are added in order afterwards.
+__global__ void split_rows_kernel(int* meta, int splits, int chunk, int padded) {
+  const int g = threadIdx.x;
+  if (g <= splits) meta[g] = min(g * chunk, padded);
+}
+__global__ void add_partials_kernel(float* __restrict__ dst, const float* __restrict__ part, long long n, int splits, int accumulate) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = accumulate ? dst[i] : 0.f;
+  for (int s = 0; s < splits; ++s) acc += part[(long long)s * n + i];
+  dst[i] = acc;
+}
+int dense_wgrad(moe_layer* L, const tc::Operand& A, const tc::Operand& B, int rows, int M, int N, float* out, int acc, cudaStream_t st) {
+  const int tiles = ceil_div(M, tc::BM) * ceil_div(N, tc::BN);
+  const int padded = round_up(rows, GROUP_ALIGN);
+  int splits = std::min(16, std::max(1, L->sm_count / std::max(1, tiles)));
+  const int chunk = round_up(ceil_div(padded, splits), GROUP_ALIGN);
+  splits = ceil_div(padded, chunk);
+  tc::GemmArgs w{};
+  w.error_flag = L->error_flag; w.M = M; w.N = N; w.ld0 = N;
+  if (splits <= 1 || !L->sh_scratch || (long long)splits * M * N > L->sh_scratch_elems) {
+    w.group_row0 = L->shared_meta; w.n_groups = 1; w.out0 = out; w.group_stride0 = (long long)M * N; w.accumulate = acc;
+    CK(tc::gemm_rows_tn(A, B, w, L->sm_count, st));
+    return MOE_OK;
+  }
+  split_rows_kernel<<<1, 32, 0, st>>>(L->sh_meta, splits, chunk, padded); count_launch();
+  w.group_row0 = L->sh_meta; w.n_groups = splits; w.out0 = L->sh_scratch; w.group_stride0 = (long long)M * N; w.accumulate = 0;
+  CK(tc::gemm_rows_tn(A, B, w, L->sm_count, st));
+  const long long n = (long long)M * N;
+  add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, L->sh_scratch, n, splits, acc); count_launch();
+  CK(cudaGetLastError());
   return MOE_OK;
 }
 
@@ -438,7 +512,9 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     wd.M = d; wd.N = Fp; wd.out0 = L->g + io.w_d; wd.ld0 = Fp; wd.group_stride0 = (long long)d * Fp; wd.accumulate = acc;
     tc::Operand Ad{io.dy, G.in_rows, d, 1};
     tc::Operand Bd{io.h, G.cap_rows, Fp, 1};
-    { Span sp(L, routed ? 7 : -1, st); CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st)); }
+    { Span sp(L, routed ? 7 : -1, st);
+      if (routed) CK(tc::gemm_rows_tn(Ad, Bd, wd, L->sm_count, st));
+      else { const int r_ = dense_wgrad(L, Ad, Bd, G.in_rows, d, Fp, L->g + io.w_d, acc, st); if (r_ != MOE_OK) return r_; } }
     }
     if (parts & 1) {
     tc::GemmArgs b{};
@@ -454,7 +530,9 @@ int experts_backward(moe_layer* L, const Groups& G, const ExpertIO& io, cudaStre
     wg.M = 2 * Fp; wg.N = d; wg.out0 = L->g + io.w_gu; wg.ld0 = d; wg.group_stride0 = 2ll * Fp * d; wg.accumulate = acc;
     tc::Operand Ag{io.dgu, G.cap_rows, 2 * Fp, 1};
     tc::Operand Bg{io.x, G.in_rows, d, 1};
-    { Span sp(L, routed ? 9 : -1, st); CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st)); }
+    { Span sp(L, routed ? 9 : -1, st);
+      if (routed) CK(tc::gemm_rows_tn(Ag, Bg, wg, L->sm_count, st));
+      else { const int r_ = dense_wgrad(L, Ag, Bg, G.in_rows, 2 * Fp, d, L->g + io.w_gu, acc, st); if (r_ != MOE_OK) return r_; } }
     }
   } else {
     if (parts & 1) {
@@ -876,6 +954,16 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     }
     if (L->act == PREC_BF16) DA(L->wb, L->n_params * 2, true);
   }
+  {
+    // f32 handle, shapes that fit the tensor-core tiles: forward expert products on tcgen05 (MOE_B200_F32_TC=0: FMA kernels)
+    static const bool f32_tc = [] { const char* e = getenv("MOE_B200_F32_TC"); return !(e && *e == '0'); }();
+    if (f32_tc && L->act == PREC_F32 && L->precision == MOE_PRECISION_F32 && d % 32 == 0 && L->ep_size == 1 && L->E_local <= 256) {
+      DA(L->w3, 6 * L->n_params * 2, true);
+      const long long rows = std::max<long long>(L->rows_cap, L->shared_rows_cap);
+      DA(L->xa3, rows * 6 * d * 2, true);
+      DA(L->ha3, rows * 6 * Fp * 2, true);
+    }
+  }
   L->stage_elems = std::max((long long)E * d, 2ll * Fp * d);
   DA(L->stage, L->stage_elems * 4 * 2, false);
 
@@ -941,6 +1029,15 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     }
     DA(L->grad_gates, T * k * 4, true); DA(L->grad_logits, T * E * 4, true);
     if (L->tc_router) { DA(L->gl_bf16, T * E * 2, true); DA(L->dx_r, sc * d * es, true); }
+    if (L->shared && L->act == PREC_BF16) {
+      const int tiles = std::min(ceil_div(2 * (int)Fp, tc::BM) * ceil_div((int)d, tc::BN), ceil_div((int)d, tc::BM) * ceil_div((int)Fp, tc::BN));
+      if (tiles < L->sm_count) {
+        const int splits = std::min(16, std::max(1, L->sm_count / std::max(1, tiles)));
+        L->sh_scratch_elems = (long long)splits * 2 * Fp * d;
+        DA(L->sh_scratch, L->sh_scratch_elems * 4, false);
+        DA(L->sh_meta, 32 * 4, true);
+      }
+    }
     L->rw_splits = (int)std::min<long long>(64, std::max<long long>(1, T / 256));
     DA(L->rw_scratch, (long long)L->rw_splits * E * d * 4, false);
     DA(L->rw_meta, 130 * 4, true);
@@ -1005,6 +1102,7 @@ int32_t moe_set_weight_f32(moe_layer_t* L, int32_t which, int32_t expert, const 
   }
   pack_kernel<<<(unsigned)((n + 255) / 256), 256>>>(dev_src, L->w + s.offset, L->wb ? L->wb + s.offset : nullptr, rows, cols, s.ld, s.kind); count_launch();
   if (L->lora_rank > 0) L->lora_dirty = true;
+  L->w3_dirty = true;
   CK(cudaGetLastError());
   CK(cudaDeviceSynchronize());
   return MOE_OK;
@@ -1150,6 +1248,7 @@ int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, f
   a.c1 = 1.0f - powf(b1, (float)step);
   a.c2 = 1.0f - powf(b2, (float)step);
   { Span sp(L, 15, st); CK(launch_adam(a, st)); }
+  L->w3_dirty = true;
   L->grad_valid = false;   // the kernel cleared the gradients
   return MOE_OK;
 }
@@ -1416,6 +1515,7 @@ int32_t moe_lora_merge(moe_layer_t* L) {
   count_launch();
   CK(cudaGetLastError());
   CK(cudaDeviceSynchronize());
+  L->w3_dirty = true;
   L->lora_rank = 0;          // the arenas stay allocated until the handle is destroyed
   L->lora_dirty = false;
   L->wc = L->w;
