@@ -639,7 +639,8 @@ def run_layer(args, w, torch, dist, world, rank, local, device, with_e2e, with_c
     es = 4 if w["precision"] == "f32" else 2
     if w["precision"] == "f32":
         roof = {"bound": "hbm", "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None, "traffic": None,
-                "note": "the f32 configuration runs its products as f32 FMA on the CUDA cores (1e-5 parity bar), so no tensor-core roofline applies"}
+                "note": "f32 configuration (1e-5 parity bar): forward expert products on tcgen05 with three bf16 pieces per operand "
+                        "(6 x the bf16 FLOPs), backward as f32 FMA on the CUDA cores; no single roofline applies to the step"}
     else:
         ach = gemm_flops / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
         # Operand and result bytes of the six launches (every matrix once): activations R x {d, F, 2F} in

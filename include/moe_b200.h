@@ -110,7 +110,9 @@ int32_t moe_get_weight_f32(moe_layer_t* layer, int32_t which, int32_t expert, fl
 int32_t moe_get_grad_f32(moe_layer_t* layer, int32_t which, int32_t expert, float* host, int32_t rows, int32_t cols);
 int32_t moe_get_moments_f32(moe_layer_t* layer, int32_t which, int32_t expert, float* m_host, float* v_host, int32_t rows, int32_t cols);
 int32_t moe_set_moments_f32(moe_layer_t* layer, int32_t which, int32_t expert, const float* m_host, const float* v_host, int32_t rows, int32_t cols);
-/* Quantized (quantized.rs:17-24): int8 [rows, cols] + f32 scale[rows], w ~ q * scale. MOE_PRECISION_Q8 handles only. */
+/* Quantized (quantized.rs:17-24): int8 [rows, cols] + f32 scale[rows], w ~ q * scale. MOE_PRECISION_Q8 handles only.
+ * MOE_W_ROUTER is accepted too (TransformerLm::quantize quantizes the router as well, transformer.rs:899-910): the
+ * router then computes with the values q * scale. */
 int32_t moe_set_weight_q8(moe_layer_t* layer, int32_t which, int32_t expert, const int8_t* q_host, const float* scale_host, int32_t rows, int32_t cols);
 
 /* MoeLayer::forward_train / forward (moe.rs:237-341), device pointers.

@@ -957,7 +957,10 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   {
     // f32 handle, shapes that fit the tensor-core tiles: forward expert products on tcgen05 (MOE_B200_F32_TC=0: FMA kernels)
     static const bool f32_tc = [] { const char* e = getenv("MOE_B200_F32_TC"); return !(e && *e == '0'); }();
-    if (f32_tc && L->act == PREC_F32 && L->precision == MOE_PRECISION_F32 && d % 32 == 0 && L->ep_size == 1 && L->E_local <= 256) {
+    // (reductions of at most 2048: the tensor core adds into its accumulator with truncation, a bias of about
+    // 2^-25 per 16 reduction elements, which stays below the 1e-5 bar up to there)
+    if (f32_tc && L->act == PREC_F32 && L->precision == MOE_PRECISION_F32 && d % 32 == 0 && d <= 2048 && Fp <= 2048 &&
+        L->ep_size == 1 && L->E_local <= 256) {
       DA(L->w3, 6 * L->n_params * 2, true);
       const long long rows = std::max<long long>(L->rows_cap, L->shared_rows_cap);
       DA(L->xa3, rows * 6 * d * 2, true);
@@ -1181,7 +1184,20 @@ int32_t moe_set_weight_q8(moe_layer_t* L, int32_t which, int32_t expert, const i
     case MOE_W_SHARED_GATE: kind = 1; group = L->E; break;
     case MOE_W_SHARED_UP: kind = 2; group = L->E; break;
     case MOE_W_SHARED_DOWN: down = true; ld = Fp; group = L->E; break;
-    default: L->err = "InvalidInput: the router of a quantized layer stays f32 (moe_set_weight_f32)"; return MOE_INVALID_INPUT;
+    case MOE_W_ROUTER: {
+      // TransformerLm::quantize also quantizes the router (transformer.rs:899-910).  Its product is tiny, so the
+      // int8 grid is kept by value: the router's weights become q * scale (quantized.rs:17-24) and run on the
+      // ordinary router path; the logits are those of the reference's Quantized::matmul up to summation order.
+      if (rows != L->E || cols != L->d) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }
+      std::vector<int8_t> hq((size_t)rows * cols);
+      std::vector<float> hs((size_t)rows), hw((size_t)rows * cols);
+      CK(cudaMemcpy(hq.data(), q, hq.size(), cudaMemcpyDefault));
+      CK(cudaMemcpy(hs.data(), scale, hs.size() * 4, cudaMemcpyDefault));
+      for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c) hw[(size_t)r * cols + c] = (float)hq[(size_t)r * cols + c] * hs[r];
+      return moe_set_weight_f32(L, MOE_W_ROUTER, 0, hw.data(), rows, cols);
+    }
+    default: L->err = "InvalidInput: unknown weight id"; return MOE_INVALID_INPUT;
   }
   if (group < 0 || group > L->E || (group == L->E && !L->shared)) { L->err = "InvalidInput: no such expert"; return MOE_INVALID_INPUT; }
   if ((!down && (rows != F || cols != d)) || (down && (rows != d || cols != F))) { L->err = "InvalidInput: weight shape mismatch"; return MOE_INVALID_INPUT; }

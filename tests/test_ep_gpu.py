@@ -169,3 +169,35 @@ def test_rows_beyond_a_ranks_capacity_are_refused_on_every_rank(transport):
         ret = mgr.dict()
         mp.spawn(_overflow_worker, args=(2, port, transport, ret), nprocs=2, join=True)
         assert dict(ret) == {0: True, 1: True}
+
+
+def test_one_process_can_hold_layers_on_two_devices():
+    """The opt-in to large dynamic shared memory is a per-device attribute of the tensor-core kernels: a second
+    device used from the same process must get it too (bf16 layer -> grouped GEMM; head_dim 128 cache -> the
+    decode-attention kernel with 96 KB of shared memory)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from helpers import seeded_weights
+    from rustingbrain_b200 import MoeConfig, MoeLayer
+    from rustingbrain_b200.kv_attention import KvCache
+    d, E, k, F, T = 128, 4, 2, 64, 96
+    w = seeded_weights(d, E, F, False, 5, std=0.05, router_std=0.05)
+    x = np.random.Generator(np.random.Philox(9)).standard_normal((T, d)).astype(np.float32)
+    outs = []
+    for dev in (0, 1):
+        torch.cuda.set_device(dev)
+        layer = MoeLayer(d, MoeConfig(E, k, F), precision="bf16", max_tokens=T, device=dev, training=False)
+        layer.set_weights(w["router"], w["gate"], w["up"], w["down"], None)
+        y = layer.forward(torch.from_numpy(x).to("cuda:%d" % dev).bfloat16())
+        layer.synchronize()
+        outs.append(y.float().cpu().numpy())
+        cache = KvCache(2, 4, 2, 128, capacity=64, precision="bf16", device=dev)
+        q = torch.randn(2, 4 * 128, device="cuda:%d" % dev).bfloat16()
+        kv = torch.randn(2, 2 * 128, device="cuda:%d" % dev).bfloat16()
+        out = cache.forward_cached(q, kv, kv.clone())
+        torch.cuda.synchronize(dev)
+        assert bool(torch.isfinite(out.float()).all())
+        layer.close()
+    torch.cuda.set_device(0)
+    assert np.array_equal(outs[0], outs[1])

@@ -48,6 +48,26 @@ def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
     assert torch.equal(y, y2)
 
 
+def test_a_quantized_router_routes_like_the_checkers():  # transformer.rs:899-910: quantize() includes the router
+    T, d, E, k, F = 48, 128, 8, 2, 64
+    dev, ora, x = _pair(T, d, E, k, F, True, seed=12)
+    g = np.random.Generator(np.random.Philox(13))
+    q = g.integers(-127, 128, (E, d)).astype(np.int8)
+    s = g.uniform(1e-3, 4e-3, E).astype(np.float32)
+    dev.set_weight_q8(ROUTER, 0, q, s)
+    ora.set_weight_q8(ROUTER, 0, q, s)
+    np.testing.assert_allclose(dev.get_weight(ROUTER), q.astype(np.float32) * s[:, None], rtol=0, atol=0)
+    xd = torch.from_numpy(x).cuda().bfloat16()
+    y, cache = dev.forward_train(xd)
+    logits = dev.router_cache(T)[0]
+    yo = ora.forward(xd.float().cpu().numpy(), logits=logits)
+    assert np.array_equal(cache.routing()[0], ora.routing()[0])
+    assert rel_l2(y.float().cpu().numpy(), yo) <= 2e-2
+    # the devices' own logits are those of the quantized router to bf16 rounding of its weights
+    want = xd.float().cpu().numpy() @ (q.astype(np.float32) * s[:, None]).T
+    assert rel_l2(logits, want) <= 1e-2
+
+
 def test_activations_beyond_the_f16_range_saturate_instead_of_becoming_infinite():
     """The int8 kernels multiply in f16: a bf16 activation (or hidden value) beyond 65504 is clamped to +-65504 when
     the token tile is staged, so an outlier gives a finite row and leaves the other rows of the batch alone."""
