@@ -730,6 +730,9 @@ def run_model(args, w):
             "clocks": clocks, "gpu_launches": int(launches), "device_ms_per_step": dev_ms,
             "phase_ms": {"forward": float(phases[0]), "head_and_loss": float(phases[1]), "backward": float(phases[2]), "adam": float(phases[3])},
             "loss": {"lm_loss": loss.lm_loss, "auxiliary_loss": loss.auxiliary_loss},
+            "reference_published": {"value": 36302, "unit": "tokens/s", "hardware": "RTX 3060 12 GB", "batch": "16 x 512 tokens",
+                                    "note": "the reference's own figure for this model on other hardware and another batch shape "
+                                            "(docs/baseline.md:21); context only, vs_baseline stays null"},
             "roofline": {"bound": "tensor", "achieved": ach, "peak": pk["tf_sustained"], "unit": "TFLOP/s", "frac": ach / pk["tf_sustained"],
                          "traffic": None, "flops_per_step": flops,
                          "note": "whole step: 6 x active parameters + attention, per token; device time of the four phases"},

@@ -138,6 +138,11 @@ int32_t moe_zero_grad(moe_layer_t* layer, void* stream);
  * `step` is the already incremented global step, `scale` multiplies the gradient. Clears gradients. */
 int32_t moe_step_adam(moe_layer_t* layer, float lr, float beta1, float beta2, float eps, float weight_decay,
                       int32_t step, float scale, void* stream);
+/* Param::step with Optimizer::Sgd (param.rs:557-561): value -= lr * grad * scale.  Clears gradients. */
+int32_t moe_step_sgd(moe_layer_t* layer, float lr, float scale, void* stream);
+/* Param::step with Optimizer::Lion (param.rs:590-613): the sign of beta1 * m + (1 - beta1) * grad, decoupled weight
+ * decay; the first-moment buffer is the one Adam uses (as the reference's Param::m).  Clears gradients. */
+int32_t moe_step_lion(moe_layer_t* layer, float lr, float beta1, float beta2, float weight_decay, float scale, void* stream);
 
 /* The same calls with HOST buffers: f32 [tokens, d_model] in and out, copies included
  * (what TransformerLm::forward_batch does around the device path). valid_host may be null. */

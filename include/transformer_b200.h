@@ -13,7 +13,7 @@
  *   SwiGlu (dense layers)                src/ffn.rs:56-120
  *   Embedding gather / scatter / tied head   src/embedding.rs:49-152
  *   causal_lm_loss_batch                 src/causal_lm_loss.rs:66-150
- *   Param::step (Adam)                   src/param.rs:562-589
+ *   Param::step (Sgd, Adam, Lion)        src/param.rs:547-617
  *
  * Arithmetic: bf16 tensor-core products over f32 master weights (the reference's mixed_precision mode),
  * f32 normalisation, softmax, loss and optimizer.  Every matrix product runs on the grouped tcgen05 GEMM of
@@ -102,6 +102,9 @@ int32_t lm_accumulate_step(lm_model_t* model, const uint32_t* ids_host, const in
 /* zero_grad (a flag, as DeviceParam::zero_grad) and step with Adam; `scale` multiplies the gradients. */
 int32_t lm_zero_grad(lm_model_t* model);
 int32_t lm_step_adam(lm_model_t* model, float lr, float beta1, float beta2, float eps, float weight_decay, float scale);
+/* step with Optimizer::Sgd / Optimizer::Lion (param.rs:557-561, 590-613). */
+int32_t lm_step_sgd(lm_model_t* model, float lr, float scale);
+int32_t lm_step_lion(lm_model_t* model, float lr, float beta1, float beta2, float weight_decay, float scale);
 /* train_step_batch: zero_grad, accumulate_step, step(1.0).  Returns TotalLoss{lm_loss, auxiliary_loss}. */
 int32_t lm_train_step(lm_model_t* model, const uint32_t* ids_host, const int32_t* lengths_host,
                       const uint8_t* loss_mask_host, int32_t batch, int32_t seq_len, float lr, float beta1, float beta2,

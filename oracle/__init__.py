@@ -70,6 +70,10 @@ def lib() -> C.CDLL:
         L.orc_backward.restype = C.c_int
         L.orc_backward.argtypes = [vp, fp, fp]
         L.orc_adam_step.argtypes = [vp] + [C.c_float] * 5 + [C.c_int, C.c_float]
+        L.orc_sgd_step.argtypes = [vp, C.c_float, C.c_float]
+        L.orc_sgd_apply.argtypes = [vp, vp, C.c_longlong, C.c_float, C.c_float]
+        L.orc_lion_apply.argtypes = [vp, vp, vp, C.c_longlong] + [C.c_float] * 5
+        L.orc_lion_step.argtypes = [vp] + [C.c_float] * 5
         _lib = L
     return _lib
 
@@ -137,6 +141,19 @@ def silu(x: float) -> float:
 
 def silu_derivative(x: float) -> float:
     return lib().orc_silu_derivative(float(x))
+
+
+def sgd_apply(value, grad, lr, scale=1.0):
+    """Param::step, Sgd arm (param.rs:557-561), in place on two f32 arrays; the gradient is cleared."""
+    assert value.dtype == np.float32 and grad.dtype == np.float32 and value.flags.c_contiguous and grad.flags.c_contiguous
+    lib().orc_sgd_apply(value.ctypes.data, grad.ctypes.data, value.size, lr, scale)
+
+
+def lion_apply(value, grad, moment, lr, beta1=0.9, beta2=0.99, wd=0.0, scale=1.0):
+    """Param::step, Lion arm (param.rs:590-613), in place on three f32 arrays; the gradient is cleared."""
+    for a in (value, grad, moment):
+        assert a.dtype == np.float32 and a.flags.c_contiguous
+    lib().orc_lion_apply(value.ctypes.data, grad.ctypes.data, moment.ctypes.data, value.size, lr, beta1, beta2, wd, scale)
 
 
 class OracleMoe:
@@ -257,3 +274,9 @@ class OracleMoe:
 
     def adam_step(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, step=1, scale=1.0):
         lib().orc_adam_step(self.h, lr, beta1, beta2, eps, wd, step, scale)
+
+    def sgd_step(self, lr=1e-2, scale=1.0):
+        lib().orc_sgd_step(self.h, lr, scale)
+
+    def lion_step(self, lr=1e-4, beta1=0.9, beta2=0.99, wd=0.0, scale=1.0):
+        lib().orc_lion_step(self.h, lr, beta1, beta2, wd, scale)

@@ -14,7 +14,7 @@
 //   src/activations.rs:56-70  softmax               -> softmax_inplace
 //   src/ffn.rs:56-120,227-238 SwiGlu fwd/bwd, silu  -> swiglu_* / silu
 //   src/param.rs:762-825  Linear fwd/bwd ([out,in] weights, y = x W^T)
-//   src/param.rs:562-589  Param::step (Adam)        -> orc_adam_step
+//   src/param.rs:547-617  Param::step (Sgd, Adam, Lion) -> orc_sgd_step / orc_adam_step / orc_lion_step
 //   src/quantized.rs:29-99,154-177 int8 rows + f32 scale, 32-lane dot
 //   src/batch.rs:247-268  Layout (padding mask)
 //
@@ -865,6 +865,48 @@ void orc_adam_step(void* h, float lr, float beta1, float beta2, float eps, float
       w.value[i] -= c.lr * m_hat / (std::sqrt(v_hat) + c.eps);
       w.grad[i] = 0.f;
     }
+  }, &ctx);
+}
+
+// Param::step with Optimizer::Sgd (param.rs:557-561) over one buffer: value -= learning_rate * grad * scale.
+// Clears the gradients, as Param::step does at its end.
+void orc_sgd_apply(float* value, float* grad, long long n, float lr, float scale) {
+  for (long long i = 0; i < n; ++i) {
+    value[i] -= lr * grad[i] * scale;
+    grad[i] = 0.f;
+  }
+}
+
+// Param::step with Optimizer::Lion (param.rs:590-613) over one buffer: the step is the sign of
+// beta1 * m + (1 - beta1) * g taken from the moment as it was, then m = beta2 * m + (1 - beta2) * g;
+// sign(0) = 0 (optimizers.rs:50-58).
+void orc_lion_apply(float* value, float* grad, float* m, long long n, float lr, float beta1, float beta2, float wd, float scale) {
+  for (long long i = 0; i < n; ++i) {
+    const float g = grad[i] * scale;
+    const float update = beta1 * m[i] + (1.0f - beta1) * g;
+    m[i] = beta2 * m[i] + (1.0f - beta2) * g;
+    const float sg = update > 0.f ? 1.0f : (update < 0.f ? -1.0f : 0.0f);
+    value[i] -= lr * (sg + wd * value[i]);
+    grad[i] = 0.f;
+  }
+}
+
+void orc_sgd_step(void* h, float lr, float scale) {
+  struct Ctx { float lr, scale; } ctx{lr, scale};
+  for_each_weight(*(Layer*)h, [](Weight& w, void* p) {
+    const Ctx& c = *(const Ctx*)p;
+    w.need_grad();
+    orc_sgd_apply(w.value.data(), w.grad.data(), (long long)w.value.size(), c.lr, c.scale);
+  }, &ctx);
+}
+
+void orc_lion_step(void* h, float lr, float beta1, float beta2, float wd, float scale) {
+  struct Ctx { float lr, b1, b2, wd, scale; } ctx{lr, beta1, beta2, wd, scale};
+  for_each_weight(*(Layer*)h, [](Weight& w, void* p) {
+    const Ctx& c = *(const Ctx*)p;
+    w.need_grad();
+    w.need_moments();
+    orc_lion_apply(w.value.data(), w.grad.data(), w.m.data(), (long long)w.value.size(), c.lr, c.b1, c.b2, c.wd, c.scale);
   }, &ctx);
 }
 

@@ -14,7 +14,7 @@ Follows, in f32 numpy (the MoE feed-forward itself is the C++ restatement, ``Ora
   * TransformerBlock forward_train / backward                   reference transformer_block.rs:205-270
   * TransformerLm forward_batch / backward / train_step_batch   reference transformer.rs:676-735, 1214-1246, 1394-1425
   * causal_lm_loss_batch / cross_entropy_rows                   reference causal_lm_loss.rs:66-150
-  * Param::step (Adam)                                          reference param.rs:562-589
+  * Param::step (Sgd, Adam, Lion)                               reference param.rs:547-617
 
 Pinned by the reference's own tests, restated in tests/test_transformer_oracle.py: causal_lm_loss.rs:152-186
 (uniform logits give ln(vocab), the last position has no target, gradient against finite differences),
@@ -272,7 +272,7 @@ def seeded_model_weights(c, seed, std=0.02):
 
 
 class OracleLm:
-    """TransformerLm on the host: forward_batch, backward, train_step_batch (Adam), with injected weights."""
+    """TransformerLm on the host: forward_batch, backward, train_step_batch, with injected weights (stepped in place)."""
 
     def __init__(self, config, weights):
         from . import OracleMoe
@@ -370,14 +370,24 @@ class OracleLm:
         self.backward(grad_logits)
         return loss, self.aux
 
-    def step(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, scale=1.0):
-        """TransformerLm::step with Adam (param.rs:562-589) over every parameter; clears the gradients."""
+    def step(self, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, wd=0.0, scale=1.0, kind="adam"):
+        """TransformerLm::step over every parameter with Param::step's Sgd, Adam or Lion arm (param.rs:547-617);
+        clears the gradients.  The step counter advances for every kind."""
         self.step_count += 1
         t = self.step_count
 
         def upd(key, wv, gv):
-            m, v = self.moments.get(key, (np.zeros_like(wv), np.zeros_like(wv)))
             gsc = (gv * F(scale)).astype(F)
+            if kind == "sgd":
+                wv -= (F(lr) * gv * F(scale)).astype(F)
+                return
+            m, v = self.moments.get(key, (np.zeros_like(wv), np.zeros_like(wv)))
+            if kind == "lion":
+                update = (F(beta1) * m + F(1 - beta1) * gsc).astype(F)
+                m = (F(beta2) * m + F(1 - beta2) * gsc).astype(F)
+                self.moments[key] = (m, v)
+                wv -= (F(lr) * (np.sign(update).astype(F) + F(wd) * wv)).astype(F)
+                return
             m = (F(beta1) * m + F(1 - beta1) * gsc).astype(F)
             v = (F(beta2) * v + F(1 - beta2) * gsc * gsc).astype(F)
             self.moments[key] = (m, v)
@@ -396,7 +406,12 @@ class OracleLm:
                 if k != "moe":
                     upd((layer, k), b[k], g["blocks"][layer][k])
         for m in self.moe.values():
-            m.adam_step(lr, beta1, beta2, eps, wd, t, scale)
+            if kind == "sgd":
+                m.sgd_step(lr, scale)
+            elif kind == "lion":
+                m.lion_step(lr, beta1, beta2, wd, scale)
+            else:
+                m.adam_step(lr, beta1, beta2, eps, wd, t, scale)
         self.zero_grad()
 
     def train_step(self, batch, moe_logits=None, **adam):

@@ -94,6 +94,8 @@ def lib() -> C.CDLL:
         "moe_backward": (i32, [vp, vp, vp, i32, vp]),
         "moe_zero_grad": (i32, [vp, vp]),
         "moe_step_adam": (i32, [vp, f32, f32, f32, f32, f32, i32, f32, vp]),
+        "moe_step_sgd": (i32, [vp, f32, f32, vp]),
+        "moe_step_lion": (i32, [vp, f32, f32, f32, f32, f32, vp]),
         "moe_forward_host": (i32, [vp, fp, i32, i32, bp, fp, i32]),
         "moe_backward_host": (i32, [vp, fp, fp]),
         "moe_get_losses": (i32, [vp, fp, fp]),
@@ -129,6 +131,8 @@ def lib() -> C.CDLL:
         "lm_accumulate_step": (i32, [vp, vp, vp, vp, i32, i32, fp, fp]),
         "lm_zero_grad": (i32, [vp]),
         "lm_step_adam": (i32, [vp, f32, f32, f32, f32, f32, f32]),
+        "lm_step_sgd": (i32, [vp, f32, f32]),
+        "lm_step_lion": (i32, [vp, f32, f32, f32, f32, f32]),
         "lm_train_step": (i32, [vp, vp, vp, vp, i32, i32, f32, f32, f32, f32, f32, fp, fp]),
         "lm_optimizer_step": (C.c_int64, [vp]),
         "lm_set_optimizer_step": (i32, [vp, C.c_int64]),

@@ -205,6 +205,42 @@ __global__ void adam_kernel(AdamArgs a) {
   }
 }
 
+// Param::step for Optimizer::Sgd (param.rs:557-561) and Optimizer::Lion (param.rs:590-613), operation for operation;
+// the gradient is cleared and the bf16 compute copy refreshed in the same pass.  sign(0) = 0 (optimizers.rs:50-58).
+__global__ void sgd_kernel(AdamArgs a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    const float w = __fsub_rn(a.w[i], __fmul_rn(__fmul_rn(a.lr, a.g[i]), a.scale));
+    a.w[i] = w; a.g[i] = 0.f;
+    if (a.w_bf16) a.w_bf16[i] = __float2bfloat16_rn(w);
+  }
+}
+__global__ void lion_kernel(AdamArgs a) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n; i += stride) {
+    const float g = __fmul_rn(a.g[i], a.scale);
+    const float m = a.m[i];
+    const float update = __fadd_rn(__fmul_rn(a.beta1, m), __fmul_rn(1.0f - a.beta1, g));
+    a.m[i] = __fadd_rn(__fmul_rn(a.beta2, m), __fmul_rn(1.0f - a.beta2, g));
+    const float sg = update > 0.f ? 1.0f : (update < 0.f ? -1.0f : 0.0f);
+    float w = a.w[i];
+    w = __fsub_rn(w, __fmul_rn(a.lr, __fadd_rn(sg, __fmul_rn(a.wd, w))));
+    a.w[i] = w; a.g[i] = 0.f;
+    if (a.w_bf16) a.w_bf16[i] = __float2bfloat16_rn(w);
+  }
+}
+static unsigned opt_grid(long long n) { const long long b = (n + 255) / 256; return (unsigned)(b < 148 * 16 ? b : 148 * 16); }
+cudaError_t launch_sgd(const AdamArgs& a, cudaStream_t stream) {
+  if (a.n <= 0) return cudaSuccess;
+  sgd_kernel<<<opt_grid(a.n), 256, 0, stream>>>(a); count_launch();
+  return cudaGetLastError();
+}
+cudaError_t launch_lion(const AdamArgs& a, cudaStream_t stream) {
+  if (a.n <= 0) return cudaSuccess;
+  lion_kernel<<<opt_grid(a.n), 256, 0, stream>>>(a); count_launch();
+  return cudaGetLastError();
+}
+
 cudaError_t launch_adam(const AdamArgs& a, cudaStream_t stream) {
   if (a.n <= 0) return cudaSuccess;
   const long long blocks = (a.n + 255) / 256;

@@ -223,6 +223,8 @@ struct AdamArgs {
   float lr, beta1, beta2, eps, wd, c1, c2, scale;
 };
 cudaError_t launch_adam(const AdamArgs& a, cudaStream_t stream);
+cudaError_t launch_sgd(const AdamArgs& a, cudaStream_t stream);    // uses lr, scale
+cudaError_t launch_lion(const AdamArgs& a, cudaStream_t stream);   // uses lr, beta1, beta2, wd, scale and the first moment
 cudaError_t launch_cast_f32_to_bf16(const float* src, bf16* dst, long long n, cudaStream_t stream);
 cudaError_t launch_cast_bf16_to_f32(const bf16* src, float* dst, long long n, cudaStream_t stream);
 cudaError_t launch_fill_f32(float* dst, float v, long long n, cudaStream_t stream);

@@ -756,7 +756,9 @@ int accumulate_impl(lm_model* M, const uint32_t* ids, const int32_t* lengths, co
   return MOE_OK;
 }
 
-int step_impl(lm_model* M, float lr, float b1, float b2, float eps, float wd, float scale) {
+// kind 0 Adam, 1 Sgd, 2 Lion (Param::step, param.rs:547-617); the step counter advances for all three
+// (TransformerLm::step, transformer.rs:1576-1606).
+int step_impl(lm_model* M, int kind, float lr, float b1, float b2, float eps, float wd, float scale) {
   M->step += 1;
   LCK(cudaEventRecord(M->ev[3], M->st));
   if (!M->grad_valid) LCK(cudaMemsetAsync(M->g, 0, (size_t)M->n_params * 4, M->st));
@@ -765,11 +767,23 @@ int step_impl(lm_model* M, float lr, float b1, float b2, float eps, float wd, fl
   a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
   a.c1 = 1.0f - powf(b1, (float)M->step);
   a.c2 = 1.0f - powf(b2, (float)M->step);
-  LCK(launch_adam(a, M->st));
-  for (auto& b : M->blocks)
-    if (b.is_moe) RC(moe_rc(M, b, moe_step_adam(b.moe, lr, b1, b2, eps, wd, (int)M->step, scale, M->st)));
+  LCK(kind == 0 ? launch_adam(a, M->st) : kind == 1 ? launch_sgd(a, M->st) : launch_lion(a, M->st));
+  for (auto& b : M->blocks) {
+    if (!b.is_moe) continue;
+    const int rc = kind == 0   ? moe_step_adam(b.moe, lr, b1, b2, eps, wd, (int)M->step, scale, M->st)
+                   : kind == 1 ? moe_step_sgd(b.moe, lr, scale, M->st)
+                               : moe_step_lion(b.moe, lr, b1, b2, wd, scale, M->st);
+    RC(moe_rc(M, b, rc));
+  }
   LCK(cudaEventRecord(M->ev[4], M->st));
   M->grad_valid = false;   // the optimizer kernels cleared the gradients
+  return MOE_OK;
+}
+
+int step_and_time(lm_model* M, int kind, float lr, float b1, float b2, float eps, float wd, float scale) {
+  RC(step_impl(M, kind, lr, b1, b2, eps, wd, scale));
+  LCK(cudaStreamSynchronize(M->st));
+  cudaEventElapsedTime(&M->last_ms[3], M->ev[3], M->ev[4]);
   return MOE_OK;
 }
 
@@ -822,10 +836,17 @@ int32_t lm_zero_grad(lm_model_t* M) {
 
 int32_t lm_step_adam(lm_model_t* M, float lr, float b1, float b2, float eps, float wd, float scale) {
   LENTER(M);
-  RC(step_impl(M, lr, b1, b2, eps, wd, scale));
-  LCK(cudaStreamSynchronize(M->st));
-  cudaEventElapsedTime(&M->last_ms[3], M->ev[3], M->ev[4]);
-  return MOE_OK;
+  return step_and_time(M, 0, lr, b1, b2, eps, wd, scale);
+}
+
+int32_t lm_step_sgd(lm_model_t* M, float lr, float scale) {
+  LENTER(M);
+  return step_and_time(M, 1, lr, 0.f, 0.f, 0.f, 0.f, scale);
+}
+
+int32_t lm_step_lion(lm_model_t* M, float lr, float b1, float b2, float wd, float scale) {
+  LENTER(M);
+  return step_and_time(M, 2, lr, b1, b2, 0.f, wd, scale);
 }
 
 int32_t lm_train_step(lm_model_t* M, const uint32_t* ids, const int32_t* lengths, const uint8_t* mask, int32_t B, int32_t S,

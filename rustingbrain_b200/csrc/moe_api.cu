@@ -124,14 +124,16 @@ struct Span {
 long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
 
 // How backward overlaps its HBM-bound tail with the tensor-core work (MOE_B200_OVERLAP):
-//   0 (default) none; 1 un-permute on a side stream beside the gate|up weight gradient;
+//   0 none; 1 un-permute on a side stream beside the gate|up weight gradient;
 //   2 both routed weight-gradient GEMMs deferred to the side stream past the end of the call.
-// Measured on cfg 4 at 1, 2 and 8 GPUs the three modes give the same step time: the step runs at the
-// board's power cap, and work that overlaps the GEMMs slows them by what it saves.
+// Unset (-1 here): 0 on one GPU and on two ranks, 1 from four ranks on.  Measured on cfg 4 the three modes give the
+// same step time at 1 and 2 GPUs (the step runs at the board's power cap, and work that overlaps the GEMMs slows
+// them by what it saves); at 4 ranks, where each GPU's GEMMs are shorter and the exchange tail relatively longer,
+// mode 1 took 35.5 ms against 37.0 ms.
 int overlap_mode() {
   static const int mode = [] {
     const char* e = getenv("MOE_B200_OVERLAP");
-    return e && *e >= '0' && *e <= '2' ? *e - '0' : 0;
+    return e && *e >= '0' && *e <= '2' ? *e - '0' : -1;
   }();
   return mode;
 }
@@ -785,7 +787,8 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
   // go to the side stream and are joined by whichever later call needs their inputs or outputs
   // stage timing brackets launches on the caller's stream; mode 1 keeps every bracketed stage there (only the
   // un-permute moves to the side stream and goes untimed), modes 2 and 3 do not
-  const int want = force_mode == 3 && !ep ? 3 : overlap_mode();
+  const int chosen = overlap_mode() >= 0 ? overlap_mode() : (L->ep_size >= 4 ? 1 : 0);
+  const int want = force_mode == 3 && !ep ? 3 : chosen;
   const int mode = L->prof_on && want != 1 ? 0 : want;
   const int first_parts = mode >= 2 ? 1 : 3;
   Groups G{L->meta.pad_off, L->meta.tile_start, L->E, L->rows_cap, L->rows_cap};
@@ -1243,12 +1246,11 @@ int32_t moe_zero_grad(moe_layer_t* L, void*) {
   return MOE_OK;
 }
 
-int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, float wd, int32_t step, float scale, void* stream) {
-  ENTER(L);
+// Param::step over every weight of the layer (param.rs:547-617): kind 0 Adam, 1 Sgd, 2 Lion.  `a` carries the
+// hyper-parameters; the pointers are filled here.
+static int step_common(moe_layer* L, int kind, AdamArgs a, cudaStream_t st) {
   if (!L->training) { L->err = "InvalidConfig: the handle was created with training = 0"; return MOE_INVALID_CONFIG; }
-  cudaStream_t st = (cudaStream_t)stream;
   { const int jr = join_side(L, st); if (jr != MOE_OK) return jr; }
-  AdamArgs a{};
   if (L->lora_rank > 0) {
     // base weights are frozen (the reference's add_lora): only the adapters move
     const int pr = lora_project_grads(L, st);
@@ -1260,13 +1262,33 @@ int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, f
     if (!L->grad_valid) CK(cudaMemsetAsync(L->g, 0, (size_t)L->n_params * 4, st));
     a.w = L->w; a.g = L->g; a.m = L->m; a.v = L->v; a.w_bf16 = L->wb; a.n = L->n_params;
   }
-  a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
-  a.c1 = 1.0f - powf(b1, (float)step);
-  a.c2 = 1.0f - powf(b2, (float)step);
-  { Span sp(L, 15, st); CK(launch_adam(a, st)); }
+  { Span sp(L, 15, st); CK(kind == 0 ? launch_adam(a, st) : kind == 1 ? launch_sgd(a, st) : launch_lion(a, st)); }
   L->w3_dirty = true;
   L->grad_valid = false;   // the kernel cleared the gradients
   return MOE_OK;
+}
+
+int32_t moe_step_adam(moe_layer_t* L, float lr, float b1, float b2, float eps, float wd, int32_t step, float scale, void* stream) {
+  ENTER(L);
+  AdamArgs a{};
+  a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.eps = eps; a.wd = wd; a.scale = scale;
+  a.c1 = 1.0f - powf(b1, (float)step);
+  a.c2 = 1.0f - powf(b2, (float)step);
+  return step_common(L, 0, a, (cudaStream_t)stream);
+}
+
+int32_t moe_step_sgd(moe_layer_t* L, float lr, float scale, void* stream) {
+  ENTER(L);
+  AdamArgs a{};
+  a.lr = lr; a.scale = scale;
+  return step_common(L, 1, a, (cudaStream_t)stream);
+}
+
+int32_t moe_step_lion(moe_layer_t* L, float lr, float b1, float b2, float wd, float scale, void* stream) {
+  ENTER(L);
+  AdamArgs a{};
+  a.lr = lr; a.beta1 = b1; a.beta2 = b2; a.wd = wd; a.scale = scale;
+  return step_common(L, 2, a, (cudaStream_t)stream);
 }
 
 int32_t moe_forward_host(moe_layer_t* L, const float* x, int32_t tokens, int32_t cols, const uint8_t* valid, float* y, int32_t save) {

@@ -332,6 +332,14 @@ class MoeLayer:
         """``Param::step`` with ``Optimizer::Adam`` over the whole layer (param.rs:562-589)."""
         self._ck(_lib.lib().moe_step_adam(self._h, lr, beta1, beta2, eps, weight_decay, step, scale, _stream(stream)))
 
+    def step_sgd(self, lr=1e-2, scale=1.0, stream=None):
+        """``Param::step`` with ``Optimizer::Sgd`` (param.rs:557-561)."""
+        self._ck(_lib.lib().moe_step_sgd(self._h, lr, scale, _stream(stream)))
+
+    def step_lion(self, lr=1e-4, beta1=0.9, beta2=0.99, weight_decay=0.0, scale=1.0, stream=None):
+        """``Param::step`` with ``Optimizer::Lion`` (param.rs:590-613); betas default as ``Optimizer::lion``."""
+        self._ck(_lib.lib().moe_step_lion(self._h, lr, beta1, beta2, weight_decay, scale, _stream(stream)))
+
     # -- forward / backward ----------------------------------------------
     def forward(self, x, valid=None, out=None, stream=None):
         """``MoeLayer::forward`` (moe.rs:237): the output only, nothing kept for a backward pass."""

@@ -39,6 +39,21 @@ class Adam:
 
 
 @dataclass(frozen=True)
+class Sgd:
+    """``Optimizer::sgd(learning_rate)`` (optimizers.rs:61-63)."""
+    learning_rate: float = 1e-2
+
+
+@dataclass(frozen=True)
+class Lion:
+    """``Optimizer::lion(learning_rate)`` / ``lion_with_weight_decay`` (optimizers.rs:86-104)."""
+    learning_rate: float = 3e-5
+    beta1: float = 0.9
+    beta2: float = 0.99
+    weight_decay: float = 0.0
+
+
+@dataclass(frozen=True)
 class TotalLoss:
     """causal_lm_loss.rs:30-49."""
     lm_loss: float
@@ -163,7 +178,7 @@ class TransformerBuilder:
     def tie_embeddings(self, on: bool): return self._set(tie_embeddings=on)
     def aux_loss_weight(self, w: float): return self._set(aux_loss_weight=w)
     def router_z_loss_weight(self, w: float): return self._set(router_z_loss_weight=w)
-    def optimizer(self, optimizer: Adam): self._optimizer = optimizer; return self
+    def optimizer(self, optimizer): self._optimizer = optimizer; return self
     def seed(self, seed: int): self._seed = seed; return self
 
     def mixed_precision(self, on: bool):
@@ -330,12 +345,23 @@ class TransformerLm:
         self._ck(_lib.lib().lm_zero_grad(self._h))
 
     def step(self, scale: float = 1.0) -> None:
+        """``TransformerLm::step`` (transformer.rs:1576-1606) with whichever optimizer the model holds."""
         o = self.optimizer
-        self._ck(_lib.lib().lm_step_adam(self._h, o.learning_rate, o.beta1, o.beta2, o.epsilon, o.weight_decay, scale))
+        if isinstance(o, Sgd):
+            self._ck(_lib.lib().lm_step_sgd(self._h, o.learning_rate, scale))
+        elif isinstance(o, Lion):
+            self._ck(_lib.lib().lm_step_lion(self._h, o.learning_rate, o.beta1, o.beta2, o.weight_decay, scale))
+        else:
+            self._ck(_lib.lib().lm_step_adam(self._h, o.learning_rate, o.beta1, o.beta2, o.epsilon, o.weight_decay, scale))
 
     def train_step_batch(self, batch) -> TotalLoss:
-        b = self._batch(batch)
         o = self.optimizer
+        if not isinstance(o, Adam):
+            self.zero_grad()
+            out = self.accumulate_step(batch)
+            self.step(1.0)
+            return out
+        b = self._batch(batch)
         lm, aux = C.c_float(), C.c_float()
         ids, lengths = self._args(b)
         mask = b.loss_mask.ctypes.data_as(C.c_void_p) if b.loss_mask is not None else None
@@ -399,4 +425,4 @@ class KvCaches:
             self._h = C.c_void_p()
 
 
-__all__ = ["KvCaches", "Adam", "TotalLoss", "TransformerConfig", "TransformerBuilder", "TransformerLm", "TokenBatch", "NetworkError"]
+__all__ = ["KvCaches", "Adam", "Sgd", "Lion", "TotalLoss", "TransformerConfig", "TransformerBuilder", "TransformerLm", "TokenBatch", "NetworkError"]

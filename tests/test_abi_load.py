@@ -77,3 +77,24 @@ def test_rmsnorm_and_kv_cache_arguments_are_checked_before_any_device_work():
               precision=_lib.PRECISION_F32, device=0)
     assert L.kv_cache_create(C.byref(_lib.KvCacheConfigC(**kw)), C.byref(h)) == _lib.UNSUPPORTED   # even, but no kernel
     L.kv_cache_destroy(h)
+
+
+def test_language_model_configuration_is_checked_without_a_device():  # transformer.rs:132-172, 195-235
+    from rustingbrain_b200.transformer import TransformerConfig, TransformerLm, TokenBatch
+    assert TransformerConfig().parameter_counts() == (55_181_824, 35_717_632)      # the README's 55.2M / 35.7M
+    dense = TransformerConfig(moe_layers=())
+    assert dense.parameter_counts()[0] == dense.parameter_counts()[1]
+    TransformerConfig().validate()
+    for bad, text in ((dict(moe_layers=(9,)), "moe_layers names layer 9"), (dict(n_heads=6, n_kv_heads=4), "multiple of n_kv_heads"),
+                      (dict(head_dim=7), "head_dim must be even"), (dict(experts_per_token=9), "experts_per_token"),
+                      (dict(d_model=100), "multiples of 32"), (dict(vocab_size=0), "vocab_size must be non-zero")):
+        with pytest.raises(InvalidConfig, match=text):
+            TransformerConfig(**bad).validate()
+    with pytest.raises(InvalidConfig):
+        TokenBatch([[1]])
+    b = TokenBatch([[1, 2, 3, 4], [5, 6]])
+    assert b.is_padded() and b.seq_len == 4 and list(b.ids) == [1, 2, 3, 4, 5, 6, 0, 0] and list(b.lengths) == [4, 2]
+    import torch
+    if not torch.cuda.is_available():
+        with pytest.raises(Exception):                      # fails closed: there is no host model behind the builder
+            TransformerLm.builder().build()

@@ -166,6 +166,37 @@ def test_adam_step_matches_the_checker():  # gpu_transformer.rs:1652 accepts 1e-
     assert np.all(dev.get_grad(DOWN, 1) == 0)
 
 
+@pytest.mark.parametrize("kind", ["sgd", "lion"])
+def test_sgd_and_lion_steps_match_the_checker(kind):  # param.rs:557-561, 590-613; gpu_transformer.rs:1855-1884 accepts 1e-3
+    T, d, E, k, F = 12, 8, 4, 2, 6
+    dev, ora, _ = make_pair(d, E, k, F, True, seed=10, precision="f32", max_tokens=T, std=0.5, router_std=0.5)
+    x = ramp(T * d, 29, 17, 8, (T, d))
+    gy = ramp(T * d, 13, 11, 5, (T, d))
+    for _ in range(2):                       # the second Lion step reads the moment the first one left
+        _fwd_bwd(dev, ora, x, gy, "f32")
+        if kind == "sgd":
+            dev.step_sgd(lr=0.05, scale=0.5)
+            ora.sgd_step(lr=0.05, scale=0.5)
+        else:
+            dev.step_lion(lr=1e-2, weight_decay=0.1)
+            ora.lion_step(lr=1e-2, wd=0.1)
+    dev.synchronize()
+    # a sign taken the wrong way round is off by twice the learning rate; entries whose smoothed gradient is
+    # within rounding of zero may differ by one learning rate, so the band is checked on the rest
+    for e in range(E):
+        for which in (GATE, UP, DOWN):
+            a, b = dev.get_weight(which, e), ora.get_weight(which, e)
+            if kind == "sgd":
+                np.testing.assert_allclose(a, b, atol=1e-5)
+            else:
+                assert np.mean(np.abs(a - b) > 1e-4) <= 0.02
+    if kind == "lion":
+        m_d, v_d = dev.get_moments(DOWN, 1)
+        m_o, v_o = ora.get_moments(DOWN, 1)
+        assert rel_l2(m_d, m_o) <= 1e-4 and np.all(v_d == 0)
+    assert np.all(dev.get_grad(DOWN, 1) == 0)
+
+
 def test_errors_follow_the_reference():
     cfg = MoeConfig(4, 2, 6)
     layer = MoeLayer(8, cfg, precision="f32", max_tokens=4)

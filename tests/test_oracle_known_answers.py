@@ -271,3 +271,39 @@ def test_adam_step_follows_the_reference_rule():  # param.rs:562-589
     upd = w["router"] - 1e-2 * (0.1 * g / 0.1) / (np.sqrt(0.001 * g * g / 0.001) + 1e-8)
     np.testing.assert_allclose(m.get_weight(ROUTER), upd, rtol=1e-4, atol=1e-6)
     assert np.all(m.get_grad(ROUTER) == 0)  # step clears the gradient
+
+
+def test_lion_step_follows_the_reference_known_answers():  # param.rs:996-1018
+    import oracle
+    value, grad, m = (np.array([v], np.float32) for v in (1.0, 0.5, 0.0))
+    oracle.lion_apply(value, grad, m, lr=0.1)               # Optimizer::lion(0.1): betas 0.9 / 0.99, no decay
+    assert abs(value[0] - 0.9) < 1e-6 and abs(m[0] - 0.005) < 1e-7 and grad[0] == 0
+    grad[0] = -0.5
+    oracle.lion_apply(value, grad, m, lr=0.1)
+    assert abs(value[0] - 1.0) < 1e-6 and abs(m[0] - -0.00005) < 1e-7
+    # a vanished smoothed gradient moves nothing (optimizers.rs:45-58) and decay is decoupled
+    value, grad, m = (np.array([v], np.float32) for v in (2.0, 0.0, 0.0))
+    oracle.lion_apply(value, grad, m, lr=0.1)
+    assert value[0] == 2.0
+    oracle.lion_apply(value, grad, m, lr=0.1, wd=0.5)
+    assert abs(value[0] - 1.9) < 1e-6
+
+
+def test_sgd_and_lion_layer_steps_follow_the_rule():  # param.rs:557-561, 590-613
+    for kind in ("sgd", "lion"):
+        m, w = make(4, 2, 1, 3, seed=43)
+        x = ramp(12, 13, 11, 5, (3, 4))
+        m.forward(x)
+        m.backward(np.ones((3, 4), np.float32))
+        g = m.get_grad(ROUTER).astype(np.float32)
+        if kind == "sgd":
+            m.sgd_step(lr=0.25, scale=0.5)
+            want = w["router"] - np.float32(0.25) * g * np.float32(0.5)
+        else:
+            m.lion_step(lr=1e-2, wd=0.1)
+            want = w["router"] - np.float32(1e-2) * (np.sign(g) + np.float32(0.1) * w["router"])
+            mm, vv = m.get_moments(ROUTER)
+            np.testing.assert_allclose(mm, 0.01 * g, rtol=1e-5, atol=1e-9)
+            assert np.all(vv == 0)                          # Lion keeps one moment
+        np.testing.assert_allclose(m.get_weight(ROUTER), want, rtol=1e-6, atol=1e-7)
+        assert np.all(m.get_grad(ROUTER) == 0)

@@ -48,11 +48,11 @@ def _config(**over):
     return c
 
 
-def _pair(c, seed=3, std=0.08, rows=256):
+def _pair(c, seed=3, std=0.08, rows=256, optimizer=None):
     w = _round_weights(T.seeded_model_weights(c, seed, std=std))
     ora = T.OracleLm(c, w)
     dc = D.TransformerConfig(**{k: v for k, v in c.items()})
-    dev = D.TransformerLm.builder().config(dc).max_batch_rows(rows).optimizer(D.Adam(1e-2)).build()
+    dev = D.TransformerLm.builder().config(dc).max_batch_rows(rows).optimizer(optimizer or D.Adam(1e-2)).build()
     dev.load_weights(w)
     return dev, ora, w
 
@@ -177,6 +177,39 @@ def test_train_steps_follow_the_checker_and_drive_the_loss_down():
     # the weights moved as Adam moves them: first step of size ~lr on every touched weight
     w_after = dev.get_param(D.WO, 0)
     assert np.isfinite(w_after).all()
+    dev.close()
+
+
+@pytest.mark.parametrize("kind", ["sgd", "lion"])
+def test_sgd_and_lion_train_steps_follow_the_checker(kind):  # gpu_transformer.rs:1855-1884; param.rs:557-561, 590-613
+    c = _config()
+    opt = D.Sgd(0.05) if kind == "sgd" else D.Lion(1e-2, weight_decay=0.1)
+    dev, ora, w = _pair(c, std=0.05, optimizer=opt)
+    seqs = _sequences(c, [32, 32], seed=4)
+    batch = T.TokenBatch(seqs)
+    router = dev.forward_batch(seqs, return_router_logits=True)[1]
+    before = [a.copy() for a in (w["blocks"][0]["wo"], w["blocks"][0]["down"], w["blocks"][1]["moe"]["router"],
+                                 w["blocks"][2]["moe"]["down"][1], w["embedding"])]   # the checker steps `w` in place
+    dev.train_step_batch(seqs)
+    if kind == "sgd":
+        ora.train_step(batch, _router_logits(c, router), lr=0.05, kind="sgd")
+    else:
+        ora.train_step(batch, _router_logits(c, router), lr=1e-2, beta1=0.9, beta2=0.99, wd=0.1, kind="lion")
+    assert dev.optimizer_step() == 1
+    after = [(dev.get_param(D.WO, 0), ora.w["blocks"][0]["wo"]),
+             (dev.get_param(D.FFN_DOWN, 0), ora.w["blocks"][0]["down"]),
+             (dev.get_param(D.MOE_ROUTER, 1), ora.moe[1].get_weight(0)),
+             (dev.get_param(D.MOE_DOWN, 2, expert=1), ora.moe[2].get_weight(3, 1)),
+             (dev.get_param(D.EMBEDDING), ora.w["embedding"])]
+    for (after_dev, after_ora), before in zip(after, before):
+        if kind == "sgd":
+            assert rel_l2(after_dev - before, after_ora - before) <= TOL
+        else:
+            # every touched weight moves by the learning rate; the sign can differ only where the bf16 and f32
+            # gradients straddle zero
+            assert np.mean(np.abs(after_dev - after_ora) > 5e-3) <= 0.03
+            assert np.abs(after_dev - before).max() <= 1e-2 * (1 + 0.1 * np.abs(before).max()) + 1e-6
+    assert np.all(dev.get_grad(D.WO, 0) == 0)
     dev.close()
 
 

@@ -232,3 +232,27 @@ def test_a_train_step_moves_the_loss_down():
     for _ in range(5):
         last = m.train_step(batch, lr=1e-2)[0]
     assert last < first
+
+
+def test_sgd_and_lion_steps_of_the_model_follow_the_rule():  # param.rs:557-561, 590-613; gpu_transformer.rs:1855-1884
+    c = _tiny()
+    batch = T.TokenBatch([[3, 14, 15, 9, 2, 6], [6, 5, 35, 8, 9, 7]])
+    for kind in ("sgd", "lion"):
+        w = T.seeded_model_weights(c, 2, std=0.2)
+        m = T.OracleLm(c, w)
+        before = m.w["blocks"][0]["wo"].copy()
+        m.zero_grad()
+        m.accumulate_step(batch)
+        g = m.grads["blocks"][0]["wo"].copy()
+        m.step(lr=1e-2, beta1=0.9, beta2=0.99, wd=0.0, kind=kind)
+        moved = m.w["blocks"][0]["wo"] - before
+        if kind == "sgd":
+            np.testing.assert_allclose(moved, -np.float32(1e-2) * g, rtol=1e-5, atol=1e-7)   # one rounding of the weight
+        else:
+            np.testing.assert_allclose(moved, -np.float32(1e-2) * np.sign(g), rtol=1e-5, atol=1e-7)
+        assert m.step_count == 1 and np.all(m.grads["blocks"][0]["wo"] == 0)
+    m = T.OracleLm(c, T.seeded_model_weights(c, 2, std=0.2))
+    first = m.train_step(batch, lr=2e-3, beta2=0.99, kind="lion")[0]
+    for _ in range(8):
+        last = m.train_step(batch, lr=2e-3, beta2=0.99, kind="lion")[0]
+    assert last < first
