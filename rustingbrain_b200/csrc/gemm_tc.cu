@@ -182,7 +182,15 @@ __host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
 // ---------------------------------------------------------------------------
 struct Tile {
   int group, row0 /*first row of the row-indexed operands*/, m0, n0, k_iters;
+  int skip;   // causal products: the tile lies wholly above the diagonal, nobody touches it
 };
+
+// rows-as-K causal products: does K-stage ki (64 query rows) reach the tile's keys [m0, m0 + 128)?
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ bool k_stage_live(const GemmArgs& p, const Tile& tl, int ki) {
+  if (!ROWS_ARE_K || p.causal == 0) return true;
+  return (ki * BK) % p.causal + BK > tl.m0;
+}
 
 template <bool ROWS_ARE_K>
 __device__ __forceinline__ int total_tiles(const SharedTail* st, const GemmArgs& p) {
@@ -194,6 +202,7 @@ __device__ __forceinline__ int total_tiles(const SharedTail* st, const GemmArgs&
 template <bool ROWS_ARE_K>
 __device__ __forceinline__ Tile decode_tile(const SharedTail* st, const GemmArgs& p, int t) {
   Tile tl;
+  tl.skip = 0;
   const int nt = ceil_div(p.N, BN);
   if (ROWS_ARE_K) {
     const int mt = ceil_div(p.M, BM);
@@ -220,6 +229,13 @@ __device__ __forceinline__ Tile decode_tile(const SharedTail* st, const GemmArgs
     tl.m0 = 0;
     tl.row0 = st->row0[g] + (local % mt) * BM;
     tl.k_iters = ceil_div(p.K, BK);
+    if (p.causal) {
+      // the last query position among the tile's rows (a tile that crosses into the next head sees them all)
+      const int s_first = ((local % mt) * BM) % p.causal;
+      const int s_last = s_first + BM > p.causal ? p.causal - 1 : s_first + BM - 1;
+      if (p.causal_kind == CAUSAL_COLS) tl.skip = tl.n0 > s_last;
+      else if (p.causal_kind == CAUSAL_K) tl.k_iters = min(tl.k_iters, s_last / BK + 1);
+    }
   }
   return tl;
 }
@@ -488,7 +504,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // p.starve (test hook): the producer loads nothing, so the consumers' bounded waits run out
       for (int t = blockIdx.x; t < n_tiles && ok && !p.starve; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+        if (tl.skip) continue;
         for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!k_stage_live<ROWS_ARE_K>(p, tl, ki)) continue;
           if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 101, p.wait_limit)) { ok = false; break; }
           const uint32_t bar = smem_u32(&st->full[stage]);
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -529,13 +547,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+        if (tl.skip) continue;
         if (!mbar_wait(smem_u32(&st->tmem_empty[acc]), acc_phase ^ 1, p.error_flag, 102, p.wait_limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         // the last column tile may be narrower: issue an MMA only as wide as needed (multiple of 16)
         const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
         const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
+        uint32_t accumulate = 0;   // the first MMA of the tile overwrites the accumulator
         for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!k_stage_live<ROWS_ARE_K>(p, tl, ki)) continue;
           if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 103, p.wait_limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = tiles_base + stage * STAGE_BYTES;
@@ -544,13 +565,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
           for (int kk = 0; kk < BK / UMMA_K; ++kk) {
             const uint64_t da = make_desc(sa + kk * a_adv, a_lbo, a_sbo);
             const uint64_t db = make_desc(sb + kk * b_adv, b_lbo, b_sbo);
-            umma_bf16(d_tmem, da, db, idesc, (ki | kk) != 0 ? 1u : 0u);
+            umma_bf16(d_tmem, da, db, idesc, accumulate);
+            accumulate = 1;
           }
           umma_commit(smem_u32(&st->empty[stage]));   // frees the stage once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        if (tl.k_iters > 0) umma_commit(smem_u32(&st->tmem_full[acc]));
+        if (accumulate) umma_commit(smem_u32(&st->tmem_full[acc]));
         else mbar_arrive(smem_u32(&st->tmem_full[acc]));   // empty group: nothing was accumulated
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
@@ -569,6 +591,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const Tile tl = decode_tile<ROWS_ARE_K>(st, p, t);
+      if (tl.skip) continue;
       if (!mbar_wait(smem_u32(&st->tmem_full[acc]), acc_phase, p.error_flag, 104, p.wait_limit)) { ok = false; break; }
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
@@ -867,7 +890,7 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN;
       if (!tl.skip) {
         Tile one;
-        one.group = tl.group; one.row0 = tl.row0; one.m0 = tl.m0; one.n0 = tl.n0; one.k_iters = tl.k_iters;
+        one.group = tl.group; one.row0 = tl.row0; one.m0 = tl.m0; one.n0 = tl.n0; one.k_iters = tl.k_iters; one.skip = 0;
         epilogue_tile<EPI>(p, one, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0, stg_all + (warp - 2) * STG_BYTES_PER_WARP);
       }
       tc_fence_before();

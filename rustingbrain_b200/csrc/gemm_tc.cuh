@@ -35,7 +35,18 @@ struct GemmArgs {
   int* error_flag;             // device int, set non-zero when a bounded wait gives up
   long long wait_limit = 0;    // filled at launch: clock cycles a barrier wait may take before it gives up
   int starve = 0;              // filled at launch (test hook): the producer loads nothing
+  // Causal attention products (0: off).  `causal` is the sequence length S: row r of a group is query position
+  // r % S (the g query heads of a group follow one another), key positions are 0 .. S-1, and entries with
+  // key > query are known zeros (or never read).  What is skipped depends on where the keys sit:
+  //   CAUSAL_COLS  rows-as-M, output columns are keys (Q K^T, dO V^T): tiles wholly above the diagonal are neither
+  //                computed nor stored;
+  //   CAUSAL_K     rows-as-M, the reduction runs over keys (P V, dS K): it stops after the tile's last visible key;
+  //   rows-as-K    (P^T dO, dS^T Q: output rows are keys, the reduction runs over queries): K-stages whose queries
+  //                all come before the tile's first key are skipped.  causal_kind is ignored.
+  int causal = 0;
+  int causal_kind = 0;
 };
+enum { CAUSAL_COLS = 1, CAUSAL_K = 2 };
 
 // Operand descriptions for tensor-map construction (bf16, row-major).
 struct Operand {

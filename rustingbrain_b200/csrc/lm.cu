@@ -168,28 +168,28 @@ Meta dense_meta(lm_model* M, int rows) { return Meta{M->meta_table + 4 * rows, M
 
 // out[rows, N] = A[rows, K] * B_g[N, K]^T
 int mm_nt(lm_model* M, const void* A, long long a_rows, int K, const void* B, int N, Meta mt, void* out, long long ld,
-          int epi = tc::EPI_STORE, void* out1 = nullptr, long long ld1 = 0) {
+          int epi = tc::EPI_STORE, void* out1 = nullptr, long long ld1 = 0, int causal = 0, int causal_kind = 0) {
   tc::GemmArgs a{};
   a.group_row0 = mt.row0; a.tile_start = mt.tstart; a.n_groups = mt.groups; a.error_flag = M->error_flag;
-  a.N = N; a.K = K; a.out0 = out; a.ld0 = ld; a.out1 = out1; a.ld1 = ld1;
+  a.N = N; a.K = K; a.out0 = out; a.ld0 = ld; a.out1 = out1; a.ld1 = ld1; a.causal = causal; a.causal_kind = causal_kind;
   LCK(tc::gemm_rows_nt(tc::Operand{A, a_rows, K, 1}, tc::Operand{B, N, K, mt.groups}, a, epi, M->sm_count, M->st));
   return MOE_OK;
 }
 // out[rows, N] = A[rows, K] * B_g[K, N]
 int mm_nn(lm_model* M, const void* A, long long a_rows, int K, const void* B, int N, Meta mt, void* out, long long ld,
-          int epi = tc::EPI_STORE, const void* aux = nullptr, long long ldaux = 0) {
+          int epi = tc::EPI_STORE, const void* aux = nullptr, long long ldaux = 0, int causal = 0, int causal_kind = 0) {
   tc::GemmArgs a{};
   a.group_row0 = mt.row0; a.tile_start = mt.tstart; a.n_groups = mt.groups; a.error_flag = M->error_flag;
-  a.N = N; a.K = K; a.out0 = out; a.ld0 = ld; a.aux = aux; a.ldaux = ldaux;
+  a.N = N; a.K = K; a.out0 = out; a.ld0 = ld; a.aux = aux; a.ldaux = ldaux; a.causal = causal; a.causal_kind = causal_kind;
   LCK(tc::gemm_rows_nn(tc::Operand{A, a_rows, K, 1}, tc::Operand{B, K, N, mt.groups}, a, epi, M->sm_count, M->st));
   return MOE_OK;
 }
 // C_g[Mo, N] (+)= A[rows_g, Mo]^T * B[rows_g, N]   (f32 out)
 int mm_tn(lm_model* M, const void* A, long long a_rows, int Mo, const void* B, long long b_rows, int N, Meta mt, float* out,
-          long long ld, long long group_stride, int accumulate) {
+          long long ld, long long group_stride, int accumulate, int causal = 0) {
   tc::GemmArgs a{};
   a.group_row0 = mt.row0; a.n_groups = mt.groups; a.error_flag = M->error_flag;
-  a.M = Mo; a.N = N; a.out0 = out; a.ld0 = ld; a.group_stride0 = group_stride; a.accumulate = accumulate;
+  a.M = Mo; a.N = N; a.out0 = out; a.ld0 = ld; a.group_stride0 = group_stride; a.accumulate = accumulate; a.causal = causal;
   LCK(tc::gemm_rows_tn(tc::Operand{A, a_rows, Mo, 1}, tc::Operand{B, b_rows, N, 1}, a, M->sm_count, M->st));
   return MOE_OK;
 }
@@ -633,9 +633,11 @@ int forward_blocks(lm_model* M, const Batch& bt, bool save) {
     RC(norm_fwd(M, M->xs[l], b.attn_norm, b.xn1, rows));
     RC(mm_nt(M, b.xn1, rows, d, M->wb + b.wqkv, M->QN, dm, M->qkv, M->QN));
     LCK(lm::launch_rope_pack(M->qkv, M->cos_t, M->sin_t, b.q_hm, b.k_hm, b.v_hm, a, M->st));
-    RC(mm_nt(M, b.q_hm, bt.TQ, M->hd, b.k_hm, a.S_pad, am, M->scores, a.S_pad));
+    // the half of the square above the diagonal is never computed: score tiles there are skipped (the softmax reads
+    // the visible prefix only and writes the rest of the row as zeros), and P V stops at the last visible key
+    RC(mm_nt(M, b.q_hm, bt.TQ, M->hd, b.k_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));
     LCK(lm::launch_softmax_causal(M->scores, b.probs, a, scale, 1, M->st));
-    RC(mm_nn(M, b.probs, bt.TQ, a.S_pad, b.v_hm, M->hd, am, M->o_hm, M->hd));
+    RC(mm_nn(M, b.probs, bt.TQ, a.S_pad, b.v_hm, M->hd, am, M->o_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));
     LCK(lm::launch_heads_to_tokens(M->o_hm, b.merged, a, M->st));
     RC(mm_nt(M, b.merged, rows, HD, M->wb + b.wo, d, dm, M->tmp, d));
     LCK(lm::launch_add(M->tmp, M->xs[l], b.res, (long long)rows * d, M->st));
@@ -699,11 +701,14 @@ int backward_blocks(lm_model* M, const Batch& bt) {
     RC(mm_nn(M, other, rows, d, M->wb + b.wo, HD, dm, M->d_merged, HD));
     RC(mm_tn_dense(M, other, rows, d, b.merged, HD, M->g + b.wo, HD));
     LCK(lm::launch_tokens_to_heads(M->d_merged, M->do_hm, a, M->st));
-    RC(mm_nt(M, M->do_hm, bt.TQ, M->hd, b.v_hm, a.S_pad, am, M->scores, a.S_pad));                       // dL/dP
-    RC(mm_tn(M, b.probs, bt.TQ, a.S_pad, M->do_hm, bt.TQ, M->hd, am, M->dv_hm, M->hd, kv_stride, 0));    // dL/dV, summed over the group
-    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, M->st));                               // dL/dscore
-    RC(mm_nn(M, M->scores, bt.TQ, a.S_pad, b.k_hm, M->hd, am, M->dq_hm, M->hd));                         // dL/dQ
-    RC(mm_tn(M, M->scores, bt.TQ, a.S_pad, b.q_hm, bt.TQ, M->hd, am, M->dk_hm, M->hd, kv_stride, 0));    // dL/dK
+    // as in the forward pass, nothing above the diagonal is computed: dL/dP tiles there are skipped (the softmax
+    // backward reads the visible prefix and writes zeros behind it), the two reductions over keys stop at the last
+    // visible key, and the two reductions over queries skip the queries that come before the tile's keys
+    RC(mm_nt(M, M->do_hm, bt.TQ, M->hd, b.v_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));   // dL/dP
+    RC(mm_tn(M, b.probs, bt.TQ, a.S_pad, M->do_hm, bt.TQ, M->hd, am, M->dv_hm, M->hd, kv_stride, 0, a.S));    // dL/dV, summed over the group
+    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, 1, M->st));                            // dL/dscore
+    RC(mm_nn(M, M->scores, bt.TQ, a.S_pad, b.k_hm, M->hd, am, M->dq_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));   // dL/dQ
+    RC(mm_tn(M, M->scores, bt.TQ, a.S_pad, b.q_hm, bt.TQ, M->hd, am, M->dk_hm, M->hd, kv_stride, 0, a.S));    // dL/dK
     LCK(lm::launch_qkv_grad_unpack(M->dq_hm, M->dk_hm, M->dv_hm, M->cos_t, M->sin_t, M->dqkv, a, M->st));
     RC(mm_nn(M, M->dqkv, rows, M->QN, M->wb + b.wqkv, d, dm, M->dxn, d));
     RC(mm_tn_dense(M, M->dqkv, rows, M->QN, b.xn1, d, M->g + b.wqkv, d));

@@ -196,28 +196,42 @@ softmax_causal_kernel(const bf16* __restrict__ scores, bf16* __restrict__ probs,
   }
 }
 
-// in place on grad: dL/dscore = p * (dL/dp - sum_j p_j dL/dp_j) * scale
+// in place on grad: dL/dscore = p * (dL/dp - sum_j p_j dL/dp_j) * scale.  With `causal` the entries behind the
+// visible prefix are not read (the product that made dL/dp skipped them) and are written as zeros, like padding rows.
 __global__ void __launch_bounds__(256)
-softmax_backward_kernel(const bf16* __restrict__ probs, bf16* __restrict__ grad, AttnShape a, float scale) {
+softmax_backward_kernel(const bf16* __restrict__ probs, bf16* __restrict__ grad, AttnShape a, float scale, int causal) {
   const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= (long long)a.G * a.GR) return;
   const uint4* p = reinterpret_cast<const uint4*>(probs + row * a.S_pad);
   uint4* g = reinterpret_cast<uint4*>(grad + row * a.S_pad);
   const int chunks = a.S_pad / 8;
+  const int within = (int)(row % a.GR);
+  if (within >= a.g * a.S) {                      // padding row of the group
+    for (int c = lane; c < chunks; c += 32) g[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int visible = causal ? within % a.S + 1 : a.S;
+  const int vchunks = (visible + 7) / 8;
   float dot = 0.f;
-  for (int c = lane; c < chunks; c += 32) {
+  for (int c = lane; c < vchunks; c += 32) {
     float fp[8], fg[8];
     unpack8(p[c], fp); unpack8(g[c], fg);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dot += fp[i] * fg[i];
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) dot += fp[i] * fg[i];
   }
   dot = warp_sum(dot);
   for (int c = lane; c < chunks; c += 32) {
     float fp[8], fg[8];
-    unpack8(p[c], fp); unpack8(g[c], fg);
+    if (c < vchunks) {
+      unpack8(p[c], fp); unpack8(g[c], fg);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) fg[i] = fp[i] * (fg[i] - dot) * scale;
+      for (int i = 0; i < 8; ++i) fg[i] = c * 8 + i < visible ? fp[i] * (fg[i] - dot) * scale : 0.f;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) fg[i] = 0.f;
+    }
     g[c] = pack8(fg);
   }
 }
@@ -386,9 +400,9 @@ cudaError_t launch_softmax_causal(const bf16* scores, bf16* probs, AttnShape a, 
   softmax_causal_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(scores, probs, a, scale, causal); count_launch();
   return cudaGetLastError();
 }
-cudaError_t launch_softmax_backward(const bf16* probs, bf16* grad, AttnShape a, float scale, cudaStream_t st) {
+cudaError_t launch_softmax_backward(const bf16* probs, bf16* grad, AttnShape a, float scale, int causal, cudaStream_t st) {
   const long long rows = (long long)a.G * a.GR;
-  softmax_backward_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(probs, grad, a, scale); count_launch();
+  softmax_backward_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(probs, grad, a, scale, causal); count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_heads_to_tokens(const bf16* o_hm, bf16* merged, AttnShape a, cudaStream_t st) {

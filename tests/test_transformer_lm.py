@@ -102,10 +102,14 @@ def _check_grads(c, dev, ora, tol=TOL):
     (dict(head_dim=32, n_heads=4, n_kv_heads=1), [24, 24]),      # one kv head for all, head_dim 32
     (dict(tie_embeddings=False, moe_layers=(0,), shared_expert=False, n_layers=2), [16, 16, 16]),
     (dict(moe_layers=()), [32, 17]),                             # dense only
+    # sequences longer than one tile of the attention products: the tiles and K-stages above the diagonal are skipped
+    (dict(max_seq_len=512, n_layers=2, moe_layers=(1,)), [384, 300]),          # 128 | S: tiles line up with the heads
+    (dict(max_seq_len=512, n_layers=2, moe_layers=()), [320]),                 # tiles that cross from one head into the next
+    (dict(max_seq_len=512, n_layers=2, moe_layers=(), n_kv_heads=4), [416, 100]),   # one query head per key/value head
 ])
 def test_logits_loss_and_every_gradient_match_the_checker(over, lengths):
     c = _config(**over)
-    dev, ora, _ = _pair(c)
+    dev, ora, _ = _pair(c, rows=max(256, len(lengths) * max(lengths)))
     seqs = _sequences(c, lengths)
     logits, router = dev.forward_batch(seqs, return_router_logits=True)
     batch = T.TokenBatch(seqs)
