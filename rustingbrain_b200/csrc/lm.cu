@@ -68,7 +68,9 @@ struct lm_model {
   std::vector<int> last_seen;       // per vocabulary id: last row that held it (host scratch of the scatter chains)
   float* split_scratch = nullptr;   // partial weight gradients of the row-split products
   long long split_elems = 0;
-  int* split_meta = nullptr;        // group tables of the row-split products
+  int* split_meta = nullptr;        // group tables of the row-split products: SPLIT_SLOTS tables of 32 entries
+  struct SplitKey { int splits, chunk, padded; };
+  std::vector<SplitKey> split_keys; // which (splits, chunk, padded) each filled slot holds
   cudaStream_t st = nullptr;
   cudaEvent_t ev[5] = {};
   float last_ms[4] = {0, 0, 0, 0};
@@ -198,6 +200,7 @@ int mm_tn(lm_model* M, const void* A, long long a_rows, int Mo, const void* B, l
     const int rc_ = (call);              \
     if (rc_ != MOE_OK) return rc_;       \
   } while (0)
+constexpr int SPLIT_SLOTS = 16;
 // Row ranges of a product whose rows are the reduction, cut into `splits` chunks: meta[g] = min(g * chunk, padded).
 __global__ void split_rows_kernel(int* meta, int splits, int chunk, int padded) {
   const int g = threadIdx.x;
@@ -224,8 +227,18 @@ int mm_tn_dense(lm_model* M, const void* A, int rows, int Mo, const void* B, int
   splits = ceil_div(padded, chunk);
   if (splits <= 1 || ld != N || (long long)splits * Mo * N > M->split_elems)
     return mm_tn(M, A, rows, Mo, B, rows, N, dense_meta(M, rows), out, ld, 0, 1);
-  split_rows_kernel<<<1, 32, 0, M->st>>>(M->split_meta, splits, chunk, padded); count_launch();
-  RC_(mm_tn(M, A, rows, Mo, B, rows, N, Meta{M->split_meta, nullptr, splits}, M->split_scratch, N, (long long)Mo * N, 0));
+  // the table depends on (splits, chunk, padded) only: a step uses a handful of them, each written once
+  int slot = -1;
+  for (size_t i = 0; i < M->split_keys.size(); ++i) {
+    const auto& k = M->split_keys[i];
+    if (k.splits == splits && k.chunk == chunk && k.padded == padded) { slot = (int)i; break; }
+  }
+  if (slot < 0) {
+    slot = M->split_keys.size() < (size_t)SPLIT_SLOTS - 1 ? (int)M->split_keys.size() : SPLIT_SLOTS - 1;   // the last slot is rewritten
+    split_rows_kernel<<<1, 32, 0, M->st>>>(M->split_meta + 32 * slot, splits, chunk, padded); count_launch();
+    if (slot < SPLIT_SLOTS - 1) M->split_keys.push_back({splits, chunk, padded});
+  }
+  RC_(mm_tn(M, A, rows, Mo, B, rows, N, Meta{M->split_meta + 32 * slot, nullptr, splits}, M->split_scratch, N, (long long)Mo * N, 0));
   const long long n = (long long)Mo * N;
   add_partials_kernel<<<(unsigned)((n + 255) / 256), 256, 0, M->st>>>(out, M->split_scratch, n, splits); count_launch();
   LCK(cudaGetLastError());
@@ -379,7 +392,7 @@ int32_t lm_create(const lm_config_t* config, lm_model_t** out) {
   LCK(cudaMallocHost((void**)&M->first_pin, (size_t)R * 4)); LCK(cudaMallocHost((void**)&M->next_pin, (size_t)R * 4));
   M->last_seen.assign(M->V, -1);
   M->split_elems = 16ll * std::max<long long>(std::max(QN, HD) * d, 2 * Fp * d);   // at most 16 partial results of the widest matrix
-  LA(M->split_scratch, M->split_elems * 4, false); LA(M->split_meta, 64 * 4, true);
+  LA(M->split_scratch, M->split_elems * 4, false); LA(M->split_meta, SPLIT_SLOTS * 32 * 4, true);
 
   // the MoE blocks: handles of the layer library, bf16 products over f32 master weights
   for (int l = 0; l < M->L; ++l) {
@@ -636,7 +649,7 @@ int forward_blocks(lm_model* M, const Batch& bt, bool save) {
     // the half of the square above the diagonal is never computed: score tiles there are skipped (the softmax reads
     // the visible prefix only and writes the rest of the row as zeros), and P V stops at the last visible key
     RC(mm_nt(M, b.q_hm, bt.TQ, M->hd, b.k_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));
-    LCK(lm::launch_softmax_causal(M->scores, b.probs, a, scale, 1, M->st));
+    LCK(lm::launch_softmax_causal(M->scores, b.probs, a, scale, 1, !tc::pair_mode(), M->st));   // the two-SM kernel skips nothing
     RC(mm_nn(M, b.probs, bt.TQ, a.S_pad, b.v_hm, M->hd, am, M->o_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));
     LCK(lm::launch_heads_to_tokens(M->o_hm, b.merged, a, M->st));
     RC(mm_nt(M, b.merged, rows, HD, M->wb + b.wo, d, dm, M->tmp, d));
@@ -706,7 +719,7 @@ int backward_blocks(lm_model* M, const Batch& bt) {
     // visible key, and the two reductions over queries skip the queries that come before the tile's keys
     RC(mm_nt(M, M->do_hm, bt.TQ, M->hd, b.v_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));   // dL/dP
     RC(mm_tn(M, b.probs, bt.TQ, a.S_pad, M->do_hm, bt.TQ, M->hd, am, M->dv_hm, M->hd, kv_stride, 0, a.S));    // dL/dV, summed over the group
-    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, 1, M->st));                            // dL/dscore
+    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, 1, !tc::pair_mode(), M->st));                            // dL/dscore
     RC(mm_nn(M, M->scores, bt.TQ, a.S_pad, b.k_hm, M->hd, am, M->dq_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));   // dL/dQ
     RC(mm_tn(M, M->scores, bt.TQ, a.S_pad, b.q_hm, bt.TQ, M->hd, am, M->dk_hm, M->hd, kv_stride, 0, a.S));    // dL/dK
     LCK(lm::launch_qkv_grad_unpack(M->dq_hm, M->dk_hm, M->dv_hm, M->cos_t, M->sin_t, M->dqkv, a, M->st));

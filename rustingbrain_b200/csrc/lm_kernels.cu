@@ -236,6 +236,118 @@ softmax_backward_kernel(const bf16* __restrict__ probs, bf16* __restrict__ grad,
   }
 }
 
+// Register-resident variants for rows of at most NC * 256 entries: every lane keeps its NC 16-byte pieces of the row,
+// so the scores (and dL/dp) cross the memory system once.  `zero_cols` is how far behind the visible prefix zeros are
+// written, rounded up to 128 from the query position: the causal products that read these rows never look further
+// (a caller that cannot promise that passes zero_tail_all and the whole tail is written).
+template <int NC>
+__global__ void __launch_bounds__(256)
+softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ probs, AttnShape a, float scale, int causal,
+                           int zero_tail_all) {
+  const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (long long)a.G * a.GR) return;
+  const int within = (int)(row % a.GR);
+  const uint4* src = reinterpret_cast<const uint4*>(scores + row * a.S_pad);
+  uint4* dst = reinterpret_cast<uint4*>(probs + row * a.S_pad);
+  const int chunks = a.S_pad / 8;
+  if (within >= a.g * a.S) {                      // padding row of the group
+    for (int c = lane; c < chunks; c += 32) dst[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int visible = causal ? within % a.S + 1 : a.S;
+  const int vchunks = (visible + 7) / 8;
+  const int zchunks = zero_tail_all ? chunks : min(chunks, ((visible + 127) & ~127) / 8);
+  uint4 v[NC];
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    v[j] = c < vchunks ? src[c] : make_uint4(0, 0, 0, 0);
+  }
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    float f[8];
+    unpack8(v[j], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) mx = fmaxf(mx, f[i] * scale);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    float f[8];
+    unpack8(v[j], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) sum += expf(f[i] * scale - mx);
+  }
+  sum = warp_sum(sum);
+  const float inv = sum > 0.f ? 1.0f / sum : 1.0f;   // activations.rs:65-69
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    if (c >= zchunks) break;
+    float f[8];
+    unpack8(v[j], f);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = c * 8 + i < visible ? expf(f[i] * scale - mx) * inv : 0.f;
+    dst[c] = pack8(f);
+  }
+}
+
+template <int NC>
+__global__ void __launch_bounds__(256)
+softmax_backward_regs_kernel(const bf16* __restrict__ probs, bf16* __restrict__ grad, AttnShape a, float scale, int causal,
+                             int zero_tail_all) {
+  const long long row = (long long)blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= (long long)a.G * a.GR) return;
+  const uint4* p = reinterpret_cast<const uint4*>(probs + row * a.S_pad);
+  uint4* g = reinterpret_cast<uint4*>(grad + row * a.S_pad);
+  const int chunks = a.S_pad / 8;
+  const int within = (int)(row % a.GR);
+  if (within >= a.g * a.S) {                      // padding row of the group
+    for (int c = lane; c < chunks; c += 32) g[c] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const int visible = causal ? within % a.S + 1 : a.S;
+  const int vchunks = (visible + 7) / 8;
+  const int zchunks = zero_tail_all ? chunks : min(chunks, ((visible + 127) & ~127) / 8);
+  uint4 vp[NC], vg[NC];
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    vp[j] = c < vchunks ? p[c] : make_uint4(0, 0, 0, 0);
+    vg[j] = c < vchunks ? g[c] : make_uint4(0, 0, 0, 0);
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    float fp[8], fg[8];
+    unpack8(vp[j], fp); unpack8(vg[j], fg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (c * 8 + i < visible) dot += fp[i] * fg[i];
+  }
+  dot = warp_sum(dot);
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = lane + 32 * j;
+    if (c >= zchunks) break;
+    float fp[8], fg[8];
+    unpack8(vp[j], fp); unpack8(vg[j], fg);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) fg[i] = c * 8 + i < visible ? fp[i] * (fg[i] - dot) * scale : 0.f;
+    g[c] = pack8(fg);
+  }
+}
+
 __global__ void add_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ out, long long n8) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n8) return;
@@ -278,6 +390,9 @@ __device__ __forceinline__ float block_reduce(float v, float* sh, bool is_max) {
 }
 
 // ld is a multiple of 32, so a row is a whole number of 16-byte vectors; columns past `vocab` are padding.
+// Two exponentials per logit make this kernel instruction bound with expf (262 M logits per step of the 55M model),
+// so the bulk uses the hardware exponential (relative error about 2^-21 per term, far inside the bf16 logits'
+// own rounding); the row's loss, one term, uses expf and logf.
 __global__ void __launch_bounds__(256)
 cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss, int vocab,
                      int ld, float inv_predicted) {
@@ -299,10 +414,10 @@ cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets,
 #pragma unroll
     for (int i = 0; i < 8; ++i)
       if (c * 8 + i < vocab) cm = fmaxf(cm, f[i]);
-    if (cm > mx) { sum *= expf(mx - cm); mx = cm; }
+    if (cm > mx) { sum *= __expf(mx - cm); mx = cm; }
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      if (c * 8 + i < vocab) sum += expf(f[i] - mx);
+      if (c * 8 + i < vocab) sum += __expf(f[i] - mx);
   }
   const float bm = block_reduce(mx, sh, true);
   sum = block_reduce(mx > -INFINITY ? sum * expf(mx - bm) : 0.f, sh, false);
@@ -318,7 +433,7 @@ cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets,
       const int j = c * 8 + i;
       float g = 0.f;
       if (j < vocab) {
-        g = expf(f[i] - bm) * inv * inv_predicted;
+        g = __expf(f[i] - bm) * inv * inv_predicted;
         if (j == target) g -= inv_predicted;
       }
       f[i] = g;
@@ -395,14 +510,32 @@ cudaError_t launch_rope_pack(const bf16* qkv, const float* cos_t, const float* s
   rope_pack_kernel<<<a.B * a.S, 128, 0, st>>>(qkv, cos_t, sin_t, q_hm, k_hm, v_hm, a); count_launch();
   return cudaGetLastError();
 }
-cudaError_t launch_softmax_causal(const bf16* scores, bf16* probs, AttnShape a, float scale, int causal, cudaStream_t st) {
+// The bounded zero tail is only right when a 128-row tile never crosses from one query head into the next.
+static int tail_all(const AttnShape& a, int causal, int bounded_tail) { return !(causal && bounded_tail && a.S % 128 == 0); }
+cudaError_t launch_softmax_causal(const bf16* scores, bf16* probs, AttnShape a, float scale, int causal, int bounded_tail,
+                                  cudaStream_t st) {
   const long long rows = (long long)a.G * a.GR;
-  softmax_causal_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(scores, probs, a, scale, causal); count_launch();
+  const unsigned grid = blocks_for(rows, 8);
+  const int all = tail_all(a, causal, bounded_tail);
+  if (a.S_pad <= 256) softmax_causal_regs_kernel<1><<<grid, 256, 0, st>>>(scores, probs, a, scale, causal, all);
+  else if (a.S_pad <= 512) softmax_causal_regs_kernel<2><<<grid, 256, 0, st>>>(scores, probs, a, scale, causal, all);
+  else if (a.S_pad <= 1024) softmax_causal_regs_kernel<4><<<grid, 256, 0, st>>>(scores, probs, a, scale, causal, all);
+  else if (a.S_pad <= 2048) softmax_causal_regs_kernel<8><<<grid, 256, 0, st>>>(scores, probs, a, scale, causal, all);
+  else softmax_causal_kernel<<<grid, 256, 0, st>>>(scores, probs, a, scale, causal);
+  count_launch();
   return cudaGetLastError();
 }
-cudaError_t launch_softmax_backward(const bf16* probs, bf16* grad, AttnShape a, float scale, int causal, cudaStream_t st) {
+cudaError_t launch_softmax_backward(const bf16* probs, bf16* grad, AttnShape a, float scale, int causal, int bounded_tail,
+                                    cudaStream_t st) {
   const long long rows = (long long)a.G * a.GR;
-  softmax_backward_kernel<<<blocks_for(rows, 8), 256, 0, st>>>(probs, grad, a, scale, causal); count_launch();
+  const unsigned grid = blocks_for(rows, 8);
+  const int all = tail_all(a, causal, bounded_tail);
+  if (a.S_pad <= 256) softmax_backward_regs_kernel<1><<<grid, 256, 0, st>>>(probs, grad, a, scale, causal, all);
+  else if (a.S_pad <= 512) softmax_backward_regs_kernel<2><<<grid, 256, 0, st>>>(probs, grad, a, scale, causal, all);
+  else if (a.S_pad <= 1024) softmax_backward_regs_kernel<4><<<grid, 256, 0, st>>>(probs, grad, a, scale, causal, all);
+  else if (a.S_pad <= 2048) softmax_backward_regs_kernel<8><<<grid, 256, 0, st>>>(probs, grad, a, scale, causal, all);
+  else softmax_backward_kernel<<<grid, 256, 0, st>>>(probs, grad, a, scale, causal);
+  count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_heads_to_tokens(const bf16* o_hm, bf16* merged, AttnShape a, cudaStream_t st) {

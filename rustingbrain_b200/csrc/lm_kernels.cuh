@@ -31,10 +31,13 @@ cudaError_t launch_embed_scatter(const uint32_t* ids, const bf16* grad_x, float*
 
 cudaError_t launch_rope_pack(const bf16* qkv, const float* cos_t, const float* sin_t, bf16* q_hm, bf16* k_hm, bf16* v_hm,
                              AttnShape a, cudaStream_t st);
-cudaError_t launch_softmax_causal(const bf16* scores, bf16* probs, AttnShape a, float scale, int causal, cudaStream_t st);
-// causal: only the visible prefix of a row is read; everything behind it is written as zeros
+// causal: only the visible prefix of a row is read.  bounded_tail: zeros are written only as far behind the prefix as
+// the causal tensor-core products read (up to the next multiple of 128 from the query position); otherwise the whole
+// rest of the row is written.
+cudaError_t launch_softmax_causal(const bf16* scores, bf16* probs, AttnShape a, float scale, int causal, int bounded_tail,
+                                  cudaStream_t st);
 cudaError_t launch_softmax_backward(const bf16* probs, bf16* grad_probs_to_scores, AttnShape a, float scale, int causal,
-                                    cudaStream_t st);
+                                    int bounded_tail, cudaStream_t st);
 cudaError_t launch_heads_to_tokens(const bf16* o_hm, bf16* merged, AttnShape a, cudaStream_t st);
 cudaError_t launch_tokens_to_heads(const bf16* grad_merged, bf16* do_hm, AttnShape a, cudaStream_t st);
 cudaError_t launch_qkv_grad_unpack(const bf16* dq_hm, const float* dk_hm, const float* dv_hm, const float* cos_t,
