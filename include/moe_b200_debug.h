@@ -36,8 +36,9 @@ struct moe_layer;
 int32_t moe_debug_profile(struct moe_layer* layer, int32_t enable);
 int32_t moe_debug_profile_read(struct moe_layer* layer, float* milliseconds, int32_t* stages);
 
-/* Selects the two-SM (cta_group::2) variant of the grouped tensor-core GEMM for later launches. */
-int32_t moe_debug_set_tc_pair(int32_t on);
+/* Selects the tile variant of the grouped tensor-core GEMM for later launches: 0 one-SM 128x256 tiles,
+ * 1 two-SM (cta_group::2) 256x256 tiles, 2 one-SM 256x256 tiles, 3 a choice per launch between 0 and 2 (the default). */
+int32_t moe_debug_set_tc_pair(int32_t mode);
 
 /* The polling wait behind moe_ep_set_deadline_ms, driven by a clock instead of a stream (needs no device):
  * the condition becomes true `ready_after_ms` after the call starts; returns MOE_OK (0) if that happens within

@@ -32,8 +32,8 @@ int32_t moe_debug_tc_gemm(int32_t variant, const void* a, const void* b, void* o
   return e == cudaSuccess ? 0 : 3;
 }
 
-int32_t moe_debug_set_tc_pair(int32_t on) {
-  tc::set_pair_mode(on);
+int32_t moe_debug_set_tc_pair(int32_t mode) {
+  tc::set_tile_mode(mode);
   return 0;
 }
 

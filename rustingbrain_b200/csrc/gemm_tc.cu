@@ -914,6 +914,231 @@ grouped_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
 }
 
 // ---------------------------------------------------------------------------
+// Wide variant: one CTA computes a 256x256 tile as two 128-row sub-tiles that share the B stage.
+// A K-stage is 64 KiB (two A sub-tiles of 16 KiB + 32 KiB of B) for 2 x 4 MMAs, so the bytes that enter
+// the SM per MMA clock drop from 96 to 64; the ring holds 3 stages.  The two 128x256 fp32 accumulators are all
+// 512 tensor-memory columns, so they are not double buffered: the epilogue of a tile does not overlap the
+// next tile's MMAs (its loads do: the ring refills meanwhile).  A group with an odd number of 128-row
+// tiles ends in a tile with one live sub-tile: nothing is loaded, multiplied or stored for the other.
+// Causal skipping is not implemented here (the products are computed in full, which is still correct).
+// ---------------------------------------------------------------------------
+constexpr int W_STAGES = 3;
+constexpr int W_A_BYTES = 2 * A_BYTES;                    // 32 KiB
+constexpr int W_STAGE_BYTES = W_A_BYTES + B_BYTES;        // 64 KiB
+
+struct __align__(8) WideTail {
+  unsigned long long full[W_STAGES];
+  unsigned long long empty[W_STAGES];
+  unsigned long long tmem_full;
+  unsigned long long tmem_empty;
+  uint32_t tmem_base;
+  int dead;
+  int row0[MAX_GROUPS + 1];
+  int pstart[MAX_GROUPS + 1];   // exclusive prefix of ceil(m-tiles / 2) per group
+  int mtiles[MAX_GROUPS + 1];
+};
+constexpr int W_SMEM_BYTES = W_STAGES * W_STAGE_BYTES + STG_TOTAL + 1024 + (int)sizeof(WideTail);
+static_assert(W_SMEM_BYTES <= 232448, "wide tiles do not fit the shared memory of one CTA");
+
+struct WideTile {
+  int group, row0, m0, n0, k_iters, msub;   // msub: live 128-row sub-tiles (1 or 2)
+};
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ int wide_total(const WideTail* st, const GemmArgs& p) {
+  const int nt = ceil_div(p.N, BN);
+  if (ROWS_ARE_K) return p.n_groups * ceil_div(ceil_div(p.M, BM), 2) * nt;
+  return st->pstart[p.n_groups] * nt;
+}
+
+template <bool ROWS_ARE_K>
+__device__ __forceinline__ WideTile wide_decode(const WideTail* st, const GemmArgs& p, int t) {
+  WideTile tl;
+  const int nt = ceil_div(p.N, BN);
+  if (ROWS_ARE_K) {
+    const int mt = ceil_div(p.M, BM);
+    const int pt = ceil_div(mt, 2);
+    const int g = t / (pt * nt);
+    const int rem = t - g * pt * nt;
+    tl.group = g;
+    tl.n0 = (rem / pt) * BN;
+    tl.m0 = (rem % pt) * 2 * BM;
+    tl.msub = min(2, mt - (rem % pt) * 2);
+    tl.row0 = st->row0[g];
+    tl.k_iters = (st->row0[g + 1] - st->row0[g]) / BK;
+  } else {
+    int lo = 0, hi = p.n_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (st->pstart[mid] * nt <= t) lo = mid; else hi = mid;
+    }
+    const int g = lo;
+    const int pt = st->pstart[g + 1] - st->pstart[g];
+    const int local = t - st->pstart[g] * nt;
+    tl.group = g;
+    tl.n0 = (local / pt) * BN;
+    tl.m0 = 0;
+    tl.msub = min(2, st->mtiles[g] - (local % pt) * 2);
+    tl.row0 = st->row0[g] + (local % pt) * 2 * BM;
+    tl.k_iters = ceil_div(p.K, BK);
+  }
+  return tl;
+}
+
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         const GemmArgs p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t tiles_base = (raw + 1023u) & ~1023u;
+  uint8_t* stg_all = smem_raw + (tiles_base - raw) + W_STAGES * W_STAGE_BYTES;
+  WideTail* st = reinterpret_cast<WideTail*>(stg_all + STG_TOTAL);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  for (int i = threadIdx.x; i <= p.n_groups; i += NUM_THREADS) st->row0[i] = p.group_row0[i];
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int g = 0; g < p.n_groups; ++g) {
+      const int mt = ROWS_ARE_K ? 0 : p.tile_start[g + 1] - p.tile_start[g];
+      st->mtiles[g] = mt;
+      st->pstart[g] = run;
+      run += (mt + 1) >> 1;
+    }
+    st->pstart[p.n_groups] = run;
+    for (int s = 0; s < W_STAGES; ++s) {
+      mbar_init(smem_u32(&st->full[s]), 1);
+      mbar_init(smem_u32(&st->empty[s]), 1);
+    }
+    mbar_init(smem_u32(&st->tmem_full), 1);
+    mbar_init(smem_u32(&st->tmem_empty), EPI_WARPS);
+    st->dead = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&st->tmem_base), TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = st->tmem_base;
+  const int n_tiles = wide_total<ROWS_ARE_K>(st, p);
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok && !p.starve; t += gridDim.x) {
+        const WideTile tl = wide_decode<ROWS_ARE_K>(st, p, t);
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->empty[stage]), phase ^ 1, p.error_flag, 301, p.wait_limit)) { ok = false; break; }
+          const uint32_t bar = smem_u32(&st->full[stage]);
+          const uint32_t sa = tiles_base + stage * W_STAGE_BYTES;
+          const uint32_t sb = sa + W_A_BYTES;
+          mbar_expect_tx(bar, tl.msub * A_BYTES + B_BYTES);
+          if (ROWS_ARE_K) {
+            const int krow = tl.row0 + ki * BK;
+            for (int mi = 0; mi < tl.msub; ++mi) {
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j)
+                tma_load_2d(sa + mi * A_BYTES + j * BOX_BYTES, &map_a, bar, tl.m0 + mi * BM + 64 * j, krow);
+            }
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * BOX_BYTES, &map_b, bar, tl.n0 + 64 * j, krow);
+          } else {
+            for (int mi = 0; mi < tl.msub; ++mi) tma_load_2d(sa + mi * A_BYTES, &map_a, bar, ki * BK, tl.row0 + mi * BM);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j)
+                tma_load_3d(sb + j * BOX_BYTES, &map_b, bar, tl.n0 + 64 * j, ki * BK, tl.group);
+            } else {
+              tma_load_3d(sb, &map_b, bar, ki * BK, tl.n0, tl.group);
+            }
+          }
+          if (++stage == W_STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) st->dead = 1;
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuer --------------------------------
+      constexpr uint32_t a_lbo = A_MN ? BOX_BYTES : 16, a_sbo = 1024, a_adv = A_MN ? 2048 : 32;
+      constexpr uint32_t b_lbo = B_MN ? BOX_BYTES : 16, b_sbo = 1024, b_adv = B_MN ? 2048 : 32;
+      uint32_t stage = 0, phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const WideTile tl = wide_decode<ROWS_ARE_K>(st, p, t);
+        if (!mbar_wait(smem_u32(&st->tmem_empty), acc_phase ^ 1, p.error_flag, 302, p.wait_limit)) { ok = false; break; }
+        tc_fence_after();
+        const int n_live = min(BN, ((p.N - tl.n0) + 15) & ~15);
+        const uint32_t idesc = make_idesc(A_MN, B_MN, n_live);
+        uint32_t accumulate = 0;
+        for (int ki = 0; ki < tl.k_iters; ++ki) {
+          if (!mbar_wait(smem_u32(&st->full[stage]), phase, p.error_flag, 303, p.wait_limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = tiles_base + stage * W_STAGE_BYTES;
+          const uint32_t sb = sa + W_A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t db = make_desc(sb + kk * b_adv, b_lbo, b_sbo);
+            umma_bf16(tmem_base, make_desc(sa + kk * a_adv, a_lbo, a_sbo), db, idesc, accumulate);
+            if (tl.msub > 1) umma_bf16(tmem_base + BN, make_desc(sa + A_BYTES + kk * a_adv, a_lbo, a_sbo), db, idesc, accumulate);
+            accumulate = 1;
+          }
+          umma_commit(smem_u32(&st->empty[stage]));
+          if (++stage == W_STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        if (accumulate) umma_commit(smem_u32(&st->tmem_full));
+        else mbar_arrive(smem_u32(&st->tmem_full));   // empty group: nothing was accumulated
+        acc_phase ^= 1;
+      }
+      if (!ok) st->dead = 1;
+    }
+    __syncwarp();
+  } else {
+    // -------------------------------- epilogue ----------------------------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int half = (warp - 2) >> 2;
+    const int c_begin = half * (BN / 2), c_end = c_begin + BN / 2;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const WideTile tl = wide_decode<ROWS_ARE_K>(st, p, t);
+      if (!mbar_wait(smem_u32(&st->tmem_full), acc_phase, p.error_flag, 304, p.wait_limit)) { ok = false; break; }
+      tc_fence_after();
+      for (int mi = 0; mi < tl.msub; ++mi) {
+        Tile one;
+        one.group = tl.group; one.n0 = tl.n0; one.k_iters = tl.k_iters; one.skip = 0;
+        one.row0 = ROWS_ARE_K ? tl.row0 : tl.row0 + mi * BM;
+        one.m0 = ROWS_ARE_K ? tl.m0 + mi * BM : 0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + mi * BN;
+        epilogue_tile<EPI>(p, one, taddr, row_in_tile, c_begin, c_end, tl.k_iters > 0, stg_all + (warp - 2) * STG_BYTES_PER_WARP);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&st->tmem_empty));
+      acc_phase ^= 1;
+    }
+  }
+
+  __syncthreads();
+  if (st->dead || *(volatile int*)p.error_flag != 0) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Host side: tensor maps and launches
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -952,15 +1177,17 @@ static bool operand_ok(const Operand& op) {
          (op.ld == 0 || (op.ld >= op.cols && op.ld % 8 == 0));
 }
 
-static int g_pair_mode = -1;   // -1: read MOE_B200_TC_PAIR from the environment on first use
-void set_pair_mode(int on) { g_pair_mode = on ? 1 : 0; }
-bool pair_mode() {
-  if (g_pair_mode < 0) {
+static int g_tile_mode = -1;   // -1: read the environment on first use
+void set_tile_mode(int mode) { g_tile_mode = mode >= TILE_ONE_SM && mode <= TILE_AUTO ? mode : TILE_AUTO; }
+int tile_mode() {
+  if (g_tile_mode < 0) {
     const char* e = getenv("MOE_B200_TC_PAIR");
-    g_pair_mode = (e && e[0] == '1') ? 1 : 0;
+    const char* w = getenv("MOE_B200_TC_WIDE");
+    g_tile_mode = (e && e[0] == '1') ? TILE_PAIR : (w && w[0] == '1') ? TILE_WIDE : (w && w[0] == '0') ? TILE_ONE_SM : TILE_AUTO;
   }
-  return g_pair_mode == 1;
+  return g_tile_mode;
 }
+bool pair_mode() { return tile_mode() == TILE_PAIR; }
 
 // The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of the kernel:
 // one flag per device, so a process that holds layers on several GPUs configures each of them.
@@ -1017,10 +1244,32 @@ static cudaError_t launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, con
 }
 
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
-static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args_in, int sm_count,
-                          cudaStream_t stream) {
+static cudaError_t launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args, int sm_count,
+                               cudaStream_t stream) {   // args: already through with_wait_limit
+  auto kern = grouped_gemm_wide_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
+  static bool configured[MAX_DEVICES] = {};
+  { const cudaError_t e = opt_in_smem(kern, configured, W_SMEM_BYTES); if (e != cudaSuccess) return e; }
+  kern<<<sm_count, NUM_THREADS, W_SMEM_BYTES, stream>>>(ma, mb, args); count_launch();
+  return cudaGetLastError();
+}
+
+// TILE_AUTO: 256x256 tiles where they pay.  They need a third fewer operand bytes per MMA, but their epilogue does not
+// overlap the next tile's MMAs and there are half as many tiles to spread over the SMs: so only for products of
+// several waves of wide tiles, not for the SwiGLU-backward epilogue (it reads the saved g|u rows and is the longest),
+// not for the f32 store, and not for causal products (only the 128-row tiles skip the masked part).
+template <int EPI>
+static bool wide_pays(const GemmArgs& a, long long wide_tiles, int sm_count) {
+  return a.causal == 0 && EPI != EPI_SWIGLU_BWD && EPI != EPI_STORE_F32 && wide_tiles >= 4ll * sm_count;
+}
+
+template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
+static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args_in, long long wide_tiles,
+                          int sm_count, cudaStream_t stream) {
   const GemmArgs args = with_wait_limit(args_in);
-  if (pair_mode()) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
+  const int mode = tile_mode();
+  if (mode == TILE_PAIR) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
+  if (mode == TILE_WIDE || (mode == TILE_AUTO && wide_pays<EPI>(args, wide_tiles, sm_count)))
+    return launch_wide<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
   auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
   static bool configured[MAX_DEVICES] = {};
   { const cudaError_t e = opt_in_smem(kern, configured, SMEM_BYTES); if (e != cudaSuccess) return e; }
@@ -1035,10 +1284,11 @@ cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& arg
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, pair_mode() ? BN / 2 : BN, true)) return cudaErrorInvalidValue;
+  const long long wide_tiles = (A.rows / (2 * BM)) * ceil_div(args.N, BN);   // an estimate: the host does not know the groups
   switch (epilogue) {
-    case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, sm_count, stream);
-    case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, sm_count, stream);
-    case EPI_STORE_F32: return launch<false, false, false, EPI_STORE_F32>(ma, mb, args, sm_count, stream);
+    case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, wide_tiles, sm_count, stream);
+    case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, wide_tiles, sm_count, stream);
+    case EPI_STORE_F32: return launch<false, false, false, EPI_STORE_F32>(ma, mb, args, wide_tiles, sm_count, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -1049,9 +1299,10 @@ cudaError_t gemm_rows_nn(const Operand& A, const Operand& B, const GemmArgs& arg
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, 64, 64, true)) return cudaErrorInvalidValue;
+  const long long wide_tiles = (A.rows / (2 * BM)) * ceil_div(args.N, BN);
   switch (epilogue) {
-    case EPI_STORE: return launch<false, true, false, EPI_STORE>(ma, mb, args, sm_count, stream);
-    case EPI_SWIGLU_BWD: return launch<false, true, false, EPI_SWIGLU_BWD>(ma, mb, args, sm_count, stream);
+    case EPI_STORE: return launch<false, true, false, EPI_STORE>(ma, mb, args, wide_tiles, sm_count, stream);
+    case EPI_SWIGLU_BWD: return launch<false, true, false, EPI_SWIGLU_BWD>(ma, mb, args, wide_tiles, sm_count, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -1062,7 +1313,8 @@ cudaError_t gemm_rows_tn(const Operand& A, const Operand& B, const GemmArgs& arg
     return cudaErrorInvalidValue;
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, 64, 64, false) || !make_map(&mb, B, 64, 64, false)) return cudaErrorInvalidValue;
-  return launch<true, true, true, EPI_ACCUM_F32>(ma, mb, args, sm_count, stream);
+  const long long wide_tiles = (long long)args.n_groups * ceil_div(ceil_div(args.M, BM), 2) * ceil_div(args.N, BN);
+  return launch<true, true, true, EPI_ACCUM_F32>(ma, mb, args, wide_tiles, sm_count, stream);
 }
 
 }  // namespace tc

@@ -57,11 +57,17 @@ struct Operand {
   long long ld = 0;    // elements between consecutive rows (0: cols); lets a product read a column range of a wider matrix
 };
 
-// Two-SM tiles (cta_group::2, clusters of two CTAs) instead of one-SM tiles; also MOE_B200_TC_PAIR=1.
-void set_pair_mode(int on);
+// Which kernel runs a product: 128x256 tiles on one SM, 256x256 tiles on a pair of SMs (cta_group::2, clusters of two
+// CTAs; also MOE_B200_TC_PAIR=1), 256x256 tiles on one SM (forced with MOE_B200_TC_WIDE=1, never with =0), or - the
+// default - a choice per launch between the first and the third (see wide_pays in gemm_tc.cu).
+enum { TILE_ONE_SM = 0, TILE_PAIR = 1, TILE_WIDE = 2, TILE_AUTO = 3 };
+void set_tile_mode(int mode);
+int tile_mode();
+// Only the 128-row kernel skips the masked part of a causal product; forced to the others, it is computed in full.
+inline bool causal_skipping() { return tile_mode() == TILE_ONE_SM || tile_mode() == TILE_AUTO; }
+bool pair_mode();
 // Test hook: the next launch runs with a producer that loads nothing and this wait limit (clock cycles).
 void set_starve_next_launch(long long wait_limit_cycles);
-bool pair_mode();
 
 // y[rows, N] = A[rows, K] * B_g[N, K]^T            (forward projections)
 cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& args, int epilogue, int sm_count,

@@ -649,7 +649,7 @@ int forward_blocks(lm_model* M, const Batch& bt, bool save) {
     // the half of the square above the diagonal is never computed: score tiles there are skipped (the softmax reads
     // the visible prefix only and writes the rest of the row as zeros), and P V stops at the last visible key
     RC(mm_nt(M, b.q_hm, bt.TQ, M->hd, b.k_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));
-    LCK(lm::launch_softmax_causal(M->scores, b.probs, a, scale, 1, !tc::pair_mode(), M->st));   // the two-SM kernel skips nothing
+    LCK(lm::launch_softmax_causal(M->scores, b.probs, a, scale, 1, tc::causal_skipping(), M->st));   // only the default tiles skip the masked part
     RC(mm_nn(M, b.probs, bt.TQ, a.S_pad, b.v_hm, M->hd, am, M->o_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));
     LCK(lm::launch_heads_to_tokens(M->o_hm, b.merged, a, M->st));
     RC(mm_nt(M, b.merged, rows, HD, M->wb + b.wo, d, dm, M->tmp, d));
@@ -719,7 +719,7 @@ int backward_blocks(lm_model* M, const Batch& bt) {
     // visible key, and the two reductions over queries skip the queries that come before the tile's keys
     RC(mm_nt(M, M->do_hm, bt.TQ, M->hd, b.v_hm, a.S_pad, am, M->scores, a.S_pad, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_COLS));   // dL/dP
     RC(mm_tn(M, b.probs, bt.TQ, a.S_pad, M->do_hm, bt.TQ, M->hd, am, M->dv_hm, M->hd, kv_stride, 0, a.S));    // dL/dV, summed over the group
-    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, 1, !tc::pair_mode(), M->st));                            // dL/dscore
+    LCK(lm::launch_softmax_backward(b.probs, M->scores, a, scale, 1, tc::causal_skipping(), M->st));                      // dL/dscore
     RC(mm_nn(M, M->scores, bt.TQ, a.S_pad, b.k_hm, M->hd, am, M->dq_hm, M->hd, tc::EPI_STORE, nullptr, 0, a.S, tc::CAUSAL_K));   // dL/dQ
     RC(mm_tn(M, M->scores, bt.TQ, a.S_pad, b.q_hm, bt.TQ, M->hd, am, M->dk_hm, M->hd, kv_stride, 0, a.S));    // dL/dK
     LCK(lm::launch_qkv_grad_unpack(M->dq_hm, M->dk_hm, M->dv_hm, M->cos_t, M->sin_t, M->dqkv, a, M->st));

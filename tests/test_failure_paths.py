@@ -15,7 +15,7 @@ from rustingbrain_b200 import NetworkError, Timeout, _lib
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("pair", [0, 1], ids=["one_sm", "two_sm"])
+@pytest.mark.parametrize("pair", [0, 1, 2], ids=["one_sm", "two_sm", "wide"])
 def test_a_starved_gemm_reports_timeout_and_the_handle_recovers(pair):
     T, d, E, k, F = 256, 256, 8, 2, 128
     dev, ora, _ = make_pair(d, E, k, F, False, seed=6, precision="bf16", max_tokens=T, std=0.05, router_std=0.05)
@@ -35,5 +35,5 @@ def test_a_starved_gemm_reports_timeout_and_the_handle_recovers(pair):
         dev.synchronize()
         assert torch.equal(y0, y1)                             # tensor memory was released: the next launch got all of it
     finally:
-        _lib.lib().moe_debug_set_tc_pair(0)
+        _lib.lib().moe_debug_set_tc_pair(3)   # back to the per-launch choice
         dev.close()

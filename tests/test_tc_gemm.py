@@ -10,12 +10,12 @@ from rustingbrain_b200 import _lib
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[0, 1], ids=["one_sm", "two_sm"], autouse=True)
+@pytest.fixture(params=[0, 1, 2], ids=["one_sm", "two_sm", "wide"], autouse=True)
 def tc_variant(request):
-    """Every case runs on the one-SM tiles and on the two-SM (cta_group::2) tiles."""
+    """Every case runs on the one-SM tiles, on the two-SM (cta_group::2) tiles and on the one-SM 256x256 tiles."""
     _lib.lib().moe_debug_set_tc_pair(request.param)
     yield request.param
-    _lib.lib().moe_debug_set_tc_pair(0)
+    _lib.lib().moe_debug_set_tc_pair(3)   # back to the per-launch choice
 
 
 def _groups(rows_per_group):
