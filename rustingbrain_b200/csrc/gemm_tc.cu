@@ -71,10 +71,10 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(20000u)   // the thread may stay suspended for up to 20 microseconds per try
       : "memory");
   return ok;
 }
@@ -1255,20 +1255,21 @@ static cudaError_t launch_wide(const CUtensorMap& ma, const CUtensorMap& mb, con
 
 // TILE_AUTO: 256x256 tiles where they pay.  They need a third fewer operand bytes per MMA, but their epilogue does not
 // overlap the next tile's MMAs and there are half as many tiles to spread over the SMs: so only for products of
-// several waves of wide tiles, not for the SwiGLU-backward epilogue (it reads the saved g|u rows and is the longest),
+// several waves of wide tiles and a reduction long enough to amortise the epilogue (measured: a 256x256 bf16 tile
+// leaves the SM in about 4000 clocks, the MMAs of 1024 reduction elements take 16384), not for the SwiGLU-backward epilogue (it reads the saved g|u rows and is the longest),
 // not for the f32 store, and not for causal products (only the 128-row tiles skip the masked part).
 template <int EPI>
-static bool wide_pays(const GemmArgs& a, long long wide_tiles, int sm_count) {
-  return a.causal == 0 && EPI != EPI_SWIGLU_BWD && EPI != EPI_STORE_F32 && wide_tiles >= 4ll * sm_count;
+static bool wide_pays(const GemmArgs& a, long long wide_tiles, long long reduction, int sm_count) {
+  return a.causal == 0 && EPI != EPI_SWIGLU_BWD && EPI != EPI_STORE_F32 && wide_tiles >= 4ll * sm_count && reduction >= 1024;
 }
 
 template <bool A_MN, bool B_MN, bool ROWS_ARE_K, int EPI>
 static cudaError_t launch(const CUtensorMap& ma, const CUtensorMap& mb, const GemmArgs& args_in, long long wide_tiles,
-                          int sm_count, cudaStream_t stream) {
+                          long long reduction, int sm_count, cudaStream_t stream) {
   const GemmArgs args = with_wait_limit(args_in);
   const int mode = tile_mode();
   if (mode == TILE_PAIR) return launch_pair<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
-  if (mode == TILE_WIDE || (mode == TILE_AUTO && wide_pays<EPI>(args, wide_tiles, sm_count)))
+  if (mode == TILE_WIDE || (mode == TILE_AUTO && wide_pays<EPI>(args, wide_tiles, reduction, sm_count)))
     return launch_wide<A_MN, B_MN, ROWS_ARE_K, EPI>(ma, mb, args, sm_count, stream);
   auto kern = grouped_gemm_kernel<A_MN, B_MN, ROWS_ARE_K, EPI>;
   static bool configured[MAX_DEVICES] = {};
@@ -1285,10 +1286,11 @@ cudaError_t gemm_rows_nt(const Operand& A, const Operand& B, const GemmArgs& arg
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, BK, pair_mode() ? BN / 2 : BN, true)) return cudaErrorInvalidValue;
   const long long wide_tiles = (A.rows / (2 * BM)) * ceil_div(args.N, BN);   // an estimate: the host does not know the groups
+  const long long reduction = A.cols;
   switch (epilogue) {
-    case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, wide_tiles, sm_count, stream);
-    case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, wide_tiles, sm_count, stream);
-    case EPI_STORE_F32: return launch<false, false, false, EPI_STORE_F32>(ma, mb, args, wide_tiles, sm_count, stream);
+    case EPI_STORE: return launch<false, false, false, EPI_STORE>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
+    case EPI_SWIGLU: return launch<false, false, false, EPI_SWIGLU>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
+    case EPI_STORE_F32: return launch<false, false, false, EPI_STORE_F32>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -1300,9 +1302,10 @@ cudaError_t gemm_rows_nn(const Operand& A, const Operand& B, const GemmArgs& arg
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, BK, BM, false) || !make_map(&mb, B, 64, 64, true)) return cudaErrorInvalidValue;
   const long long wide_tiles = (A.rows / (2 * BM)) * ceil_div(args.N, BN);
+  const long long reduction = A.cols;
   switch (epilogue) {
-    case EPI_STORE: return launch<false, true, false, EPI_STORE>(ma, mb, args, wide_tiles, sm_count, stream);
-    case EPI_SWIGLU_BWD: return launch<false, true, false, EPI_SWIGLU_BWD>(ma, mb, args, wide_tiles, sm_count, stream);
+    case EPI_STORE: return launch<false, true, false, EPI_STORE>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
+    case EPI_SWIGLU_BWD: return launch<false, true, false, EPI_SWIGLU_BWD>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
     default: return cudaErrorInvalidValue;
   }
 }
@@ -1314,7 +1317,8 @@ cudaError_t gemm_rows_tn(const Operand& A, const Operand& B, const GemmArgs& arg
   CUtensorMap ma, mb;
   if (!make_map(&ma, A, 64, 64, false) || !make_map(&mb, B, 64, 64, false)) return cudaErrorInvalidValue;
   const long long wide_tiles = (long long)args.n_groups * ceil_div(ceil_div(args.M, BM), 2) * ceil_div(args.N, BN);
-  return launch<true, true, true, EPI_ACCUM_F32>(ma, mb, args, wide_tiles, sm_count, stream);
+  const long long reduction = A.rows / (args.n_groups > 0 ? args.n_groups : 1);   // rows per group on average
+  return launch<true, true, true, EPI_ACCUM_F32>(ma, mb, args, wide_tiles, reduction, sm_count, stream);
 }
 
 }  // namespace tc
