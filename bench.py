@@ -656,7 +656,8 @@ def run_layer(args, w, torch, dist, world, rank, local, device, with_e2e, with_c
                 "frac": ach / pk["tf_sustained"] if ach else None, "traffic": 0.95 * gemm_bytes / 6.0,
                 "traffic_unit": "bytes per launch (mean of the 6), ncu DRAM bytes of the reduced case scaled by rows",
                 "algorithmic_bytes_per_launch": gemm_bytes / 6.0,
-                "kernel": "grouped_gemm_kernel (6 launches per step: gate|up, down, 2 dgrad, 2 wgrad)",
+                "kernel": "grouped_gemm_wide_kernel (256x256 tiles; 5 of the 6 launches per step: gate|up, down, gate|up dgrad, "
+                          "2 wgrad) and grouped_gemm_kernel (128x256 tiles; the down dgrad with the SwiGLU-backward epilogue)",
                 "launches": gemm_launches, "ms_per_launch": gemm_ms / max(gemm_launches, 1),
                 "flops_per_step": gemm_flops / args.steps, "peak_source": pk["src"] + " sustained bf16",
                 "frac_of_measured_burst": ach / pk["tf_burst"] if ach else None,

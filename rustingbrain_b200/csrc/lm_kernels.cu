@@ -258,21 +258,22 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
   const int visible = causal ? within % a.S + 1 : a.S;
   const int vchunks = (visible + 7) / 8;
   const int zchunks = zero_tail_all ? chunks : min(chunks, ((visible + 127) & ~127) / 8);
-  uint4 v[NC];
-#pragma unroll
-  for (int j = 0; j < NC; ++j) {
-    const int c = lane + 32 * j;
-    v[j] = c < vchunks ? src[c] : make_uint4(0, 0, 0, 0);
-  }
+  // The row stays in registers as scaled scores, then as exponentials: one exponential per entry.  With expf twice
+  // per entry the kernel was bound by instruction issue (80 microseconds for 65536 rows of 1024); the hardware
+  // exponential's relative error of about 2^-21 disappears in the bf16 rounding of the probabilities.
+  float e[NC][8];
   float mx = -INFINITY;
 #pragma unroll
   for (int j = 0; j < NC; ++j) {
     const int c = lane + 32 * j;
-    float f[8];
-    unpack8(v[j], f);
+    if (c < vchunks) {
+      unpack8(src[c], e[j]);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (c * 8 + i < visible) mx = fmaxf(mx, f[i] * scale);
+      for (int i = 0; i < 8; ++i) {
+        e[j][i] = c * 8 + i < visible ? e[j][i] * scale : -INFINITY;
+        mx = fmaxf(mx, e[j][i]);
+      }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -280,11 +281,13 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
 #pragma unroll
   for (int j = 0; j < NC; ++j) {
     const int c = lane + 32 * j;
-    float f[8];
-    unpack8(v[j], f);
+    if (c < vchunks) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (c * 8 + i < visible) sum += expf(f[i] * scale - mx);
+      for (int i = 0; i < 8; ++i) {
+        e[j][i] = __expf(e[j][i] - mx);     // exp(-inf) = 0 behind the visible prefix
+        sum += e[j][i];
+      }
+    }
   }
   sum = warp_sum(sum);
   const float inv = sum > 0.f ? 1.0f / sum : 1.0f;   // activations.rs:65-69
@@ -293,9 +296,8 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
     const int c = lane + 32 * j;
     if (c >= zchunks) break;
     float f[8];
-    unpack8(v[j], f);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) f[i] = c * 8 + i < visible ? expf(f[i] * scale - mx) * inv : 0.f;
+    for (int i = 0; i < 8; ++i) f[i] = c < vchunks ? e[j][i] * inv : 0.f;
     dst[c] = pack8(f);
   }
 }
@@ -442,6 +444,68 @@ cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets,
   }
 }
 
+// The same for rows of at most 512 * 8 * NC logits, with the row in registers: the logits cross the memory system
+// once and every entry takes one exponential.  512 threads per row.
+template <int NC>
+__global__ void __launch_bounds__(512)
+cross_entropy_regs_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss, int vocab,
+                          int ld, float inv_predicted) {
+  __shared__ float sh[16];
+  const int r = blockIdx.x, target = targets[r];
+  uint4* row = reinterpret_cast<uint4*>(logits + (size_t)r * ld);
+  const int chunks = ld / 8;
+  if (target < 0) {                               // predicts nothing: zero gradient, no loss
+    for (int c = threadIdx.x; c < chunks; c += blockDim.x) row[c] = make_uint4(0, 0, 0, 0);
+    if (threadIdx.x == 0) row_loss[r] = 0.f;
+    return;
+  }
+  float e[NC][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = threadIdx.x + 512 * j;
+    if (c < chunks) {
+      unpack8(row[c], e[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (c * 8 + i >= vocab) e[j][i] = -INFINITY;
+        mx = fmaxf(mx, e[j][i]);
+      }
+    }
+  }
+  const float bm = block_reduce(mx, sh, true);
+  const float target_logit = bf(logits[(size_t)r * ld + target]);   // read before any thread overwrites the row
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = threadIdx.x + 512 * j;
+    if (c < chunks) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        e[j][i] = __expf(e[j][i] - bm);
+        sum += e[j][i];
+      }
+    }
+  }
+  sum = block_reduce(sum, sh, false);             // has a barrier: every thread holds target_logit by now
+  const float inv = sum > 0.f ? 1.0f / sum : 1.0f;
+  if (threadIdx.x == 0) row_loss[r] = -logf(fmaxf(expf(target_logit - bm) * inv, FLT_MIN));
+#pragma unroll
+  for (int j = 0; j < NC; ++j) {
+    const int c = threadIdx.x + 512 * j;
+    if (c < chunks) {
+      float f[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int col = c * 8 + i;
+        f[i] = e[j][i] * inv * inv_predicted;     // exp(-inf) = 0 in the padding columns
+        if (col == target) f[i] -= inv_predicted;
+      }
+      row[c] = pack8(f);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(256) loss_sum_kernel(const float* __restrict__ row_loss, int rows, float inv_predicted,
                                                        float* __restrict__ out) {
   __shared__ float sh[256];
@@ -573,7 +637,12 @@ cudaError_t launch_cast_rows_to_f32(const bf16* src, long long ld, float* dst, i
 cudaError_t launch_cross_entropy(bf16* logits, const int* targets, float* row_loss, int rows, int vocab, int ld,
                                  float inv_predicted, cudaStream_t st) {
   if (rows <= 0) return cudaSuccess;
-  cross_entropy_kernel<<<rows, 256, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted); count_launch();
+  const int per_thread = (ld / 8 + 511) / 512;    // 16-byte pieces of a row per thread of a 512-thread block
+  if (per_thread <= 2) cross_entropy_regs_kernel<2><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
+  else if (per_thread <= 4) cross_entropy_regs_kernel<4><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
+  else if (per_thread <= 8) cross_entropy_regs_kernel<8><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
+  else cross_entropy_kernel<<<rows, 256, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
+  count_launch();
   return cudaGetLastError();
 }
 cudaError_t launch_loss_sum(const float* row_loss, int rows, float inv_predicted, float* out, cudaStream_t st) {
