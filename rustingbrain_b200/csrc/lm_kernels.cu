@@ -258,9 +258,10 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
   const int visible = causal ? within % a.S + 1 : a.S;
   const int vchunks = (visible + 7) / 8;
   const int zchunks = zero_tail_all ? chunks : min(chunks, ((visible + 127) & ~127) / 8);
-  // The row stays in registers as scaled scores, then as exponentials: one exponential per entry.  With expf twice
-  // per entry the kernel was bound by instruction issue (80 microseconds for 65536 rows of 1024); the hardware
-  // exponential's relative error of about 2^-21 disappears in the bf16 rounding of the probabilities.
+  // The row stays in registers as scores, then as exponentials: one exponential per entry (with two the kernel was
+  // bound by instruction issue: 80 microseconds for 65536 rows of 1024).  expf, not the hardware exponential: its
+  // 2^-21 is enough to flip bf16 roundings of the probabilities, and the parity case with head_dim 32 sits at the
+  // 2e-2 bar (one gradient moved from below it to 2.007e-2).
   float e[NC][8];
   float mx = -INFINITY;
 #pragma unroll
@@ -270,8 +271,8 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
       unpack8(src[c], e[j]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        e[j][i] = c * 8 + i < visible ? e[j][i] * scale : -INFINITY;
-        mx = fmaxf(mx, e[j][i]);
+        if (c * 8 + i >= visible) e[j][i] = -INFINITY;
+        mx = fmaxf(mx, e[j][i] * scale);           // scale > 0
       }
     }
   }
@@ -284,7 +285,7 @@ softmax_causal_regs_kernel(const bf16* __restrict__ scores, bf16* __restrict__ p
     if (c < vchunks) {
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        e[j][i] = __expf(e[j][i] - mx);     // exp(-inf) = 0 behind the visible prefix
+        e[j][i] = expf(fmaf(e[j][i], scale, -mx));     // exp(-inf) = 0 behind the visible prefix
         sum += e[j][i];
       }
     }
@@ -444,68 +445,6 @@ cross_entropy_kernel(bf16* __restrict__ logits, const int* __restrict__ targets,
   }
 }
 
-// The same for rows of at most 512 * 8 * NC logits, with the row in registers: the logits cross the memory system
-// once and every entry takes one exponential.  512 threads per row.
-template <int NC>
-__global__ void __launch_bounds__(512)
-cross_entropy_regs_kernel(bf16* __restrict__ logits, const int* __restrict__ targets, float* __restrict__ row_loss, int vocab,
-                          int ld, float inv_predicted) {
-  __shared__ float sh[16];
-  const int r = blockIdx.x, target = targets[r];
-  uint4* row = reinterpret_cast<uint4*>(logits + (size_t)r * ld);
-  const int chunks = ld / 8;
-  if (target < 0) {                               // predicts nothing: zero gradient, no loss
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) row[c] = make_uint4(0, 0, 0, 0);
-    if (threadIdx.x == 0) row_loss[r] = 0.f;
-    return;
-  }
-  float e[NC][8];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < NC; ++j) {
-    const int c = threadIdx.x + 512 * j;
-    if (c < chunks) {
-      unpack8(row[c], e[j]);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (c * 8 + i >= vocab) e[j][i] = -INFINITY;
-        mx = fmaxf(mx, e[j][i]);
-      }
-    }
-  }
-  const float bm = block_reduce(mx, sh, true);
-  const float target_logit = bf(logits[(size_t)r * ld + target]);   // read before any thread overwrites the row
-  float sum = 0.f;
-#pragma unroll
-  for (int j = 0; j < NC; ++j) {
-    const int c = threadIdx.x + 512 * j;
-    if (c < chunks) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        e[j][i] = __expf(e[j][i] - bm);
-        sum += e[j][i];
-      }
-    }
-  }
-  sum = block_reduce(sum, sh, false);             // has a barrier: every thread holds target_logit by now
-  const float inv = sum > 0.f ? 1.0f / sum : 1.0f;
-  if (threadIdx.x == 0) row_loss[r] = -logf(fmaxf(expf(target_logit - bm) * inv, FLT_MIN));
-#pragma unroll
-  for (int j = 0; j < NC; ++j) {
-    const int c = threadIdx.x + 512 * j;
-    if (c < chunks) {
-      float f[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int col = c * 8 + i;
-        f[i] = e[j][i] * inv * inv_predicted;     // exp(-inf) = 0 in the padding columns
-        if (col == target) f[i] -= inv_predicted;
-      }
-      row[c] = pack8(f);
-    }
-  }
-}
-
 __global__ void __launch_bounds__(256) loss_sum_kernel(const float* __restrict__ row_loss, int rows, float inv_predicted,
                                                        float* __restrict__ out) {
   __shared__ float sh[256];
@@ -637,11 +576,7 @@ cudaError_t launch_cast_rows_to_f32(const bf16* src, long long ld, float* dst, i
 cudaError_t launch_cross_entropy(bf16* logits, const int* targets, float* row_loss, int rows, int vocab, int ld,
                                  float inv_predicted, cudaStream_t st) {
   if (rows <= 0) return cudaSuccess;
-  const int per_thread = (ld / 8 + 511) / 512;    // 16-byte pieces of a row per thread of a 512-thread block
-  if (per_thread <= 2) cross_entropy_regs_kernel<2><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
-  else if (per_thread <= 4) cross_entropy_regs_kernel<4><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
-  else if (per_thread <= 8) cross_entropy_regs_kernel<8><<<rows, 512, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
-  else cross_entropy_kernel<<<rows, 256, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
+  cross_entropy_kernel<<<rows, 256, 0, st>>>(logits, targets, row_loss, vocab, ld, inv_predicted);
   count_launch();
   return cudaGetLastError();
 }
