@@ -308,6 +308,54 @@ __device__ __forceinline__ void load32_bf16_staged(const bf16* warp_row0_ptr, lo
   __syncwarp();
 }
 
+// 32 columns of 32 rows that a lane already holds as 16 packed bf16 pairs.
+__device__ __forceinline__ void store32_packed_staged(bf16* warp_row0_ptr, long long ld, const uint32_t* pk, uint8_t* stg,
+                                                      int lane) {
+  uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) mine[i] = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+  __syncwarp();
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int row = it * 8 + (lane >> 2), ch = lane & 3;
+    const uint4 q = *reinterpret_cast<const uint4*>(stg + row * STG_PITCH + ch * 16);
+    *reinterpret_cast<uint4*>(reinterpret_cast<char*>(warp_row0_ptr + (long long)row * ld) + ch * 16) = q;
+  }
+  __syncwarp();
+}
+
+// 32 f32 columns of 32 rows into out_warp (first row m_warp of a matrix with p.M rows), through the warp's staging
+// tile, 16 columns (64 bytes per row) at a time: a lane holds one ROW, so direct stores would touch 32 rows per
+// instruction, 16 bytes each; staged, an instruction covers 8 rows x 64 contiguous bytes (and the read-modify-write
+// of the accumulate mode loads the same way).
+__device__ __forceinline__ void store32_f32_staged(const GemmArgs& p, float* out_warp, int m_warp, const float* v, uint8_t* stg,
+                                                   int lane) {
+#pragma unroll
+  for (int hseg = 0; hseg < 2; ++hseg) {
+    uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      mine[i] = make_uint4(__float_as_uint(v[16 * hseg + 4 * i]), __float_as_uint(v[16 * hseg + 4 * i + 1]),
+                           __float_as_uint(v[16 * hseg + 4 * i + 2]), __float_as_uint(v[16 * hseg + 4 * i + 3]));
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int row = it * 8 + (lane >> 2), ch = lane & 3;
+      if (m_warp + row < p.M) {
+        const uint4 q = *reinterpret_cast<const uint4*>(stg + row * STG_PITCH + ch * 16);
+        float4 r = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+        float4* o = reinterpret_cast<float4*>(out_warp + (long long)row * p.ld0 + 16 * hseg + 4 * ch);
+        if (p.accumulate) {
+          const float4 old = *o;
+          r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+        }
+        *o = r;
+      }
+    }
+    __syncwarp();
+  }
+}
+
 // The tensor-core path rounds its outputs to bf16 (2^-9), so the pointwise step uses
 // the fast exponential and reciprocal; the f32 path keeps expf and IEEE division.
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
@@ -422,35 +470,9 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& p, const Tile& tl,
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.f;
       }
-      // Through the warp's staging tile, 16 columns (64 bytes per row) at a time: a lane holds one ROW, so direct
-      // stores would touch 32 rows per instruction, 16 bytes each; staged, an instruction covers 8 rows x 64
-      // contiguous bytes (and the read-modify-write of the accumulate mode loads the same way).
       const int m_warp = tl.m0 + (row_in_tile & ~31);
       float* out_warp = (float*)p.out0 + (long long)tl.group * p.group_stride0 + (long long)m_warp * p.ld0 + tl.n0 + c;
-#pragma unroll
-      for (int hseg = 0; hseg < 2; ++hseg) {
-        uint4* mine = reinterpret_cast<uint4*>(stg + lane * STG_PITCH);
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          mine[i] = make_uint4(__float_as_uint(v[16 * hseg + 4 * i]), __float_as_uint(v[16 * hseg + 4 * i + 1]),
-                               __float_as_uint(v[16 * hseg + 4 * i + 2]), __float_as_uint(v[16 * hseg + 4 * i + 3]));
-        __syncwarp();
-#pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int row = it * 8 + (lane >> 2), ch = lane & 3;
-          if (m_warp + row < p.M) {
-            const uint4 q = *reinterpret_cast<const uint4*>(stg + row * STG_PITCH + ch * 16);
-            float4 r = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
-            float4* o = reinterpret_cast<float4*>(out_warp + (long long)row * p.ld0 + 16 * hseg + 4 * ch);
-            if (p.accumulate) {
-              const float4 old = *o;
-              r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
-            }
-            *o = r;
-          }
-        }
-        __syncwarp();
-      }
+      store32_f32_staged(p, out_warp, m_warp, v, stg, lane);
     }
   }
 }
@@ -1111,6 +1133,45 @@ grouped_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
       const WideTile tl = wide_decode<ROWS_ARE_K>(st, p, t);
       if (!mbar_wait(smem_u32(&st->tmem_full), acc_phase, p.error_flag, 304, p.wait_limit)) { ok = false; break; }
       tc_fence_after();
+      // The accumulators are single buffered, so the MMAs of the next tile wait for this epilogue.  For the plain bf16
+      // store the warp first moves its whole share of both sub-tiles into registers as packed pairs (2 x 4 pieces of
+      // 32 columns = 128 registers), hands tensor memory back, and only then writes the rows out: those stores (about
+      // 4000 clocks for a 256x256 tile) run under the next tile's MMAs (+5 % on the two products that use it).  The
+      // SwiGLU and f32 epilogues have registers for one sub-tile only; holding that one while the other is written
+      // straight from tensor memory was measured and gained nothing, so they keep the plain order.
+      uint8_t* stg = stg_all + (warp - 2) * STG_BYTES_PER_WARP;
+      const uint32_t tq = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      if (EPI == EPI_STORE) {
+        uint32_t pk[2][4][16];
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          if (mi < tl.msub) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              if (tl.n0 + c_begin + 32 * ch < p.N) {   // warp-uniform
+                float v[32];
+                tmem_ld32(tq + mi * BN + c_begin + 32 * ch, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pk[mi][ch][i] = pack2(v[2 * i], v[2 * i + 1]);
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&st->tmem_empty));
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+          if (mi < tl.msub) {
+            bf16* out = (bf16*)p.out0 + ((long long)tl.row0 + mi * BM + quarter * 32) * p.ld0 + tl.n0 + c_begin;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch)
+              if (tl.n0 + c_begin + 32 * ch < p.N) store32_packed_staged(out + 32 * ch, p.ld0, pk[mi][ch], stg, lane);
+          }
+        }
+        acc_phase ^= 1;
+        continue;
+      }
       for (int mi = 0; mi < tl.msub; ++mi) {
         Tile one;
         one.group = tl.group; one.n0 = tl.n0; one.k_iters = tl.k_iters; one.skip = 0;
