@@ -158,10 +158,12 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
     const int g = mc.g, m0 = (mc.tile - tile_start[g]) * Q8_ROWS;
     int rows;
     const bf16* xin;
+    const int* xidx = nullptr;                        // rows gathered through an index (routed rows of the first pass)
     if (g < a.E) {
       rows = a.counts[g];
       const size_t base = (size_t)a.pad_off[g];
       xin = a.x_rows + (base + m0) * K;
+      if (a.x_row_index) { xin = a.x_rows; xidx = a.x_row_index + base + m0; }
       out = a.out_rows + (base + m0) * a.ldo;
     } else {
       rows = a.tokens;
@@ -184,7 +186,7 @@ __global__ void __launch_bounds__(Q8_WARPS * 32, 2) q8_rows_kernel(Q8Args a) {
       for (int u = 0; u < SU; ++u) {
         rr[u] = r; cc[u] = c;
         v[u] = make_uint4(0, 0, 0, 0);
-        if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)r * K + c * 8);
+        if (r < mrows) v[u] = *reinterpret_cast<const uint4*>(xin + (size_t)(xidx ? xidx[r] : r) * K + c * 8);
         r += dr; c += dc;
         if (c >= cpr) { c -= cpr; ++r; }
       }

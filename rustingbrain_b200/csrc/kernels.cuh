@@ -52,6 +52,12 @@ cudaError_t launch_router(const RouterArgs& a, int precision, cudaStream_t strea
 // bf16 logits product for decode-sized batches (d a multiple of 8): one CTA per token row
 cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
                                       cudaStream_t stream);
+// Routing of a decode-sized batch (at most 64 rows and 64 experts, one GPU) in one launch: logits, softmax / top-k,
+// finalize and the placement (slot_pos, row_token, ...) WITHOUT the row copy; ra.logits_in names the buffer the logits
+// go through, `done` a zeroed device counter.  MOE_B200_DECODE_ROUTE=0 turns it off.
+bool decode_route_supported(const RouterArgs& ra, const PermuteArgs& pa);
+cudaError_t launch_decode_route_rows(const RouterArgs& ra, const PermuteArgs& pa, const void* w_router_bf16, int* done,
+                                     cudaStream_t stream);
 // `align`: every expert's row group starts at a multiple of this many rows (128 for the
 // local expert GEMMs, 1 for the compact send layout of an expert-parallel rank).
 cudaError_t launch_finalize(const RouterArgs& a, RouteMeta meta, float aux_w, float z_w, float* stats, float* losses,
@@ -194,7 +200,8 @@ cudaError_t launch_router_wgrad_sum(const RouterWgradArgs& a, cudaStream_t strea
 // padded expert-major buffers, group E (optional) = the shared expert over every token row.
 // swiglu: q holds the interleaved gate|up rows [2N, K]; out = silu(gate) * up, N hidden columns.
 struct Q8Args {
-  const bf16* x_rows;      // [padded rows, K]
+  const bf16* x_rows;      // [padded rows, K]; with x_row_index: [tokens, K], row r of a group is x_rows[x_row_index[r]]
+  const int* x_row_index;  // optional [padded rows]: gather the routed rows instead of reading them in place
   const bf16* x_shared;    // optional [tokens, K]
   bf16* out_rows;          // [padded rows, ldo]
   bf16* out_shared;        // [tokens, ldo]

@@ -71,6 +71,7 @@ struct moe_layer {
   int* shared_meta = nullptr;   // [4]: row0[0..1], tstart[0..1] of the dense (shared expert) group: entry `tokens` of the table
   int* shared_meta_table = nullptr;   // [max_tokens + 1][4]
   int* error_flag = nullptr;
+  int* route_done = nullptr;    // counter of the decode routing kernel (zero between launches)
 
   // activations (element type `act`)
   void *x_perm = nullptr, *gu = nullptr, *h = nullptr, *y_perm = nullptr;

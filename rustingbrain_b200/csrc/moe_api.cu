@@ -601,8 +601,24 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
   ra.partial = L->partial; ra.hist = L->hist;
   ra.fin = RouterFinalize{1, L->aux_w, L->z_w, L->meta, L->stats, L->losses, ep ? 1 : GROUP_ALIGN};
   L->shared_meta = L->shared_meta_table + 4 * tokens;
+  PermuteArgs pa{};
+  pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
+  pa.tokens = tokens; pa.d = L->d; pa.E = L->E; pa.k = L->k;
+  pa.x_perm = ep ? ep_rows(L, 0, L->x_perm) : local_rows(L->x_perm); pa.slot_pos = L->slot_pos;
+  pa.dest_base = (ep && L->peer_ready) ? L->dest_base : nullptr; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
+  pa.token_of = L->token_of; pa.slot_of = L->slot_of;
+  pa.skip_pad = L->precision == MOE_PRECISION_Q8 ? 1 : 0;   // the int8 kernels never read padding rows
+  // int8 decode layer on a decode-sized batch: the whole routing in one launch, and no row copy (the first int8
+  // pass gathers its token rows through row_token); not with the tcgen05 variant, whose loads want the rows in place
+  bool gather_rows = false;
   { Span sp(L, 0, st);
-  if (L->tc_router && !logits_in && tokens <= 256 && L->d % 8 == 0 && ((uintptr_t)x & 15) == 0) {
+  RouterArgs fa = ra;
+  fa.logits_in = L->logits; fa.logits_out = nullptr;
+  if (L->precision == MOE_PRECISION_Q8 && L->tc_router && !logits_in && !ep && !L->prof_on && !q8_tc_mode() &&
+      decode_route_supported(fa, pa)) {
+    CK(launch_decode_route_rows(fa, pa, L->wb + L->off_router, L->route_done, st));
+    gather_rows = true;
+  } else if (L->tc_router && !logits_in && tokens <= 256 && L->d % 8 == 0 && ((uintptr_t)x & 15) == 0) {
     // decode-sized batch: a CTA per token row beats one tensor-core tile on one SM
     CK(launch_router_logits_rows(x, L->wb + L->off_router, L->logits, tokens, L->d, L->E, st));
     ra.logits_in = L->logits;
@@ -618,22 +634,17 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     ra.logits_in = L->logits;
     ra.logits_out = nullptr;
   }
-  CK(launch_router(ra, L->act, st));
-  CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, ep ? 1 : GROUP_ALIGN, st)); }
+  if (!gather_rows) {
+    CK(launch_router(ra, L->act, st));
+    CK(launch_finalize(ra, L->meta, L->aux_w, L->z_w, L->stats, L->losses, ep ? 1 : GROUP_ALIGN, st));
+  } }
 
   if (ep) {
     Span sp(L, 1, st);
     int rc0 = ep_dispatch(L, st);
     if (rc0 != MOE_OK) return rc0;
   }
-  PermuteArgs pa{};
-  pa.x = x; pa.expert_of = L->expert_of; pa.gates = L->gates; pa.cursor = L->hist; pa.meta = L->meta;
-  pa.tokens = tokens; pa.d = L->d; pa.E = L->E; pa.k = L->k;
-  pa.x_perm = ep ? ep_rows(L, 0, L->x_perm) : local_rows(L->x_perm); pa.slot_pos = L->slot_pos;
-  pa.dest_base = (ep && L->peer_ready) ? L->dest_base : nullptr; pa.row_token = L->row_token; pa.row_gate = L->row_gate;
-  pa.token_of = L->token_of; pa.slot_of = L->slot_of;
-  pa.skip_pad = L->precision == MOE_PRECISION_Q8 ? 1 : 0;   // the int8 kernels never read padding rows
-  { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
+  if (!gather_rows) { Span sp(L, 1, st); CK(launch_permute(pa, L->act, st)); }
 
   int rc;
   if (L->precision == MOE_PRECISION_Q8) {
@@ -642,6 +653,7 @@ int forward_impl(moe_layer* L, const void* x, const float* logits_in, int tokens
     const int d = L->d, Fp = L->F_pad;
     Q8Args qa{};
     qa.x_rows = (const bf16*)L->x_perm; qa.x_shared = L->shared ? (const bf16*)x : nullptr;
+    if (gather_rows) { qa.x_rows = (const bf16*)x; qa.x_row_index = L->row_token; }
     qa.out_rows = (bf16*)L->h; qa.out_shared = (bf16*)L->h_s;
     qa.w = L->q_gu; qa.scale = L->s_gu; qa.counts = L->meta.counts; qa.pad_off = L->meta.pad_off;
     qa.w_group_stride = 2ll * Fp * d; qa.s_group_stride = 2ll * Fp;
@@ -985,7 +997,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
   DA(L->stats, (E + 2) * 4, true); DA(L->losses, 2 * 4, true);
   DA(L->slot_pos, T * k * 4, false); DA(L->token_of, T * k * 4, false); DA(L->slot_of, T * k * 4, false);
   DA(L->row_token, (long long)L->rows_cap * 4, false); DA(L->row_gate, (long long)L->rows_cap * 4, false);
-  DA(L->shared_meta_table, (T + 1) * 16, false); DA(L->error_flag, 4, true);
+  DA(L->shared_meta_table, (T + 1) * 16, false); DA(L->error_flag, 4, true); DA(L->route_done, 4, true);
   shared_meta_table_kernel<<<(unsigned)((T + 256) / 256), 256>>>(L->shared_meta_table, (int)T);
   CK(cudaGetLastError());
   L->shared_meta = L->shared_meta_table;

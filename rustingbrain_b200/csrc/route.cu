@@ -22,6 +22,9 @@
 // expert order, so the probabilities (and therefore the chosen experts) agree bit
 // for bit with a host evaluation of the same logits.
 
+#include <algorithm>
+#include <cstdlib>
+
 #include "kernels.cuh"
 
 namespace moe {
@@ -471,22 +474,26 @@ __global__ void cursor_base_kernel(int* __restrict__ hist, int nb, int E, const 
   if (i < nb * E) hist[i] += pad_off[i % E];
 }
 
-template <typename T, int KMAX>
-__global__ void __launch_bounds__(256)
-permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const float* __restrict__ gates,
-               const int* __restrict__ cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
-               const RowSpace x_perm, const int* __restrict__ dest_base, int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/,
-               float* __restrict__ row_gate /*[Rp]*/, int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of) {
-  pdl_enter();
-  extern __shared__ int pm_smem[];
+// The work of block (bx, by) of a grid with `ny` blocks per 64-token group (any whole number of warps, pm_smem of
+// (E + 64 k) ints).  COPY = false stops after the placement: slot_pos, row_token, row_gate, token_of, slot_of are
+// written and no row is copied (the int8 decode pass gathers its token rows through row_token itself).
+// expert_of, gates and cursor carry no __restrict__: the decode routing kernel below reads what other blocks of
+// the same launch have written, which a read-only (non-coherent) load must not serve.
+template <typename T, int KMAX, bool COPY>
+__device__ __forceinline__ void permute_body(const T* __restrict__ x, const int* expert_of, const float* gates,
+                                             const int* cursor /*[nb,E]*/, RouteMeta meta, int tokens, int d, int E, int k,
+                                             const RowSpace x_perm, const int* __restrict__ dest_base, int* __restrict__ slot_pos /*[T*k]*/,
+                                             int* __restrict__ row_token /*[Rp]*/, float* __restrict__ row_gate /*[Rp]*/,
+                                             int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of, int bx, int by, int ny,
+                                             int* pm_smem) {
   int* cnt = pm_smem;        // [E] running cursors
   int* spos = cnt + E;       // [64*k] padded row of every slot of this block
-  const int t0 = blockIdx.x * ROUTER_ROWS;
+  const int t0 = bx * ROUTER_ROWS;
   const int rows = min(ROUTER_ROWS, tokens - t0);
   const int nslots = rows * k;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  for (int e = tid; e < E; e += blockDim.x) cnt[e] = cursor[(size_t)blockIdx.x * E + e];
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = cursor[(size_t)bx * E + e];
   __syncthreads();
   if (warp == 0) {
     // Slots in ascending order, 32 at a time; equal experts inside a chunk are ranked
@@ -506,7 +513,7 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       __syncwarp();
       if (i < nslots) {
         int dest = pos;
-        if (pos >= 0 && blockIdx.y != 0) {
+        if (pos >= 0 && by != 0) {
           if (dest_base) dest = dest_base[e] + (pos - meta.pad_off[e]);
           if (dest < 0) dest = -1;
         } else if (pos >= 0) {
@@ -522,11 +529,12 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
           }
         }
         spos[i] = dest;
-        if (blockIdx.y == 0) slot_pos[slot] = dest;
+        if (by == 0) slot_pos[slot] = dest;
       }
     }
   }
   __syncthreads();
+  if (!COPY) return;
 
   constexpr int VEC = 16 / sizeof(T);
   const bool vec_ok = (d % VEC) == 0;
@@ -538,8 +546,8 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
     const int cpr = d / VEC;                 // chunks per row
     // small batches: gridDim.y blocks share one 64-token group; each repeats the (cheap) ranking
     // and copies its own slice of the rows, so the copy is not one block's latency chain
-    const int slice = ceil_div(rows, (int)gridDim.y);
-    const int r_begin = min(rows, (int)blockIdx.y * slice), r_end = min(rows, r_begin + slice);
+    const int slice = ceil_div(rows, ny);
+    const int r_begin = min(rows, by * slice), r_end = min(rows, r_begin + slice);
     constexpr int U = 16;   // 16-byte chunks per lane held at once: 8 KB of the row per pass
     for (int r = r_begin + warp; r < r_end; r += blockDim.x / 32) {
       const int* p = spos + r * k;
@@ -569,7 +577,7 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       }
     }
   } else {
-    for (int r = warp + (int)blockIdx.y * (blockDim.x / 32); r < rows; r += (blockDim.x / 32) * gridDim.y) {
+    for (int r = warp + by * (blockDim.x / 32); r < rows; r += (blockDim.x / 32) * ny) {
       const T* src = x + (size_t)(t0 + r) * d;
       const int* p = spos + r * k;
       if (p[0] < 0) continue;
@@ -580,6 +588,18 @@ permute_kernel(const T* __restrict__ x, const int* __restrict__ expert_of, const
       }
     }
   }
+}
+
+template <typename T, int KMAX>
+__global__ void __launch_bounds__(256)
+permute_kernel(const T* __restrict__ x, const int* expert_of, const float* gates, const int* cursor /*[nb,E]*/, RouteMeta meta,
+               int tokens, int d, int E, int k, const RowSpace x_perm, const int* __restrict__ dest_base,
+               int* __restrict__ slot_pos /*[T*k]*/, int* __restrict__ row_token /*[Rp]*/, float* __restrict__ row_gate /*[Rp]*/,
+               int* __restrict__ token_of /*[R]*/, int* __restrict__ slot_of) {
+  pdl_enter();
+  extern __shared__ int pm_smem[];
+  permute_body<T, KMAX, true>(x, expert_of, gates, cursor, meta, tokens, d, E, k, x_perm, dest_base, slot_pos, row_token, row_gate,
+                              token_of, slot_of, (int)blockIdx.x, (int)blockIdx.y, (int)gridDim.y, pm_smem);
 }
 
 // Zeroes the padding rows at the end of every expert's group (they change place
@@ -669,10 +689,9 @@ cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float
 // Router logits for decode-sized batches: logits[t, e] = sum_c x[t, c] * w[e, c], bf16 operands, f32
 // sums.  One CTA per token row, a warp per expert (round robin), 16-byte loads; a single 128-row
 // tensor-core tile would leave this to one SM and a 16-step dependent pipeline.
-__global__ void __launch_bounds__(128)
-router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits, int d, int E) {
-  pdl_enter();
-  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+// Token row t by four warps (warp = 0..3 of them); out: the row's E logits.
+__device__ __forceinline__ void router_logits_row(const bf16* __restrict__ x, const bf16* __restrict__ w, float* out, int d, int E,
+                                                  int t, int warp, int lane) {
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * d);
   constexpr int EG = 8;   // experts a warp works on at once: their loads are all in flight together
   for (int e0 = warp; e0 < E; e0 += 4 * EG) {
@@ -703,9 +722,221 @@ router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], o);
       const int e = e0 + 4 * j;
-      if (lane == 0 && e < E) logits[(size_t)t * E + e] = acc[j];
+      if (lane == 0 && e < E) out[e] = acc[j];
     }
   }
+}
+__global__ void __launch_bounds__(128)
+router_logits_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, float* __restrict__ logits, int d, int E) {
+  pdl_enter();
+  router_logits_row(x, w, logits + (size_t)blockIdx.x * E, d, E, (int)blockIdx.x, (int)(threadIdx.x >> 5), (int)(threadIdx.x & 31));
+}
+
+// Routing of a decode-sized batch (at most 64 token rows, at most 64 experts, one GPU) in ONE launch instead of
+// four (logits, softmax / top-k, finalize, permutation): one CTA of four warps per token row computes the row's
+// logits (router_logits_row: the sums of router_logits_rows_kernel), then its first warp takes the softmax and the
+// top-k with the arithmetic and the order of router_body (exponentials by expf_libm, the denominator summed by one
+// lane in expert order, the scan with a strict `>` from the first free expert).  The CTA that finishes last - an
+// atomic counter, nothing waits - sums the batch statistics in row order, runs finalize_body and the stable
+// placement of permute_body.  No row is copied: the int8 projections fetch their token rows through row_token.
+template <int KMAX>
+__global__ void __launch_bounds__(128)
+decode_route_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_bf16, RouterArgs ra, PermuteArgs pa, int* done) {
+  pdl_enter();
+  extern __shared__ float dr_smem[];
+  __shared__ float s_row[MAX_EXPERTS];
+  __shared__ int s_last;
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int E = ra.E, k = ra.k;
+  float* logits = const_cast<float*>(ra.logits_in);
+  router_logits_row(x, w_bf16, s_row, ra.d, E, t, warp, lane);
+  __syncthreads();
+  if (warp == 0) {
+    for (int e = lane; e < E; e += 32) logits[(size_t)t * E + e] = s_row[e];
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_row[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int e = lane; e < E; e += 32) s_row[e] = expf_libm(__fsub_rn(s_row[e], mx));
+    __syncwarp();
+    float sum = 0.f;
+    if (lane == 0)
+      for (int e = 0; e < E; ++e) sum = __fadd_rn(sum, s_row[e]);
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (int e = lane; e < E; e += 32) {
+      const float p = sum > 0.f ? __fdiv_rn(s_row[e], sum) : s_row[e];
+      s_row[e] = p;
+      ra.probs[(size_t)t * E + e] = p;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      ra.lse[t] = mx + logf(sum);
+      const bool is_valid = ra.valid == nullptr || ra.valid[t] != 0;
+      if (!is_valid) {
+        for (int j = 0; j < k; ++j) { ra.expert_of[(size_t)t * k + j] = -1; ra.gates[(size_t)t * k + j] = 0.f; }
+      } else {
+        unsigned long long taken = 0ull;   // E <= 64
+        int chosen[KMAX];
+        float total = 0.f;
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+          if (j < k) {
+            int best = -1;
+            for (int e = 0; e < E; ++e) {
+              if ((taken >> e) & 1ull) continue;
+              if (best < 0 || s_row[e] > s_row[best]) best = e;   // from the first free expert; a NaN there is never replaced
+            }
+            taken |= 1ull << best;
+            chosen[j] = best;
+            total = __fadd_rn(total, s_row[best]);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+          if (j < k) {
+            const float p = s_row[chosen[j]];
+            ra.expert_of[(size_t)t * k + j] = chosen[j];
+            ra.gates[(size_t)t * k + j] = total > 0.f ? __fdiv_rn(p, total) : p;
+          }
+        }
+      }
+    }
+  }
+  // the last CTA to get here does the batch-wide part
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    s_last = atomicAdd(done, 1) == (int)gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid == 0) *done = 0;                         // ready for the next launch
+  const int T = ra.tokens;
+  // What the other CTAs wrote comes into shared memory in one round of loads, and everything after that works on
+  // shared memory: a loop that reads global memory pays the L2 latency per step, and with finalize_body and
+  // permute_body on global arrays that chain cost more than the launches it replaced.  The sums, the two losses
+  // and the tables are those of router_body's tail + finalize_body for a single router block (the double sums
+  // of one block are that block's values), the placement is permute_body's stable counting sort.
+  float* s_probs = dr_smem;                                   // [T][E]
+  float* s_lse = s_probs + (size_t)T * E;                     // [T]
+  float* s_gates = s_lse + T;                                 // [T * k]
+  int* s_sel = reinterpret_cast<int*>(s_gates + (size_t)T * k);   // [T * k]
+  int* s_valid = s_sel + (size_t)T * k;                       // [T]
+  __shared__ float s_sums[MAX_EXPERTS + 2];
+  __shared__ int s_counts[MAX_EXPERTS], s_pad[MAX_EXPERTS + 1], s_off[MAX_EXPERTS + 1];
+  for (int i = tid; i < T * E; i += blockDim.x) s_probs[i] = __ldcg(ra.probs + i);
+  for (int i = tid; i < T * k; i += blockDim.x) { s_sel[i] = __ldcg(ra.expert_of + i); s_gates[i] = __ldcg(ra.gates + i); }
+  for (int r = tid; r < T; r += blockDim.x) {
+    s_lse[r] = __ldcg(ra.lse + r);
+    s_valid[r] = (ra.valid == nullptr || ra.valid[r] != 0) ? 1 : 0;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    float sm = 0.f;
+    int h = 0;
+    for (int r = 0; r < T; ++r)
+      if (s_valid[r]) sm += s_probs[r * E + e];
+    for (int i = 0; i < T * k; ++i) h += (s_sel[i] == e) ? 1 : 0;
+    s_sums[e] = sm;
+    s_counts[e] = h;
+  }
+  if (tid == blockDim.x - 1) {
+    float sm = 0.f;
+    int v = 0;
+    for (int r = 0; r < T; ++r)
+      if (s_valid[r]) { sm += s_lse[r] * s_lse[r]; ++v; }
+    s_sums[E] = sm;
+    s_sums[E + 1] = (float)v;
+  }
+  __syncthreads();
+  const RouteMeta meta = ra.fin.meta;
+  for (int c = tid; c < E + 2; c += blockDim.x) { ra.partial[c] = s_sums[c]; ra.fin.stats[c] = s_sums[c]; }
+  for (int e = tid; e < E; e += blockDim.x) meta.counts[e] = s_counts[e];
+  if (tid == 0) {
+    int off = 0, pad = 0, tiles = 0;
+    for (int e = 0; e < E; ++e) {
+      s_off[e] = off; s_pad[e] = pad;
+      meta.offsets[e] = off;
+      meta.pad_off[e] = pad;
+      meta.tile_start[e] = tiles;
+      off += s_counts[e];
+      const int padded = round_up(s_counts[e], ra.fin.align);
+      pad += padded;
+      tiles += ceil_div(padded, GROUP_ALIGN);
+    }
+    meta.offsets[E] = off;
+    meta.pad_off[E] = pad;
+    meta.tile_start[E] = tiles;
+    const int V = (int)s_sums[E + 1];
+    meta.total[0] = off;
+    meta.total[1] = pad;
+    meta.total[2] = tiles;
+    meta.total[3] = V;
+    // auxiliary_losses (moe.rs:602-639), the arithmetic of finalize_body
+    const float Vf = (float)V;
+    float aux = 0.f, z = 0.f;
+    if (Vf > 0.f) {
+      const float slots = Vf * (float)k;
+      for (int e = 0; e < E; ++e) {
+        const float load = (float)s_counts[e] / slots;
+        const float mass = s_sums[e] / Vf;
+        aux += load * mass;
+      }
+      aux *= (float)E * ra.fin.aux_w;
+      z = ra.fin.z_w * s_sums[E] / Vf;
+    }
+    ra.fin.losses[0] = aux;
+    ra.fin.losses[1] = z;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) ra.hist[e] = s_pad[e];   // the block's write cursors, as finalize leaves them
+  if (warp == 0) {
+    // slots in ascending order, 32 at a time; equal experts inside a chunk are ranked by lane (permute_body)
+    int* cnt = s_counts;                                     // reused as running cursors
+    for (int e = lane; e < E; e += 32) cnt[e] = s_pad[e];
+    __syncwarp();
+    const int nslots = T * k;
+    for (int base = 0; base < nslots; base += 32) {
+      const int i = base + lane;
+      const int e = i < nslots ? s_sel[i] : -1;
+      const unsigned peers = __match_any_sync(0xffffffffu, e);
+      int pos = -1;
+      if (e >= 0) pos = cnt[e] + __popc(peers & ((1u << lane) - 1u));
+      __syncwarp();
+      if (e >= 0 && lane == 31 - __clz(peers)) cnt[e] += __popc(peers);
+      __syncwarp();
+      if (i < nslots) {
+        if (pos >= 0) {
+          const int cpos = s_off[e] + (pos - s_pad[e]);
+          pa.token_of[cpos] = i / k;
+          pa.slot_of[cpos] = i;
+          pa.row_token[pos] = i / k;
+          pa.row_gate[pos] = s_gates[i];
+        }
+        pa.slot_pos[i] = pos;
+      }
+    }
+  }
+}
+
+bool decode_route_supported(const RouterArgs& ra, const PermuteArgs& pa) {
+  static const bool on = [] { const char* e = getenv("MOE_B200_DECODE_ROUTE"); return !(e && *e == '0'); }();
+  return on && ra.tokens > 0 && ra.tokens <= ROUTER_ROWS && ra.fin.enabled && ra.logits_in && !pa.dest_base && ra.E <= 64 &&
+         ra.k <= 8 && ra.k <= ra.E && ra.d % 8 == 0 && ((uintptr_t)ra.x & 15) == 0;
+}
+
+cudaError_t launch_decode_route_rows(const RouterArgs& ra, const PermuteArgs& pa, const void* w_bf16, int* done, cudaStream_t stream) {
+  const size_t smem = sizeof(float) * (size_t)ROUTER_ROWS * ((size_t)ra.E + 2 + 2 * (size_t)ra.k);
+  const bf16* xb = (const bf16*)ra.x;
+  const bf16* wb = (const bf16*)w_bf16;
+  cudaError_t e;
+  if (ra.k <= 1) e = launch_kernel(decode_route_rows_kernel<1>, dim3(ra.tokens), dim3(128), smem, stream, xb, wb, ra, pa, done);
+  else if (ra.k <= 2) e = launch_kernel(decode_route_rows_kernel<2>, dim3(ra.tokens), dim3(128), smem, stream, xb, wb, ra, pa, done);
+  else if (ra.k <= 4) e = launch_kernel(decode_route_rows_kernel<4>, dim3(ra.tokens), dim3(128), smem, stream, xb, wb, ra, pa, done);
+  else e = launch_kernel(decode_route_rows_kernel<8>, dim3(ra.tokens), dim3(128), smem, stream, xb, wb, ra, pa, done);
+  count_launch();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 cudaError_t launch_router_logits_rows(const void* x, const void* w_bf16, float* logits, int tokens, int d, int E,
                                       cudaStream_t stream) {
