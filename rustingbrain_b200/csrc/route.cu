@@ -47,7 +47,9 @@ __device__ const unsigned long long kExp2Tab[32] = {
     0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
     0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
 
-__device__ __forceinline__ float expf_libm(float x) {
+// `table(i)` returns entry i of kExp2Tab (from memory, or from wherever the caller keeps a copy).
+template <typename Table>
+__device__ __forceinline__ float expf_libm_with(float x, Table table) {
   if (!(fabsf(x) < 88.0f)) {
     if (x == -INFINITY) return 0.f;
     if (!(fabsf(x) < INFINITY)) return x + x;
@@ -65,7 +67,7 @@ __device__ __forceinline__ float expf_libm(float x) {
   const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
   kd = __dsub_rn(kd, kShift);
   const double r = __dsub_rn(z, kd);
-  const unsigned long long t = kExp2Tab[ki & 31] + (ki << 47);
+  const unsigned long long t = table((int)(ki & 31)) + (ki << 47);
   const double s = __longlong_as_double((long long)t);
   const double p = fma(c0, r, c1);
   const double r2 = __dmul_rn(r, r);
@@ -73,6 +75,9 @@ __device__ __forceinline__ float expf_libm(float x) {
   y = fma(p, r2, y);
   y = __dmul_rn(y, s);
   return (float)y;
+}
+__device__ __forceinline__ float expf_libm(float x) {
+  return expf_libm_with(x, [](int i) { return kExp2Tab[i]; });
 }
 
 constexpr int RT_THREADS = 256;
@@ -689,31 +694,47 @@ cudaError_t launch_ep_losses(const int* gathered, int ranks, int E, int k, float
 // Router logits for decode-sized batches: logits[t, e] = sum_c x[t, c] * w[e, c], bf16 operands, f32
 // sums.  One CTA per token row, a warp per expert (round robin), 16-byte loads; a single 128-row
 // tensor-core tile would leave this to one SM and a 16-step dependent pipeline.
-// Token row t by four warps (warp = 0..3 of them); out: the row's E logits.
+// Token row t by four warps (warp = 0..3 of them); out: the row's E logits.  A warp works on EG experts at once,
+// 1024 reduction values at a time, and ALL 16-byte loads of such a step (4 of the token row, 4 per expert) are
+// issued before the first is used: written as a plain loop the compiler chained every load to its FMAs, and the
+// row took 20 L2 round trips (16000 clocks) instead of one or two.
 __device__ __forceinline__ void router_logits_row(const bf16* __restrict__ x, const bf16* __restrict__ w, float* out, int d, int E,
                                                   int t, int warp, int lane) {
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * d);
-  constexpr int EG = 8;   // experts a warp works on at once: their loads are all in flight together
+  constexpr int EG = 4, NI = 4;
+  const int cpr = d / 8;                       // 16-byte chunks per row
   for (int e0 = warp; e0 < E; e0 += 4 * EG) {
     float acc[EG];
 #pragma unroll
     for (int j = 0; j < EG; ++j) acc[j] = 0.f;
-    for (int c = lane; c < d / 8; c += 32) {
-      const uint4 a = __ldg(xr + c);
-      uint4 b[EG];
+    for (int c0 = lane; c0 < cpr; c0 += 32 * NI) {
+      uint4 a[NI], b[EG][NI];
+#pragma unroll
+      for (int i = 0; i < NI; ++i) {
+        const int c = c0 + 32 * i;
+        a[i] = c < cpr ? __ldg(xr + c) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
       for (int j = 0; j < EG; ++j) {
         const int e = e0 + 4 * j;
-        b[j] = e < E ? __ldg(reinterpret_cast<const uint4*>(w + (size_t)e * d) + c) : make_uint4(0, 0, 0, 0);
+        const uint4* wr = reinterpret_cast<const uint4*>(w + (size_t)(e < E ? e : 0) * d);
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+          const int c = c0 + 32 * i;
+          b[j][i] = (e < E && c < cpr) ? __ldg(wr + c) : make_uint4(0, 0, 0, 0);
+        }
       }
-      const uint32_t av[4] = {a.x, a.y, a.z, a.w};
 #pragma unroll
-      for (int j = 0; j < EG; ++j) {
-        const uint32_t bv[4] = {b[j].x, b[j].y, b[j].z, b[j].w};
+      for (int i = 0; i < NI; ++i) {
+        const uint32_t av[4] = {a[i].x, a[i].y, a[i].z, a[i].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          acc[j] = fmaf(__uint_as_float(av[i] << 16), __uint_as_float(bv[i] << 16), acc[j]);
-          acc[j] = fmaf(__uint_as_float(av[i] & 0xffff0000u), __uint_as_float(bv[i] & 0xffff0000u), acc[j]);
+        for (int j = 0; j < EG; ++j) {
+          const uint32_t bv[4] = {b[j][i].x, b[j][i].y, b[j][i].z, b[j][i].w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            acc[j] = fmaf(__uint_as_float(av[q] << 16), __uint_as_float(bv[q] << 16), acc[j]);
+            acc[j] = fmaf(__uint_as_float(av[q] & 0xffff0000u), __uint_as_float(bv[q] & 0xffff0000u), acc[j]);
+          }
         }
       }
     }
@@ -745,9 +766,11 @@ decode_route_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_
   pdl_enter();
   extern __shared__ float dr_smem[];
   __shared__ float s_row[MAX_EXPERTS];
+  __shared__ unsigned long long s_tab[32];   // the exponential's table: fetched while the logits are computed
   __shared__ int s_last;
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int E = ra.E, k = ra.k;
+  if (tid < 32) s_tab[tid] = kExp2Tab[tid];
   float* logits = const_cast<float*>(ra.logits_in);
   router_logits_row(x, w_bf16, s_row, ra.d, E, t, warp, lane);
   __syncthreads();
@@ -757,7 +780,7 @@ decode_route_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_
     for (int e = lane; e < E; e += 32) mx = fmaxf(mx, s_row[e]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    for (int e = lane; e < E; e += 32) s_row[e] = expf_libm(__fsub_rn(s_row[e], mx));
+    for (int e = lane; e < E; e += 32) s_row[e] = expf_libm_with(__fsub_rn(s_row[e], mx), [&](int i) { return s_tab[i]; });
     __syncwarp();
     float sum = 0.f;
     if (lane == 0)
@@ -825,27 +848,49 @@ decode_route_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_
   int* s_valid = s_sel + (size_t)T * k;                       // [T]
   __shared__ float s_sums[MAX_EXPERTS + 2];
   __shared__ int s_counts[MAX_EXPERTS], s_pad[MAX_EXPERTS + 1], s_off[MAX_EXPERTS + 1];
-  for (int i = tid; i < T * E; i += blockDim.x) s_probs[i] = __ldcg(ra.probs + i);
-  for (int i = tid; i < T * k; i += blockDim.x) { s_sel[i] = __ldcg(ra.expert_of + i); s_gates[i] = __ldcg(ra.gates + i); }
-  for (int r = tid; r < T; r += blockDim.x) {
-    s_lse[r] = __ldcg(ra.lse + r);
-    s_valid[r] = (ra.valid == nullptr || ra.valid[r] != 0) ? 1 : 0;
+  {
+    // every load of a thread is issued before its first store (eight at a time for the probabilities)
+    const int nk = T * k;
+    const int i1 = tid < nk ? __ldcg(ra.expert_of + tid) : -1;
+    const float g1 = tid < nk ? __ldcg(ra.gates + tid) : 0.f;
+    const float l1 = tid < T ? __ldcg(ra.lse + tid) : 0.f;
+    const int v1 = tid < T ? ((ra.valid == nullptr || ra.valid[tid] != 0) ? 1 : 0) : 0;
+    for (int base = tid; base < T * E; base += 8 * (int)blockDim.x) {
+      float pv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * (int)blockDim.x;
+        pv[u] = i < T * E ? __ldcg(ra.probs + i) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = base + u * (int)blockDim.x;
+        if (i < T * E) s_probs[i] = pv[u];
+      }
+    }
+    if (tid < nk) { s_sel[tid] = i1; s_gates[tid] = g1; }
+    if (tid < T) { s_lse[tid] = l1; s_valid[tid] = v1; }
+    for (int i = tid + (int)blockDim.x; i < nk; i += blockDim.x) { s_sel[i] = __ldcg(ra.expert_of + i); s_gates[i] = __ldcg(ra.gates + i); }
+    if (tid < E) s_counts[tid] = 0;
   }
   __syncthreads();
+  // rows per expert: integer counting in shared memory (the order does not matter)
+  for (int i = tid; i < T * k; i += blockDim.x) {
+    const int e = s_sel[i];
+    if (e >= 0) atomicAdd(&s_counts[e], 1);
+  }
+  // column sums over the valid rows, rows in order; an invalid row adds +0, which leaves the sum as it is
   for (int e = tid; e < E; e += blockDim.x) {
     float sm = 0.f;
-    int h = 0;
-    for (int r = 0; r < T; ++r)
-      if (s_valid[r]) sm += s_probs[r * E + e];
-    for (int i = 0; i < T * k; ++i) h += (s_sel[i] == e) ? 1 : 0;
+#pragma unroll 8
+    for (int r = 0; r < T; ++r) sm += s_valid[r] ? s_probs[r * E + e] : 0.f;
     s_sums[e] = sm;
-    s_counts[e] = h;
   }
   if (tid == blockDim.x - 1) {
     float sm = 0.f;
     int v = 0;
-    for (int r = 0; r < T; ++r)
-      if (s_valid[r]) { sm += s_lse[r] * s_lse[r]; ++v; }
+#pragma unroll 8
+    for (int r = 0; r < T; ++r) { sm += s_valid[r] ? s_lse[r] * s_lse[r] : 0.f; v += s_valid[r]; }
     s_sums[E] = sm;
     s_sums[E + 1] = (float)v;
   }
