@@ -898,41 +898,69 @@ decode_route_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_
   const RouteMeta meta = ra.fin.meta;
   for (int c = tid; c < E + 2; c += blockDim.x) { ra.partial[c] = s_sums[c]; ra.fin.stats[c] = s_sums[c]; }
   for (int e = tid; e < E; e += blockDim.x) meta.counts[e] = s_counts[e];
-  if (tid == 0) {
-    int off = 0, pad = 0, tiles = 0;
-    for (int e = 0; e < E; ++e) {
-      s_off[e] = off; s_pad[e] = pad;
-      meta.offsets[e] = off;
-      meta.pad_off[e] = pad;
-      meta.tile_start[e] = tiles;
-      off += s_counts[e];
-      const int padded = round_up(s_counts[e], ra.fin.align);
-      pad += padded;
-      tiles += ceil_div(padded, GROUP_ALIGN);
+  if (warp == 1) {
+    // offsets, padded offsets and tile numbers: exclusive prefix sums over the experts, by warp scans (E <= 64:
+    // two experts per lane, the second half continues from the first half's totals)
+    int base_off = 0, base_pad = 0, base_tiles = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int c = e < E ? s_counts[e] : 0;
+      const int padded = round_up(c, ra.fin.align);
+      const int tl = ceil_div(padded, GROUP_ALIGN);
+      int so = c, sp = padded, stl = tl;                      // inclusive scans
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, so, o), b = __shfl_up_sync(0xffffffffu, sp, o),
+                  d2 = __shfl_up_sync(0xffffffffu, stl, o);
+        if (lane >= o) { so += a; sp += b; stl += d2; }
+      }
+      if (e < E) {
+        const int off = base_off + so - c, pad = base_pad + sp - padded, tiles = base_tiles + stl - tl;
+        s_off[e] = off; s_pad[e] = pad;
+        meta.offsets[e] = off;
+        meta.pad_off[e] = pad;
+        meta.tile_start[e] = tiles;
+      }
+      base_off += __shfl_sync(0xffffffffu, so, 31);
+      base_pad += __shfl_sync(0xffffffffu, sp, 31);
+      base_tiles += __shfl_sync(0xffffffffu, stl, 31);
     }
-    meta.offsets[E] = off;
-    meta.pad_off[E] = pad;
-    meta.tile_start[E] = tiles;
+    if (lane == 0) {
+      meta.offsets[E] = base_off;
+      meta.pad_off[E] = base_pad;
+      meta.tile_start[E] = base_tiles;
+      meta.total[0] = base_off;
+      meta.total[1] = base_pad;
+      meta.total[2] = base_tiles;
+      meta.total[3] = (int)s_sums[E + 1];
+    }
+  } else if (warp == 0) {
+    // auxiliary_losses (moe.rs:602-639), the arithmetic of finalize_body: the quotients of all experts at once,
+    // their products summed by one lane in expert order
     const int V = (int)s_sums[E + 1];
-    meta.total[0] = off;
-    meta.total[1] = pad;
-    meta.total[2] = tiles;
-    meta.total[3] = V;
-    // auxiliary_losses (moe.rs:602-639), the arithmetic of finalize_body
     const float Vf = (float)V;
     float aux = 0.f, z = 0.f;
     if (Vf > 0.f) {
       const float slots = Vf * (float)k;
+      float ld[2], ms[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int e = lane + 32 * h;
+        ld[h] = e < E ? (float)s_counts[e] / slots : 0.f;
+        ms[h] = e < E ? s_sums[e] / Vf : 0.f;
+      }
       for (int e = 0; e < E; ++e) {
-        const float load = (float)s_counts[e] / slots;
-        const float mass = s_sums[e] / Vf;
+        const float load = __shfl_sync(0xffffffffu, ld[e >> 5], e & 31);
+        const float mass = __shfl_sync(0xffffffffu, ms[e >> 5], e & 31);
         aux += load * mass;
       }
       aux *= (float)E * ra.fin.aux_w;
       z = ra.fin.z_w * s_sums[E] / Vf;
     }
-    ra.fin.losses[0] = aux;
-    ra.fin.losses[1] = z;
+    if (lane == 0) {
+      ra.fin.losses[0] = aux;
+      ra.fin.losses[1] = z;
+    }
   }
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) ra.hist[e] = s_pad[e];   // the block's write cursors, as finalize leaves them
