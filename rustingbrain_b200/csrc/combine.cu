@@ -18,6 +18,8 @@
 //
 // One warp handles one token; rows move as 16-byte vectors.
 
+#include <algorithm>
+
 #include "kernels.cuh"
 
 namespace moe {
@@ -129,10 +131,14 @@ __device__ __forceinline__ int slots_by_expert(const int* expert_of, const int* 
     count_launch();                                                                              \
   } while (0)
 
+// a.split > 1 (decode-sized batches): `split` warps share a token, each lane owns one 16-byte piece of the row, so
+// a token's loads are one round trip instead of one per 512 bytes of a lane's loop.
 template <typename T, int KMAX>
 __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   pdl_enter();
-  const int t = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int item = blockIdx.x * CB_WARPS + (threadIdx.x >> 5);
+  const int split = a.split > 1 ? a.split : 1;
+  const int t = item / split, part = item - t * split;
   const int lane = threadIdx.x & 31;
   if (t >= a.tokens) return;
   int pos[KMAX];
@@ -145,10 +151,12 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   constexpr int RB = KMAX < ROW_BATCH ? KMAX : ROW_BATCH;
   const int d = a.d;
   if (d % V == 0) {
-    for (int c = lane * V; c < d; c += 32 * V) {
+    for (int c = (part * 32 + lane) * V; c < d; c += split * 32 * V) {
       float acc[V];
 #pragma unroll
       for (int i = 0; i < V; ++i) acc[i] = 0.f;
+      uint4 sh_raw = make_uint4(0, 0, 0, 0);
+      if (sh) sh_raw = *reinterpret_cast<const uint4*>(sh + (size_t)t * d + c);   // in flight with the rows
 #pragma unroll
       for (int j0 = 0; j0 < KMAX; j0 += RB) {
         if (j0 >= n) break;
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
       }
       if (sh) {
         float v[V];
-        Vec16<T>::load(sh + (size_t)t * d + c, v);
+        unpack16<T>(sh_raw, v);
 #pragma unroll
         for (int i = 0; i < V; ++i) acc[i] = __fadd_rn(acc[i], v[i]);
       }
@@ -181,7 +189,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
       Vec16<T>::store(y + c, acc);
     }
   } else {
-    for (int c = lane; c < d; c += 32) {
+    for (int c = part * 32 + lane; c < d; c += split * 32) {
       float acc = 0.f;
 #pragma unroll
       for (int j = 0; j < KMAX; ++j)
@@ -193,9 +201,13 @@ __global__ void __launch_bounds__(CB_WARPS * 32) combine_kernel(CombineArgs a) {
   }
 }
 
-cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t stream) {
-  if (a.tokens <= 0) return cudaSuccess;
-  const int grid = ceil_div(a.tokens, CB_WARPS);
+cudaError_t launch_combine(const CombineArgs& a_in, int precision, cudaStream_t stream) {
+  if (a_in.tokens <= 0) return cudaSuccess;
+  CombineArgs a = a_in;
+  // decode-sized batches: as many warps per token as the row has 512-byte (32 x 16 B) pieces
+  const int pieces = ceil_div(a.d * (precision == PREC_BF16 ? 2 : 4), 512);
+  a.split = a.tokens <= 256 ? std::max(1, std::min(pieces, 16)) : 1;
+  const int grid = ceil_div(a.tokens * a.split, CB_WARPS);
   if (precision == PREC_BF16) DISPATCH_KMAX(combine_kernel, bf16, a.k, grid, stream, a);
   else DISPATCH_KMAX(combine_kernel, float, a.k, grid, stream, a);
   return cudaGetLastError();

@@ -79,6 +79,7 @@ struct CombineArgs {
   const int* slot_pos;      // [tokens*k]
   void* y;                  // [tokens, d]
   int tokens, d, k, accumulate;
+  int split = 0;            // set by launch_combine: warps that share one token (decode-sized batches)
 };
 cudaError_t launch_combine(const CombineArgs& a, int precision, cudaStream_t stream);
 
