@@ -848,7 +848,8 @@ def main():
         extra["cfg3"] = {k: c3[k] for k in ("value", "unit", "ms_per_step", "steps", "roofline", "hbm_kernels", "clocks", "config")}
         short.steps = 4
         c5 = run_decode(short, WORKLOADS["cfg5"])
-        extra["cfg5"] = {k: c5[k] for k in ("value", "unit", "steps", "roofline", "clocks", "config", "p90_us")}
+        extra["cfg5"] = {k: c5[k] for k in ("value", "unit", "steps", "roofline", "clocks", "config", "p90_us",
+                                               "p50_us_two_layers_taking_turns_no_flush")}
         line["extra"] = extra
     sys.stdout.flush()
     os.dup2(real_stdout, 1)
