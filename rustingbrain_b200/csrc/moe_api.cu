@@ -128,8 +128,8 @@ long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
 //   2 both routed weight-gradient GEMMs deferred to the side stream past the end of the call.
 // Unset (-1 here): 0 on one GPU and on two ranks, 1 from four ranks on.  Measured on cfg 4 the three modes give the
 // same step time at 1 and 2 GPUs (the step runs at the board's power cap, and work that overlaps the GEMMs slows
-// them by what it saves); at 4 ranks, where each GPU's GEMMs are shorter and the exchange tail relatively longer,
-// mode 1 took 35.5 ms against 37.0 ms.
+// them by what it saves); from 4 ranks on, where each GPU's GEMMs are shorter and the exchange tail relatively
+// longer, mode 1 is faster: 33.8 against 34.3 ms at 4 ranks, 35.8 against 37.8 ms at 8.
 int overlap_mode() {
   static const int mode = [] {
     const char* e = getenv("MOE_B200_OVERLAP");
