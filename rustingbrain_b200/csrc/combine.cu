@@ -322,10 +322,27 @@ __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a
   slots_in_order<KMAX>(a.slot_pos, a.gates, t, k, lane, pos, gate);
 #pragma unroll
   for (int j = 0; j < KMAX; ++j)
-    if (lane == j && pos[j] >= 0) *aux_ptr(a.rows, pos[j], a.aux_off, 0) = gate[j];
+    if (lane == j && pos[j] >= 0) {
+      *aux_ptr(a.rows, pos[j], a.aux_off, 0) = gate[j];
+      if (a.dedup) *reinterpret_cast<int*>(aux_ptr(a.rows, pos[j], a.aux_off, 2)) = a.stage_base + t;
+    }
   const T* gy = (const T*)a.grad_y + (size_t)t * d;
   const size_t rb = (size_t)d * sizeof(T);
   constexpr int V = Vec16<T>::N;
+  if (a.dedup) {
+    // the destinations become the token's staging rows, one per distinct owner rank (later slots of a rank are dropped)
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      const int rj = pos[j] >= 0 ? pos[j] / a.rows.cap : -1;
+      bool first = rj >= 0;
+#pragma unroll
+      for (int i = 0; i < KMAX; ++i)
+        if (i < j && pos[i] >= 0 && pos[i] / a.rows.cap == rj) first = false;
+      // pos[] now names rows of `stage` (or -1); the gates and indices above are written already
+      pos[j] = first ? rj * a.stage.cap + a.stage_base + t : -1;
+    }
+  }
+  const RowSpace& dst_space = a.dedup ? a.stage : a.rows;
   if (d % V == 0) {
     // row by row, 8 KB pieces: the writes of one DRAM page (or one NVLink destination) stay together
     constexpr int U = 16;
@@ -339,7 +356,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a
 #pragma unroll
       for (int j = 0; j < KMAX; ++j) {
         if (pos[j] >= 0) {
-          uint4* drow = reinterpret_cast<uint4*>(row_ptr(a.rows, pos[j], rb));
+          uint4* drow = reinterpret_cast<uint4*>(row_ptr(dst_space, pos[j], rb));
 #pragma unroll
           for (int u = 0; u < U; ++u)
             if (c0 + 32 * u < cpr) drow[c0 + 32 * u] = gq[u];
@@ -351,7 +368,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) push_grad_kernel(PushGradArgs a
       const T g = gy[c];
 #pragma unroll
       for (int j = 0; j < KMAX; ++j)
-        if (pos[j] >= 0) ((T*)row_ptr(a.rows, pos[j], rb))[c] = g;
+        if (pos[j] >= 0) ((T*)row_ptr(dst_space, pos[j], rb))[c] = g;
     }
   }
 }
@@ -382,11 +399,12 @@ __global__ void __launch_bounds__(CB_WARPS * 32) scale_dot_kernel(ScaleDotArgs a
       continue;
     }
     const float gate = a.gate_in[row];
+    const T* gin = a.stage ? (const T*)a.stage + (size_t)a.src_index[row] * d : gy;   // the unscaled row
     float dot = 0.f;
     if (d % V == 0) {
       for (int c = lane * V; c < d; c += 32 * V) {
         float gv[V], o[V], s[V];
-        Vec16<T>::load(gy + c, gv);
+        Vec16<T>::load(gin + c, gv);
         Vec16<T>::load(y + c, o);
 #pragma unroll
         for (int i = 0; i < V; ++i) {
@@ -397,7 +415,7 @@ __global__ void __launch_bounds__(CB_WARPS * 32) scale_dot_kernel(ScaleDotArgs a
       }
     } else {
       for (int c = lane; c < d; c += 32) {
-        const float gv = to_f32<T>(gy[c]);
+        const float gv = to_f32<T>(gin[c]);
         dot = fmaf(gv, to_f32<T>(y[c]), dot);
         gy[c] = from_f32<T>(gate * gv);
       }

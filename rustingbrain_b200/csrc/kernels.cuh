@@ -124,8 +124,8 @@ struct GatherGradArgs {
 cudaError_t launch_gather_grad(const GatherGradArgs& a, int precision, cudaStream_t stream);
 
 // Expert-parallel peer transport: gate gradient computed on the expert owner.  `aux_off` is the byte
-// offset, inside every rank's gradient receive buffer, of two float arrays of `rows.cap` entries:
-// the gates pushed with the rows, then the dots the owner computes.
+// offset, inside every rank's gradient receive buffer, of three 4-byte arrays of `rows.cap` entries:
+// the gates pushed with the rows, the dots the owner computes, and (with dedup) the staging row of each row.
 struct PushGradArgs {
   const void* grad_y;     // [tokens, d]
   RowSpace rows;          // the owners' gradient receive buffers
@@ -133,6 +133,13 @@ struct PushGradArgs {
   const float* gates;     // [tokens*k]
   size_t aux_off;
   int tokens, d, k;
+  // One crossing per (token, destination rank) instead of one per slot: the row goes once into a staging area on
+  // every rank that owns one of the token's experts (row stage_base + token of `stage`, which is the owners'
+  // input-gradient receive buffer, idle until their GEMMs write it), and each slot's row of the receive buffer gets
+  // the gate and the staging row's index; the owner's scale_dot pass reads the staged row and writes the scaled one.
+  RowSpace stage;
+  int stage_base;         // this rank's first staging row on every owner (rank * max_tokens)
+  int dedup;
 };
 cudaError_t launch_push_grad(const PushGradArgs& a, int precision, cudaStream_t stream);
 struct ScaleDotArgs {
@@ -140,6 +147,8 @@ struct ScaleDotArgs {
   const void* y;          // local pre-gate expert outputs, same row layout
   const float* gate_in;   // [rows]
   float* dot_out;         // [rows]
+  const void* stage;      // optional: the unscaled rows come from here, row src_index[row], instead of grad_y itself
+  const int* src_index;   // [rows]
   const int* row0;        // [groups+1] padded group starts
   const int* counts;      // [groups]
   int groups, d;

@@ -730,6 +730,8 @@ int backward_impl(moe_layer* L, const void* gy, void* gx, int accumulate, cudaSt
     PushGradArgs pa{};
     pa.grad_y = gy; pa.rows = ep_rows(L, 2, L->dy_perm); pa.slot_pos = L->slot_pos; pa.gates = L->gates;
     pa.aux_off = aux_off; pa.tokens = tokens; pa.d = L->d; pa.k = L->k;
+    pa.dedup = ep_push_dedup(L) ? 1 : 0;
+    pa.stage = ep_rows(L, 3, L->dx_perm); pa.stage_base = L->ep_rank * L->max_tokens;
     Span sp(L, 5, st); CK(launch_push_grad(pa, L->act, st));
   } else {
     GatherGradArgs ga{};
@@ -1040,7 +1042,7 @@ int32_t moe_create(const moe_config_t* cfg, moe_layer_t** out) {
     DA(L->dy_perm, rc * d * es, true); DA(L->dgu, rl * 2 * Fp * es, true); DA(L->dx_perm, rc * d * es, true);
     if (L->act == PREC_F32) DA(L->dh, rl * Fp * es, true);
     // behind the gradient rows: the gates pushed with them and the dots computed from them (peer transport)
-    if (ep) { DA(L->dy_recv, rl * d * es + rl * 8, true); DA(L->dx_recv, rl * d * es, true); }
+    if (ep) { DA(L->dy_recv, rl * d * es + rl * 12, true); DA(L->dx_recv, rl * d * es, true); }
     if (L->shared) {
       DA(L->dgu_s, sc * 2 * Fp * es, true); DA(L->dx_s, sc * d * es, true);
       if (L->act == PREC_F32) DA(L->dh_s, sc * Fp * es, true);
