@@ -99,8 +99,12 @@ def _worker(rank, world, port, precision, transport, ret):
 
 @pytest.mark.parametrize("precision,transport,overlap", [
     ("f32", "nccl", "0"), ("bf16", "nccl", "0"), ("f32", "peer", "0"), ("bf16", "peer", "0"),
-    ("bf16", "peer", "1"), ("bf16", "peer", "2"), ("bf16", "nccl", "2")])
+    ("bf16", "peer", "1"), ("bf16", "peer", "2"), ("bf16", "nccl", "2"),
+    ("bf16", "peer", "0-rowperslot")])   # the gradient push with one row per slot instead of one per destination rank
 def test_expert_parallel_matches_single_device(precision, transport, overlap, monkeypatch):
+    if overlap.endswith("-rowperslot"):
+        overlap = overlap.split("-")[0]
+        monkeypatch.setenv("MOE_B200_EP_DEDUP", "0")
     monkeypatch.setenv("MOE_B200_OVERLAP", overlap)   # read by the spawned ranks' copy of the library
     world = _world()
     if world < 2:
