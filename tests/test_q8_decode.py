@@ -4,6 +4,7 @@ import pytest
 
 torch = pytest.importorskip("torch")
 from helpers import rel_l2
+from gpu_common import assert_routing_equal
 from oracle import OracleMoe, ROUTER, GATE, UP, DOWN, SHARED_GATE, SHARED_UP, SHARED_DOWN
 from rustingbrain_b200 import MoeConfig, MoeLayer, InvalidConfig
 
@@ -34,7 +35,8 @@ def _pair(T, d, E, k, F, shared, seed):
 
 @pytest.mark.parametrize("T,d,E,k,F,shared", [(64, 1024, 16, 2, 2816, True),   # benchmark configuration 5
                                               (200, 128, 4, 2, 96, True),      # many rows per expert, padded d_ff
-                                              (5, 64, 8, 1, 64, False)])       # most experts empty
+                                              (5, 64, 8, 1, 64, False),        # most experts empty
+                                              (33, 256, 64, 8, 64, True)])     # the widest shape of the one-launch routing
 def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
     dev, ora, x = _pair(T, d, E, k, F, shared, seed=9)
     xd = torch.from_numpy(x).cuda().bfloat16()
@@ -46,6 +48,23 @@ def test_q8_forward_matches_the_quantized_checker(T, d, E, k, F, shared):
     assert rel_l2(y.float().cpu().numpy(), yo) <= 2e-2
     y2 = dev.forward(xd)
     assert torch.equal(y, y2)
+
+
+def test_padding_rows_of_a_decode_batch_are_routed_nowhere():  # batch.rs:225-269 through the one-launch routing
+    T, d, E, k, F = 40, 128, 16, 2, 96
+    dev, ora, x = _pair(T, d, E, k, F, True, seed=13)
+    valid = np.ones(T, np.uint8)
+    valid[[0, 7, 8, 31, 39]] = 0
+    xd = torch.from_numpy(x).cuda().bfloat16()
+    y, cache = dev.forward_train(xd, valid=valid)
+    logits = dev.router_cache(T)[0]
+    yo = ora.forward(xd.float().cpu().numpy(), valid=valid, logits=logits)
+    assert_routing_equal(cache, ora)             # expert_of, counts and the permutation bit-equal, gates to 1e-6
+    assert np.all(cache.routing()[0][valid == 0] == -1)
+    a_o, z_o = ora.losses()
+    assert abs(cache.auxiliary_loss() - (a_o + z_o)) <= 1e-6 * max(1.0, abs(a_o + z_o))
+    keep = valid != 0
+    assert rel_l2(y.float().cpu().numpy()[keep], yo[keep]) <= 2e-2
 
 
 def test_a_quantized_router_routes_like_the_checkers():  # transformer.rs:899-910: quantize() includes the router
@@ -99,4 +118,4 @@ def test_the_tensor_core_variant_passes_the_same_parity_cases():
                           "-k", "matches_the_quantized_checker", "-p", "no:cacheprovider"],
                          env=env, cwd=os.path.dirname(here), capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
-    assert "3 passed" in out.stdout
+    assert "4 passed" in out.stdout
